@@ -1,0 +1,461 @@
+/*
+ * agb_oracle.c -- CPU restatement of cgadimpl's RMSNorm path.  TEST INFRASTRUCTURE ONLY.
+ * See agb_oracle.h for what is pinned and what is not ("parity unpinned" at the OwnTensor
+ * boundary).  Compile with:  gcc -O2 -fopenmp -ffp-contract=off -fPIC -shared
+ *
+ * Every ot_* function stands in for exactly one OwnTensor call of the reference and makes
+ * one pass over memory, rounding its result to fp32 like a materialised Tensor does.
+ */
+#include "agb_oracle.h"
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+int agb_oracle_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+float agb_bf16_to_f32(uint16_t b) {
+    uint32_t u = (uint32_t)b << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+uint16_t agb_f32_to_bf16(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u); /* quiet NaN */
+    uint32_t lsb = (u >> 16) & 1u;
+    u += 0x7fffu + lsb; /* round to nearest even */
+    return (uint16_t)(u >> 16);
+}
+
+/* ------------------------------------------------------------------ primitives */
+
+void ot_mul(const float* a, const float* b, float* out, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = a[i] * b[i];
+}
+void ot_add(const float* a, const float* b, float* out, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = a[i] + b[i];
+}
+void ot_sub(const float* a, const float* b, float* out, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = a[i] - b[i];
+}
+void ot_mul_rowstat(const float* a, const float* s, float* out, int64_t R, int64_t H) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r) {
+        const float sv = s[r];
+        const float* ar = a + r * H;
+        float* o = out + r * H;
+        for (int64_t j = 0; j < H; ++j) o[j] = ar[j] * sv;
+    }
+}
+void ot_mul_lastvec(const float* a, const float* g, float* out, int64_t R, int64_t H) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r) {
+        const float* ar = a + r * H;
+        float* o = out + r * H;
+        for (int64_t j = 0; j < H; ++j) o[j] = ar[j] * g[j];
+    }
+}
+void ot_div_scalar(const float* a, float d, float* out, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = a[i] / d;
+}
+void ot_mul_scalar(const float* a, float d, float* out, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = a[i] * d;
+}
+void ot_add_scalar(const float* a, float d, float* out, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = a[i] + d;
+}
+void ot_sqrt(const float* a, float* out, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = sqrtf(a[i]);
+}
+void ot_rdiv_scalar(float d, const float* a, float* out, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = d / a[i];
+}
+
+static inline float row_sum(const float* a, int64_t H, int red) {
+    if (red == AGB_RED_F64) {
+        double s = 0.0;
+        for (int64_t j = 0; j < H; ++j) s += (double)a[j];
+        return (float)s;
+    }
+    float s = 0.0f;
+    for (int64_t j = 0; j < H; ++j) s += a[j];
+    return s;
+}
+static inline float row_mean(const float* a, int64_t H, int red) {
+    if (red == AGB_RED_F64) {
+        double s = 0.0;
+        for (int64_t j = 0; j < H; ++j) s += (double)a[j];
+        return (float)(s / (double)H);
+    }
+    float s = 0.0f;
+    for (int64_t j = 0; j < H; ++j) s += a[j];
+    return s / (float)H;
+}
+
+void ot_reduce_sum_last(const float* a, float* out, int64_t R, int64_t H, int red) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r) out[r] = row_sum(a + r * H, H, red);
+}
+void ot_reduce_mean_last(const float* a, float* out, int64_t R, int64_t H, int red) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r) out[r] = row_mean(a + r * H, H, red);
+}
+void ot_reduce_max_last(const float* a, float* out, int64_t R, int64_t H) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r) {
+        const float* ar = a + r * H;
+        float m = ar[0];
+        for (int64_t j = 1; j < H; ++j) m = ar[j] > m ? ar[j] : m;
+        out[r] = m;
+    }
+}
+/* Sum over all leading axes: out[j] = sum_r a[r,j], rows visited in order 0..R-1. */
+void ot_reduce_sum_lead(const float* a, float* out, int64_t R, int64_t H, int red) {
+    const int64_t CB = 256; /* column block, keeps the accumulators in L1 */
+#pragma omp parallel for schedule(static)
+    for (int64_t j0 = 0; j0 < H; j0 += CB) {
+        const int64_t w = (H - j0) < CB ? (H - j0) : CB;
+        if (red == AGB_RED_F64) {
+            double acc[256];
+            for (int64_t j = 0; j < w; ++j) acc[j] = 0.0;
+            for (int64_t r = 0; r < R; ++r) {
+                const float* ar = a + r * H + j0;
+                for (int64_t j = 0; j < w; ++j) acc[j] += (double)ar[j];
+            }
+            for (int64_t j = 0; j < w; ++j) out[j0 + j] = (float)acc[j];
+        } else {
+            float acc[256];
+            for (int64_t j = 0; j < w; ++j) acc[j] = 0.0f;
+            for (int64_t r = 0; r < R; ++r) {
+                const float* ar = a + r * H + j0;
+                for (int64_t j = 0; j < w; ++j) acc[j] += ar[j];
+            }
+            for (int64_t j = 0; j < w; ++j) out[j0 + j] = acc[j];
+        }
+    }
+}
+float ot_reduce_sum_all(const float* a, int64_t n, int red) {
+    if (red == AGB_RED_F64) {
+        double s = 0.0;
+        for (int64_t i = 0; i < n; ++i) s += (double)a[i];
+        return (float)s;
+    }
+    float s = 0.0f;
+    for (int64_t i = 0; i < n; ++i) s += a[i];
+    return s;
+}
+float ot_reduce_mean_all(const float* a, int64_t n, int red) {
+    if (red == AGB_RED_F64) {
+        double s = 0.0;
+        for (int64_t i = 0; i < n; ++i) s += (double)a[i];
+        return (float)(s / (double)n);
+    }
+    float s = 0.0f;
+    for (int64_t i = 0; i < n; ++i) s += a[i];
+    return s / (float)n;
+}
+
+static float* falloc(int64_t n) {
+    float* p = (float*)malloc((size_t)(n > 0 ? n : 1) * sizeof(float));
+    if (!p) abort();
+    return p;
+}
+
+/* ------------------------------------------------------------------ compositions */
+
+/* normalization.cpp:24-27, one temporary per call:
+ *   x_squared = x*x; variance = reduce_mean(x_squared,{-1},true);
+ *   rsqrt_var = 1.0f / sqrt(variance + 1e-5f); y = x * rsqrt_var                      */
+void agb_oracle_rms_forward(const float* x, float* yhat, float* rstd,
+                            int64_t R, int64_t H, float eps, int red) {
+    float* xsq = falloc(R * H);
+    float* var = falloc(R);
+    float* tmp = falloc(R);
+    ot_mul(x, x, xsq, R * H);                    /* :24 */
+    ot_reduce_mean_last(xsq, var, R, H, red);    /* :25 */
+    ot_add_scalar(var, eps, tmp, R);             /* :26 variance + eps  */
+    ot_sqrt(tmp, var, R);                        /* :26 sqrt(.)         */
+    ot_rdiv_scalar(1.0f, var, rstd, R);          /* :26 1.0f / .        */
+    ot_mul_rowstat(x, rstd, yhat, R, H);         /* :27 */
+    free(xsq); free(var); free(tmp);
+}
+
+void agb_oracle_scale_forward(const float* yhat, const float* gamma, float* y, int64_t R, int64_t H) {
+    ot_mul_lastvec(yhat, gamma, y, R, H);        /* arithmetic.cpp:32 */
+}
+
+/* autodiff_vjp_ops.cpp:57  A.grad += reduce_for_broadcast(gy * B, A)   (identity reduce)
+ *                     :58  B.grad += reduce_for_broadcast(gy * A, B)   (sum over rows, :32) */
+void agb_oracle_vjp_scale(const float* gy, const float* yhat, const float* gamma,
+                          float* dyhat, float* dgamma, int64_t R, int64_t H, int red) {
+    if (dyhat) ot_mul_lastvec(gy, gamma, dyhat, R, H);
+    if (dgamma) {
+        float* prod = falloc(R * H);
+        ot_mul(gy, yhat, prod, R * H);
+        ot_reduce_sum_lead(prod, dgamma, R, H, red);
+        free(prod);
+    }
+}
+
+/* autodiff_vjp_ops.cpp:374-375:
+ *   dot = reduce_sum(gy * x, {-1}, true);
+ *   dx  = rsqrt_var * (gy - x * (rsqrt_var * rsqrt_var) * dot / D)
+ * C++ evaluation order: ((x * (r*r)) * dot) / D, then gy - ., then r * .                */
+void agb_oracle_vjp_rms(const float* x, const float* rstd, const float* gy, float* dx,
+                        int64_t R, int64_t H, int red) {
+    float* t = falloc(R * H);
+    float* dot = falloc(R);
+    float* r2 = falloc(R);
+    ot_mul(gy, x, t, R * H);                     /* gy * x                    */
+    ot_reduce_sum_last(t, dot, R, H, red);       /* reduce_sum(., {-1}, true) */
+    ot_mul(rstd, rstd, r2, R);                   /* rsqrt_var * rsqrt_var     */
+    ot_mul_rowstat(x, r2, t, R, H);              /* x * (.)                   */
+    ot_mul_rowstat(t, dot, t, R, H);             /* . * dot                   */
+    ot_div_scalar(t, (float)H, t, R * H);        /* . / float(D)              */
+    ot_sub(gy, t, t, R * H);                     /* gy - .                    */
+    ot_mul_rowstat(t, rstd, dx, R, H);           /* rsqrt_var * (.)           */
+    free(t); free(dot); free(r2);
+}
+
+void agb_oracle_add_forward(const float* a, const float* b, float* out, int64_t n) {
+    ot_add(a, b, out, n);                        /* arithmetic.cpp:12 */
+}
+
+void agb_oracle_rmsnorm_fwd(const float* x, const float* gamma, float* y, float* rstd,
+                            int64_t R, int64_t H, float eps, int red) {
+    if (!gamma) { agb_oracle_rms_forward(x, y, rstd, R, H, eps, red); return; }
+    float* yhat = falloc(R * H);
+    agb_oracle_rms_forward(x, yhat, rstd, R, H, eps, red);
+    agb_oracle_scale_forward(yhat, gamma, y, R, H);
+    free(yhat);
+}
+
+void agb_oracle_rmsnorm_fwd_bwd(const float* x, const float* gamma, const float* gy,
+                                float* y, float* rstd, float* dx, float* dgamma,
+                                int64_t R, int64_t H, float eps, int red) {
+    if (!gamma) {
+        agb_oracle_rms_forward(x, y, rstd, R, H, eps, red);
+        agb_oracle_vjp_rms(x, rstd, gy, dx, R, H, red);
+        return;
+    }
+    float* yhat = falloc(R * H);
+    float* dyhat = falloc(R * H);
+    agb_oracle_rms_forward(x, yhat, rstd, R, H, eps, red);
+    agb_oracle_scale_forward(yhat, gamma, y, R, H);
+    agb_oracle_vjp_scale(gy, yhat, gamma, dyhat, dgamma, R, H, red);
+    agb_oracle_vjp_rms(x, rstd, dyhat, dx, R, H, red);
+    free(yhat); free(dyhat);
+}
+
+/* Same arithmetic, same rounding points, fp64 reductions, fused per row (one OpenMP loop). */
+void agb_oracle_rmsnorm_fwd_bwd_fused(const float* x, const float* gamma, const float* gy,
+                                      float* y, float* rstd, float* dx, float* dgamma,
+                                      int64_t R, int64_t H, float eps) {
+    int nt = agb_oracle_num_threads();
+    double* part = gamma ? (double*)calloc((size_t)nt * (size_t)H, sizeof(double)) : NULL;
+#pragma omp parallel
+    {
+#ifdef _OPENMP
+        int tid = omp_get_thread_num();
+#else
+        int tid = 0;
+#endif
+        double* acc = part ? part + (size_t)tid * H : NULL;
+#pragma omp for schedule(static)
+        for (int64_t r = 0; r < R; ++r) {
+            const float* xr = x + r * H;
+            const float* gr = gy + r * H;
+            float* yr = y + r * H;
+            float* dr = dx + r * H;
+            double ss = 0.0;
+            for (int64_t j = 0; j < H; ++j) { float q = xr[j] * xr[j]; ss += (double)q; }
+            float var = (float)(ss / (double)H);
+            float v = var + eps;
+            float s = sqrtf(v);
+            float rs = 1.0f / s;
+            rstd[r] = rs;
+            double dot = 0.0;
+            for (int64_t j = 0; j < H; ++j) {
+                float yh = xr[j] * rs;
+                float dy = gr[j];
+                if (gamma) {
+                    yr[j] = yh * gamma[j];
+                    float p = gr[j] * yh;
+                    acc[j] += (double)p;
+                    dy = gr[j] * gamma[j];
+                } else {
+                    yr[j] = yh;
+                }
+                float p2 = dy * xr[j];
+                dot += (double)p2;
+            }
+            float dotf = (float)dot;
+            float r2 = rs * rs;
+            for (int64_t j = 0; j < H; ++j) {
+                float dy = gamma ? gr[j] * gamma[j] : gr[j];
+                float t = xr[j] * r2;
+                t = t * dotf;
+                t = t / (float)H;
+                t = dy - t;
+                dr[j] = t * rs;
+            }
+        }
+    }
+    if (gamma) {
+        /* NB: per-thread partials are combined in thread order, so dgamma here can differ from
+         * the row-ordered fp64 sum in the last bit of the double, i.e. practically never after
+         * rounding to fp32. */
+        for (int64_t j = 0; j < H; ++j) {
+            double s = 0.0;
+            for (int t = 0; t < nt; ++t) s += part[(size_t)t * H + j];
+            dgamma[j] = (float)s;
+        }
+        free(part);
+    }
+}
+
+void agb_oracle_rmsnorm_fwd_bwd_bf16(const uint16_t* x, const uint16_t* gamma, const uint16_t* gy,
+                                     uint16_t* y, float* rstd, uint16_t* dx, float* dgamma,
+                                     int64_t R, int64_t H, float eps, int red) {
+    const int64_t n = R * H;
+    float* xf = falloc(n);
+    float* gf = falloc(n);
+    float* yf = falloc(n);
+    float* dxf = falloc(n);
+    float* gam = gamma ? falloc(H) : NULL;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) { xf[i] = agb_bf16_to_f32(x[i]); gf[i] = agb_bf16_to_f32(gy[i]); }
+    if (gamma) for (int64_t j = 0; j < H; ++j) gam[j] = agb_bf16_to_f32(gamma[j]);
+    agb_oracle_rmsnorm_fwd_bwd(xf, gam, gf, yf, rstd, dxf, dgamma, R, H, eps, red);
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) { y[i] = agb_f32_to_bf16(yf[i]); dx[i] = agb_f32_to_bf16(dxf[i]); }
+    free(xf); free(gf); free(yf); free(dxf); free(gam);
+}
+
+/* autodiff_jvp_ops.cpp:366-379, to the letter:
+ *   dot = reduce_sum(T*y,{-1},true);  return (T / rms) - (y * dot / (rms * N));
+ * where `rms` is tape[0], which the forward filled with rsqrt_var. */
+void agb_oracle_jvp_rms_literal(const float* t, const float* yhat, const float* rstd, float* ty,
+                                int64_t R, int64_t H, int red) {
+    float* a = falloc(R * H);
+    float* b = falloc(R * H);
+    float* dot = falloc(R);
+    float* rn = falloc(R);
+    ot_mul(t, yhat, a, R * H);
+    ot_reduce_sum_last(a, dot, R, H, red);
+    ot_mul_scalar(rstd, (float)H, rn, R);        /* rms * N */
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r)
+        for (int64_t j = 0; j < H; ++j) {
+            float q = t[r * H + j] / rstd[r];    /* T / rms       */
+            float p = yhat[r * H + j] * dot[r];  /* y * dot       */
+            p = p / rn[r];                       /* . / (rms * N) */
+            ty[r * H + j] = q - p;
+        }
+    free(a); free(b); free(dot); free(rn);
+}
+
+/* The same composition with tape[0] used as what it is (rstd):
+ *   ty = (T * rstd) - ((y * dot) * (rstd / N))                                          */
+void agb_oracle_jvp_rms_corrected(const float* t, const float* yhat, const float* rstd, float* ty,
+                                  int64_t R, int64_t H, int red) {
+    float* a = falloc(R * H);
+    float* dot = falloc(R);
+    float* c = falloc(R);
+    ot_mul(t, yhat, a, R * H);
+    ot_reduce_sum_last(a, dot, R, H, red);
+    ot_div_scalar(rstd, (float)H, c, R);         /* rstd / N */
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r)
+        for (int64_t j = 0; j < H; ++j) {
+            float q = t[r * H + j] * rstd[r];
+            float p = yhat[r * H + j] * dot[r];
+            p = p * c[r];
+            ty[r * H + j] = q - p;
+        }
+    free(a); free(dot); free(c);
+}
+
+/* autodiff_jvp_ops.cpp:30:  (T(A) * B) + (A * T(B)) */
+void agb_oracle_jvp_scale(const float* tyhat, const float* yhat, const float* gamma,
+                          const float* tgamma, float* tout, int64_t R, int64_t H) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r)
+        for (int64_t j = 0; j < H; ++j) {
+            float a = tyhat[r * H + j] * gamma[j];
+            if (tgamma) {
+                float b = yhat[r * H + j] * tgamma[j];
+                tout[r * H + j] = a + b;
+            } else {
+                tout[r * H + j] = a;
+            }
+        }
+}
+
+void agb_oracle_rowsum(const float* x, float* out, int64_t R, int64_t H, int red) {
+    ot_reduce_sum_last(x, out, R, H, red);       /* reduction.cpp:26 */
+}
+void agb_oracle_rowmax(const float* x, float* out, int64_t R, int64_t H) {
+    ot_reduce_max_last(x, out, R, H);            /* reduction.cpp:34 */
+}
+float agb_oracle_sum(const float* x, int64_t n, int red) { return ot_reduce_sum_all(x, n, red); }        /* :10 */
+float agb_oracle_mean_all(const float* x, int64_t n, int red) { return ot_reduce_mean_all(x, n, red); }  /* :18 */
+
+void agb_oracle_residual_stack(const float* x, const float* r, const float* gammas, const float* g,
+                               float* y_last, float* dh0, float* dgammas,
+                               int64_t R, int64_t H, int L, float eps, int red) {
+    const int64_t n = R * H;
+    float** h = (float**)malloc(sizeof(float*) * (size_t)L);
+    float** rs = (float**)malloc(sizeof(float*) * (size_t)L);
+    float* yhat = falloc(n);
+    float* y = falloc(n);
+    const float* xl = x;
+    const float* rl = r;
+    float* yprev = falloc(n);
+    for (int l = 0; l < L; ++l) {
+        h[l] = falloc(n);
+        rs[l] = falloc(R);
+        agb_oracle_add_forward(xl, rl, h[l], n);
+        agb_oracle_rms_forward(h[l], yhat, rs[l], R, H, eps, red);
+        agb_oracle_scale_forward(yhat, gammas + (int64_t)l * H, y, R, H);
+        memcpy(yprev, y, sizeof(float) * (size_t)n);
+        xl = h[l];
+        rl = yprev;
+    }
+    memcpy(y_last, y, sizeof(float) * (size_t)n);
+    /* backward */
+    float* gh = falloc(n);      /* grad of h_{l+1} (already final) */
+    float* dyhat = falloc(n);
+    float* dx = falloc(n);
+    for (int l = L - 1; l >= 0; --l) {
+        const float* gy = (l == L - 1) ? g : gh;   /* y_l.grad = 0 + gh_{l+1} via vjp_Add */
+        /* yhat_l is the rms node's value; recomputing it repeats the same two roundings */
+        ot_mul_rowstat(h[l], rs[l], yhat, R, H);
+        agb_oracle_vjp_scale(gy, yhat, gammas + (int64_t)l * H, dyhat, dgammas + (int64_t)l * H, R, H, red);
+        agb_oracle_vjp_rms(h[l], rs[l], dyhat, dx, R, H, red);
+        if (l == L - 1) memcpy(gh, dx, sizeof(float) * (size_t)n);   /* 0 + dx */
+        else ot_add(dx, gh, gh, n);                                  /* accumulate_grad: += */
+    }
+    memcpy(dh0, gh, sizeof(float) * (size_t)n);
+    for (int l = 0; l < L; ++l) { free(h[l]); free(rs[l]); }
+    free(h); free(rs); free(yhat); free(y); free(yprev); free(gh); free(dyhat); free(dx);
+}
