@@ -1,0 +1,373 @@
+#!/usr/bin/env python
+"""RMSNorm forward + VJP throughput on B200 (rows/s), with roofline and CPU baseline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A "step" is one forward + VJP pass over the workload's rows: rmsnorm_fwd, rmsnorm_bwd (dx fused
+with the dgamma partials), the fixed-order dgamma reduction and, for N > 1, the NCCL all-reduce
+of the fp64 dgamma sums.  N > 1 is launched by torchrun, one rank per GPU; every rank holds the
+same number of rows (weak scaling) and `value` counts the rows of all ranks.
+
+Workload (default): x [16,2048,4096] fp32 ~ N(0,1), gamma = 1 + 0.02 N(0,1), gy ~ N(0,1),
+eps 1e-5 -- 32768 rows per GPU, synthetic, seed 0.  Inputs (2 x 537 MB) and outputs are far
+larger than the 126 MB L2, so no flush is needed between iterations.
+
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (rows per GPU, hidden, dtype, eps)
+    "rmsnorm_fwd_vjp_fp32_16x2048x4096": (16 * 2048, 4096, "float32", 1e-5),
+    "rmsnorm_fwd_vjp_fp32_8x512x1024": (8 * 512, 1024, "float32", 1e-6),
+    "rmsnorm_fwd_vjp_bf16_65536x8192": (65536, 8192, "bfloat16", 1e-6),
+    "rmsnorm_fwd_vjp_bf16_65536x1000": (65536, 1000, "bfloat16", 1e-6),
+    "rmsnorm_fwd_vjp_bf16_65536x5120": (65536, 5120, "bfloat16", 1e-6),
+    "rmsnorm_fwd_vjp_bf16_65536x12288": (65536, 12288, "bfloat16", 1e-6),
+}
+DEFAULT_WORKLOAD = "rmsnorm_fwd_vjp_fp32_16x2048x4096"
+METRIC = "rmsnorm_fwd_vjp_rows_per_s"
+UNIT = "rows/s"
+SPEC_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def bytes_per_row(hidden, elem):
+    """Algorithmic traffic: fwd reads x, writes y, writes rstd; vjp reads x, gy, rstd, writes dx."""
+    return 5 * hidden * elem + 8
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            p = [s.strip() for s in ln.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1]))
+                mx.append(float(p[2]))
+                power.append(float(p[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, p[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_pass(hidden, eps, sample_rows, reps, seed=0):
+    """Times the op-by-op CPU restatement of the reference (all host threads) on a bounded sample
+    of the workload.  Returns (rows/s, threads, seconds per pass)."""
+    import numpy as np
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_ffi as O
+
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((sample_rows, hidden), dtype=np.float32)
+    gy = rng.standard_normal((sample_rows, hidden), dtype=np.float32)
+    gamma = (1 + 0.02 * rng.standard_normal(hidden)).astype(np.float32)
+    O.rmsnorm_fwd_bwd(x, gamma, gy, eps, O.RED_F32)  # warm-up (page faults, thread pool)
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        O.rmsnorm_fwd_bwd(x, gamma, gy, eps, O.RED_F32)
+        ts.append(time.perf_counter() - t0)
+    best = min(ts)
+    return sample_rows / best, O.num_threads(), best
+
+
+def run_reference_arm(args, rank, world):
+    """The reference's own CPU path for this workload.  cgadimpl cannot be built (its tensor
+    library is an absent submodule), so this times the call-by-call CPU restatement of its
+    composition, fp32 reductions, OpenMP over all host cores.  Rank 0 only."""
+    if rank != 0:
+        return
+    rows, hidden, dtype, eps = WORKLOADS[args.workload]
+    sample_rows = min(rows, 4096)
+    import numpy as np
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_ffi as O
+
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((sample_rows, hidden), dtype=np.float32)
+    gy = rng.standard_normal((sample_rows, hidden), dtype=np.float32)
+    gamma = (1 + 0.02 * rng.standard_normal(hidden)).astype(np.float32)
+    for _ in range(max(1, args.warmup)):
+        O.rmsnorm_fwd_bwd(x, gamma, gy, eps, O.RED_F32)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.rmsnorm_fwd_bwd(x, gamma, gy, eps, O.RED_F32)
+    dt = time.perf_counter() - t0
+    value = sample_rows * args.steps / dt
+    elem = 4 if dtype == "float32" else 2
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "rows_per_gpu": rows, "hidden": hidden, "eps": eps,
+                   "io_dtype": dtype, "sample_rows_per_step": sample_rows},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
+                         "sample": f"{sample_rows} of {rows} rows per step, op-by-op restatement of the "
+                                   f"reference composition (cgadimpl itself cannot be built: OwnTensor absent)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "hbm_gbs": value * bytes_per_row(hidden, elem) / 1e9,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+
+    from cgadimpl_b200 import ops
+    from cgadimpl_b200.executor import RowShardedRMSNorm
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if args.gpus != world and rank == 0 and world > 1:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE {world}", file=sys.stderr)
+
+    rows, hidden, dtype_name, eps = WORKLOADS[args.workload]
+    dtype = getattr(torch, dtype_name)
+    elem = 4 if dtype == torch.float32 else 2
+    gen = torch.Generator(device="cuda").manual_seed(1000 * rank)
+    x = torch.randn(rows, hidden, device="cuda", generator=gen, dtype=torch.float32).to(dtype)
+    gy = torch.randn(rows, hidden, device="cuda", generator=gen, dtype=torch.float32).to(dtype)
+    ggen = torch.Generator(device="cuda").manual_seed(7)
+    gamma = (1 + 0.02 * torch.randn(hidden, device="cuda", generator=ggen)).to(dtype)
+    y = torch.empty_like(x)
+    dx = torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device="cuda")
+    dgamma = torch.empty(hidden, dtype=torch.float32, device="cuda")
+    ex = RowShardedRMSNorm(hidden, dtype, eps)
+
+    def step():
+        ex.fwd_bwd(x, gy, gamma, y=y, rstd=rstd, dx=dx, dgamma=dgamma)
+
+    def sync_all():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    sync_all()
+    ops.device_status()
+
+    # ---- timed region: K steps, device-timed, plus per-kernel events on the launching stream
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.3)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = ops.launch_count()
+    sync_all()
+    t_start.record()
+    for k in range(args.steps):
+        ev[k][0].record()
+        y_, rstd_ = ops.rmsnorm_fwd(x, gamma, eps, out=y, rstd=rstd)
+        ev[k][1].record()
+        if world == 1:
+            ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=dgamma, workspace=ex._workspace(x))
+            ev[k][2].record()
+        else:
+            ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=ex._dg64, workspace=ex._workspace(x))
+            ev[k][2].record()
+            dist.all_reduce(ex._dg64, op=dist.ReduceOp.SUM)
+            ops.dgamma_finalize(ex._dg64, dgamma)
+    t_end.record()
+    sync_all()
+    launches = ops.launch_count() - launches0
+    elapsed_ms = t_start.elapsed_time(t_end)
+    if dist is not None:
+        t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    if sampler:
+        time.sleep(0.2)
+    clocks = sampler.stop() if sampler else None
+    ops.device_status()
+
+    fwd_ms = statistics.mean(ev[k][0].elapsed_time(ev[k][1]) for k in range(args.steps))
+    bwd_ms = statistics.mean(ev[k][1].elapsed_time(ev[k][2]) for k in range(args.steps))
+    total_rows = rows * world
+    value = total_rows * args.steps / (elapsed_ms / 1e3)
+    bpr = bytes_per_row(hidden, elem)
+    peak, peak_kind = measured_peak()
+
+    # dominant launch: the backward call (rmsnorm_bwd_staged followed by the ~µs dgamma reduction)
+    bwd_bytes = rows * (3 * hidden * elem + 4)
+    fwd_bytes = rows * (2 * hidden * elem + 4)
+    achieved = bwd_bytes / (bwd_ms / 1e3) / 1e9
+    roofline = {
+        "bound": "hbm", "kernel": "rmsnorm_bwd_staged (+dgamma_reduce_kernel)", "achieved": achieved, "peak": peak,
+        "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+        "algorithmic_bytes_per_launch": bwd_bytes, "avg_launch_ms": bwd_ms,
+        "fwd": {"kernel": "rmsnorm_fwd_staged", "achieved": fwd_bytes / (fwd_ms / 1e3) / 1e9,
+                "frac": fwd_bytes / (fwd_ms / 1e3) / 1e9 / peak, "avg_launch_ms": fwd_ms,
+                "algorithmic_bytes_per_launch": fwd_bytes},
+        "step_gbs": value / world * bpr / 1e9,
+        "step_frac_of_spec_8TBs": value / world * bpr / 1e9 / SPEC_HBM_GBS,
+        "step_frac_of_peak": value / world * bpr / 1e9 / peak,
+    }
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(traffic_file) as f:
+            tr = json.load(f).get(args.workload)
+        if tr:
+            roofline["traffic"] = tr["bwd_dram_bytes_per_launch"]
+            roofline["traffic_source"] = tr.get("source")
+    except Exception:
+        pass
+
+    # ---- end to end: pinned host buffers in, host buffers out, copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        xh = torch.empty(rows, hidden, dtype=dtype).pin_memory()
+        gyh = torch.empty(rows, hidden, dtype=dtype).pin_memory()
+        xh.copy_(x)
+        gyh.copy_(gy)
+        gh = gamma.cpu().pin_memory()
+        yh = torch.empty(rows, hidden, dtype=dtype).pin_memory()
+        dxh = torch.empty(rows, hidden, dtype=dtype).pin_memory()
+        dgh = torch.empty(hidden, dtype=torch.float32).pin_memory()
+        for _ in range(2):
+            ex.fwd_bwd_host(xh, gyh, gh, yh, dxh, dgh)
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.e2e_steps):
+            ex.fwd_bwd_host(xh, gyh, gh, yh, dxh, dgh)
+        e1.record()
+        sync_all()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        # the host results must be the device results
+        assert torch.equal(yh[:64].cuda(), y[:64]) and torch.equal(dxh[-64:].cuda(), dx[-64:]), "e2e mismatch"
+        h2d = rows * hidden * elem * 2 + hidden * elem
+        d2h = rows * hidden * elem * 2 + hidden * 4
+        e2e = {"value": total_rows * args.e2e_steps / (ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "steps": args.e2e_steps, "ms_per_step": ms / args.e2e_steps,
+               "api": "cgadimpl_b200.executor.RowShardedRMSNorm.fwd_bwd_host (pinned host buffers, chunked "
+                      "copy/compute overlap on three streams)"}
+        del xh, gyh, yh, dxh
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sample_rows = min(rows, 4096)
+        v, cores, secs = cpu_pass(hidden, eps, sample_rows, reps=8)
+        cpu_baseline = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                        "sample": f"{sample_rows} of {rows} rows, best of 8 passes ({secs*1e3:.1f} ms each), "
+                                  f"op-by-op fp32 restatement of the reference composition"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "rows_per_gpu": rows, "global_rows": total_rows, "hidden": hidden,
+                       "io_dtype": dtype_name, "eps": eps, "parallelism": f"rows{world}",
+                       "l2": "inputs+outputs per step (>= 2 GB) exceed the 126 MB L2; no flush needed",
+                       "launch": {"fwd": ops.describe_launch("fwd", rows, hidden, dtype),
+                                  "bwd": ops.describe_launch("bwd", rows, hidden, dtype)}},
+            "hbm_gbs": value / world * bpr / 1e9, "bytes_per_row": bpr,
+            "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
+            "e2e": e2e, "cpu_baseline": cpu_baseline,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,69 @@
+"""ctypes binding of libagb_cuda.so -- the same entry points a C++ or cgo caller binds.
+
+There is no fallback: if the library is missing this raises, and without a CUDA device every
+compute call returns AGB_ERR_CUDA, which is raised as AgbError.
+"""
+import ctypes as C
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libagb_cuda.so")
+
+AGB_OK = 0
+AGB_F32, AGB_BF16, AGB_F64 = 0, 1, 2
+REDUCE_SUM, REDUCE_MEAN, REDUCE_MAX = 0, 1, 2
+
+# name -> (restype, argtypes); must list every symbol include/agb/agb.h declares
+_vp, _i64, _i, _f, _sz = C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_size_t
+SIGNATURES = {
+    "agb_version": (_i, []),
+    "agb_status_string": (C.c_char_p, [_i]),
+    "agb_last_error": (C.c_char_p, []),
+    "agb_launch_count": (C.c_uint64, []),
+    "agb_device_status": (_i, []),
+    "agb_set_option": (_i, [C.c_char_p, _i64]),
+    "agb_describe_launch": (_i, [_i, _i64, _i64, _i, _i, C.POINTER(_i64)]),
+    "agb_rmsnorm_fwd": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _vp]),
+    "agb_add_rmsnorm_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _vp]),
+    "agb_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64, _i]),
+    "agb_rmsnorm_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _sz, _i64, _i64, _i, _vp]),
+    "agb_dgamma_finalize": (_i, [_vp, _vp, _i64, _i, _vp]),
+    "agb_rmsnorm_jvp": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i, _vp]),
+    "agb_residual_add": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
+    "agb_vjp_add": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
+    "agb_scale_lastdim": (_i, [_vp, _vp, _vp, _i64, _i64, _i, _vp]),
+    "agb_row_reduce": (_i, [_i, _vp, _vp, _i64, _i64, _i, _vp]),
+    "agb_reduce_all_workspace_bytes": (_sz, [_i64]),
+    "agb_reduce_all": (_i, [_i, _vp, _vp, _i64, _i, _vp, _sz, _vp]),
+}
+
+
+class AgbError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__(f"agb status {status}: {message}")
+        self.status = status
+
+
+_lib = None
+
+
+def lib():
+    """Loads the library once; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m cgadimpl_b200.build` "
+                "(there is no CPU or PyTorch fallback)")
+        h = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(h, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = h
+    return _lib
+
+
+def check(status):
+    if status != AGB_OK:
+        raise AgbError(status, lib().agb_last_error().decode())

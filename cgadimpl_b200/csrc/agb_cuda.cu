@@ -1,0 +1,616 @@
+// agb_cuda.cu -- the C ABI of libagb_cuda.so (declared in include/agb/agb.h) and the launch
+// heuristics behind it.  Single translation unit: all kernels are included here.
+#include "agb/agb.h"
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "agb_device.cuh"
+#include "elementwise.cuh"
+#include "rmsnorm_generic.cuh"
+#include "rmsnorm_staged.cuh"
+
+namespace {
+
+using agb::PipeGeom;
+typedef __nv_bfloat16 bf16;
+
+// ------------------------------------------------------------------ errors
+thread_local char t_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_err, sizeof(t_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+int cuda_fail(cudaError_t e, const char* what) {
+    return fail(AGB_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+#define AGB_CUDA(call)                                     \
+    do {                                                   \
+        cudaError_t e__ = (call);                          \
+        if (e__ != cudaSuccess) return cuda_fail(e__, #call); \
+    } while (0)
+
+std::atomic<uint64_t> g_launches{0};
+
+int after_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, what);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return AGB_OK;
+}
+
+// ------------------------------------------------------------------ device properties
+struct DevInfo {
+    int sms = 0;
+    int smem_optin = 0;   // max dynamic shared memory per block
+    int smem_per_sm = 0;
+    bool ok = false;
+};
+constexpr int kMaxDevices = 64;
+DevInfo g_dev[kMaxDevices];
+std::mutex g_dev_mu;
+
+int device_info(const DevInfo** out) {
+    int dev = 0;
+    AGB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(AGB_ERR_CUDA, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_dev_mu);
+    DevInfo& d = g_dev[dev];
+    if (!d.ok) {
+        AGB_CUDA(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev));
+        AGB_CUDA(cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        AGB_CUDA(cudaDeviceGetAttribute(&d.smem_per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev));
+        d.ok = true;
+    }
+    *out = &d;
+    return AGB_OK;
+}
+
+// ------------------------------------------------------------------ options
+std::atomic<int64_t> opt_stages{0}, opt_ctas_per_sm{0}, opt_threads{0}, opt_force_generic{0};
+
+// ------------------------------------------------------------------ launch planning
+struct Plan {
+    bool generic = true;
+    int grid = 0, block = 0, smem = 0, vpt = 0;
+    PipeGeom g{};
+};
+
+inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+enum Which { kFwd = 0, kBwd = 1, kJvp = 2 };
+
+// narr: arrays staged per tile; ngamma: [hidden] vectors kept in shared memory.
+void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, int ngamma, const DevInfo& d,
+                 Plan* p) {
+    p->generic = true;
+    if (opt_force_generic.load() || rows <= 0) return;
+    const int64_t row_bytes64 = hidden * elem;
+    if (row_bytes64 % 16 != 0 || row_bytes64 > (1 << 20)) return;
+    const int row_bytes = static_cast<int>(row_bytes64);
+    const int nvec = row_bytes / 16;
+    const int epv = 16 / elem;
+
+    // threads per row: aim at 4 vectors per thread
+    int vpt = 4;
+    int G = round_up((nvec + vpt - 1) / vpt, 32);
+    const int max_threads = which == kBwd ? 512 : 1024;
+    if (G > max_threads) {
+        if (which == kBwd) {
+            // the backward keeps vpt*epv fp64 column sums in registers: at most 32 per thread
+            vpt = 32 / epv;
+            G = round_up((nvec + vpt - 1) / vpt, 32);
+            if (G > max_threads) return;
+        } else {
+            G = max_threads;  // the forward / jvp loops simply take more trips
+        }
+    }
+    int target = static_cast<int>(opt_threads.load());
+    if (target <= 0) target = which == kBwd ? 256 : 512;
+    if (target > max_threads) target = max_threads;
+    int rpt = target / G;
+    if (rpt < 1) rpt = 1;
+    if (rpt > rows) rpt = static_cast<int>(rows);
+    const int block = rpt * G;
+    const int nwarps = block / 32;
+
+    const int tile_stride = round_up(rpt * row_bytes, 128);
+    const int stage_stride = narr * tile_stride;
+    const int gamma_bytes = round_up(row_bytes, 16);
+    const int fixed = ngamma * gamma_bytes + 2 * nwarps * 8 + 8 * 16 /*barriers*/ + 16 /*flag*/ + 128 /*slack*/;
+
+    int ctas = static_cast<int>(opt_ctas_per_sm.load());
+    int want_stages = static_cast<int>(opt_stages.load());
+    const int max_stages = 8;
+    auto stages_for = [&](int c) {
+        int avail = d.smem_per_sm / c - 1024;  // the runtime reserves 1 KB per resident CTA
+        if (avail > d.smem_optin) avail = d.smem_optin;
+        int s = (avail - fixed) / stage_stride;
+        return s > max_stages ? max_stages : s;
+    };
+    if (ctas <= 0) ctas = (stages_for(2) >= 4 && block <= 512) ? 2 : 1;
+    int S = stages_for(ctas);
+    if (S < 2 && ctas > 1) { ctas = 1; S = stages_for(1); }
+    if (S < 2) return;
+    if (want_stages >= 2 && want_stages < S) S = want_stages;
+
+    PipeGeom& g = p->g;
+    g.rows = rows;
+    g.hidden = static_cast<int>(hidden);
+    g.nvec = nvec;
+    g.row_bytes = row_bytes;
+    g.rows_per_tile = rpt;
+    g.group_threads = G;
+    g.stages = S;
+    g.tile_stride = tile_stride;
+    g.stage_stride = stage_stride;
+    g.ntiles = (rows + rpt - 1) / rpt;
+    int off = S * stage_stride;
+    g.off_gamma = off;
+    off += gamma_bytes * (ngamma > 0 ? 1 : 0);
+    g.off_gamma2 = off;
+    off += gamma_bytes * (ngamma > 1 ? 1 : 0);
+    off = round_up(off, 16);
+    g.off_red = off;
+    off += 2 * nwarps * 8;
+    g.off_bar = off;
+    off += 8 * 16;
+    g.off_flag = off;
+    off += 16;
+    p->smem = off;
+    p->block = block;
+    p->vpt = vpt;
+    int64_t grid = static_cast<int64_t>(d.sms) * ctas;
+    if (grid > g.ntiles) grid = g.ntiles;
+    p->grid = static_cast<int>(grid);
+    p->generic = false;
+}
+
+template <typename K>
+int set_smem(K kernel, int bytes) {
+    // Raising the limit is idempotent and cheap; doing it on every call keeps this correct for
+    // every device and context without a cache.
+    AGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    return AGB_OK;
+}
+
+int check_common(int64_t rows, int64_t hidden, int dtype) {
+    if (rows < 0 || hidden <= 0) return fail(AGB_ERR_INVALID_ARG, "rows=%lld hidden=%lld", (long long)rows, (long long)hidden);
+    if (dtype != AGB_F32 && dtype != AGB_BF16) return fail(AGB_ERR_UNSUPPORTED, "dtype %d (only AGB_F32, AGB_BF16)", dtype);
+    if (hidden > (1LL << 30)) return fail(AGB_ERR_UNSUPPORTED, "hidden %lld too large", (long long)hidden);
+    return AGB_OK;
+}
+int check_ptr(const void* p, const char* name, int elem, bool required = true) {
+    if (!p) return required ? fail(AGB_ERR_INVALID_ARG, "%s is NULL", name) : AGB_OK;
+    if (reinterpret_cast<uintptr_t>(p) % elem) return fail(AGB_ERR_MISALIGNED, "%s not aligned to %d bytes", name, elem);
+    return AGB_OK;
+}
+#define AGB_TRY(expr)                 \
+    do {                              \
+        int s__ = (expr);             \
+        if (s__ != AGB_OK) return s__; \
+    } while (0)
+
+inline int generic_grid(int64_t rows, const DevInfo& d) {
+    int64_t g = static_cast<int64_t>(d.sms) * 8;
+    return static_cast<int>(rows < g ? rows : g);
+}
+inline int max_partials(const DevInfo& d) { return 2 * d.sms; }
+
+// ------------------------------------------------------------------ typed launchers
+template <typename T>
+int launch_fwd(const void* x, const void* r, const void* gamma, void* h, void* y, float* rstd, int64_t rows,
+               int64_t hidden, float eps, bool fuse, cudaStream_t st) {
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    Plan p;
+    const bool al = aligned16(x) && aligned16(y) && (!fuse || (aligned16(r) && aligned16(h))) && (!gamma || aligned16(gamma));
+    if (al) plan_launch(kFwd, rows, hidden, sizeof(T), fuse ? 2 : 1, gamma ? 1 : 0, *d, &p);
+    if (p.generic) {
+        const int grid = generic_grid(rows, *d);
+        if (fuse)
+            agb::rmsnorm_fwd_generic<T, true><<<grid, agb::kGenericThreads, 0, st>>>(
+                (const T*)x, (const T*)r, (const T*)gamma, (T*)h, (T*)y, rstd, rows, (int)hidden, eps);
+        else
+            agb::rmsnorm_fwd_generic<T, false><<<grid, agb::kGenericThreads, 0, st>>>(
+                (const T*)x, nullptr, (const T*)gamma, nullptr, (T*)y, rstd, rows, (int)hidden, eps);
+        return after_launch("rmsnorm_fwd_generic");
+    }
+    agb::FwdArgs a{p.g, x, r, gamma, h, y, rstd, eps};
+#define AGB_LAUNCH_FWD(HG, FA)                                                          \
+    do {                                                                                \
+        AGB_TRY(set_smem(agb::rmsnorm_fwd_staged<T, HG, FA>, p.smem));                  \
+        agb::rmsnorm_fwd_staged<T, HG, FA><<<p.grid, p.block, p.smem, st>>>(a);         \
+    } while (0)
+    if (gamma && fuse) AGB_LAUNCH_FWD(true, true);
+    else if (gamma) AGB_LAUNCH_FWD(true, false);
+    else if (fuse) AGB_LAUNCH_FWD(false, true);
+    else AGB_LAUNCH_FWD(false, false);
+#undef AGB_LAUNCH_FWD
+    return after_launch("rmsnorm_fwd_staged");
+}
+
+int launch_dgamma_reduce(const double* partials, int P, int64_t hidden, void* dgamma, int dgamma_dtype,
+                         int accumulate, cudaStream_t st) {
+    const int mode = dgamma_dtype == AGB_F64 ? (accumulate ? 3 : 2) : (accumulate ? 1 : 0);
+    dim3 block(32, 8);
+    const int grid = static_cast<int>((hidden + 31) / 32);
+    agb::dgamma_reduce_kernel<<<grid, block, 0, st>>>(partials, P, (int)hidden, dgamma, mode);
+    return after_launch("dgamma_reduce");
+}
+
+template <typename T>
+int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* gy, const void* dx_add, void* dx,
+               void* dgamma, int dgamma_dtype, int accumulate_dgamma, void* workspace, size_t workspace_bytes,
+               int64_t rows, int64_t hidden, cudaStream_t st) {
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    const bool want_dg = gamma != nullptr && dgamma != nullptr;
+    if (want_dg) {
+        const size_t need = static_cast<size_t>(max_partials(*d)) * hidden * sizeof(double);
+        if (!workspace || workspace_bytes < need)
+            return fail(AGB_ERR_WORKSPACE, "workspace %zu bytes, need %zu", workspace_bytes, need);
+        if (reinterpret_cast<uintptr_t>(workspace) % 16) return fail(AGB_ERR_MISALIGNED, "workspace not 16-byte aligned");
+    }
+    if (rows == 0) {
+        if (want_dg && !accumulate_dgamma)
+            AGB_CUDA(cudaMemsetAsync(dgamma, 0, hidden * (dgamma_dtype == AGB_F64 ? 8 : 4), st));
+        return AGB_OK;
+    }
+    int add_mode = 0;
+    if (dx_add) add_mode = (dx_add == gy) ? 2 : 1;
+    Plan p;
+    const bool al = aligned16(x) && aligned16(gy) && aligned16(dx) && (!gamma || aligned16(gamma)) &&
+                    (add_mode != 1 || aligned16(dx_add));
+    if (al) plan_launch(kBwd, rows, hidden, sizeof(T), add_mode == 1 ? 3 : 2, gamma ? 1 : 0, *d, &p);
+    double* partials = static_cast<double*>(workspace);
+    int P = 0;
+    if (p.generic) {
+        if (want_dg) {
+            // column sums first: dx may alias an input of theirs only through dx_add, never x or gy
+            P = static_cast<int>(rows < max_partials(*d) ? rows : max_partials(*d));
+            const int64_t rpc = (rows + P - 1) / P;
+            P = static_cast<int>((rows + rpc - 1) / rpc);
+            dim3 grid((unsigned)((hidden + agb::kGenericThreads - 1) / agb::kGenericThreads), (unsigned)P);
+            agb::dgamma_generic_partial<T><<<grid, agb::kGenericThreads, 0, st>>>((const T*)x, (const T*)gy, rstd,
+                                                                                 partials, rows, (int)hidden, rpc);
+            AGB_TRY(after_launch("dgamma_generic_partial"));
+        }
+        const float hf = static_cast<float>(hidden);
+        agb::rmsnorm_bwd_generic<T><<<generic_grid(rows, *d), agb::kGenericThreads, 0, st>>>(
+            (const T*)x, (const T*)gamma, rstd, (const T*)gy, (const T*)dx_add, (T*)dx, rows, (int)hidden, hf, 1.0f / hf);
+        AGB_TRY(after_launch("rmsnorm_bwd_generic"));
+    } else {
+        const float hf = static_cast<float>(hidden);
+        agb::BwdArgs a{p.g, x, gy, dx_add, gamma, rstd, dx, want_dg ? partials : nullptr, add_mode, hf, 1.0f / hf};
+        P = p.grid;
+#define AGB_LAUNCH_BWD(V, HG)                                                           \
+    do {                                                                                \
+        AGB_TRY(set_smem(agb::rmsnorm_bwd_staged<T, V, HG>, p.smem));                   \
+        agb::rmsnorm_bwd_staged<T, V, HG><<<p.grid, p.block, p.smem, st>>>(a);          \
+    } while (0)
+        // vpt is 4, or 8 for wide fp32 rows (never for bf16: 32 column sums per thread at most)
+        if constexpr (sizeof(T) == 4) {
+            if (p.vpt == 8) {
+                if (gamma) AGB_LAUNCH_BWD(8, true);
+                else AGB_LAUNCH_BWD(8, false);
+            }
+        }
+        if (p.vpt == 4) {
+            if (gamma) AGB_LAUNCH_BWD(4, true);
+            else AGB_LAUNCH_BWD(4, false);
+        }
+#undef AGB_LAUNCH_BWD
+        AGB_TRY(after_launch("rmsnorm_bwd_staged"));
+    }
+    if (want_dg) AGB_TRY(launch_dgamma_reduce(partials, P, hidden, dgamma, dgamma_dtype, accumulate_dgamma, st));
+    return AGB_OK;
+}
+
+template <typename T>
+int launch_jvp(const void* x, const void* gamma, const float* rstd, const void* tx, const void* tgamma, void* ty,
+               int64_t rows, int64_t hidden, cudaStream_t st) {
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    Plan p;
+    const bool al = aligned16(x) && aligned16(tx) && aligned16(ty) && (!gamma || aligned16(gamma)) &&
+                    (!tgamma || aligned16(tgamma));
+    if (al) plan_launch(kJvp, rows, hidden, sizeof(T), 2, (gamma ? 1 : 0) + (tgamma ? 1 : 0), *d, &p);
+    const float hf = static_cast<float>(hidden);
+    if (p.generic) {
+        agb::rmsnorm_jvp_generic<T><<<generic_grid(rows, *d), agb::kGenericThreads, 0, st>>>(
+            (const T*)x, (const T*)gamma, rstd, (const T*)tx, (const T*)tgamma, (T*)ty, rows, (int)hidden, hf);
+        return after_launch("rmsnorm_jvp_generic");
+    }
+    agb::JvpArgs a{p.g, x, tx, gamma, tgamma, rstd, ty, hf};
+    AGB_TRY(set_smem(agb::rmsnorm_jvp_staged<T>, p.smem));
+    agb::rmsnorm_jvp_staged<T><<<p.grid, p.block, p.smem, st>>>(a);
+    return after_launch("rmsnorm_jvp_staged");
+}
+
+inline int ew_grid(int64_t work_items, const DevInfo& d) {
+    int64_t g = (work_items + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(d.sms) * 16;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return static_cast<int>(g);
+}
+
+}  // namespace
+
+// ====================================================================== C ABI
+extern "C" {
+
+int agb_version(void) { return 100; }
+
+const char* agb_status_string(int s) {
+    switch (s) {
+        case AGB_OK: return "ok";
+        case AGB_ERR_INVALID_ARG: return "invalid argument";
+        case AGB_ERR_UNSUPPORTED: return "unsupported dtype or shape";
+        case AGB_ERR_MISALIGNED: return "misaligned pointer";
+        case AGB_ERR_CUDA: return "CUDA error";
+        case AGB_ERR_WORKSPACE: return "workspace missing or too small";
+        case AGB_ERR_TIMEOUT: return "device-side wait timed out";
+        default: return "unknown status";
+    }
+}
+const char* agb_last_error(void) { return t_err; }
+uint64_t agb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int agb_device_status(void) {
+    int v = 0, zero = 0;
+    AGB_CUDA(cudaDeviceSynchronize());
+    AGB_CUDA(cudaMemcpyFromSymbol(&v, agb::g_device_status, sizeof(int)));
+    if (v != 0) AGB_CUDA(cudaMemcpyToSymbol(agb::g_device_status, &zero, sizeof(int)));
+    if (v != 0) return fail(v, "a kernel's bounded shared-memory wait ran out");
+    return AGB_OK;
+}
+
+int agb_set_option(const char* key, int64_t value) {
+    if (!key) return fail(AGB_ERR_INVALID_ARG, "key is NULL");
+    if (!strcmp(key, "stages")) opt_stages = value;
+    else if (!strcmp(key, "ctas_per_sm")) opt_ctas_per_sm = value;
+    else if (!strcmp(key, "threads")) opt_threads = value;
+    else if (!strcmp(key, "force_generic")) opt_force_generic = value;
+    else return fail(AGB_ERR_INVALID_ARG, "unknown option '%s'", key);
+    return AGB_OK;
+}
+
+int agb_describe_launch(int which, int64_t rows, int64_t hidden, int dtype, int fused_add, int64_t out[6]) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    if (!out || which < 0 || which > 2) return fail(AGB_ERR_INVALID_ARG, "bad arguments");
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    Plan p;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    const int narr = which == kFwd ? (fused_add ? 2 : 1) : (which == kBwd ? (fused_add == 1 ? 3 : 2) : 2);
+    plan_launch(static_cast<Which>(which), rows, hidden, elem, narr, 1, *d, &p);
+    if (p.generic) {
+        out[0] = generic_grid(rows, *d); out[1] = agb::kGenericThreads; out[2] = 0; out[3] = 0; out[4] = 1; out[5] = 1;
+    } else {
+        out[0] = p.grid; out[1] = p.block; out[2] = p.smem; out[3] = p.g.stages; out[4] = p.g.rows_per_tile; out[5] = 0;
+    }
+    return AGB_OK;
+}
+
+int agb_rmsnorm_fwd(const void* x, const void* gamma, void* y, float* rstd, int64_t rows, int64_t hidden, float eps,
+                    int dtype, agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    if (rows == 0) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(x, "x", elem));
+    AGB_TRY(check_ptr(y, "y", elem));
+    AGB_TRY(check_ptr(rstd, "rstd", 4));
+    AGB_TRY(check_ptr(gamma, "gamma", elem, false));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == AGB_F32 ? launch_fwd<float>(x, nullptr, gamma, nullptr, y, rstd, rows, hidden, eps, false, st)
+                            : launch_fwd<bf16>(x, nullptr, gamma, nullptr, y, rstd, rows, hidden, eps, false, st);
+}
+
+int agb_add_rmsnorm_fwd(const void* x, const void* r, const void* gamma, void* h, void* y, float* rstd, int64_t rows,
+                        int64_t hidden, float eps, int dtype, agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    if (rows == 0) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(x, "x", elem));
+    AGB_TRY(check_ptr(r, "r", elem));
+    AGB_TRY(check_ptr(h, "h", elem));
+    AGB_TRY(check_ptr(y, "y", elem));
+    AGB_TRY(check_ptr(rstd, "rstd", 4));
+    AGB_TRY(check_ptr(gamma, "gamma", elem, false));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == AGB_F32 ? launch_fwd<float>(x, r, gamma, h, y, rstd, rows, hidden, eps, true, st)
+                            : launch_fwd<bf16>(x, r, gamma, h, y, rstd, rows, hidden, eps, true, st);
+}
+
+size_t agb_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t hidden, int dtype) {
+    (void)rows;
+    (void)dtype;
+    const DevInfo* d;
+    if (hidden <= 0 || device_info(&d) != AGB_OK) return 0;
+    return static_cast<size_t>(max_partials(*d)) * hidden * sizeof(double);
+}
+
+int agb_rmsnorm_bwd(const void* x, const void* gamma, const float* rstd, const void* gy, const void* dx_add, void* dx,
+                    void* dgamma, int dgamma_dtype, int accumulate_dgamma, void* workspace, size_t workspace_bytes,
+                    int64_t rows, int64_t hidden, int dtype, agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    if (dgamma && dgamma_dtype != AGB_F32 && dgamma_dtype != AGB_F64)
+        return fail(AGB_ERR_INVALID_ARG, "dgamma_dtype must be AGB_F32 or AGB_F64");
+    if (dgamma && !gamma) return fail(AGB_ERR_INVALID_ARG, "dgamma requested without gamma");
+    if (rows > 0) {
+        AGB_TRY(check_ptr(x, "x", elem));
+        AGB_TRY(check_ptr(gy, "gy", elem));
+        AGB_TRY(check_ptr(dx, "dx", elem));
+        AGB_TRY(check_ptr(rstd, "rstd", 4));
+        AGB_TRY(check_ptr(dx_add, "dx_add", elem, false));
+    }
+    AGB_TRY(check_ptr(gamma, "gamma", elem, false));
+    AGB_TRY(check_ptr(dgamma, "dgamma", dgamma_dtype == AGB_F64 ? 8 : 4, false));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == AGB_F32
+               ? launch_bwd<float>(x, gamma, rstd, gy, dx_add, dx, dgamma, dgamma_dtype, accumulate_dgamma, workspace,
+                                   workspace_bytes, rows, hidden, st)
+               : launch_bwd<bf16>(x, gamma, rstd, gy, dx_add, dx, dgamma, dgamma_dtype, accumulate_dgamma, workspace,
+                                  workspace_bytes, rows, hidden, st);
+}
+
+int agb_dgamma_finalize(const double* sum, float* dgamma, int64_t hidden, int accumulate, agb_stream_t stream) {
+    if (hidden <= 0) return fail(AGB_ERR_INVALID_ARG, "hidden=%lld", (long long)hidden);
+    AGB_TRY(check_ptr(sum, "sum", 8));
+    AGB_TRY(check_ptr(dgamma, "dgamma", 4));
+    agb::dgamma_finalize_kernel<<<(unsigned)((hidden + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        sum, dgamma, (int)hidden, accumulate);
+    return after_launch("dgamma_finalize");
+}
+
+int agb_rmsnorm_jvp(const void* x, const void* gamma, const float* rstd, const void* tx, const void* tgamma, void* ty,
+                    int64_t rows, int64_t hidden, int dtype, agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    if (rows == 0) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(x, "x", elem));
+    AGB_TRY(check_ptr(tx, "tx", elem));
+    AGB_TRY(check_ptr(ty, "ty", elem));
+    AGB_TRY(check_ptr(rstd, "rstd", 4));
+    AGB_TRY(check_ptr(gamma, "gamma", elem, false));
+    AGB_TRY(check_ptr(tgamma, "tgamma", elem, false));
+    if (tgamma && !gamma) return fail(AGB_ERR_INVALID_ARG, "tgamma given without gamma");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == AGB_F32 ? launch_jvp<float>(x, gamma, rstd, tx, tgamma, ty, rows, hidden, st)
+                            : launch_jvp<bf16>(x, gamma, rstd, tx, tgamma, ty, rows, hidden, st);
+}
+
+int agb_residual_add(const void* a, const void* b, void* out, int64_t n, int dtype, agb_stream_t stream) {
+    if (n < 0) return fail(AGB_ERR_INVALID_ARG, "n=%lld", (long long)n);
+    if (dtype != AGB_F32 && dtype != AGB_BF16) return fail(AGB_ERR_UNSUPPORTED, "dtype %d", dtype);
+    if (n == 0) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(a, "a", elem));
+    AGB_TRY(check_ptr(b, "b", elem));
+    AGB_TRY(check_ptr(out, "out", elem));
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    const int vec = aligned16(a) && aligned16(b) && aligned16(out);
+    const int grid = ew_grid(n / (16 / elem) + 1, *d);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == AGB_F32) agb::residual_add_kernel<float><<<grid, 256, 0, st>>>((const float*)a, (const float*)b, (float*)out, n, vec);
+    else agb::residual_add_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)a, (const bf16*)b, (bf16*)out, n, vec);
+    return after_launch("residual_add");
+}
+
+int agb_vjp_add(void* ga, void* gb, const void* gy, int64_t n, int dtype, agb_stream_t stream) {
+    if (n < 0) return fail(AGB_ERR_INVALID_ARG, "n=%lld", (long long)n);
+    if (dtype != AGB_F32 && dtype != AGB_BF16) return fail(AGB_ERR_UNSUPPORTED, "dtype %d", dtype);
+    if (n == 0 || (!ga && !gb)) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(gy, "gy", elem));
+    AGB_TRY(check_ptr(ga, "ga", elem, false));
+    AGB_TRY(check_ptr(gb, "gb", elem, false));
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    const int vec = aligned16(gy) && (!ga || aligned16(ga)) && (!gb || aligned16(gb));
+    const int grid = ew_grid(n / (16 / elem) + 1, *d);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == AGB_F32) agb::vjp_add_kernel<float><<<grid, 256, 0, st>>>((float*)ga, (float*)gb, (const float*)gy, n, vec);
+    else agb::vjp_add_kernel<bf16><<<grid, 256, 0, st>>>((bf16*)ga, (bf16*)gb, (const bf16*)gy, n, vec);
+    return after_launch("vjp_add");
+}
+
+int agb_scale_lastdim(const void* a, const void* g, void* out, int64_t rows, int64_t hidden, int dtype,
+                      agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    if (rows == 0) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(a, "a", elem));
+    AGB_TRY(check_ptr(g, "g", elem));
+    AGB_TRY(check_ptr(out, "out", elem));
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    const int vec = aligned16(a) && aligned16(g) && aligned16(out) && (hidden * elem) % 16 == 0;
+    const int grid = ew_grid(rows * hidden / (16 / elem) + 1, *d);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == AGB_F32) agb::scale_lastdim_kernel<float><<<grid, 256, 0, st>>>((const float*)a, (const float*)g, (float*)out, rows, (int)hidden, vec);
+    else agb::scale_lastdim_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)a, (const bf16*)g, (bf16*)out, rows, (int)hidden, vec);
+    return after_launch("scale_lastdim");
+}
+
+int agb_row_reduce(int op, const void* x, void* out, int64_t rows, int64_t hidden, int dtype, agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    if (op < AGB_REDUCE_SUM || op > AGB_REDUCE_MAX) return fail(AGB_ERR_INVALID_ARG, "op %d", op);
+    if (rows == 0) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(x, "x", elem));
+    AGB_TRY(check_ptr(out, "out", elem));
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool wide = hidden >= 1024;
+    const int rpc = wide ? 1 : 8;
+    int64_t g = (rows + rpc - 1) / rpc;
+    const int64_t cap = static_cast<int64_t>(d->sms) * 8;
+    const int grid = static_cast<int>(g < cap ? g : cap);
+    if (dtype == AGB_F32) {
+        if (wide) agb::row_reduce_kernel<float, 256><<<grid, 256, 0, st>>>((const float*)x, (float*)out, rows, (int)hidden, op);
+        else agb::row_reduce_kernel<float, 32><<<grid, 256, 0, st>>>((const float*)x, (float*)out, rows, (int)hidden, op);
+    } else {
+        if (wide) agb::row_reduce_kernel<bf16, 256><<<grid, 256, 0, st>>>((const bf16*)x, (bf16*)out, rows, (int)hidden, op);
+        else agb::row_reduce_kernel<bf16, 32><<<grid, 256, 0, st>>>((const bf16*)x, (bf16*)out, rows, (int)hidden, op);
+    }
+    return after_launch("row_reduce");
+}
+
+static inline void reduce_all_shape(int64_t n, int* nblocks, int64_t* chunk) {
+    // a function of n only, so the summation order (and the result) depends on nothing else
+    int64_t nb = (n + 16383) / 16384;
+    if (nb > 1024) nb = 1024;
+    if (nb < 1) nb = 1;
+    *chunk = (n + nb - 1) / nb;
+    *nblocks = static_cast<int>((n + *chunk - 1) / *chunk);
+    if (*nblocks < 1) *nblocks = 1;
+}
+
+size_t agb_reduce_all_workspace_bytes(int64_t n) {
+    (void)n;
+    return 1024 * sizeof(double);
+}
+
+int agb_reduce_all(int op, const void* x, void* out, int64_t n, int dtype, void* workspace, size_t workspace_bytes,
+                   agb_stream_t stream) {
+    if (n <= 0) return fail(AGB_ERR_INVALID_ARG, "n=%lld", (long long)n);
+    if (dtype != AGB_F32 && dtype != AGB_BF16) return fail(AGB_ERR_UNSUPPORTED, "dtype %d", dtype);
+    if (op != AGB_REDUCE_SUM && op != AGB_REDUCE_MEAN) return fail(AGB_ERR_INVALID_ARG, "op %d (sum or mean)", op);
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(x, "x", elem));
+    AGB_TRY(check_ptr(out, "out", elem));
+    if (!workspace || workspace_bytes < agb_reduce_all_workspace_bytes(n))
+        return fail(AGB_ERR_WORKSPACE, "workspace %zu bytes, need %zu", workspace_bytes, agb_reduce_all_workspace_bytes(n));
+    AGB_TRY(check_ptr(workspace, "workspace", 8));
+    int nb;
+    int64_t chunk;
+    reduce_all_shape(n, &nb, &chunk);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    double* part = static_cast<double*>(workspace);
+    if (dtype == AGB_F32) {
+        agb::reduce_all_stage1<float><<<nb, 256, 0, st>>>((const float*)x, part, n, chunk);
+        AGB_TRY(after_launch("reduce_all_stage1"));
+        agb::reduce_all_stage2<float><<<1, 32, 0, st>>>(part, nb, (float*)out, n, op);
+    } else {
+        agb::reduce_all_stage1<bf16><<<nb, 256, 0, st>>>((const bf16*)x, part, n, chunk);
+        AGB_TRY(after_launch("reduce_all_stage1"));
+        agb::reduce_all_stage2<bf16><<<1, 32, 0, st>>>(part, nb, (bf16*)out, n, op);
+    }
+    return after_launch("reduce_all_stage2");
+}
+
+}  // extern "C"

@@ -1,0 +1,166 @@
+// elementwise.cuh -- the small kernels either side of the norm: residual add and its VJP, the
+// broadcast gamma product, row reductions and the deterministic global sum / mean.
+#pragma once
+#include "agb_device.cuh"
+
+namespace agb {
+
+// out = a + b.  16-byte vectors when `vec` (all pointers 16-byte aligned), scalar tail otherwise.
+template <typename T>
+__global__ void __launch_bounds__(256) residual_add_kernel(const T* a, const T* b, T* out, long long n, int vec) {
+    constexpr int EPV = Vec<T>::EPV;
+    const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+    const long long nv = vec ? n / EPV : 0;
+    for (long long v = tid; v < nv; v += nthreads) {
+        float av[EPV], bv[EPV];
+        Vec<T>::unpack(reinterpret_cast<const uint4*>(a)[v], av);
+        Vec<T>::unpack(reinterpret_cast<const uint4*>(b)[v], bv);
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) av[e] = add_rn(av[e], bv[e]);
+        reinterpret_cast<uint4*>(out)[v] = Vec<T>::pack(av);
+    }
+    for (long long i = nv * EPV + tid; i < n; i += nthreads)
+        Vec<T>::store1(out + i, add_rn(Vec<T>::load1(a + i), Vec<T>::load1(b + i)));
+}
+
+// ga += gy; gb += gy (either may be null).
+template <typename T>
+__global__ void __launch_bounds__(256) vjp_add_kernel(T* ga, T* gb, const T* gy, long long n, int vec) {
+    constexpr int EPV = Vec<T>::EPV;
+    const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+    const long long nv = vec ? n / EPV : 0;
+    for (long long v = tid; v < nv; v += nthreads) {
+        float gv[EPV], t[EPV];
+        Vec<T>::unpack(reinterpret_cast<const uint4*>(gy)[v], gv);
+        if (ga) {
+            Vec<T>::unpack(reinterpret_cast<const uint4*>(ga)[v], t);
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) t[e] = add_rn(t[e], gv[e]);
+            reinterpret_cast<uint4*>(ga)[v] = Vec<T>::pack(t);
+        }
+        if (gb) {
+            Vec<T>::unpack(reinterpret_cast<const uint4*>(gb)[v], t);
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) t[e] = add_rn(t[e], gv[e]);
+            reinterpret_cast<uint4*>(gb)[v] = Vec<T>::pack(t);
+        }
+    }
+    for (long long i = nv * EPV + tid; i < n; i += nthreads) {
+        const float g = Vec<T>::load1(gy + i);
+        if (ga) Vec<T>::store1(ga + i, add_rn(Vec<T>::load1(ga + i), g));
+        if (gb) Vec<T>::store1(gb + i, add_rn(Vec<T>::load1(gb + i), g));
+    }
+}
+
+// out[r, j] = a[r, j] * g[j]
+template <typename T>
+__global__ void __launch_bounds__(256) scale_lastdim_kernel(const T* a, const T* g, T* out, long long rows, int hidden,
+                                                            int vec) {
+    constexpr int EPV = Vec<T>::EPV;
+    const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+    if (vec) {
+        const int nvec = hidden / EPV;
+        const long long total = rows * nvec;
+        for (long long v = tid; v < total; v += nthreads) {
+            const int cv = static_cast<int>(v % nvec);
+            float av[EPV], gv[EPV];
+            Vec<T>::unpack(reinterpret_cast<const uint4*>(a)[v], av);
+            Vec<T>::unpack(reinterpret_cast<const uint4*>(g)[cv], gv);
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) av[e] = mul_rn(av[e], gv[e]);
+            reinterpret_cast<uint4*>(out)[v] = Vec<T>::pack(av);
+        }
+    } else {
+        const long long total = rows * hidden;
+        for (long long i = tid; i < total; i += nthreads)
+            Vec<T>::store1(out + i, mul_rn(Vec<T>::load1(a + i), Vec<T>::load1(g + (i % hidden))));
+    }
+}
+
+// out[r] = op_j x[r, j]; TPR threads per row (32 or 256), 256 threads per CTA.
+// op: 0 sum, 1 mean, 2 max.  Sums in fp64, rounded once (mean: divided in fp64 first).
+template <typename T, int TPR>
+__global__ void __launch_bounds__(256) row_reduce_kernel(const T* __restrict__ x, T* __restrict__ out, long long rows,
+                                                         int hidden, int op) {
+    __shared__ double s_sum[2][8];
+    __shared__ float s_max[2][8];
+    constexpr int RPC = 256 / TPR;
+    const int grp = threadIdx.x / TPR, tig = threadIdx.x % TPR;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int phase = 0;
+    for (long long row0 = static_cast<long long>(blockIdx.x) * RPC; row0 < rows;
+         row0 += static_cast<long long>(gridDim.x) * RPC, phase ^= 1) {
+        const long long row = row0 + grp;
+        double s = 0.0;
+        float m = -INFINITY;
+        if (row < rows) {
+            const T* xr = x + row * hidden;
+            for (int j = tig; j < hidden; j += TPR) {
+                const float v = Vec<T>::load1(xr + j);
+                s += static_cast<double>(v);
+                m = fmaxf(m, v);
+            }
+        }
+        s = warp_sum(s);
+        m = warp_max(m);
+        if (TPR > 32) {
+            if (lane == 0) {
+                s_sum[phase][warp] = s;
+                s_max[phase][warp] = m;
+            }
+            __syncthreads();
+            s = 0.0;
+            m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {
+                s += s_sum[phase][w];
+                m = fmaxf(m, s_max[phase][w]);
+            }
+        }
+        if (row < rows && tig == 0) {
+            float r;
+            if (op == 0) r = static_cast<float>(s);
+            else if (op == 1) r = static_cast<float>(s / static_cast<double>(hidden));
+            else r = m;
+            Vec<T>::store1(out + row, r);
+        }
+    }
+}
+
+// Global sum, stage 1: block b reduces elements [b*chunk, (b+1)*chunk) to partial[b].
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_all_stage1(const T* __restrict__ x, double* __restrict__ partial,
+                                                         long long n, long long chunk) {
+    __shared__ double s[8];
+    const long long i0 = static_cast<long long>(blockIdx.x) * chunk;
+    long long i1 = i0 + chunk;
+    if (i1 > n) i1 = n;
+    double v = 0.0;
+    for (long long i = i0 + threadIdx.x; i < i1; i += 256) v += static_cast<double>(Vec<T>::load1(x + i));
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += s[w];
+        partial[blockIdx.x] = t;
+    }
+}
+// Stage 2: one warp adds the partials in index order (lane-strided, then a fixed shuffle tree).
+template <typename T>
+__global__ void __launch_bounds__(32) reduce_all_stage2(const double* __restrict__ partial, int nblocks, T* out,
+                                                        long long n, int op) {
+    double v = 0.0;
+    for (int i = threadIdx.x; i < nblocks; i += 32) v += partial[i];
+    v = warp_sum(v);
+    if (threadIdx.x == 0) {
+        const float r = op == 1 ? static_cast<float>(v / static_cast<double>(n)) : static_cast<float>(v);
+        Vec<T>::store1(out, r);
+    }
+}
+
+}  // namespace agb

@@ -1,0 +1,142 @@
+"""Row-sharded executor for the RMSNorm forward + VJP path.
+
+Rows are independent in the forward and in dx; only dgamma couples them.  So each rank (one
+process per GPU) owns a contiguous block of rows, runs the same two kernels on it, and the
+ranks exchange exactly one thing: the [hidden] fp64 column sum of dgamma, all-reduced over
+NCCL (NVLink / NVSwitch) and rounded to fp32 once afterwards.  Reducing in fp64 keeps the
+N-GPU dgamma equal to the 1-GPU result up to fp64 rounding, i.e. the same fp32 bits in all
+but rare tie cases.
+
+Two entry points:
+  fwd_bwd(x, gy, gamma)           device tensors of this rank's shard
+  fwd_bwd_host(...)               pinned HOST buffers; chunks of rows are copied in, processed
+                                  and copied out on three streams so PCIe transfers in both
+                                  directions overlap the kernels
+"""
+import torch
+
+from . import ops
+
+
+def shard_rows(total_rows, world_size, rank):
+    """Contiguous, near-equal split: first (total % world) ranks get one extra row."""
+    base, extra = divmod(total_rows, world_size)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+class RowShardedRMSNorm:
+    def __init__(self, hidden, dtype=torch.float32, eps=1e-5, device=None, group=None, chunk_rows=None):
+        self.hidden = int(hidden)
+        self.dtype = dtype
+        self.eps = float(eps)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.group = group
+        self.world = 1
+        if torch.distributed.is_available() and torch.distributed.is_initialized():
+            self.world = torch.distributed.get_world_size(group)
+        self._ws = None
+        self._dg64 = torch.zeros(self.hidden, dtype=torch.float64, device=self.device)
+        self._chunk_rows = chunk_rows
+        self._slots = None
+        self._streams = None
+
+    # ------------------------------------------------------------------ device-resident path
+    def _workspace(self, x):
+        if self._ws is None:
+            self._ws = ops.bwd_workspace(x)
+        return self._ws
+
+    def fwd_bwd(self, x, gy, gamma, y=None, rstd=None, dx=None, dgamma=None):
+        """One pass over this rank's rows.  Returns (y, rstd, dx, dgamma); dgamma is the sum over
+        ALL ranks' rows (fp32 [hidden])."""
+        y, rstd = ops.rmsnorm_fwd(x, gamma, self.eps, out=y, rstd=rstd)
+        if gamma is None:
+            dx, _ = ops.rmsnorm_bwd(x, None, rstd, gy, dx=dx)
+            return y, rstd, dx, None
+        if self.world == 1:
+            dx, dgamma = ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=dgamma, workspace=self._workspace(x))
+            return y, rstd, dx, dgamma
+        dx, _ = ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=self._dg64, workspace=self._workspace(x))
+        torch.distributed.all_reduce(self._dg64, op=torch.distributed.ReduceOp.SUM, group=self.group)
+        dgamma = ops.dgamma_finalize(self._dg64, dgamma)
+        return y, rstd, dx, dgamma
+
+    # ------------------------------------------------------------------ host-buffer path
+    def _ensure_slots(self, chunk_rows, nslots=3):
+        if self._slots is not None and self._slots[0]["x"].shape[0] >= chunk_rows:
+            return
+        mk = lambda: torch.empty(chunk_rows, self.hidden, dtype=self.dtype, device=self.device)  # noqa: E731
+        self._slots = []
+        for _ in range(nslots):
+            s = dict(x=mk(), gy=mk(), y=mk(), dx=mk(),
+                     rstd=torch.empty(chunk_rows, dtype=torch.float32, device=self.device),
+                     in_ready=torch.cuda.Event(), done=torch.cuda.Event(), out_done=torch.cuda.Event())
+            self._slots.append(s)
+        self._streams = dict(h2d=torch.cuda.Stream(self.device), compute=torch.cuda.Stream(self.device),
+                             d2h=torch.cuda.Stream(self.device))
+        self._gamma_dev = torch.empty(self.hidden, dtype=self.dtype, device=self.device)
+        self._dg32 = torch.empty(self.hidden, dtype=torch.float32, device=self.device)
+
+    def default_chunk_rows(self, rows):
+        if self._chunk_rows:
+            return min(rows, self._chunk_rows)
+        # ~64 MB per array and chunk: long enough to run PCIe at full rate, short enough to overlap
+        per_row = self.hidden * torch.empty((), dtype=self.dtype).element_size()
+        return max(1, min(rows, (64 << 20) // per_row))
+
+    def fwd_bwd_host(self, x_host, gy_host, gamma_host, y_host, dx_host, dgamma_host, rstd_host=None):
+        """x_host, gy_host [rows, hidden] and gamma_host [hidden] are pinned host tensors; y_host,
+        dx_host, dgamma_host (fp32 [hidden]) and optionally rstd_host receive the results.
+        Returns when everything has landed in host memory."""
+        rows = x_host.shape[0]
+        chunk = self.default_chunk_rows(rows)
+        self._ensure_slots(chunk)
+        st = self._streams
+        cur = torch.cuda.current_stream(self.device)
+        for s in st.values():
+            s.wait_stream(cur)
+        with torch.cuda.stream(st["h2d"]):
+            self._gamma_dev.copy_(gamma_host, non_blocking=True)
+            gamma_ready = torch.cuda.Event()
+            gamma_ready.record()
+        nchunks = (rows + chunk - 1) // chunk
+        first = True
+        for c in range(nchunks):
+            r0, r1 = c * chunk, min(rows, (c + 1) * chunk)
+            n = r1 - r0
+            s = self._slots[c % len(self._slots)]
+            with torch.cuda.stream(st["h2d"]):
+                if c >= len(self._slots):
+                    st["h2d"].wait_event(s["done"])      # kernels of the chunk that used this slot
+                s["x"][:n].copy_(x_host[r0:r1], non_blocking=True)
+                s["gy"][:n].copy_(gy_host[r0:r1], non_blocking=True)
+                s["in_ready"].record()
+            with torch.cuda.stream(st["compute"]):
+                st["compute"].wait_event(s["in_ready"])
+                if first:
+                    st["compute"].wait_event(gamma_ready)
+                if c >= len(self._slots):
+                    st["compute"].wait_event(s["out_done"])  # outputs of the previous user copied out
+                x, gy = s["x"][:n], s["gy"][:n]
+                y, rstd = ops.rmsnorm_fwd(x, self._gamma_dev, self.eps, out=s["y"][:n], rstd=s["rstd"][:n])
+                ops.rmsnorm_bwd(x, self._gamma_dev, rstd, gy, dx=s["dx"][:n], dgamma=self._dg64,
+                                accumulate_dgamma=not first, workspace=self._workspace(x))
+                s["done"].record()
+                first = False
+            with torch.cuda.stream(st["d2h"]):
+                st["d2h"].wait_event(s["done"])
+                y_host[r0:r1].copy_(s["y"][:n], non_blocking=True)
+                dx_host[r0:r1].copy_(s["dx"][:n], non_blocking=True)
+                if rstd_host is not None:
+                    rstd_host[r0:r1].copy_(s["rstd"][:n], non_blocking=True)
+                s["out_done"].record()
+        with torch.cuda.stream(st["compute"]):
+            if self.world > 1:
+                torch.distributed.all_reduce(self._dg64, op=torch.distributed.ReduceOp.SUM, group=self.group)
+            ops.dgamma_finalize(self._dg64, self._dg32)
+            dgamma_host.copy_(self._dg32, non_blocking=True)
+        for s in st.values():
+            cur.wait_stream(s)
+        cur.synchronize()
+        return y_host, dx_host, dgamma_host

@@ -1,0 +1,157 @@
+"""Thin wrappers that hand torch CUDA tensors to the C ABI (data_ptr + current stream).
+
+torch is used for device memory and streams only; every computation below is one of the
+library's own kernels.  Argument meaning follows include/agb/agb.h.
+"""
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import AGB_BF16, AGB_F32, AGB_F64, check
+
+_DT = {torch.float32: AGB_F32, torch.bfloat16: AGB_BF16}
+
+
+def _dt(t):
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}: float32 or bfloat16 only") from None
+
+
+def _p(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _rows_hidden(x):
+    if not x.is_cuda:
+        raise ValueError("tensor must live on a CUDA device (no CPU path exists)")
+    if not x.is_contiguous():
+        raise ValueError("tensor must be contiguous")
+    hidden = x.shape[-1]
+    return x.numel() // hidden if hidden else 0, hidden
+
+
+def rmsnorm_fwd(x, gamma=None, eps=1e-5, out=None, rstd=None):
+    """y = (x * rstd) * gamma; returns (y, rstd[rows] fp32).  gamma=None is cgadimpl's `rms(x)`."""
+    rows, hidden = _rows_hidden(x)
+    y = torch.empty_like(x) if out is None else out
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device) if rstd is None else rstd
+    check(_lib.lib().agb_rmsnorm_fwd(_p(x), _p(gamma), _p(y), _p(rstd), rows, hidden, eps, _dt(x), _stream()))
+    return y, rstd
+
+
+def add_rmsnorm_fwd(x, r, gamma=None, eps=1e-5, h=None, out=None, rstd=None):
+    """h = x + r; y = rmsnorm(h) * gamma; returns (h, y, rstd)."""
+    rows, hidden = _rows_hidden(x)
+    h = torch.empty_like(x) if h is None else h
+    y = torch.empty_like(x) if out is None else out
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device) if rstd is None else rstd
+    check(_lib.lib().agb_add_rmsnorm_fwd(_p(x), _p(r), _p(gamma), _p(h), _p(y), _p(rstd), rows, hidden, eps,
+                                         _dt(x), _stream()))
+    return h, y, rstd
+
+
+def bwd_workspace(x):
+    rows, hidden = _rows_hidden(x)
+    nbytes = _lib.lib().agb_rmsnorm_bwd_workspace_bytes(rows, hidden, _dt(x))
+    return torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+
+
+def rmsnorm_bwd(x, gamma, rstd, gy, dx_add=None, dx=None, dgamma=None, accumulate_dgamma=False,
+                workspace=None, dgamma_f64=False):
+    """Returns (dx, dgamma).  dgamma is fp32 [hidden] (or the un-rounded fp64 sum when
+    dgamma_f64), None when gamma is None.  dx_add is added to dx (may be gy or dx itself)."""
+    rows, hidden = _rows_hidden(x)
+    dx = torch.empty_like(x) if dx is None else dx
+    dg_dtype = AGB_F32
+    ws_bytes = 0
+    if gamma is not None:
+        if dgamma is None:
+            dgamma = torch.zeros(hidden, dtype=torch.float64 if dgamma_f64 else torch.float32, device=x.device)
+        dg_dtype = AGB_F64 if dgamma.dtype == torch.float64 else AGB_F32
+        if workspace is None:
+            workspace = bwd_workspace(x)
+        ws_bytes = workspace.numel() * workspace.element_size()
+    check(_lib.lib().agb_rmsnorm_bwd(_p(x), _p(gamma), _p(rstd), _p(gy), _p(dx_add), _p(dx), _p(dgamma), dg_dtype,
+                                     int(bool(accumulate_dgamma)), _p(workspace), ws_bytes, rows, hidden, _dt(x),
+                                     _stream()))
+    return dx, dgamma
+
+
+def dgamma_finalize(sum_f64, dgamma=None, accumulate=False):
+    hidden = sum_f64.numel()
+    dgamma = torch.empty(hidden, dtype=torch.float32, device=sum_f64.device) if dgamma is None else dgamma
+    check(_lib.lib().agb_dgamma_finalize(_p(sum_f64), _p(dgamma), hidden, int(bool(accumulate)), _stream()))
+    return dgamma
+
+
+def rmsnorm_jvp(x, gamma, rstd, tx, tgamma=None, out=None):
+    rows, hidden = _rows_hidden(x)
+    ty = torch.empty_like(x) if out is None else out
+    check(_lib.lib().agb_rmsnorm_jvp(_p(x), _p(gamma), _p(rstd), _p(tx), _p(tgamma), _p(ty), rows, hidden, _dt(x),
+                                     _stream()))
+    return ty
+
+
+def residual_add(a, b, out=None):
+    out = torch.empty_like(a) if out is None else out
+    check(_lib.lib().agb_residual_add(_p(a), _p(b), _p(out), a.numel(), _dt(a), _stream()))
+    return out
+
+
+def vjp_add(ga, gb, gy):
+    """ga += gy; gb += gy (either may be None)."""
+    check(_lib.lib().agb_vjp_add(_p(ga), _p(gb), _p(gy), gy.numel(), _dt(gy), _stream()))
+
+
+def scale_lastdim(a, g, out=None):
+    rows, hidden = _rows_hidden(a)
+    out = torch.empty_like(a) if out is None else out
+    check(_lib.lib().agb_scale_lastdim(_p(a), _p(g), _p(out), rows, hidden, _dt(a), _stream()))
+    return out
+
+
+def row_reduce(x, op):
+    """op: 'sum' | 'mean' | 'max' over the last axis, keepdim; result has x's dtype."""
+    rows, hidden = _rows_hidden(x)
+    code = {"sum": _lib.REDUCE_SUM, "mean": _lib.REDUCE_MEAN, "max": _lib.REDUCE_MAX}[op]
+    out = torch.empty(x.shape[:-1] + (1,), dtype=x.dtype, device=x.device)
+    check(_lib.lib().agb_row_reduce(code, _p(x), _p(out), rows, hidden, _dt(x), _stream()))
+    return out
+
+
+def reduce_all(x, op):
+    """op: 'sum' | 'mean' over all elements; one-element tensor of x's dtype."""
+    code = {"sum": _lib.REDUCE_SUM, "mean": _lib.REDUCE_MEAN}[op]
+    n = x.numel()
+    ws = torch.empty(_lib.lib().agb_reduce_all_workspace_bytes(n), dtype=torch.uint8, device=x.device)
+    out = torch.empty(1, dtype=x.dtype, device=x.device)
+    check(_lib.lib().agb_reduce_all(code, _p(x), _p(out), n, _dt(x), _p(ws), ws.numel(), _stream()))
+    return out
+
+
+def device_status():
+    """Raises AgbError(AGB_ERR_TIMEOUT) if a kernel's bounded wait ran out since the last call."""
+    check(_lib.lib().agb_device_status())
+
+
+def launch_count():
+    return int(_lib.lib().agb_launch_count())
+
+
+def set_option(key, value):
+    check(_lib.lib().agb_set_option(key.encode(), int(value)))
+
+
+def describe_launch(which, rows, hidden, dtype, fused_add=0):
+    out = (C.c_int64 * 6)()
+    code = {"fwd": 0, "bwd": 1, "jvp": 2}[which]
+    check(_lib.lib().agb_describe_launch(code, rows, hidden, _DT[dtype], fused_add, out))
+    keys = ("grid", "block", "smem", "stages", "rows_per_tile", "generic")
+    return dict(zip(keys, [int(v) for v in out]))

@@ -1,0 +1,152 @@
+/*
+ * agb.h -- C ABI of libagb_cuda.so: the RMSNorm forward / VJP / JVP path of cgadimpl,
+ * hand-written for NVIDIA B200 (sm_100a).
+ *
+ * Style follows cgadimpl's own raw-pointer kernel plugin (`ag::kernels::cuda()` loaded with
+ * `load_cuda_plugin("./libagkernels_cuda.so")`, cgadimpl/Tests/test_kernels_gpu.cpp:39-148):
+ * plain device pointers, element counts and a stream; the caller owns every buffer.
+ * Each entry point below names the reference code it replaces (paths inside the cgadimpl
+ * project).
+ *
+ * Conventions
+ *   - All tensors are row-major and contiguous: [rows, hidden]; `rows` is the product of all
+ *     leading dimensions, `hidden` the last one.  rows == 0 is a no-op.
+ *   - `dtype` is the storage type of x / y / gy / dx / gamma (AGB_F32 or AGB_BF16).  Statistics
+ *     (rstd) and dgamma are always fp32; all arithmetic is fp32 with fp64 reductions, rounded
+ *     exactly where the reference materialises a tensor.
+ *   - `stream` is a cudaStream_t (NULL = the legacy default stream).  Calls only enqueue work;
+ *     they never synchronise, allocate or free.
+ *   - Return value: AGB_OK or an agb_status_t; agb_last_error() gives a message for the
+ *     calling thread.  Nothing here calls exit() (the reference's CUDA_CHECK does,
+ *     cgadimpl/src/runtime/cuda_graphs.cpp:12-19).
+ *   - Re-entrant: no mutable global state except the launch counter and the per-device
+ *     properties cache (both atomic / locked).  cgadimpl's parallel backward calls VJP rules
+ *     from many threads (cgadimpl/src/core/autodiff.cpp:155-159).
+ *   - There is no CPU fallback: without a CUDA device every compute entry point returns
+ *     AGB_ERR_CUDA.
+ */
+#ifndef AGB_AGB_H
+#define AGB_AGB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    AGB_OK = 0,
+    AGB_ERR_INVALID_ARG = 1,   /* null pointer, negative size, bad enum */
+    AGB_ERR_UNSUPPORTED = 2,   /* dtype / shape outside what the kernels handle */
+    AGB_ERR_MISALIGNED = 3,    /* a pointer is not aligned to its element size */
+    AGB_ERR_CUDA = 4,          /* a CUDA runtime call failed (message has the CUDA error) */
+    AGB_ERR_WORKSPACE = 5,     /* workspace too small or missing */
+    AGB_ERR_TIMEOUT = 6        /* a bounded device-side wait gave up (see agb_device_status) */
+} agb_status_t;
+
+typedef enum { AGB_F32 = 0, AGB_BF16 = 1, AGB_F64 = 2 } agb_dtype_t;
+typedef enum { AGB_REDUCE_SUM = 0, AGB_REDUCE_MEAN = 1, AGB_REDUCE_MAX = 2 } agb_reduce_op_t;
+
+typedef void* agb_stream_t; /* cudaStream_t */
+
+/* ---- library ---- */
+int         agb_version(void);                 /* major*10000 + minor*100 + patch */
+const char* agb_status_string(int status);
+const char* agb_last_error(void);              /* thread-local, never NULL */
+
+/* Number of kernels this library has launched since load (all threads, all devices). */
+uint64_t agb_launch_count(void);
+
+/* Reads (and clears) the device-side status word of the current device: 0, or AGB_ERR_TIMEOUT
+ * if a kernel's bounded wait on a shared-memory barrier ran out (the kernel then skipped the
+ * rest of its work and returned; its outputs are undefined).  Synchronises the device. */
+int agb_device_status(void);
+
+/* Tuning knobs for sweeps ("stages", "ctas_per_sm", "threads", "force_generic"); value 0
+ * restores the built-in heuristic.  Returns AGB_ERR_INVALID_ARG for an unknown key. */
+int agb_set_option(const char* key, int64_t value);
+
+/* Describes the launch the heuristic would make: out[0]=grid, out[1]=block, out[2]=dynamic
+ * shared bytes, out[3]=pipeline stages, out[4]=rows per tile, out[5]=1 if the generic
+ * (unstaged) kernel is used.  `which`: 0 = forward, 1 = backward, 2 = jvp. */
+int agb_describe_launch(int which, int64_t rows, int64_t hidden, int dtype, int fused_add, int64_t out[6]);
+
+/* ---- RMSNorm forward ----
+ * Replaces rms_nodeops (cgadimpl/src/ops/normalization.cpp:23-35: x*x, reduce_mean, +eps, sqrt,
+ * 1/., x*rsqrt_var -- six tensor calls) followed, when gamma != NULL, by mul_nodeops with a
+ * [hidden] right operand (cgadimpl/src/ops/arithmetic.cpp:31-39).
+ *   y[r,j]  = (x[r,j] * rstd[r]) * gamma[j]        rstd[r] = 1 / sqrt(mean_j(x[r,j]^2) + eps)
+ * gamma == NULL gives the reference's gamma-less `rms(x)`.  rstd [rows] fp32 is tape[0]. */
+int agb_rmsnorm_fwd(const void* x, const void* gamma, void* y, float* rstd,
+                    int64_t rows, int64_t hidden, float eps, int dtype, agb_stream_t stream);
+
+/* ---- residual add + RMSNorm forward, fused ----
+ * Replaces add_nodeops (cgadimpl/src/ops/arithmetic.cpp:11-19) followed by the two calls above.
+ *   h = x + r;  y = rmsnorm(h) * gamma.   Writes h (the saved input of the norm), y and rstd. */
+int agb_add_rmsnorm_fwd(const void* x, const void* r, const void* gamma, void* h, void* y, float* rstd,
+                        int64_t rows, int64_t hidden, float eps, int dtype, agb_stream_t stream);
+
+/* ---- RMSNorm VJP ----
+ * Replaces vjp_Mul for the gamma product (cgadimpl/src/autodiff/autodiff_vjp_ops.cpp:54-59, with
+ * the column reduction of reduce_for_broadcast :15-35) and vjp_RMSNorm (:368-377):
+ *   dy   = gy * gamma                                  (gy itself when gamma == NULL)
+ *   dot  = sum_j dy[r,j] * x[r,j]
+ *   dx   = rstd * (dy - x * (rstd*rstd) * dot / hidden)   [+ dx_add]
+ *   dgamma[j] = sum_r gy[r,j] * (x[r,j] * rstd[r])
+ * dx_add (nullable) is added to dx: it fuses Node::accumulate_grad's `grad +=`
+ * (cgadimpl/src/core/graph.cpp:44-47) and the second parent of vjp_Add (:40-45).  dx_add may
+ * alias gy or dx (in-place accumulation).
+ * dgamma is produced in two deterministic stages: per-CTA fp64 partials in `workspace`
+ * (agb_rmsnorm_bwd_workspace_bytes), then a fixed-order column reduction.  `dgamma_dtype`:
+ * AGB_F32 writes the final fp32 [hidden]; AGB_F64 writes the un-rounded fp64 [hidden] sum, for
+ * a cross-device all-reduce or for accumulation over row chunks, to be finished with
+ * agb_dgamma_finalize.  With accumulate_dgamma the result is added to the old contents.
+ * dgamma == NULL skips it (then workspace may be NULL). */
+size_t agb_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t hidden, int dtype);
+int agb_rmsnorm_bwd(const void* x, const void* gamma, const float* rstd, const void* gy,
+                    const void* dx_add, void* dx, void* dgamma, int dgamma_dtype, int accumulate_dgamma,
+                    void* workspace, size_t workspace_bytes,
+                    int64_t rows, int64_t hidden, int dtype, agb_stream_t stream);
+
+/* Rounds an fp64 [hidden] column sum to fp32 (dgamma = (float)sum, or += when accumulate). */
+int agb_dgamma_finalize(const double* sum, float* dgamma, int64_t hidden, int accumulate, agb_stream_t stream);
+
+/* ---- RMSNorm JVP ----
+ * Replaces jvp_RMSNorm (cgadimpl/src/autodiff/autodiff_jvp_ops.cpp:366-379) and jvp_Mul (:24-31).
+ * The reference divides by tape[0] as if it held rms, but the forward stores rstd there, so its
+ * result is off by 1/rstd^2 per row; this entry point computes the mathematically correct
+ *   tyhat = tx*rstd - (yhat*dot)*(rstd/hidden),  dot = sum_j tx*yhat,  yhat = x*rstd
+ *   ty    = tyhat*gamma + yhat*tgamma            (tgamma may be NULL; gamma NULL -> ty = tyhat) */
+int agb_rmsnorm_jvp(const void* x, const void* gamma, const float* rstd, const void* tx, const void* tgamma,
+                    void* ty, int64_t rows, int64_t hidden, int dtype, agb_stream_t stream);
+
+/* ---- residual add and its VJP ----
+ * add_nodeops (arithmetic.cpp:11-19): out = a + b over n elements.
+ * vjp_Add (autodiff_vjp_ops.cpp:40-45) with accumulate_grad: ga += gy; gb += gy (either may be
+ * NULL).  Same shape as the legacy plugin's vjp_add(ga, gb, gy, n, stream)
+ * (cgadimpl/Tests/test_kernels_gpu.cpp:90). */
+int agb_residual_add(const void* a, const void* b, void* out, int64_t n, int dtype, agb_stream_t stream);
+int agb_vjp_add(void* ga, void* gb, const void* gy, int64_t n, int dtype, agb_stream_t stream);
+
+/* ---- broadcast scale and its VJP (the unfused gamma product) ----
+ * mul_nodeops with a [hidden] operand: out[r,j] = a[r,j] * g[j].
+ * vjp_Mul: da += gy*g (da nullable); dg += sum_r gy*a (dg fp32 [hidden], nullable, needs the
+ * same workspace as agb_rmsnorm_bwd). */
+int agb_scale_lastdim(const void* a, const void* g, void* out, int64_t rows, int64_t hidden, int dtype,
+                      agb_stream_t stream);
+
+/* ---- row and global reductions ----
+ * rowsum / rowmax (cgadimpl/src/ops/reduction.cpp:25-40) and the reduce_sum / reduce_mean
+ * (., {-1}, keepdim) primitive inside the norm: out[r] = op_j x[r,j], out has x's dtype.
+ * sum / mean_all (reduction.cpp:9-24): out[0] = op over all n elements, fp64 accumulation in a
+ * fixed order; workspace from agb_reduce_all_workspace_bytes. */
+int agb_row_reduce(int op, const void* x, void* out, int64_t rows, int64_t hidden, int dtype, agb_stream_t stream);
+size_t agb_reduce_all_workspace_bytes(int64_t n);
+int agb_reduce_all(int op, const void* x, void* out, int64_t n, int dtype,
+                   void* workspace, size_t workspace_bytes, agb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AGB_AGB_H */

@@ -1,0 +1,71 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the header declares, and
+rejects bad arguments before touching CUDA.  No compute call is made here."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from cgadimpl_b200 import _lib, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _lib.lib()
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "agb", "agb.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(agb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree(lib):
+    declared = _declared_symbols()
+    assert declared, "no declarations found"
+    assert sorted(_lib.SIGNATURES) == declared
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in agb.h but not exported"
+
+
+def test_version_and_strings(lib):
+    assert lib.agb_version() >= 100
+    assert lib.agb_status_string(0) == b"ok"
+    assert b"workspace" in lib.agb_status_string(5)
+    assert lib.agb_last_error() is not None
+
+
+def test_argument_validation_needs_no_device(lib):
+    one = C.c_void_p(0x1000)
+    # negative rows / zero hidden
+    assert lib.agb_rmsnorm_fwd(one, None, one, one, -1, 8, 1e-5, 0, None) == 1
+    assert lib.agb_rmsnorm_fwd(one, None, one, one, 4, 0, 1e-5, 0, None) == 1
+    # unknown dtype
+    assert lib.agb_rmsnorm_fwd(one, None, one, one, 4, 8, 1e-5, 7, None) == 2
+    # null x
+    assert lib.agb_rmsnorm_fwd(None, None, one, one, 4, 8, 1e-5, 0, None) == 1
+    assert b"x is NULL" in lib.agb_last_error()
+    # misaligned fp32 pointer
+    assert lib.agb_rmsnorm_fwd(C.c_void_p(0x1002), None, one, one, 4, 8, 1e-5, 0, None) == 3
+    # dgamma without gamma, bad dgamma dtype
+    assert lib.agb_rmsnorm_bwd(one, None, one, one, None, one, one, 0, 0, None, 0, 4, 8, 0, None) == 1
+    assert lib.agb_rmsnorm_bwd(one, one, one, one, None, one, one, 1, 0, None, 0, 4, 8, 0, None) == 1
+    # tgamma without gamma
+    assert lib.agb_rmsnorm_jvp(one, None, one, one, one, one, 4, 8, 0, None) == 1
+    # rows == 0 is a no-op that succeeds without a device
+    assert lib.agb_rmsnorm_fwd(None, None, None, None, 0, 8, 1e-5, 0, None) == 0
+    assert lib.agb_set_option(b"no_such_option", 1) == 1
+    assert lib.agb_set_option(b"stages", 0) == 0
+    assert lib.agb_reduce_all(2, one, one, 8, 0, one, 8192, None) == 1  # max is not a global op
+
+
+def test_no_cpu_fallback_without_device(lib):
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    one = C.c_void_p(0x1000)
+    assert lib.agb_rmsnorm_fwd(one, None, one, one, 4, 8, 1e-5, 0, None) == 4  # AGB_ERR_CUDA
