@@ -30,6 +30,8 @@ WORKLOADS = {
     # name: (rows per GPU, hidden, dtype, eps)
     "rmsnorm_fwd_vjp_fp32_16x2048x4096": (16 * 2048, 4096, "float32", 1e-5),
     "rmsnorm_fwd_vjp_fp32_8x512x1024": (8 * 512, 1024, "float32", 1e-6),
+    "rmsnorm_fwd_vjp_fp32_8192x4096": (8192, 4096, "float32", 1e-5),     # small case for ncu captures
+    "rmsnorm_fwd_vjp_bf16_16384x8192": (16384, 8192, "bfloat16", 1e-6),  # small case for ncu captures
     "rmsnorm_fwd_vjp_bf16_65536x8192": (65536, 8192, "bfloat16", 1e-6),
     "rmsnorm_fwd_vjp_bf16_65536x1000": (65536, 1000, "bfloat16", 1e-6),
     "rmsnorm_fwd_vjp_bf16_65536x5120": (65536, 5120, "bfloat16", 1e-6),

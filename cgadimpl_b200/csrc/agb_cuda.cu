@@ -114,7 +114,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
         }
     }
     int target = static_cast<int>(opt_threads.load());
-    if (target <= 0) target = which == kBwd ? 256 : 512;
+    if (target <= 0) target = which == kBwd ? 256 : 1024;
     if (target > max_threads) target = max_threads;
     int rpt = target / G;
     if (rpt < 1) rpt = 1;
@@ -129,14 +129,14 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
 
     int ctas = static_cast<int>(opt_ctas_per_sm.load());
     int want_stages = static_cast<int>(opt_stages.load());
-    const int max_stages = 8;
+    const int max_stages = 4;  // measured: depth beyond 3-4 tiles buys nothing, threads per SM do
     auto stages_for = [&](int c) {
         int avail = d.smem_per_sm / c - 1024;  // the runtime reserves 1 KB per resident CTA
         if (avail > d.smem_optin) avail = d.smem_optin;
         int s = (avail - fixed) / stage_stride;
         return s > max_stages ? max_stages : s;
     };
-    if (ctas <= 0) ctas = (stages_for(2) >= 4 && block <= 512) ? 2 : 1;
+    if (ctas <= 0) ctas = (stages_for(2) >= 3 && block * 2 <= max_threads * (which == kBwd ? 1 : 1)) ? 2 : 1;
     int S = stages_for(ctas);
     if (S < 2 && ctas > 1) { ctas = 1; S = stages_for(1); }
     if (S < 2) return;
