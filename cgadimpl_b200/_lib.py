@@ -27,6 +27,7 @@ SIGNATURES = {
     "agb_add_rmsnorm_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _vp]),
     "agb_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64, _i]),
     "agb_rmsnorm_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _sz, _i64, _i64, _i, _vp]),
+    "agb_rmsnorm_bwd_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i, _vp]),
     "agb_dgamma_finalize": (_i, [_vp, _vp, _i64, _i, _vp]),
     "agb_rmsnorm_jvp": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i, _vp]),
     "agb_residual_add": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),

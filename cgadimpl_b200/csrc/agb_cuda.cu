@@ -344,6 +344,32 @@ inline int ew_grid(int64_t work_items, const DevInfo& d) {
     return static_cast<int>(g);
 }
 
+
+// ------------------------------------------------------------------ built-in scratch (agb_rmsnorm_bwd_static)
+// The partial dgamma rows of agb_rmsnorm_bwd_static live in this array instead of a caller
+// workspace.  Every device that loads the library carries it until the process exits.
+// In host code the name below is only a handle for the runtime, NOT a device address: the
+// address is asked for once per device (with that device current) and cached.
+constexpr size_t kStaticScratchBytes = AGB_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+void* g_static_scratch_addr[kMaxDevices] = {};
+std::mutex g_static_scratch_mu;
+
+int static_scratch_for_current_device(void** out) {
+    int dev = 0;
+    AGB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(AGB_ERR_CUDA, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_static_scratch_mu);
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void* p = nullptr;
+        AGB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (p == nullptr) return fail(AGB_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        g_static_scratch_addr[dev] = p;
+    }
+    *out = g_static_scratch_addr[dev];
+    return AGB_OK;
+}
+
 }  // namespace
 
 // ====================================================================== C ABI
@@ -463,6 +489,42 @@ int agb_rmsnorm_bwd(const void* x, const void* gamma, const float* rstd, const v
                                    workspace_bytes, rows, hidden, st)
                : launch_bwd<bf16>(x, gamma, rstd, gy, dx_add, dx, dgamma, dgamma_dtype, accumulate_dgamma, workspace,
                                   workspace_bytes, rows, hidden, st);
+}
+
+int agb_rmsnorm_bwd_static(const void* x, const void* gamma, const float* rstd, const void* gy, const void* dx_add,
+                           void* dx, float* dgamma, int accumulate_dgamma, int64_t rows, int64_t hidden, int dtype,
+                           agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    if (dgamma && !gamma) return fail(AGB_ERR_INVALID_ARG, "dgamma requested without gamma");
+    if (rows > 0) {
+        AGB_TRY(check_ptr(x, "x", elem));
+        AGB_TRY(check_ptr(gy, "gy", elem));
+        AGB_TRY(check_ptr(dx, "dx", elem));
+        AGB_TRY(check_ptr(rstd, "rstd", 4));
+        AGB_TRY(check_ptr(dx_add, "dx_add", elem, false));
+    }
+    AGB_TRY(check_ptr(gamma, "gamma", elem, false));
+    AGB_TRY(check_ptr(dgamma, "dgamma", 4, false));
+    void* scratch = nullptr;
+    if (gamma && dgamma) {
+        const DevInfo* d;
+        AGB_TRY(device_info(&d));
+        const size_t need = static_cast<size_t>(max_partials(*d)) * hidden * sizeof(double);
+        if (need > kStaticScratchBytes)
+            return fail(AGB_ERR_WORKSPACE,
+                        "hidden=%lld needs %zu bytes of scratch but the built-in array holds %zu "
+                        "(largest hidden on this device: %zu); use agb_rmsnorm_bwd with a caller workspace",
+                        (long long)hidden, need, kStaticScratchBytes,
+                        kStaticScratchBytes / (static_cast<size_t>(max_partials(*d)) * sizeof(double)));
+        AGB_TRY(static_scratch_for_current_device(&scratch));
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == AGB_F32
+               ? launch_bwd<float>(x, gamma, rstd, gy, dx_add, dx, dgamma, AGB_F32, accumulate_dgamma, scratch,
+                                   kStaticScratchBytes, rows, hidden, st)
+               : launch_bwd<bf16>(x, gamma, rstd, gy, dx_add, dx, dgamma, AGB_F32, accumulate_dgamma, scratch,
+                                  kStaticScratchBytes, rows, hidden, st);
 }
 
 int agb_dgamma_finalize(const double* sum, float* dgamma, int64_t hidden, int accumulate, agb_stream_t stream) {

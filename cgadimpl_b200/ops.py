@@ -84,6 +84,19 @@ def rmsnorm_bwd(x, gamma, rstd, gy, dx_add=None, dx=None, dgamma=None, accumulat
     return dx, dgamma
 
 
+def rmsnorm_bwd_static(x, gamma, rstd, gy, dx_add=None, dx=None, dgamma=None, accumulate_dgamma=False):
+    """agb_rmsnorm_bwd_static: the VJP with the library's built-in scratch array instead of a caller
+    workspace (for callers that cannot allocate).  The output tensors are still the caller's; pass
+    dx and dgamma to make this wrapper allocation-free as well."""
+    rows, hidden = _rows_hidden(x)
+    dx = torch.empty_like(x) if dx is None else dx
+    if gamma is not None and dgamma is None:
+        dgamma = torch.zeros(hidden, dtype=torch.float32, device=x.device)
+    check(_lib.lib().agb_rmsnorm_bwd_static(_p(x), _p(gamma), _p(rstd), _p(gy), _p(dx_add), _p(dx), _p(dgamma),
+                                            int(bool(accumulate_dgamma)), rows, hidden, _dt(x), _stream()))
+    return dx, dgamma
+
+
 def dgamma_finalize(sum_f64, dgamma=None, accumulate=False):
     hidden = sum_f64.numel()
     dgamma = torch.empty(hidden, dtype=torch.float32, device=sum_f64.device) if dgamma is None else dgamma

@@ -109,6 +109,30 @@ int agb_rmsnorm_bwd(const void* x, const void* gamma, const float* rstd, const v
                     void* workspace, size_t workspace_bytes,
                     int64_t rows, int64_t hidden, int dtype, agb_stream_t stream);
 
+/* ---- RMSNorm VJP without a caller workspace ----
+ * No counterpart in the reference.  Same computation and same results as agb_rmsnorm_bwd with an
+ * fp32 dgamma, for callers that cannot hand over scratch memory because they cannot allocate any:
+ * a host that was given one fixed device arena at start-up and may not grow it (a real-time loop,
+ * an inference service running under a memory budget), or a plugin that receives raw tensor
+ * pointers but no allocator handle -- for them cudaMalloc in the hot path is off limits (it
+ * synchronises the device, can fail late and fragments the budget).
+ * The per-CTA dgamma partial rows go into an array of AGB_STATIC_SCRATCH_BYTES built into the
+ * library (every GPU that loads the library holds it until the process exits).  Consequences:
+ *   - limit: partial_rows * hidden * 8 <= AGB_STATIC_SCRATCH_BYTES, partial_rows = 2 * SM count;
+ *     on a 148-SM B200 that is hidden <= 8856.  Larger sizes are refused with AGB_ERR_WORKSPACE
+ *     and nothing is launched.
+ *   - the first call on each device looks up the array's device address (one CUDA runtime query,
+ *     no allocation); make that first call outside any stream capture.
+ *   - all calls share the one array.  It keeps the previous call's partials, which is harmless:
+ *     every partial row that is read has been fully rewritten by the same call, so nothing needs
+ *     clearing.  Two calls that overlap on the GPU (different streams, no dependency) race on it
+ *     and corrupt each other's dgamma; order them on one stream or with an event.
+ * The entry point itself calls no cudaMalloc, cudaFree or any allocating routine. */
+#define AGB_STATIC_SCRATCH_BYTES (20u << 20)
+int agb_rmsnorm_bwd_static(const void* x, const void* gamma, const float* rstd, const void* gy,
+                           const void* dx_add, void* dx, float* dgamma, int accumulate_dgamma,
+                           int64_t rows, int64_t hidden, int dtype, agb_stream_t stream);
+
 /* Rounds an fp64 [hidden] column sum to fp32 (dgamma = (float)sum, or += when accumulate). */
 int agb_dgamma_finalize(const double* sum, float* dgamma, int64_t hidden, int accumulate, agb_stream_t stream);
 
