@@ -33,6 +33,10 @@ SIGNATURES = {
     "agb_residual_add": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "agb_vjp_add": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "agb_scale_lastdim": (_i, [_vp, _vp, _vp, _i64, _i64, _i, _vp]),
+    "agb_binary_broadcast": (_i, [_i, _vp, _vp, _vp, _i64, _i64, _i, _i, _vp]),
+    "agb_accumulate_broadcast": (_i, [_vp, _vp, _i64, _i64, _i, _f, _i, _vp]),
+    "agb_mul_reduce_workspace_bytes": (_sz, [_i64, _i64]),
+    "agb_mul_reduce": (_i, [_vp, _vp, _vp, _i64, _i64, _i, _i, _vp, _sz, _i, _vp]),
     "agb_row_reduce": (_i, [_i, _vp, _vp, _i64, _i64, _i, _vp]),
     "agb_reduce_all_workspace_bytes": (_sz, [_i64]),
     "agb_reduce_all": (_i, [_i, _vp, _vp, _i64, _i, _vp, _sz, _vp]),

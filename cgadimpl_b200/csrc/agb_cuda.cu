@@ -607,6 +607,106 @@ int agb_scale_lastdim(const void* a, const void* g, void* out, int64_t rows, int
     return after_launch("scale_lastdim");
 }
 
+int agb_binary_broadcast(int op, const void* a, const void* b, void* out, int64_t rows, int64_t hidden, int b_mode,
+                         int dtype, agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    if (op < 0 || op > 1 || b_mode < 0 || b_mode > 3) return fail(AGB_ERR_INVALID_ARG, "op %d b_mode %d", op, b_mode);
+    if (rows == 0) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(a, "a", elem));
+    AGB_TRY(check_ptr(b, "b", elem));
+    AGB_TRY(check_ptr(out, "out", elem));
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = ew_grid(rows * hidden, *d);
+    if (dtype == AGB_F32) agb::binary_broadcast_kernel<float><<<grid, 256, 0, st>>>((const float*)a, (const float*)b, (float*)out, rows, (int)hidden, b_mode, op);
+    else agb::binary_broadcast_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)a, (const bf16*)b, (bf16*)out, rows, (int)hidden, b_mode, op);
+    return after_launch("binary_broadcast");
+}
+
+int agb_accumulate_broadcast(void* dst, const void* src, int64_t rows, int64_t hidden, int src_mode, float scale,
+                             int dtype, agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    if (src_mode < 0 || src_mode > 3) return fail(AGB_ERR_INVALID_ARG, "src_mode %d", src_mode);
+    if (rows == 0) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(dst, "dst", elem));
+    AGB_TRY(check_ptr(src, "src", elem));
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = ew_grid(rows * hidden, *d);
+    const int use_scale = scale != 1.0f;
+    if (dtype == AGB_F32) agb::accumulate_broadcast_kernel<float><<<grid, 256, 0, st>>>((float*)dst, (const float*)src, rows, (int)hidden, src_mode, scale, use_scale);
+    else agb::accumulate_broadcast_kernel<bf16><<<grid, 256, 0, st>>>((bf16*)dst, (const bf16*)src, rows, (int)hidden, src_mode, scale, use_scale);
+    return after_launch("accumulate_broadcast");
+}
+
+size_t agb_mul_reduce_workspace_bytes(int64_t rows, int64_t hidden) {
+    (void)rows;
+    const DevInfo* d;
+    if (hidden <= 0 || device_info(&d) != AGB_OK) return 0;
+    const size_t col = static_cast<size_t>(max_partials(*d)) * hidden * sizeof(double);
+    return col > 1024 * sizeof(double) ? col : 1024 * sizeof(double);
+}
+
+}  // extern "C"
+
+template <typename T>
+static int launch_mul_reduce(const void* g, const void* a, void* out, int64_t rows, int64_t hidden, int out_mode,
+                             int accumulate, double* ws, cudaStream_t st) {
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    if (out_mode == AGB_BCAST_LASTVEC) {
+        int P = static_cast<int>(rows < max_partials(*d) ? rows : max_partials(*d));
+        const int64_t rpc = (rows + P - 1) / P;
+        P = static_cast<int>((rows + rpc - 1) / rpc);
+        dim3 grid((unsigned)((hidden + 255) / 256), (unsigned)P);
+        agb::mul_colsum_partial_kernel<T><<<grid, 256, 0, st>>>((const T*)g, (const T*)a, ws, rows, (int)hidden, rpc);
+        AGB_TRY(after_launch("mul_colsum_partial"));
+        agb::colsum_finish_kernel<T><<<(unsigned)((hidden + 255) / 256), 256, 0, st>>>(ws, P, (int)hidden, (T*)out, accumulate);
+        return after_launch("colsum_finish");
+    }
+    if (out_mode == AGB_BCAST_ROWSTAT) {
+        agb::mul_rowsum_kernel<T><<<generic_grid(rows, *d), 256, 0, st>>>((const T*)g, (const T*)a, (T*)out, rows, (int)hidden, accumulate);
+        return after_launch("mul_rowsum");
+    }
+    int nb;
+    int64_t chunk;
+    const int64_t n = rows * hidden;
+    int64_t nbl = (n + 16383) / 16384;
+    if (nbl > 1024) nbl = 1024;
+    if (nbl < 1) nbl = 1;
+    chunk = (n + nbl - 1) / nbl;
+    nb = static_cast<int>((n + chunk - 1) / chunk);
+    agb::mul_sumall_stage1<T><<<nb, 256, 0, st>>>((const T*)g, (const T*)a, ws, n, chunk);
+    AGB_TRY(after_launch("mul_sumall_stage1"));
+    agb::sumall_finish_kernel<T><<<1, 32, 0, st>>>(ws, nb, (T*)out, accumulate);
+    return after_launch("sumall_finish");
+}
+
+extern "C" {
+
+int agb_mul_reduce(const void* g, const void* a, void* out, int64_t rows, int64_t hidden, int out_mode, int accumulate,
+                   void* workspace, size_t workspace_bytes, int dtype, agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    if (out_mode < AGB_BCAST_LASTVEC || out_mode > AGB_BCAST_SCALAR) return fail(AGB_ERR_INVALID_ARG, "out_mode %d", out_mode);
+    if (rows == 0) return fail(AGB_ERR_INVALID_ARG, "rows == 0");
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(g, "g", elem));
+    AGB_TRY(check_ptr(a, "a", elem, false));
+    AGB_TRY(check_ptr(out, "out", elem));
+    if (out_mode != AGB_BCAST_ROWSTAT) {
+        if (!workspace || workspace_bytes < agb_mul_reduce_workspace_bytes(rows, hidden))
+            return fail(AGB_ERR_WORKSPACE, "workspace %zu bytes, need %zu", workspace_bytes, agb_mul_reduce_workspace_bytes(rows, hidden));
+        AGB_TRY(check_ptr(workspace, "workspace", 8));
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == AGB_F32 ? launch_mul_reduce<float>(g, a, out, rows, hidden, out_mode, accumulate, (double*)workspace, st)
+                            : launch_mul_reduce<bf16>(g, a, out, rows, hidden, out_mode, accumulate, (double*)workspace, st);
+}
+
 int agb_row_reduce(int op, const void* x, void* out, int64_t rows, int64_t hidden, int dtype, agb_stream_t stream) {
     AGB_TRY(check_common(rows, hidden, dtype));
     if (op < AGB_REDUCE_SUM || op > AGB_REDUCE_MAX) return fail(AGB_ERR_INVALID_ARG, "op %d", op);

@@ -163,4 +163,148 @@ __global__ void __launch_bounds__(32) reduce_all_stage2(const double* __restrict
     }
 }
 
+// Broadcast modes of the second operand of a [rows, hidden] elementwise op.
+enum BcastMode { kBcastFull = 0, kBcastLastVec = 1, kBcastRowStat = 2, kBcastScalar = 3 };
+
+template <typename T>
+__device__ __forceinline__ float bcast_load(const T* b, int mode, long long row, int col, long long idx) {
+    switch (mode) {
+        case kBcastFull: return Vec<T>::load1(b + idx);
+        case kBcastLastVec: return Vec<T>::load1(b + col);
+        case kBcastRowStat: return Vec<T>::load1(b + row);
+        default: return Vec<T>::load1(b);
+    }
+}
+// The value a tensor of type T would hold after storing v (identity for fp32, one rounding for bf16).
+template <typename T>
+__device__ __forceinline__ float as_stored(float v);
+template <>
+__device__ __forceinline__ float as_stored<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float as_stored<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// out = a (op) broadcast(b);  op 0 add, 1 mul.  One rounding, like one tensor call.
+template <typename T>
+__global__ void __launch_bounds__(256) binary_broadcast_kernel(const T* a, const T* b, T* out, long long rows, int hidden,
+                                                               int mode, int op) {
+    const long long total = rows * hidden;
+    const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += nthreads) {
+        const long long row = i / hidden;
+        const int col = static_cast<int>(i - row * hidden);
+        const float av = Vec<T>::load1(a + i);
+        const float bv = bcast_load(b, mode, row, col, i);
+        Vec<T>::store1(out + i, op == 0 ? add_rn(av, bv) : mul_rn(av, bv));
+    }
+}
+
+// dst += broadcast(src) [* scale].  With use_scale the product is rounded first, as the separate
+// tensor call `gy * scale` of the reference would, then the accumulation rounds once more.
+template <typename T>
+__global__ void __launch_bounds__(256) accumulate_broadcast_kernel(T* dst, const T* src, long long rows, int hidden,
+                                                                   int mode, float scale, int use_scale) {
+    const long long total = rows * hidden;
+    const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += nthreads) {
+        const long long row = i / hidden;
+        const int col = static_cast<int>(i - row * hidden);
+        float sv = bcast_load(src, mode, row, col, i);
+        if (use_scale) sv = as_stored<T>(mul_rn(sv, scale));
+        Vec<T>::store1(dst + i, add_rn(Vec<T>::load1(dst + i), sv));
+    }
+}
+
+// Column sums of a product, stage 1: partials[p, c] = sum over the p-th chunk of rows of g*a
+// (a may be null: plain column sum).  grid (ceil(hidden/256), P); rows in order, fp64.
+template <typename T>
+__global__ void __launch_bounds__(256) mul_colsum_partial_kernel(const T* __restrict__ g, const T* __restrict__ a,
+                                                                 double* __restrict__ partials, long long rows,
+                                                                 int hidden, long long rows_per_chunk) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    const long long r0 = static_cast<long long>(blockIdx.y) * rows_per_chunk;
+    long long r1 = r0 + rows_per_chunk;
+    if (r1 > rows) r1 = rows;
+    if (c >= hidden) return;
+    double acc = 0.0;
+    for (long long row = r0; row < r1; ++row) {
+        float v = Vec<T>::load1(g + row * hidden + c);
+        if (a) v = as_stored<T>(mul_rn(v, Vec<T>::load1(a + row * hidden + c)));
+        acc += static_cast<double>(v);
+    }
+    partials[static_cast<size_t>(blockIdx.y) * hidden + c] = acc;
+}
+// Stage 2 for a T-typed destination: out[c] (+)= (T) sum_p partials[p, c], p in order.
+template <typename T>
+__global__ void __launch_bounds__(256) colsum_finish_kernel(const double* __restrict__ partials, int P, int hidden,
+                                                            T* out, int accumulate) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= hidden) return;
+    double t = 0.0;
+    for (int p = 0; p < P; ++p) t += partials[static_cast<size_t>(p) * hidden + c];
+    const float v = as_stored<T>(static_cast<float>(t));
+    Vec<T>::store1(out + c, accumulate ? add_rn(Vec<T>::load1(out + c), v) : v);
+}
+
+// Row sums of a product: out[r] (+)= (T) sum_j g[r,j]*a[r,j]; one CTA of 256 threads per row.
+template <typename T>
+__global__ void __launch_bounds__(256) mul_rowsum_kernel(const T* __restrict__ g, const T* __restrict__ a, T* out,
+                                                         long long rows, int hidden, int accumulate) {
+    __shared__ double s[2][8];
+    int phase = 0;
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x, phase ^= 1) {
+        double acc = 0.0;
+        for (int j = threadIdx.x; j < hidden; j += 256) {
+            float v = Vec<T>::load1(g + row * hidden + j);
+            if (a) v = as_stored<T>(mul_rn(v, Vec<T>::load1(a + row * hidden + j)));
+            acc += static_cast<double>(v);
+        }
+        acc = warp_sum(acc);
+        if ((threadIdx.x & 31) == 0) s[phase][threadIdx.x >> 5] = acc;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0.0;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) t += s[phase][w];
+            const float v = as_stored<T>(static_cast<float>(t));
+            Vec<T>::store1(out + row, accumulate ? add_rn(Vec<T>::load1(out + row), v) : v);
+        }
+    }
+}
+
+// Global sum of a product, stage 1 (same chunking as reduce_all_stage1); stage 2 below.
+template <typename T>
+__global__ void __launch_bounds__(256) mul_sumall_stage1(const T* __restrict__ g, const T* __restrict__ a,
+                                                         double* __restrict__ partial, long long n, long long chunk) {
+    __shared__ double s[8];
+    const long long i0 = static_cast<long long>(blockIdx.x) * chunk;
+    long long i1 = i0 + chunk;
+    if (i1 > n) i1 = n;
+    double v = 0.0;
+    for (long long i = i0 + threadIdx.x; i < i1; i += 256) {
+        float t = Vec<T>::load1(g + i);
+        if (a) t = as_stored<T>(mul_rn(t, Vec<T>::load1(a + i)));
+        v += static_cast<double>(t);
+    }
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += s[w];
+        partial[blockIdx.x] = t;
+    }
+}
+template <typename T>
+__global__ void __launch_bounds__(32) sumall_finish_kernel(const double* __restrict__ partial, int nblocks, T* out,
+                                                           int accumulate) {
+    double v = 0.0;
+    for (int i = threadIdx.x; i < nblocks; i += 32) v += partial[i];
+    v = warp_sum(v);
+    if (threadIdx.x == 0) {
+        const float r = as_stored<T>(static_cast<float>(v));
+        Vec<T>::store1(out, accumulate ? add_rn(Vec<T>::load1(out), r) : r);
+    }
+}
+
 }  // namespace agb

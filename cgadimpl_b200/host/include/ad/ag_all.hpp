@@ -1,0 +1,8 @@
+// ag_all.hpp -- umbrella header (cgadimpl/include/ad/ag_all.hpp:4-10).
+#pragma once
+#include <cuda_runtime.h>
+
+#include "ad/autodiff/autodiff.hpp"
+#include "ad/detail/autodiff_ops.hpp"
+#include "ad/runtime/cuda_graphs.hpp"
+#include "ad/utils/debug.hpp"

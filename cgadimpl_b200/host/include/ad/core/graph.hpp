@@ -1,0 +1,87 @@
+// graph.hpp -- Value / Node / topo_from with the members and signatures of
+// cgadimpl/include/ad/core/graph.hpp:18-86.  Checkpointing and version-tracking members are kept
+// as plain fields (unused here) so code that touches them still compiles.
+#pragma once
+#include <atomic>
+#include <functional>
+#include <memory>
+#include <mutex>
+#include <utility>
+#include <vector>
+
+#include "ad/core/schema.hpp"
+#include "ad/runtime/cuda_graphs.hpp"
+#include "tensor.hpp"
+
+namespace ag {
+struct Node;
+using HookFn = std::function<void(Node*)>;
+
+struct Value {
+    std::shared_ptr<Node> node;
+    Value();
+    explicit Value(std::shared_ptr<Node> n);
+    Value(float v);  // scalar literal: a [1] fp32 CPU leaf that does not require grad
+    const std::vector<int64_t>& shape() const;
+    std::pair<int, int> shape_2d() const;
+    Tensor& val();
+    const Tensor& val() const;
+    Tensor& grad();
+    const Tensor& grad() const;
+    void register_hook(HookFn hook);
+};
+
+struct Node : std::enable_shared_from_this<Node> {
+    Tensor value;
+    Tensor grad;
+
+    std::vector<std::shared_ptr<Node>> inputs;
+    std::vector<Value> saved_inputs;
+    std::vector<std::shared_ptr<Tensor>> tape;
+
+    std::vector<uint8_t> saved_rng_blob;
+    bool is_checkpoint{false};
+    bool has_saved_rng{false};
+
+    const char* debug_name{""};
+    Op op{Op::Leaf};
+    bool is_leaf{false};
+    std::vector<int> input_versions;
+
+    std::atomic<int> child_grad_count{0};
+    std::mutex grad_mutex;
+
+    std::vector<HookFn> post_acc_grad_hooks;
+    void register_hook(HookFn hook) { post_acc_grad_hooks.push_back(std::move(hook)); }
+
+    struct ExecutionContext {
+        ag_cuda_stream_t stream{nullptr};
+        DeviceIndex device;
+    };
+    ExecutionContext creation_context;
+
+    float eps{1e-5f};  // normalisation nodes only (the reference hard-codes 1e-5)
+
+    bool requires_grad_flag_{false};
+    bool requires_grad() const { return requires_grad_flag_; }
+    const std::vector<int64_t>& shape() const { return value.shape().dims; }
+
+    // grad += contribution under grad_mutex; the contribution may be broadcast ([rows,1], [hidden]
+    // or [1] against [rows, hidden]), as `grad += gy` is in the reference's row-reduction rules.
+    void accumulate_grad(const Tensor& grad_contribution);
+
+    Node(const Tensor& v, Op op_, bool req_grad, const char* nm = "");
+    Node() = default;
+};
+
+inline Value make_tensor(const Tensor& v, const char* name = "") {
+    return Value(std::make_shared<Node>(v, Op::Leaf, v.requires_grad(), name));
+}
+
+std::vector<Node*> topo_from(Node* root);  // parents before children
+
+inline void Value::register_hook(HookFn hook) {
+    if (node) node->register_hook(std::move(hook));
+}
+
+}  // namespace ag

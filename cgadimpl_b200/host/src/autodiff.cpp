@@ -1,0 +1,188 @@
+// autodiff.cpp -- zero_grad / backward / jvp with the semantics of cgadimpl/src/core/autodiff.cpp:
+// reverse-topological VJP dispatch with post-accumulate hooks (:75-96), an opt-in multi-threaded
+// mode driven by per-node dependency counters (:98-170), and a forward tangent sweep (:221-252).
+#include "ad/autodiff/autodiff.hpp"
+
+#include <atomic>
+#include <condition_variable>
+#include <deque>
+#include <exception>
+#include <thread>
+
+#include "ad/detail/autodiff_ops.hpp"
+#include "ad/detail/host_util.hpp"
+
+namespace ag {
+
+void zero_grad(const Value& root) {
+    for (Node* n : topo_from(root.node.get()))
+        if (n->requires_grad()) {
+            detail::StreamGuard g(n->creation_context.stream);
+            if (n->grad.defined() && n->grad.numel() == n->value.numel()) n->grad.zero_();
+            else n->grad = Tensor::zeros(n->value.shape(), ag::options(n->value));
+        }
+}
+
+namespace {
+
+// Blocking queue of ready nodes (same job as cgadimpl/include/ad/core/ReadyQueue.hpp:12-51).
+class ReadyQueue {
+public:
+    void push(Node* n) {
+        { std::lock_guard<std::mutex> lk(mu_); q_.push_back(n); }
+        cv_.notify_one();
+    }
+    Node* pop() {  // nullptr after shutdown
+        std::unique_lock<std::mutex> lk(mu_);
+        cv_.wait(lk, [&] { return stop_ || !q_.empty(); });
+        if (q_.empty()) return nullptr;
+        Node* n = q_.front();
+        q_.pop_front();
+        return n;
+    }
+    void shutdown() {
+        { std::lock_guard<std::mutex> lk(mu_); stop_ = true; }
+        cv_.notify_all();
+    }
+private:
+    std::mutex mu_;
+    std::condition_variable cv_;
+    std::deque<Node*> q_;
+    bool stop_ = false;
+};
+
+void run_hooks(Node* n) {
+    for (auto& h : n->post_acc_grad_hooks) h(n);
+}
+
+}  // namespace
+
+void backward(const Value& root, const Tensor* grad_seed, bool enable_parallel) {
+    if (!root.node) return;
+    auto order = topo_from(root.node.get());
+
+    for (Node* n : order) n->child_grad_count = 0;
+    for (Node* n : order)
+        for (auto& p : n->inputs)
+            if (p && p->requires_grad()) p->child_grad_count++;
+
+    if (root.node->requires_grad()) {
+        if (grad_seed) {
+            root.node->grad = *grad_seed;
+        } else {
+            detail::StreamGuard g(root.node->creation_context.stream);
+            auto opts = ag::options(root.node->value);
+            root.node->grad = root.node->value.numel() == 1 ? Tensor::ones(Shape{{1}}, opts)
+                                                            : Tensor::ones(root.node->value.shape(), opts);
+        }
+    }
+
+    if (!enable_parallel) {
+        for (auto it = order.rbegin(); it != order.rend(); ++it) {
+            Node* n = *it;
+            if (!n->requires_grad()) continue;
+            debug::on_backprop_step(n, n->grad);
+            if (VjpFn fn = vjp_lookup(n->op)) fn(n, n->grad);
+            run_hooks(n);
+        }
+        return;
+    }
+
+    // Parallel mode.  A node becomes ready when every child that owes it a gradient has run.
+    // Differences from the reference: the main thread blocks on a condition variable instead of
+    // polling with 1 ms sleeps, and an exception in a rule is carried to the caller instead of
+    // being dropped.
+    int pending = 0;
+    for (Node* n : order)
+        if (n->requires_grad()) ++pending;
+    if (pending == 0) return;
+
+    ReadyQueue rq;
+    std::mutex done_mu;
+    std::condition_variable done_cv;
+    std::atomic<int> remaining{pending};
+    std::exception_ptr error;
+
+    auto finish_one = [&] {
+        if (remaining.fetch_sub(1) == 1) {
+            std::lock_guard<std::mutex> lk(done_mu);
+            done_cv.notify_all();
+        }
+    };
+    auto fail = [&](std::exception_ptr e) {
+        std::lock_guard<std::mutex> lk(done_mu);
+        if (!error) error = e;
+        remaining = 0;
+        done_cv.notify_all();
+    };
+
+    for (Node* n : order)
+        if (n->requires_grad() && n->child_grad_count == 0) {
+            run_hooks(n);
+            if (!n->is_leaf) rq.push(n);
+            else finish_one();
+        }
+
+    auto worker = [&] {
+        while (Node* n = rq.pop()) {
+            try {
+                if (VjpFn fn = vjp_lookup(n->op)) fn(n, n->grad);
+                for (auto& pp : n->inputs) {
+                    Node* p = pp.get();
+                    if (!p || !p->requires_grad()) continue;
+                    if (p->child_grad_count.fetch_sub(1) == 1) {
+                        run_hooks(p);
+                        if (!p->is_leaf) rq.push(p);
+                        else finish_one();
+                    }
+                }
+                finish_one();
+            } catch (...) {
+                fail(std::current_exception());
+            }
+        }
+    };
+
+    unsigned nthreads = std::thread::hardware_concurrency();
+    if (nthreads == 0) nthreads = 1;
+    if (nthreads > 16) nthreads = 16;
+    std::vector<std::thread> workers;
+    for (unsigned i = 0; i < nthreads; ++i) workers.emplace_back(worker);
+    {
+        std::unique_lock<std::mutex> lk(done_mu);
+        done_cv.wait(lk, [&] { return remaining.load() <= 0; });
+    }
+    rq.shutdown();
+    for (auto& w : workers) w.join();
+    if (error) std::rethrow_exception(error);
+}
+
+Tensor jvp(const Value& root, const std::unordered_map<Node*, Tensor>& seed) {
+    if (!root.node) return Tensor();
+    auto order = topo_from(root.node.get());
+    std::unordered_map<Node*, Tensor> T;
+    T.reserve(order.size());
+    static const Tensor kEmpty;
+    auto tangent_of = [&](Node* p) -> const Tensor& {
+        auto it = T.find(p);
+        return it != T.end() ? it->second : kEmpty;
+    };
+    for (Node* n : order) {
+        Tensor t;
+        if (auto it = seed.find(n); it != seed.end()) {
+            t = it->second;
+        } else if (n->is_leaf) {
+            detail::StreamGuard g(current_stream());
+            t = Tensor::zeros(n->value.shape(), ag::options(n->value).with_req_grad(false));
+        }
+        debug::on_jvp_step(n);
+        if (!n->is_leaf) {
+            T[n] = t;  // visible to the rule as "no tangent yet"
+            if (JvpFn fn = jvp_lookup(n->op)) t = fn(n, tangent_of);
+        }
+        T[n] = t;
+    }
+    return T[root.node.get()];
+}
+
+}  // namespace ag

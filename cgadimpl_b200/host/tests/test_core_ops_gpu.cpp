@@ -1,0 +1,136 @@
+// test_core_ops_gpu.cpp -- the reference's own gradient checks for the ops on this path
+// (cgadimpl/Tests/test_core_ops_gpu.cpp): central finite differences against backward(), max-abs
+// error <= 1e-3, on the same shapes: RMSNorm randn [4,10] (:262-267), broadcast Add and Mul
+// [4,5] (.) [1,5] including the reduced gradient of the broadcast operand (:182-205), Sum, Mean,
+// RowSum (:216-233).  Two deviations keep the check's own noise under its tolerance: the step is
+// 1e-2 instead of 1e-4 (fp32 forward values carry ~1e-7 of rounding; 1e-7 / 2e-4 ~ 1e-3), and the
+// perturbed losses are summed on the host in double.
+#include "ad/ag_all.hpp"
+#include "check.hpp"
+
+using namespace ag;
+
+static bool check_grad(const Tensor& analytical, const std::vector<float>& numerical, double tol = 1e-3) {
+    auto a = analytical.to_vector();
+    if (a.size() != numerical.size()) { std::fprintf(stderr, "  shape mismatch\n"); return false; }
+    double err = 0;
+    for (size_t i = 0; i < a.size(); ++i) err = std::max(err, std::fabs(double(a[i]) - double(numerical[i])));
+    if (err > tol) std::fprintf(stderr, "  max error %.3e > %.1e\n", err, tol);
+    return err <= tol;
+}
+
+static double host_sum(const Value& v) {
+    double s = 0;
+    for (float f : v.val().to_vector()) s += f;
+    return s;
+}
+
+// d sum(func()) / d param by central differences, one element at a time
+static std::vector<float> numerical_gradient(Value& param, const std::function<Value()>& func, double h = 1e-2) {
+    const Tensor original = param.val().clone();
+    const std::vector<float> base = original.to_vector();
+    std::vector<float> grad(base.size());
+    const DeviceIndex dev = param.val().device();
+    for (size_t i = 0; i < base.size(); ++i) {
+        std::vector<float> p = base;
+        p[i] = static_cast<float>(base[i] + h);
+        param.val() = Tensor::from_host(p.data(), original.shape(), ag::options(original)).to(dev);
+        const double l1 = host_sum(func());
+        p[i] = static_cast<float>(base[i] - h);
+        param.val() = Tensor::from_host(p.data(), original.shape(), ag::options(original)).to(dev);
+        const double l2 = host_sum(func());
+        grad[i] = static_cast<float>((l1 - l2) / (2.0 * h));
+    }
+    param.val() = original;
+    return grad;
+}
+
+int main() {
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) { std::printf("no CUDA device\n"); return 2; }
+    OwnTensor::manual_seed(1234);
+    const auto opts = TensorOptions().with_device(DeviceIndex(Device::CUDA)).with_req_grad(true);
+
+    run_test("Add (Broadcast)", [&] {
+        Value a = make_tensor(Tensor::randn(Shape{{4, 5}}, opts));
+        Value b = make_tensor(Tensor::randn(Shape{{1, 5}}, opts));
+        auto f = [&] { return a + b; };
+        backward(sum(f()));
+        CHECK(check_grad(a.grad(), numerical_gradient(a, f)));
+        CHECK(check_grad(b.grad(), numerical_gradient(b, f)));
+    });
+    run_test("Mul (Broadcast)", [&] {
+        Value a = make_tensor(Tensor::randn(Shape{{4, 5}}, opts));
+        Value b = make_tensor(Tensor::randn(Shape{{1, 5}}, opts));
+        auto f = [&] { return a * b; };
+        backward(sum(f()));
+        CHECK(check_grad(a.grad(), numerical_gradient(a, f)));
+        CHECK(check_grad(b.grad(), numerical_gradient(b, f)));
+    });
+    run_test("Mul (row statistic and scalar literal)", [&] {
+        Value a = make_tensor(Tensor::randn(Shape{{4, 5}}, opts));
+        Value s = make_tensor(Tensor::randn(Shape{{4, 1}}, opts));
+        auto f = [&] { return (a * s) * 0.5f; };
+        backward(sum(f()));
+        CHECK(check_grad(a.grad(), numerical_gradient(a, f)));
+        CHECK(check_grad(s.grad(), numerical_gradient(s, f)));
+    });
+    run_test("Sum (all)", [&] {
+        Value a = make_tensor(Tensor::randn(Shape{{4, 5}}, opts));
+        auto f = [&] { return sum(a); };
+        backward(f());
+        CHECK(check_grad(a.grad(), numerical_gradient(a, f)));
+    });
+    run_test("Mean (all)", [&] {
+        Value a = make_tensor(Tensor::randn(Shape{{4, 5}}, opts));
+        auto f = [&] { return mean_all(a); };
+        backward(f());
+        CHECK(check_grad(a.grad(), numerical_gradient(a, f)));
+    });
+    run_test("RowSum", [&] {
+        Value a = make_tensor(Tensor::randn(Shape{{4, 5}}, opts));
+        auto f = [&] { return rowsum(a); };
+        backward(sum(f()));
+        CHECK(check_grad(a.grad(), numerical_gradient(a, f)));
+    });
+    run_test("RowMax forward; its VJP throws like the reference", [&] {
+        Value a = make_tensor(Tensor::randn(Shape{{4, 5}}, opts));
+        auto v = a.val().to_vector(), m = rowmax(a).val().to_vector();
+        for (int r = 0; r < 4; ++r) {
+            float want = v[r * 5];
+            for (int j = 1; j < 5; ++j) want = std::max(want, v[r * 5 + j]);
+            CHECK(m[r] == want);
+        }
+        bool threw = false;
+        try { backward(sum(rowmax(a))); } catch (const std::runtime_error&) { threw = true; }
+        CHECK(threw);
+    });
+    run_test("RMSNorm", [&] {
+        Value a = make_tensor(Tensor::randn(Shape{{4, 10}}, opts));
+        auto f = [&] { return rms(a); };
+        backward(sum(f()));
+        CHECK(check_grad(a.grad(), numerical_gradient(a, f)));
+    });
+    run_test("RMSNorm with per-channel gamma (fused node)", [&] {
+        Value a = make_tensor(Tensor::randn(Shape{{4, 10}}, opts));
+        Value g = make_tensor(Tensor::randn(Shape{{10}}, opts));
+        auto f = [&] { return rmsnorm(a, g, 1e-6f); };
+        backward(sum(f()));
+        CHECK(check_grad(a.grad(), numerical_gradient(a, f)));
+        CHECK(check_grad(g.grad(), numerical_gradient(g, f)));
+    });
+    run_test("RealRMSNorm (scalar gain; the reference's rules throw)", [&] {
+        Value a = make_tensor(Tensor::randn(Shape{{4, 10}}, opts));
+        auto f = [&] { return realrms(a, 1.5f); };
+        Value y = f();
+        Node* G = y.node->inputs[1].get();
+        zero_grad(y);
+        backward(sum(y));
+        CHECK(check_grad(a.grad(), numerical_gradient(a, f)));
+        // dG = sum(yhat): compare with the sum of rms(a)
+        const double want = host_sum(rms(a));
+        CHECK(std::fabs(G->grad.to_vector()[0] - want) <= 1e-3);
+    });
+    cudaDeviceSynchronize();
+    return finish("test_core_ops_gpu");
+}

@@ -1,0 +1,136 @@
+// test_host_cpu.cpp -- the parts of the host layer that need no GPU: op registry (names, arities
+// and enum values as in the reference's registry), topological order, CPU tensors, broadcast
+// classification, the allocator's budget knob (host-side out-of-memory injection) and the error
+// behaviour of ops given CPU tensors (there is no CPU implementation of the path).
+#include "ad/ag_all.hpp"
+#include "ad/detail/host_util.hpp"
+#include "check.hpp"
+
+using namespace ag;
+
+int main() {
+    run_test("registry: names, arities, numbering", [] {
+        CHECK(static_cast<int>(Op::Leaf) == 0);
+        CHECK(static_cast<int>(Op::Add) == 1 && static_cast<int>(Op::Mul) == 3);
+        CHECK(static_cast<int>(Op::Sum) == 34 && static_cast<int>(Op::RowMax) == 37);
+        CHECK(static_cast<int>(Op::LayerNorm) == 44 && static_cast<int>(Op::RMSNorm) == 45);
+        CHECK(static_cast<int>(Op::RealRMSNorm) == 46 && static_cast<int>(Op::MAELoss) == 53);
+        CHECK(static_cast<int>(Op::RMSNormAffine) == 54 && OpCount == 55);
+        CHECK(std::string(op_name(Op::RMSNorm)) == "rmsnorm" && op_arity(Op::RMSNorm) == 1);
+        CHECK(std::string(op_name(Op::RealRMSNorm)) == "realrmsnorm");
+        CHECK(std::string(op_name(Op::Add)) == "add" && op_arity(Op::Add) == 2);
+        CHECK(std::string(op_name(Op::RowSum)) == "rowsum" && op_arity(Op::Linear) == 3);
+        CHECK(op_arity(Op::Leaf) == 0 && op_arity(Op::Dyntanh) == 4);
+        CHECK(std::string(op_name(Op::RMSNormAffine)) == "rmsnorm_affine" && op_arity(Op::RMSNormAffine) == 2);
+        for (std::size_t i = 0; i < OpCount; ++i) {
+            CHECK(vjp_lookup(static_cast<Op>(i)) != nullptr);
+            CHECK(jvp_lookup(static_cast<Op>(i)) != nullptr);
+        }
+    });
+
+    run_test("rules outside the path throw, RowMax like the reference", [] {
+        Node n;
+        Tensor t;
+        bool threw = false;
+        try { vjp_lookup(Op::MatMul)(&n, t); } catch (const std::runtime_error&) { threw = true; }
+        CHECK(threw);
+        threw = false;
+        try { vjp_lookup(Op::RowMax)(&n, t); } catch (const std::runtime_error& e) {
+            threw = std::string(e.what()).find("RowMax") != std::string::npos;
+        }
+        CHECK(threw);
+    });
+
+    run_test("CPU tensors: factories, copies, reshape", [] {
+        OwnTensor::manual_seed(7);
+        Tensor a = Tensor::randn(Shape{{3, 5}}, TensorOptions());
+        OwnTensor::manual_seed(7);
+        Tensor b = Tensor::randn(Shape{{3, 5}}, TensorOptions());
+        CHECK(a.to_vector() == b.to_vector());
+        CHECK(a.numel() == 15 && a.shape().dims.size() == 2 && !a.is_cuda());
+        Tensor z = Tensor::zeros(Shape{{4}}), o = Tensor::ones(Shape{{4}}), f = Tensor::full(Shape{{2, 2}}, TensorOptions(), 2.5f);
+        CHECK(z.to_vector() == std::vector<float>(4, 0.f) && o.to_vector() == std::vector<float>(4, 1.f));
+        CHECK(f.to_vector() == std::vector<float>(4, 2.5f));
+        Tensor c = a.clone();
+        c.data<float>()[0] = 42.f;
+        CHECK(a.data<float>()[0] != 42.f);
+        Tensor r = a.reshape(Shape{{5, 3}});
+        CHECK(r.data<float>() == a.data<float>() && r.shape().dims[0] == 5);
+        Tensor h = Tensor::full(Shape{{8}}, TensorOptions().with_dtype(Dtype::Bfloat16), 1.0f + 1.0f / 256);
+        CHECK(h.nbytes() == 16 && h.to_vector()[3] == 1.0f);  // 1 + 2^-8 rounds to even in bf16
+        Tensor e;
+        CHECK(!e.defined() && e.numel() == 0);
+    });
+
+    run_test("graph: Value, make_tensor, topo_from", [] {
+        Value s(2.0f);
+        CHECK(s.node->is_leaf && !s.node->requires_grad() && s.val().numel() == 1 && s.val().to_vector()[0] == 2.0f);
+        CHECK(s.shape_2d().first == 1 && s.shape_2d().second == 1);
+        Value a = make_tensor(Tensor::zeros(Shape{{2, 3}}, TensorOptions().with_req_grad(true)), "a");
+        CHECK(a.node->requires_grad() && a.grad().numel() == 6 && std::string(a.node->debug_name) == "a");
+        CHECK(a.shape_2d().first == 2 && a.shape_2d().second == 3);
+        // a diamond, built by hand: d depends on b and c, both depend on a
+        auto mk = [](std::initializer_list<std::shared_ptr<Node>> in) {
+            auto n = std::make_shared<Node>(Tensor::zeros(Shape{{1}}), Op::Add, false, "n");
+            n->inputs.assign(in.begin(), in.end());
+            return n;
+        };
+        auto b = mk({a.node}), c = mk({a.node}), d = mk({b, c});
+        auto order = topo_from(d.get());
+        CHECK(order.size() == 4 && order.front() == a.node.get() && order.back() == d.get());
+        // a 100000-deep chain must not overflow the stack
+        std::shared_ptr<Node> cur = a.node;
+        for (int i = 0; i < 100000; ++i) cur = mk({cur});
+        CHECK(topo_from(cur.get()).size() == 100001);
+        int fired = 0;
+        a.register_hook([&](Node*) { ++fired; });
+        for (auto& h : a.node->post_acc_grad_hooks) h(a.node.get());
+        CHECK(fired == 1);
+    });
+
+    run_test("broadcast classification", [] {
+        Tensor full = Tensor::zeros(Shape{{4, 5}});
+        CHECK(detail::classify_broadcast(full, Tensor::zeros(Shape{{4, 5}})) == AGB_BCAST_FULL);
+        CHECK(detail::classify_broadcast(full, Tensor::zeros(Shape{{5}})) == AGB_BCAST_LASTVEC);
+        CHECK(detail::classify_broadcast(full, Tensor::zeros(Shape{{1, 5}})) == AGB_BCAST_LASTVEC);
+        CHECK(detail::classify_broadcast(full, Tensor::zeros(Shape{{4, 1}})) == AGB_BCAST_ROWSTAT);
+        CHECK(detail::classify_broadcast(full, Tensor::zeros(Shape{{1}})) == AGB_BCAST_SCALAR);
+        CHECK(detail::classify_broadcast(Tensor::zeros(Shape{{2, 3, 8}}), Tensor::zeros(Shape{{2, 3, 1}})) == AGB_BCAST_ROWSTAT);
+        bool threw = false;
+        try { detail::classify_broadcast(full, Tensor::zeros(Shape{{4}})); } catch (const std::runtime_error&) { threw = true; }
+        CHECK(threw);
+    });
+
+    run_test("no CPU implementation: ops on CPU tensors throw", [] {
+        Value a = make_tensor(Tensor::randn(Shape{{4, 10}}, TensorOptions().with_req_grad(true)));
+        bool threw = false;
+        try { rms(a); } catch (const std::runtime_error& e) { threw = std::string(e.what()).find("CPU") != std::string::npos; }
+        CHECK(threw);
+        threw = false;
+        try { a + a; } catch (const std::runtime_error&) { threw = true; }
+        CHECK(threw);
+    });
+
+    run_test("allocator budget: out-of-memory is raised on the host", [] {
+        auto& al = OwnTensor::cuda::DeviceAllocator::instance();
+        al.set_memory_limit(1 << 20);
+        bool threw = false;
+        try { al.allocate(8 << 20, 0, nullptr); } catch (const std::runtime_error& e) {
+            threw = std::string(e.what()).find("out of memory") != std::string::npos;
+        }
+        al.set_memory_limit(0);
+        CHECK(threw);
+        CHECK(al.stats().device_allocs == 0);
+    });
+
+    run_test("thread-local stream slot", [] {
+        CHECK(current_stream() == nullptr);
+        set_current_stream(reinterpret_cast<ag_cuda_stream_t>(0x10));
+        CHECK(current_stream() == reinterpret_cast<ag_cuda_stream_t>(0x10));
+        set_current_stream(nullptr);
+        Node n(Tensor::zeros(Shape{{1}}), Op::Leaf, false, "ctx");
+        CHECK(n.creation_context.stream == nullptr && !n.creation_context.device.is_cuda());
+    });
+
+    return finish("test_host_cpu");
+}

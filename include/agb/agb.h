@@ -160,6 +160,28 @@ int agb_vjp_add(void* ga, void* gb, const void* gy, int64_t n, int dtype, agb_st
 int agb_scale_lastdim(const void* a, const void* g, void* out, int64_t rows, int64_t hidden, int dtype,
                       agb_stream_t stream);
 
+/* ---- general broadcast forms of add / mul and of their VJPs ----
+ * What add_nodeops / mul_nodeops (arithmetic.cpp:11-39), Node::accumulate_grad (graph.cpp:44-47) and
+ * reduce_for_broadcast (autodiff_vjp_ops.cpp:15-35) do for the operand shapes that occur on this
+ * path.  `b_mode` says how the second operand broadcasts against [rows, hidden]:
+ *   AGB_BCAST_FULL [rows,hidden], AGB_BCAST_LASTVEC [hidden] or [1,hidden],
+ *   AGB_BCAST_ROWSTAT [rows,1], AGB_BCAST_SCALAR [1].
+ * agb_binary_broadcast: out = a (+|*) broadcast(b); op 0 = add, 1 = mul.
+ * agb_accumulate_broadcast: dst += broadcast(src) * scale (scale == 1 adds src unchanged; otherwise
+ *   the product is rounded first, like the separate `gy * scale` tensor of vjp_MeanAll :405-408).
+ * agb_mul_reduce: out (+)= sum of g*a (a NULL: of g) over the axes that `out_mode` broadcasts, i.e.
+ *   the gradient of a broadcast operand: LASTVEC -> out[hidden] summed over rows, ROWSTAT ->
+ *   out[rows] summed over hidden, SCALAR -> out[1].  fp64 accumulation in a fixed order; each
+ *   product rounded to the tensor dtype first.  Workspace: agb_mul_reduce_workspace_bytes. */
+typedef enum { AGB_BCAST_FULL = 0, AGB_BCAST_LASTVEC = 1, AGB_BCAST_ROWSTAT = 2, AGB_BCAST_SCALAR = 3 } agb_bcast_t;
+int agb_binary_broadcast(int op, const void* a, const void* b, void* out, int64_t rows, int64_t hidden, int b_mode,
+                         int dtype, agb_stream_t stream);
+int agb_accumulate_broadcast(void* dst, const void* src, int64_t rows, int64_t hidden, int src_mode, float scale,
+                             int dtype, agb_stream_t stream);
+size_t agb_mul_reduce_workspace_bytes(int64_t rows, int64_t hidden);
+int agb_mul_reduce(const void* g, const void* a, void* out, int64_t rows, int64_t hidden, int out_mode,
+                   int accumulate, void* workspace, size_t workspace_bytes, int dtype, agb_stream_t stream);
+
 /* ---- row and global reductions ----
  * rowsum / rowmax (cgadimpl/src/ops/reduction.cpp:25-40) and the reduce_sum / reduce_mean
  * (., {-1}, keepdim) primitive inside the norm: out[r] = op_j x[r,j], out has x's dtype.
