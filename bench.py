@@ -36,7 +36,12 @@ WORKLOADS = {
     "rmsnorm_fwd_vjp_bf16_65536x1000": (65536, 1000, "bfloat16", 1e-6),
     "rmsnorm_fwd_vjp_bf16_65536x5120": (65536, 5120, "bfloat16", 1e-6),
     "rmsnorm_fwd_vjp_bf16_65536x12288": (65536, 12288, "bfloat16", 1e-6),
+    # configuration 5: 524288 rows in total, split evenly over the ranks (strong scaling)
+    "rmsnorm_fwd_vjp_bf16_sharded_64x8192x8192": (64 * 8192, 8192, "bfloat16", 1e-6),
 }
+STRONG_SCALING = {"rmsnorm_fwd_vjp_bf16_sharded_64x8192x8192"}
+# configuration 4: 32 fused residual-add + RMSNorm layers, forward + VJP as one CUDA graph (C++ host layer)
+STACK_WORKLOADS = {"residual_stack_fp32_32x4x4096x4096": (32, 4 * 4096, 4096, 0)}
 DEFAULT_WORKLOAD = "rmsnorm_fwd_vjp_fp32_16x2048x4096"
 METRIC = "rmsnorm_fwd_vjp_rows_per_s"
 UNIT = "rows/s"
@@ -176,6 +181,39 @@ def run_reference_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_stack(args, rank):
+    """Configuration 4 through the C++ host layer: ag::nn::ResidualRMSNormStack captured by
+    ag::CudaGraphRunner, timed by cgadimpl_b200/host/build/bench_stack.  One GPU."""
+    if rank != 0:
+        return
+    from cgadimpl_b200.host import build as host_build
+
+    host_build.build()
+    layers, rows, hidden, bf16 = STACK_WORKLOADS[args.workload]
+    exe = os.path.join(os.path.dirname(host_build.__file__), "build", "bench_stack")
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    r = subprocess.run([exe, str(layers), str(rows), str(hidden), str(args.steps), str(max(3, args.warmup)), str(bf16)],
+                       capture_output=True, text=True)
+    clocks = sampler.stop()
+    if r.returncode != 0:
+        raise SystemExit("bench_stack failed:\n" + r.stdout + r.stderr)
+    d = json.loads(r.stdout.strip().splitlines()[-1])
+    peak, peak_kind = measured_peak()
+    print(json.dumps({
+        "metric": "residual_rmsnorm_stack_row_layers_per_s", "value": d["row_layers_per_s"], "unit": "row-layers/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": d["ms_per_replay"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "layers": layers, "rows": rows, "hidden": hidden,
+                   "cuda_graph_nodes": d["graph_nodes"], "saved_activation_bytes": d["saved_activation_bytes"],
+                   "l2": "each layer streams 7*H*s bytes per row (1.9 GB per layer), far beyond the 126 MB L2"},
+        "gpu_launches": d["launches_per_replay"] * args.steps, "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": d["gbs"], "peak": peak, "unit": "GB/s", "frac": d["gbs"] / peak,
+                     "peak_kind": f"of {peak_kind}", "bytes_per_row_layer": 7 * hidden * (2 if bf16 else 4) + 8,
+                     "frac_of_spec_8TBs": d["gbs"] / SPEC_HBM_GBS, "traffic": None},
+    }), flush=True)
+
+
 # --------------------------------------------------------------------------- GPU arm
 def main():
     ap = argparse.ArgumentParser()
@@ -183,7 +221,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(STACK_WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -195,6 +233,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
 
+    if args.workload in STACK_WORKLOADS:
+        run_stack(args, rank)
+        return
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
         return
@@ -216,6 +257,13 @@ def main():
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE {world}", file=sys.stderr)
 
     rows, hidden, dtype_name, eps = WORKLOADS[args.workload]
+    strong = args.workload in STRONG_SCALING
+    if strong:
+        from cgadimpl_b200.executor import shard_rows
+
+        a, b = shard_rows(rows, world, rank)
+        total_rows_fixed = rows
+        rows = b - a
     dtype = getattr(torch, dtype_name)
     elem = 4 if dtype == torch.float32 else 2
     gen = torch.Generator(device="cuda").manual_seed(1000 * rank)
@@ -279,7 +327,7 @@ def main():
 
     fwd_ms = statistics.mean(ev[k][0].elapsed_time(ev[k][1]) for k in range(args.steps))
     bwd_ms = statistics.mean(ev[k][1].elapsed_time(ev[k][2]) for k in range(args.steps))
-    total_rows = rows * world
+    total_rows = total_rows_fixed if strong else rows * world
     value = total_rows * args.steps / (elapsed_ms / 1e3)
     bpr = bytes_per_row(hidden, elem)
     peak, peak_kind = measured_peak()
@@ -356,7 +404,7 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "rows_per_gpu": rows, "global_rows": total_rows, "hidden": hidden,
                        "io_dtype": dtype_name, "eps": eps, "parallelism": f"rows{world}",
                        "l2": "inputs+outputs per step (>= 2 GB) exceed the 126 MB L2; no flush needed",

@@ -25,6 +25,17 @@ def shard_rows(total_rows, world_size, rank):
     return start, start + base + (1 if rank < extra else 0)
 
 
+def allreduce_dgamma_f64(dg64, group=None):
+    """The path's only exchange: sum the [hidden] fp64 dgamma partials of all ranks in place.
+    Works on CUDA tensors (NCCL) and CPU tensors (gloo); a no-op without a process group."""
+    if dg64.dtype != torch.float64:
+        raise TypeError("dgamma partials are exchanged in fp64 so that the N-rank result rounds like the 1-rank one")
+    if torch.distributed.is_available() and torch.distributed.is_initialized() and \
+            torch.distributed.get_world_size(group) > 1:
+        torch.distributed.all_reduce(dg64, op=torch.distributed.ReduceOp.SUM, group=group)
+    return dg64
+
+
 class RowShardedRMSNorm:
     def __init__(self, hidden, dtype=torch.float32, eps=1e-5, device=None, group=None, chunk_rows=None):
         self.hidden = int(hidden)
@@ -58,7 +69,7 @@ class RowShardedRMSNorm:
             dx, dgamma = ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=dgamma, workspace=self._workspace(x))
             return y, rstd, dx, dgamma
         dx, _ = ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=self._dg64, workspace=self._workspace(x))
-        torch.distributed.all_reduce(self._dg64, op=torch.distributed.ReduceOp.SUM, group=self.group)
+        allreduce_dgamma_f64(self._dg64, self.group)
         dgamma = ops.dgamma_finalize(self._dg64, dgamma)
         return y, rstd, dx, dgamma
 
@@ -132,8 +143,7 @@ class RowShardedRMSNorm:
                     rstd_host[r0:r1].copy_(s["rstd"][:n], non_blocking=True)
                 s["out_done"].record()
         with torch.cuda.stream(st["compute"]):
-            if self.world > 1:
-                torch.distributed.all_reduce(self._dg64, op=torch.distributed.ReduceOp.SUM, group=self.group)
+            allreduce_dgamma_f64(self._dg64, self.group)
             ops.dgamma_finalize(self._dg64, self._dg32)
             dgamma_host.copy_(self._dg32, non_blocking=True)
         for s in st.values():
