@@ -1,0 +1,72 @@
+"""Row-sharded forward + VJP on 2 GPUs (one process per GPU, NCCL): every rank's y and dx equal the
+rows of the single-GPU result bit for bit, and the all-reduced dgamma equals the single-GPU dgamma
+(the partials are exchanged in fp64 and rounded once).  Skipped with fewer than 2 GPUs."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, rows, hidden, dtype_name, q):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from cgadimpl_b200 import ops
+        from cgadimpl_b200.executor import RowShardedRMSNorm, shard_rows
+
+        dtype = getattr(torch, dtype_name)
+        g = torch.Generator().manual_seed(0)                      # same full problem on every rank
+        x = torch.randn(rows, hidden, generator=g).to(dtype)
+        gy = torch.randn(rows, hidden, generator=g).to(dtype)
+        gamma = (1 + 0.02 * torch.randn(hidden, generator=g)).to(dtype)
+        a, b = shard_rows(rows, world, rank)
+        ex = RowShardedRMSNorm(hidden, dtype, 1e-6)
+        y, rstd, dx, dg = ex.fwd_bwd(x[a:b].cuda().contiguous(), gy[a:b].cuda().contiguous(), gamma.cuda())
+        torch.cuda.synchronize()
+        ops.device_status()
+        # single-GPU result of the whole problem, computed on this rank's own GPU
+        ys, rs = ops.rmsnorm_fwd(x.cuda(), gamma.cuda(), 1e-6)
+        dxs, dgs = ops.rmsnorm_bwd(x.cuda(), gamma.cuda(), rs, gy.cuda())
+        ok = bool(torch.equal(y, ys[a:b]) and torch.equal(dx, dxs[a:b]) and torch.equal(rstd, rs[a:b]))
+        same = float((dg == dgs).float().mean())
+        maxulp = int((dg.view(torch.int32) - dgs.view(torch.int32)).abs().max())
+        q.put((rank, ok, same, maxulp))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("dtype_name,rows,hidden", [("float32", 3001, 4096), ("bfloat16", 2048, 8192)])
+def test_two_gpu_sharded_fwd_bwd(dtype_name, rows, hidden):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, rows, hidden, dtype_name, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get() for _ in range(world)]
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    for rank, ok, same, maxulp in results:
+        assert ok, f"rank {rank}: shard outputs differ from the single-GPU rows"
+        assert same > 0.99 and maxulp <= 1, f"rank {rank}: dgamma {same:.4f} equal, max ulp {maxulp}"
