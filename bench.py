@@ -126,6 +126,7 @@ def cpu_pass(hidden, eps, sample_rows, reps, seed=0):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_ffi as O
 
+    O.use_all_cores()
     rng = np.random.default_rng(seed)
     x = rng.standard_normal((sample_rows, hidden), dtype=np.float32)
     gy = rng.standard_normal((sample_rows, hidden), dtype=np.float32)
@@ -153,6 +154,7 @@ def run_reference_arm(args, rank, world):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_ffi as O
 
+    O.use_all_cores()
     rng = np.random.default_rng(0)
     x = rng.standard_normal((sample_rows, hidden), dtype=np.float32)
     gy = rng.standard_normal((sample_rows, hidden), dtype=np.float32)

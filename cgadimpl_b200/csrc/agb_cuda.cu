@@ -74,11 +74,12 @@ int device_info(const DevInfo** out) {
 }
 
 // ------------------------------------------------------------------ options
-std::atomic<int64_t> opt_stages{0}, opt_ctas_per_sm{0}, opt_threads{0}, opt_force_generic{0};
+std::atomic<int64_t> opt_stages{0}, opt_ctas_per_sm{0}, opt_threads{0}, opt_force_generic{0}, opt_ept{0};
 
 // ------------------------------------------------------------------ launch planning
 struct Plan {
     bool generic = true;
+    bool full = false;   // every thread's VPT vectors exist: no bounds checks in the kernel
     int grid = 0, block = 0, smem = 0, vpt = 0;
     PipeGeom g{};
 };
@@ -88,7 +89,14 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 enum Which { kFwd = 0, kBwd = 1, kJvp = 2 };
 
-// narr: arrays staged per tile; ngamma: [hidden] vectors kept in shared memory.
+// Backward variants by elements per thread (= fp64 column sums held in registers): the launch
+// bound caps the registers the compiler may use, and with them the threads an SM can hold.
+struct BwdVariant {
+    int ept, max_threads, regs;
+};
+constexpr BwdVariant kBwdVariants[3] = {{8, 1024, 64}, {16, 768, 80}, {32, 512, 128}};
+
+// narr: arrays staged per tile; ngamma: [hidden] fp32 vectors kept in shared memory.
 void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, int ngamma, const DevInfo& d,
                  Plan* p) {
     p->generic = true;
@@ -99,48 +107,78 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     const int nvec = row_bytes / 16;
     const int epv = 16 / elem;
 
-    // threads per row: aim at 4 vectors per thread
-    int vpt = 4;
-    int G = round_up((nvec + vpt - 1) / vpt, 32);
-    const int max_threads = which == kBwd ? 512 : 1024;
-    if (G > max_threads) {
-        if (which == kBwd) {
-            // the backward keeps vpt*epv fp64 column sums in registers: at most 32 per thread
-            vpt = 32 / epv;
+    // threads per row (G) and vectors per thread (VPT).  Measured on B200: the fixed cost per
+    // row and thread (barrier, two reductions, statistics) is large, so MORE elements per thread
+    // win: 32 per thread in the backward (the most whose fp64 column sums fit in registers).
+    int vpt = 0, G = 0, max_threads = 1024, regs = 64;
+    if (which == kBwd) {
+        const int want = static_cast<int>(opt_ept.load());
+        bool found = false;
+        for (int pass = 0; pass < 2 && !found; ++pass)
+            for (int i = 2; i >= 0 && !found; --i) {
+                const BwdVariant& bv = kBwdVariants[i];
+                if (pass == 0 && want && bv.ept != want) continue;
+                if (bv.ept < epv) continue;
+                const int v = bv.ept / epv;
+                const int g = round_up((nvec + v - 1) / v, 32);
+                if (g > bv.max_threads) continue;
+                vpt = v; G = g; max_threads = bv.max_threads; regs = bv.regs;
+                found = true;
+            }
+        if (!found) return;
+    } else {
+        vpt = 4;
+        G = round_up((nvec + vpt - 1) / vpt, 32);
+        if (G > 1024) {
+            vpt = 8;
             G = round_up((nvec + vpt - 1) / vpt, 32);
-            if (G > max_threads) return;
-        } else {
-            G = max_threads;  // the forward / jvp loops simply take more trips
+            if (G > 1024) {
+                if (which == kFwd) return;
+                G = 1024;  // the jvp kernel loops over its vectors
+            }
         }
     }
-    int target = static_cast<int>(opt_threads.load());
-    if (target <= 0) target = which == kBwd ? 256 : 1024;
-    if (target > max_threads) target = max_threads;
-    int rpt = target / G;
-    if (rpt < 1) rpt = 1;
-    if (rpt > rows) rpt = static_cast<int>(rows);
-    const int block = rpt * G;
-    const int nwarps = block / 32;
-
-    const int tile_stride = round_up(rpt * row_bytes, 128);
-    const int stage_stride = narr * tile_stride;
-    const int gamma_bytes = round_up(row_bytes, 16);
-    const int fixed = ngamma * gamma_bytes + 2 * nwarps * 8 + 8 * 16 /*barriers*/ + 16 /*flag*/ + 128 /*slack*/;
-
-    int ctas = static_cast<int>(opt_ctas_per_sm.load());
-    int want_stages = static_cast<int>(opt_stages.load());
-    const int max_stages = 4;  // measured: depth beyond 3-4 tiles buys nothing, threads per SM do
-    auto stages_for = [&](int c) {
+    const int gamma_bytes = static_cast<int>(hidden) * 4;  // always fp32 in shared memory
+    const int max_stages = 4;                              // measured: depth beyond 3-4 tiles buys nothing
+    auto tile_stride_of = [&](int rpt) { return round_up(rpt * row_bytes, 128); };
+    auto stages_for = [&](int rpt, int c) {
+        const int nw = rpt * G / 32;
+        const int fixed = ngamma * gamma_bytes + 2 * nw * 8 + 8 * 16 /*barriers*/ + 16 /*flag*/ + 128 /*slack*/;
         int avail = d.smem_per_sm / c - 1024;  // the runtime reserves 1 KB per resident CTA
         if (avail > d.smem_optin) avail = d.smem_optin;
-        int s = (avail - fixed) / stage_stride;
+        const int s = (avail - fixed) / (narr * tile_stride_of(rpt));
         return s > max_stages ? max_stages : s;
     };
-    if (ctas <= 0) ctas = (stages_for(2) >= 3 && block * 2 <= max_threads * (which == kBwd ? 1 : 1)) ? 2 : 1;
-    int S = stages_for(ctas);
-    if (S < 2 && ctas > 1) { ctas = 1; S = stages_for(1); }
-    if (S < 2) return;
+    // Rows per tile and CTAs per SM: maximise resident threads subject to the ring depth (2 tiles
+    // per CTA when several CTAs share the SM, 3 for a lone CTA), the register file and the thread
+    // limit; on a tie prefer more, smaller CTAs.  The fp32 forward / jvp have so few instructions
+    // per byte that 512 threads per SM in one CTA are enough, and measurably better than more.
+    int target = static_cast<int>(opt_threads.load());
+    if (target <= 0) target = max_threads;
+    if (target > max_threads) target = max_threads;
+    const int want_ctas = static_cast<int>(opt_ctas_per_sm.load());
+    const bool light = which != kBwd && elem == 4;
+    const int max_resident = light && !want_ctas && !opt_threads.load() ? 512 : 2048;
+    int rpt = 0, ctas = 0, S = 0, best = 0;
+    for (int c = (want_ctas ? want_ctas : 1); c <= (want_ctas ? want_ctas : 4); ++c)
+        for (int r = target / G > 0 ? target / G : 1; r >= 1; --r) {
+            if (r > rows && r > 1) continue;
+            const int blk = r * G;
+            if (blk * c > max_resident && !(c == 1 && r == 1)) continue;
+            if (static_cast<int64_t>(regs) * blk * c > 65536) continue;
+            const int st = stages_for(r, c);
+            if (st < 2 || (c == 1 && st < 3 && r > 1)) continue;  // a lone CTA wants a 3-deep ring
+            const bool better = blk * c > best || (blk * c == best && !light);
+            if (better) { best = blk * c; rpt = r; ctas = c; S = st; }
+            break;  // the largest tile that fits for this CTA count
+        }
+    if (rpt == 0) return;
+    const int want_stages = static_cast<int>(opt_stages.load());
     if (want_stages >= 2 && want_stages < S) S = want_stages;
+    const int block = rpt * G;
+    const int nwarps = block / 32;
+    const int tile_stride = tile_stride_of(rpt);
+    const int stage_stride = narr * tile_stride;
 
     PipeGeom& g = p->g;
     g.rows = rows;
@@ -168,6 +206,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     p->smem = off;
     p->block = block;
     p->vpt = vpt;
+    p->full = (vpt * G == nvec);
     int64_t grid = static_cast<int64_t>(d.sms) * ctas;
     if (grid > g.ntiles) grid = g.ntiles;
     p->grid = static_cast<int>(grid);
@@ -225,15 +264,22 @@ int launch_fwd(const void* x, const void* r, const void* gamma, void* h, void* y
         return after_launch("rmsnorm_fwd_generic");
     }
     agb::FwdArgs a{p.g, x, r, gamma, h, y, rstd, eps};
-#define AGB_LAUNCH_FWD(HG, FA)                                                          \
+#define AGB_LAUNCH_FWD(V, HG, FA, FU)                                                   \
     do {                                                                                \
-        AGB_TRY(set_smem(agb::rmsnorm_fwd_staged<T, HG, FA>, p.smem));                  \
-        agb::rmsnorm_fwd_staged<T, HG, FA><<<p.grid, p.block, p.smem, st>>>(a);         \
+        AGB_TRY(set_smem(agb::rmsnorm_fwd_staged<T, V, HG, FA, FU>, p.smem));           \
+        agb::rmsnorm_fwd_staged<T, V, HG, FA, FU><<<p.grid, p.block, p.smem, st>>>(a);  \
     } while (0)
-    if (gamma && fuse) AGB_LAUNCH_FWD(true, true);
-    else if (gamma) AGB_LAUNCH_FWD(true, false);
-    else if (fuse) AGB_LAUNCH_FWD(false, true);
-    else AGB_LAUNCH_FWD(false, false);
+#define AGB_FWD_BY_FLAGS(V, FU)                          \
+    do {                                                 \
+        if (gamma && fuse) AGB_LAUNCH_FWD(V, true, true, FU);   \
+        else if (gamma) AGB_LAUNCH_FWD(V, true, false, FU);     \
+        else if (fuse) AGB_LAUNCH_FWD(V, false, true, FU);      \
+        else AGB_LAUNCH_FWD(V, false, false, FU);               \
+    } while (0)
+    if (p.vpt == 4 && p.full) AGB_FWD_BY_FLAGS(4, true);
+    else if (p.vpt == 4) AGB_FWD_BY_FLAGS(4, false);
+    else AGB_FWD_BY_FLAGS(8, false);
+#undef AGB_FWD_BY_FLAGS
 #undef AGB_LAUNCH_FWD
     return after_launch("rmsnorm_fwd_staged");
 }
@@ -241,7 +287,7 @@ int launch_fwd(const void* x, const void* r, const void* gamma, void* h, void* y
 int launch_dgamma_reduce(const double* partials, int P, int64_t hidden, void* dgamma, int dgamma_dtype,
                          int accumulate, cudaStream_t st) {
     const int mode = dgamma_dtype == AGB_F64 ? (accumulate ? 3 : 2) : (accumulate ? 1 : 0);
-    dim3 block(32, 8);
+    dim3 block(32, 16);
     const int grid = static_cast<int>((hidden + 31) / 32);
     agb::dgamma_reduce_kernel<<<grid, block, 0, st>>>(partials, P, (int)hidden, dgamma, mode);
     return after_launch("dgamma_reduce");
@@ -292,22 +338,25 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
         const float hf = static_cast<float>(hidden);
         agb::BwdArgs a{p.g, x, gy, dx_add, gamma, rstd, dx, want_dg ? partials : nullptr, add_mode, hf, 1.0f / hf};
         P = p.grid;
-#define AGB_LAUNCH_BWD(V, HG)                                                           \
+#define AGB_LAUNCH_BWD(V, HG, FU, MT)                                                   \
     do {                                                                                \
-        AGB_TRY(set_smem(agb::rmsnorm_bwd_staged<T, V, HG>, p.smem));                   \
-        agb::rmsnorm_bwd_staged<T, V, HG><<<p.grid, p.block, p.smem, st>>>(a);          \
+        AGB_TRY(set_smem(agb::rmsnorm_bwd_staged<T, V, HG, FU, MT>, p.smem));           \
+        agb::rmsnorm_bwd_staged<T, V, HG, FU, MT><<<p.grid, p.block, p.smem, st>>>(a);  \
     } while (0)
-        // vpt is 4, or 8 for wide fp32 rows (never for bf16: 32 column sums per thread at most)
-        if constexpr (sizeof(T) == 4) {
-            if (p.vpt == 8) {
-                if (gamma) AGB_LAUNCH_BWD(8, true);
-                else AGB_LAUNCH_BWD(8, false);
-            }
-        }
-        if (p.vpt == 4) {
-            if (gamma) AGB_LAUNCH_BWD(4, true);
-            else AGB_LAUNCH_BWD(4, false);
-        }
+#define AGB_BWD_BY_FLAGS(V, MT)                                  \
+    do {                                                         \
+        if (gamma && p.full) AGB_LAUNCH_BWD(V, true, true, MT);  \
+        else if (gamma) AGB_LAUNCH_BWD(V, true, false, MT);      \
+        else if (p.full) AGB_LAUNCH_BWD(V, false, true, MT);     \
+        else AGB_LAUNCH_BWD(V, false, false, MT);                \
+    } while (0)
+        // elements per thread 8 / 16 / 32  <->  launch bound 1024 / 768 / 512 threads
+        constexpr int kEpv = 16 / static_cast<int>(sizeof(T));
+        const int ept = p.vpt * kEpv;
+        if (ept == 8) AGB_BWD_BY_FLAGS(8 / kEpv, 1024);
+        else if (ept == 16) AGB_BWD_BY_FLAGS(16 / kEpv, 768);
+        else AGB_BWD_BY_FLAGS(32 / kEpv, 512);
+#undef AGB_BWD_BY_FLAGS
 #undef AGB_LAUNCH_BWD
         AGB_TRY(after_launch("rmsnorm_bwd_staged"));
     }
@@ -407,6 +456,7 @@ int agb_set_option(const char* key, int64_t value) {
     else if (!strcmp(key, "ctas_per_sm")) opt_ctas_per_sm = value;
     else if (!strcmp(key, "threads")) opt_threads = value;
     else if (!strcmp(key, "force_generic")) opt_force_generic = value;
+    else if (!strcmp(key, "ept")) opt_ept = value;
     else return fail(AGB_ERR_INVALID_ARG, "unknown option '%s'", key);
     return AGB_OK;
 }

@@ -14,7 +14,10 @@ namespace agb {
 // (defined here: the library is a single translation unit)
 __device__ int g_device_status = 0;
 
-constexpr int kWaitPollLimit = 1 << 22;  // polls of mbarrier.try_wait before a kernel gives up
+// A wait gives up after kWaitPollLimit polls of mbarrier.try_wait, each of which may suspend the
+// thread in hardware for up to kWaitSuspendNs: at most ~2.6 s in total.
+constexpr int kWaitPollLimit = 1 << 18;
+constexpr uint32_t kWaitSuspendNs = 10000;
 
 // ---------------------------------------------------------------- shared-memory barriers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -34,10 +37,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitSuspendNs)
         : "memory");
     return ok != 0;
 }

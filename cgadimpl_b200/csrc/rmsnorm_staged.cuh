@@ -3,17 +3,20 @@
 // One persistent CTA per SM slot walks over tiles of consecutive rows.  A tile of every input
 // array is brought into a shared-memory ring by the bulk asynchronous copy engine
 // (cp.async.bulk, untiled, no multicast) and signalled on an mbarrier, so the bytes in flight
-// are bounded by shared memory (up to ~200 KB per SM), not by registers or occupancy.  A group
-// of `group_threads` threads owns one row of the tile; each thread reads 16-byte vectors
-// (conflict-free, consecutive threads -> consecutive vectors), reduces in fp64 with warp
-// shuffles plus one shared-memory step, and writes its outputs with 16-byte streaming stores.
-// gamma sits in shared memory for the life of the CTA.  The backward kernel keeps its
-// per-column dgamma sums in fp64 registers across all its rows and writes one partial row per
-// CTA; a second, fixed-order kernel reduces the partials, so dgamma is bit-reproducible.
+// are bounded by shared memory, not by registers or occupancy.  A group of `group_threads`
+// threads owns one row of the tile; each thread reads 16-byte vectors (conflict-free, consecutive
+// threads -> consecutive vectors), reduces in fp64 with warp shuffles plus one shared-memory
+// step, and writes its outputs with 16-byte streaming stores.  gamma sits in shared memory, already
+// widened to fp32, for the life of the CTA.  The backward kernel keeps its per-column dgamma sums
+// in fp64 registers across all its rows and writes one partial row per CTA; a second, fixed-order
+// kernel reduces the partials, so dgamma is bit-reproducible.
 //
 // Rounding follows the reference's op-by-op composition: every elementwise product / sum that
 // the reference materialises as an fp32 tensor is rounded to fp32 here (no FMA contraction),
-// and every reduction is carried in fp64 and rounded once.
+// and every reduction is carried in fp64 and rounded once.  The elementwise arithmetic uses the
+// packed two-lane fp32 instructions of sm_100 (__fmul2_rn / __ffma2_rn): same IEEE result per
+// lane, half the issue slots -- these kernels are limited by instruction issue, not by DRAM, as
+// soon as the data type is 16 bits wide.
 #pragma once
 #include "agb_device.cuh"
 
@@ -30,12 +33,83 @@ struct PipeGeom {
     int stages;
     int tile_stride;    // bytes between the staged arrays inside one stage
     int stage_stride;   // bytes between stages
-    int off_gamma;      // shared-memory offsets
+    int off_gamma;      // shared-memory offsets; gamma is stored as fp32, hidden*4 bytes
     int off_gamma2;
     int off_red;
     int off_bar;
     int off_flag;
 };
+
+// ---------------------------------------------------------------- packed fp32 helpers
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+// a - b, one rounding (an FMA with multiplier -1 is exact up to that rounding)
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) { return __ffma2_rn(b, make_float2(-1.0f, -1.0f), a); }
+__device__ __forceinline__ float2 splat(float v) { return make_float2(v, v); }
+struct DivConst2 {
+    float2 d, dinv;
+    __device__ __forceinline__ float2 operator()(float2 a) const {
+        const float2 q0 = __fmul2_rn(a, dinv);
+        const float2 r = __ffma2_rn(make_float2(-q0.x, -q0.y), d, a);
+        return __ffma2_rn(r, dinv, q0);
+    }
+};
+
+// 16-byte vector <-> NP pairs of floats
+template <typename T>
+struct Pairs;
+template <>
+struct Pairs<float> {
+    static constexpr int NP = 2;
+    __device__ __forceinline__ static void unpack(const uint4& u, float2 (&p)[2]) {
+        p[0] = make_float2(__uint_as_float(u.x), __uint_as_float(u.y));
+        p[1] = make_float2(__uint_as_float(u.z), __uint_as_float(u.w));
+    }
+    __device__ __forceinline__ static uint4 pack(const float2 (&p)[2]) {
+        return make_uint4(__float_as_uint(p[0].x), __float_as_uint(p[0].y), __float_as_uint(p[1].x), __float_as_uint(p[1].y));
+    }
+};
+template <>
+struct Pairs<__nv_bfloat16> {
+    static constexpr int NP = 4;
+    __device__ __forceinline__ static void unpack(const uint4& u, float2 (&p)[4]) {
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+    }
+    __device__ __forceinline__ static uint4 pack(const float2 (&p)[4]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 b = __floats2bfloat162_rn(p[i].x, p[i].y);
+            w[i] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+// gamma in shared memory: fp32, laid out in NP/2 planes of [nvec] float4 so that every 16-byte read
+// of a warp is conflict-free.  Plane q of vector v holds pairs 2q and 2q+1 of that vector.
+template <typename T>
+__device__ __forceinline__ void stage_gamma(float4* s_gamma, const void* gamma, int nvec) {
+    constexpr int NP = Pairs<T>::NP;
+    const uint4* src = reinterpret_cast<const uint4*>(gamma);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        float2 p[NP];
+        Pairs<T>::unpack(src[v], p);
+#pragma unroll
+        for (int q = 0; q < NP / 2; ++q) s_gamma[q * nvec + v] = make_float4(p[2 * q].x, p[2 * q].y, p[2 * q + 1].x, p[2 * q + 1].y);
+    }
+}
+template <typename T>
+__device__ __forceinline__ void load_gamma(const float4* s_gamma, int nvec, int v, float2 (&w)[Pairs<T>::NP]) {
+#pragma unroll
+    for (int q = 0; q < Pairs<T>::NP / 2; ++q) {
+        const float4 f = s_gamma[q * nvec + v];
+        w[2 * q] = make_float2(f.x, f.y);
+        w[2 * q + 1] = make_float2(f.z, f.w);
+    }
+}
 
 // Issues the bulk copies of one tile into a ring slot.  Called by one thread.
 template <int NARR>
@@ -61,9 +135,16 @@ __device__ __forceinline__ void drain_after_abort(const PipeGeom& g, uint64_t* f
     atomicExch(&g_device_status, 6 /* AGB_ERR_TIMEOUT */);
 }
 
+// Sum of the `wpr` per-warp partials of this row group, identical in every thread of the group.
+__device__ __forceinline__ double group_total(const double* s_red, int wpr, int lane) {
+    double v = lane < wpr ? s_red[lane] : 0.0;
+    return warp_sum(v);
+}
+
 // ------------------------------------------------------------------------------------------
 // Forward.  y = (x*rstd)*gamma, rstd saved.  FUSE_ADD: h = x + r is formed first, written out
-// and normalised instead of x.
+// and normalised instead of x.  Each thread owns vectors tig, tig+G, ... (VPT of them; FULL means
+// every one of them exists, so no bounds checks) and keeps them in registers between the passes.
 // ------------------------------------------------------------------------------------------
 struct FwdArgs {
     PipeGeom g;
@@ -76,13 +157,13 @@ struct FwdArgs {
     float eps;
 };
 
-template <typename T, bool HAS_GAMMA, bool FUSE_ADD>
+template <typename T, int VPT, bool HAS_GAMMA, bool FUSE_ADD, bool FULL>
 __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_staged(const __grid_constant__ FwdArgs a) {
-    constexpr int EPV = Vec<T>::EPV;
+    constexpr int NP = Pairs<T>::NP;
     extern __shared__ __align__(128) unsigned char smem[];
     const PipeGeom& g = a.g;
     unsigned char* ring = smem;
-    const uint4* s_gamma = reinterpret_cast<const uint4*>(smem + g.off_gamma);
+    float4* s_gamma = reinterpret_cast<float4*>(smem + g.off_gamma);
     double* s_red = reinterpret_cast<double*>(smem + g.off_red);
     uint64_t* s_full = reinterpret_cast<uint64_t*>(smem + g.off_bar);
     volatile int* s_abort = reinterpret_cast<volatile int*>(smem + g.off_flag);
@@ -97,11 +178,7 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_staged(const __grid_const
         *s_abort = 0;
         mbar_fence_init();
     }
-    if (HAS_GAMMA) {
-        uint4* dst = reinterpret_cast<uint4*>(smem + g.off_gamma);
-        const uint4* src = reinterpret_cast<const uint4*>(a.gamma);
-        for (int v = tid; v < g.nvec; v += blockDim.x) dst[v] = src[v];
-    }
+    if (HAS_GAMMA) stage_gamma<T>(s_gamma, a.gamma, g.nvec);
     __syncthreads();
 
     const unsigned char* const src2[2] = {reinterpret_cast<const unsigned char*>(a.x),
@@ -133,66 +210,71 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_staged(const __grid_const
         const uint4* sr = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(sx) + g.tile_stride);
         uint4* gh = FUSE_ADD ? reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.h) + row * g.row_bytes) : nullptr;
 
-        // pass 1: sum of squares (each square rounded to fp32, summed in fp64)
+        // pass 1: sum of squares (each square rounded to fp32, summed in fp64); the (x+r) vectors
+        // stay in registers for pass 2
+        uint4 keep[VPT];
         double ss0 = 0.0, ss1 = 0.0;
         if (valid) {
-#pragma unroll 2
-            for (int v = tig; v < g.nvec; v += G) {
-                float xv[EPV];
-                Vec<T>::unpack(sx[v], xv);
-                if (FUSE_ADD) {
-                    float rv[EPV];
-                    Vec<T>::unpack(sr[v], rv);
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) xv[e] = add_rn(xv[e], rv[e]);
-                    const uint4 hp = Vec<T>::pack(xv);
-                    store_vec_streaming(gh + v, hp);
-                    Vec<T>::unpack(hp, xv);  // the norm sees h as stored (bf16: after rounding)
-                }
+            for (int i = 0; i < VPT; ++i) {
+                const int v = tig + i * G;
+                if (FULL || v < g.nvec) {
+                    uint4 raw = sx[v];
+                    float2 xv[NP];
+                    Pairs<T>::unpack(raw, xv);
+                    if (FUSE_ADD) {
+                        float2 rv[NP];
+                        Pairs<T>::unpack(sr[v], rv);
 #pragma unroll
-                for (int e = 0; e < EPV; e += 2) {
-                    ss0 += static_cast<double>(mul_rn(xv[e], xv[e]));
-                    ss1 += static_cast<double>(mul_rn(xv[e + 1], xv[e + 1]));
+                        for (int e = 0; e < NP; ++e) xv[e] = add2(xv[e], rv[e]);
+                        raw = Pairs<T>::pack(xv);
+                        store_vec_streaming(gh + v, raw);
+                        Pairs<T>::unpack(raw, xv);  // the norm sees h as stored (bf16: after rounding)
+                    }
+                    keep[i] = raw;
+#pragma unroll
+                    for (int e = 0; e < NP; ++e) {
+                        const float2 q = mul2(xv[e], xv[e]);
+                        ss0 += static_cast<double>(q.x);
+                        ss1 += static_cast<double>(q.y);
+                    }
                 }
             }
         }
-        double ss = warp_sum(ss0 + ss1);
+        const double ss = warp_sum(ss0 + ss1);
         if (lane == 0) s_red[(k & 1) * nwarps + warp] = ss;
         __syncthreads();
         if (*s_abort) { aborted = true; break; }
-        // every thread has finished with the slot of the previous iteration: refill it
-        if (tid == 0 && k >= 1 && issued < my_tiles) {
-            issue(first + issued * stride, static_cast<int>((k - 1) % S));
+        // every thread has its vectors in registers: the slot can be refilled right away
+        if (tid == 0 && issued < my_tiles) {
+            issue(first + issued * stride, slot);
             ++issued;
         }
-        double tot = 0.0;
-        for (int w = 0; w < wpr; ++w) tot += s_red[(k & 1) * nwarps + grp * wpr + w];
+        const double tot = group_total(s_red + (k & 1) * nwarps + grp * wpr, wpr, lane);
         const float rs = rstd_from_sumsq(tot, g.hidden, a.eps);
+        const float2 rs2 = splat(rs);
 
         // pass 2: y = (x*rstd)*gamma
         if (valid) {
             if (tig == 0) a.rstd[row] = rs;
             uint4* gy = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.y) + row * g.row_bytes);
-#pragma unroll 2
-            for (int v = tig; v < g.nvec; v += G) {
-                float xv[EPV];
-                Vec<T>::unpack(sx[v], xv);
-                if (FUSE_ADD) {
-                    float rv[EPV];
-                    Vec<T>::unpack(sr[v], rv);
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) xv[e] = add_rn(xv[e], rv[e]);
-                    const uint4 hp = Vec<T>::pack(xv);
-                    Vec<T>::unpack(hp, xv);
-                }
-                float gv[EPV];
-                if (HAS_GAMMA) Vec<T>::unpack(s_gamma[v], gv);
+            for (int i = 0; i < VPT; ++i) {
+                const int v = tig + i * G;
+                if (FULL || v < g.nvec) {
+                    float2 xv[NP];
+                    Pairs<T>::unpack(keep[i], xv);
+                    if (HAS_GAMMA) {
+                        float2 wv[NP];
+                        load_gamma<T>(s_gamma, g.nvec, v, wv);
 #pragma unroll
-                for (int e = 0; e < EPV; ++e) {
-                    float yh = mul_rn(xv[e], rs);
-                    xv[e] = HAS_GAMMA ? mul_rn(yh, gv[e]) : yh;
+                        for (int e = 0; e < NP; ++e) xv[e] = mul2(mul2(xv[e], rs2), wv[e]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < NP; ++e) xv[e] = mul2(xv[e], rs2);
+                    }
+                    store_vec_streaming(gy + v, Pairs<T>::pack(xv));
                 }
-                store_vec_streaming(gy + v, Vec<T>::pack(xv));
             }
         }
     }
@@ -216,13 +298,14 @@ struct BwdArgs {
     float hidden_f, hidden_inv;
 };
 
-template <typename T, int VPT, bool HAS_GAMMA>
-__global__ void __launch_bounds__(512, 1) rmsnorm_bwd_staged(const __grid_constant__ BwdArgs a) {
-    constexpr int EPV = Vec<T>::EPV;
+template <typename T, int VPT, bool HAS_GAMMA, bool FULL, int MAXT>
+__global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_constant__ BwdArgs a) {
+    constexpr int NP = Pairs<T>::NP;
+    constexpr int EPV = 2 * NP;
     extern __shared__ __align__(128) unsigned char smem[];
     const PipeGeom& g = a.g;
     unsigned char* ring = smem;
-    const uint4* s_gamma = reinterpret_cast<const uint4*>(smem + g.off_gamma);
+    float4* s_gamma = reinterpret_cast<float4*>(smem + g.off_gamma);
     double* s_red = reinterpret_cast<double*>(smem + g.off_red);
     uint64_t* s_full = reinterpret_cast<uint64_t*>(smem + g.off_bar);
     volatile int* s_abort = reinterpret_cast<volatile int*>(smem + g.off_flag);
@@ -232,18 +315,14 @@ __global__ void __launch_bounds__(512, 1) rmsnorm_bwd_staged(const __grid_consta
     const int grp = tid / G, tig = tid - grp * G;
     const int S = g.stages;
     const bool staged_add = a.add_mode == 1;
-    const DivConst div_h{a.hidden_f, a.hidden_inv};
+    const DivConst2 div_h{splat(a.hidden_f), splat(a.hidden_inv)};
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) mbar_init(&s_full[s], 1);
         *s_abort = 0;
         mbar_fence_init();
     }
-    if (HAS_GAMMA) {
-        uint4* dst = reinterpret_cast<uint4*>(smem + g.off_gamma);
-        const uint4* src = reinterpret_cast<const uint4*>(a.gamma);
-        for (int v = tid; v < g.nvec; v += blockDim.x) dst[v] = src[v];
-    }
+    if (HAS_GAMMA) stage_gamma<T>(s_gamma, a.gamma, g.nvec);
     __syncthreads();
 
     const unsigned char* const src3[3] = {reinterpret_cast<const unsigned char*>(a.x),
@@ -287,36 +366,36 @@ __global__ void __launch_bounds__(512, 1) rmsnorm_bwd_staged(const __grid_consta
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int v = tig + i * G;
-                if (v < g.nvec) {
-                    float xv[EPV], gv[EPV];
-                    Vec<T>::unpack(sx[v], xv);
-                    Vec<T>::unpack(sg[v], gv);
+                if (FULL || v < g.nvec) {
+                    float2 xv[NP], gv[NP];
+                    Pairs<T>::unpack(sx[v], xv);
+                    Pairs<T>::unpack(sg[v], gv);
                     if (HAS_GAMMA) {
-                        float wv[EPV];
-                        Vec<T>::unpack(s_gamma[v], wv);
+                        float2 wv[NP];
+                        load_gamma<T>(s_gamma, g.nvec, v, wv);
 #pragma unroll
-                        for (int e = 0; e < EPV; ++e) gv[e] = mul_rn(gv[e], wv[e]);
+                        for (int e = 0; e < NP; ++e) gv[e] = mul2(gv[e], wv[e]);
                     }
 #pragma unroll
-                    for (int e = 0; e < EPV; e += 2) {
-                        d0 += static_cast<double>(mul_rn(gv[e], xv[e]));
-                        d1 += static_cast<double>(mul_rn(gv[e + 1], xv[e + 1]));
+                    for (int e = 0; e < NP; ++e) {
+                        const float2 p = mul2(gv[e], xv[e]);
+                        d0 += static_cast<double>(p.x);
+                        d1 += static_cast<double>(p.y);
                     }
                 }
             }
         }
-        double dsum = warp_sum(d0 + d1);
+        const double dsum = warp_sum(d0 + d1);
         if (lane == 0) s_red[(k & 1) * nwarps + warp] = dsum;
         __syncthreads();
         if (*s_abort) { aborted = true; break; }
+        // all threads are past pass 2 of the previous tile: its slot can be refilled
         if (tid == 0 && k >= 1 && issued < my_tiles) {
             issue(first + issued * stride, static_cast<int>((k - 1) % S));
             ++issued;
         }
-        double tot = 0.0;
-        for (int w = 0; w < wpr; ++w) tot += s_red[(k & 1) * nwarps + grp * wpr + w];
-        const float dot = static_cast<float>(tot);
-        const float r2 = mul_rn(rs, rs);
+        const float dot = static_cast<float>(group_total(s_red + (k & 1) * nwarps + grp * wpr, wpr, lane));
+        const float2 dot2 = splat(dot), rs2 = splat(rs), r22 = splat(mul_rn(rs, rs));
 
         // pass 2: dx and the dgamma terms
         if (valid) {
@@ -324,35 +403,35 @@ __global__ void __launch_bounds__(512, 1) rmsnorm_bwd_staged(const __grid_consta
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int v = tig + i * G;
-                if (v < g.nvec) {
-                    float xv[EPV], gv[EPV], ov[EPV];
-                    Vec<T>::unpack(sx[v], xv);
-                    Vec<T>::unpack(sg[v], gv);
-                    float wv[EPV];
-                    if (HAS_GAMMA) Vec<T>::unpack(s_gamma[v], wv);
+                if (FULL || v < g.nvec) {
+                    float2 xv[NP], gv[NP], ov[NP], wv[NP];
+                    Pairs<T>::unpack(sx[v], xv);
+                    Pairs<T>::unpack(sg[v], gv);
+                    if (HAS_GAMMA) load_gamma<T>(s_gamma, g.nvec, v, wv);
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) {
-                        const float dy = HAS_GAMMA ? mul_rn(gv[e], wv[e]) : gv[e];
-                        float t = mul_rn(xv[e], r2);
-                        t = mul_rn(t, dot);
+                    for (int e = 0; e < NP; ++e) {
+                        const float2 dy = HAS_GAMMA ? mul2(gv[e], wv[e]) : gv[e];
+                        float2 t = mul2(xv[e], r22);
+                        t = mul2(t, dot2);
                         t = div_h(t);
-                        t = sub_rn(dy, t);
-                        ov[e] = mul_rn(rs, t);
+                        t = sub2(dy, t);
+                        ov[e] = mul2(rs2, t);
                         if (HAS_GAMMA) {
-                            const float yh = mul_rn(xv[e], rs);
-                            acc[i * EPV + e] += static_cast<double>(mul_rn(gv[e], yh));
+                            const float2 q = mul2(gv[e], mul2(xv[e], rs2));
+                            acc[i * EPV + 2 * e] += static_cast<double>(q.x);
+                            acc[i * EPV + 2 * e + 1] += static_cast<double>(q.y);
                         }
                     }
                     if (a.add_mode == 2) {
 #pragma unroll
-                        for (int e = 0; e < EPV; ++e) ov[e] = add_rn(ov[e], gv[e]);
+                        for (int e = 0; e < NP; ++e) ov[e] = add2(ov[e], gv[e]);
                     } else if (staged_add) {
-                        float av[EPV];
-                        Vec<T>::unpack(sa[v], av);
+                        float2 av[NP];
+                        Pairs<T>::unpack(sa[v], av);
 #pragma unroll
-                        for (int e = 0; e < EPV; ++e) ov[e] = add_rn(ov[e], av[e]);
+                        for (int e = 0; e < NP; ++e) ov[e] = add2(ov[e], av[e]);
                     }
-                    store_vec_streaming(gdx + v, Vec<T>::pack(ov));
+                    store_vec_streaming(gdx + v, Pairs<T>::pack(ov));
                 }
             }
         }
@@ -368,7 +447,7 @@ __global__ void __launch_bounds__(512, 1) rmsnorm_bwd_staged(const __grid_consta
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int v = tig + i * G;
-                if (v < g.nvec) {
+                if (FULL || v < g.nvec) {
 #pragma unroll
                     for (int e = 0; e < EPV; e += 2)
                         *reinterpret_cast<double2*>(prow + static_cast<size_t>(v) * EPV + e) =
@@ -384,7 +463,7 @@ __global__ void __launch_bounds__(512, 1) rmsnorm_bwd_staged(const __grid_consta
 #pragma unroll
                     for (int i = 0; i < VPT; ++i) {
                         const int v = tig + i * G;
-                        if (v < g.nvec) {
+                        if (FULL || v < g.nvec) {
 #pragma unroll
                             for (int e = 0; e < EPV; ++e) {
                                 const int c = v * EPV + e;
@@ -401,22 +480,31 @@ __global__ void __launch_bounds__(512, 1) rmsnorm_bwd_staged(const __grid_consta
 }
 
 // Stage 2: dgamma[c] = sum over partial rows p = 0..P-1, fixed order, fp64.
-// Block (32, 8): thread (cx, py) sums rows py, py+8, ... of column c, then the 8 sub-sums are
-// added in py order.  out_mode 0: fp32 store, 1: fp32 accumulate, 2: fp64 store, 3: fp64 accumulate.
-__global__ void __launch_bounds__(256) dgamma_reduce_kernel(const double* __restrict__ partials, int P, int hidden,
+// Block (32, 16): thread (cx, py) sums rows py, py+16, ... of column c with four independent
+// chains, then the 16 sub-sums are added in py order.
+// out_mode 0: fp32 store, 1: fp32 accumulate, 2: fp64 store, 3: fp64 accumulate.
+__global__ void __launch_bounds__(512) dgamma_reduce_kernel(const double* __restrict__ partials, int P, int hidden,
                                                             void* out, int out_mode) {
-    __shared__ double s[8][33];
+    __shared__ double s[16][33];
     const int cx = threadIdx.x, py = threadIdx.y;
     const int c = blockIdx.x * 32 + cx;
-    double v = 0.0;
-    if (c < hidden)
-        for (int p = py; p < P; p += 8) v += partials[static_cast<size_t>(p) * hidden + c];
-    s[py][cx] = v;
+    double v0 = 0.0, v1 = 0.0, v2 = 0.0, v3 = 0.0;
+    if (c < hidden) {
+        int p = py;
+        for (; p + 48 < P; p += 64) {
+            v0 += partials[static_cast<size_t>(p) * hidden + c];
+            v1 += partials[static_cast<size_t>(p + 16) * hidden + c];
+            v2 += partials[static_cast<size_t>(p + 32) * hidden + c];
+            v3 += partials[static_cast<size_t>(p + 48) * hidden + c];
+        }
+        for (; p < P; p += 16) v0 += partials[static_cast<size_t>(p) * hidden + c];
+    }
+    s[py][cx] = (v0 + v1) + (v2 + v3);
     __syncthreads();
     if (py == 0 && c < hidden) {
         double t = s[0][cx];
 #pragma unroll
-        for (int j = 1; j < 8; ++j) t += s[j][cx];
+        for (int j = 1; j < 16; ++j) t += s[j][cx];
         if (out_mode == 2)
             static_cast<double*>(out)[c] = t;
         else if (out_mode == 3)
@@ -453,12 +541,12 @@ struct JvpArgs {
 
 template <typename T>
 __global__ void __launch_bounds__(1024, 1) rmsnorm_jvp_staged(const __grid_constant__ JvpArgs a) {
-    constexpr int EPV = Vec<T>::EPV;
+    constexpr int NP = Pairs<T>::NP;
     extern __shared__ __align__(128) unsigned char smem[];
     const PipeGeom& g = a.g;
     unsigned char* ring = smem;
-    const uint4* s_gamma = reinterpret_cast<const uint4*>(smem + g.off_gamma);
-    const uint4* s_tgamma = reinterpret_cast<const uint4*>(smem + g.off_gamma2);
+    float4* s_gamma = reinterpret_cast<float4*>(smem + g.off_gamma);
+    float4* s_tgamma = reinterpret_cast<float4*>(smem + g.off_gamma2);
     double* s_red = reinterpret_cast<double*>(smem + g.off_red);
     uint64_t* s_full = reinterpret_cast<uint64_t*>(smem + g.off_bar);
     volatile int* s_abort = reinterpret_cast<volatile int*>(smem + g.off_flag);
@@ -474,10 +562,8 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_jvp_staged(const __grid_const
         *s_abort = 0;
         mbar_fence_init();
     }
-    for (int v = tid; v < g.nvec; v += blockDim.x) {
-        if (has_gamma) reinterpret_cast<uint4*>(smem + g.off_gamma)[v] = reinterpret_cast<const uint4*>(a.gamma)[v];
-        if (has_tgamma) reinterpret_cast<uint4*>(smem + g.off_gamma2)[v] = reinterpret_cast<const uint4*>(a.tgamma)[v];
-    }
+    if (has_gamma) stage_gamma<T>(s_gamma, a.gamma, g.nvec);
+    if (has_tgamma) stage_gamma<T>(s_tgamma, a.tgamma, g.nvec);
     __syncthreads();
 
     const unsigned char* const src2[2] = {reinterpret_cast<const unsigned char*>(a.x),
@@ -497,6 +583,7 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_jvp_staged(const __grid_const
         const long long row = (first + k * stride) * g.rows_per_tile + grp;
         const bool valid = row < g.rows;
         const float rs = valid ? a.rstd[row] : 0.0f;
+        const float2 rs2 = splat(rs);
         if (!mbar_wait_bounded(&s_full[slot], parity)) *s_abort = 1;
         const unsigned char* base = ring + static_cast<size_t>(slot) * g.stage_stride + static_cast<size_t>(grp) * g.row_bytes;
         const uint4* sx = reinterpret_cast<const uint4*>(base);
@@ -506,17 +593,18 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_jvp_staged(const __grid_const
         if (valid) {
 #pragma unroll 2
             for (int v = tig; v < g.nvec; v += G) {
-                float xv[EPV], tv[EPV];
-                Vec<T>::unpack(sx[v], xv);
-                Vec<T>::unpack(st[v], tv);
+                float2 xv[NP], tv[NP];
+                Pairs<T>::unpack(sx[v], xv);
+                Pairs<T>::unpack(st[v], tv);
 #pragma unroll
-                for (int e = 0; e < EPV; e += 2) {
-                    d0 += static_cast<double>(mul_rn(tv[e], mul_rn(xv[e], rs)));
-                    d1 += static_cast<double>(mul_rn(tv[e + 1], mul_rn(xv[e + 1], rs)));
+                for (int e = 0; e < NP; ++e) {
+                    const float2 p = mul2(tv[e], mul2(xv[e], rs2));
+                    d0 += static_cast<double>(p.x);
+                    d1 += static_cast<double>(p.y);
                 }
             }
         }
-        double dsum = warp_sum(d0 + d1);
+        const double dsum = warp_sum(d0 + d1);
         if (lane == 0) s_red[(k & 1) * nwarps + warp] = dsum;
         __syncthreads();
         if (*s_abort) { aborted = true; break; }
@@ -524,34 +612,32 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_jvp_staged(const __grid_const
             issue_tile<2>(g, ring, s_full, src2, first + issued * stride, static_cast<int>((k - 1) % S));
             ++issued;
         }
-        double tot = 0.0;
-        for (int w = 0; w < wpr; ++w) tot += s_red[(k & 1) * nwarps + grp * wpr + w];
-        const float dot = static_cast<float>(tot);
-        const float c = __fdiv_rn(rs, a.hidden_f);
+        const float dot = static_cast<float>(group_total(s_red + (k & 1) * nwarps + grp * wpr, wpr, lane));
+        const float2 dot2 = splat(dot), c2 = splat(__fdiv_rn(rs, a.hidden_f));
 
         if (valid) {
             uint4* gout = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.ty) + row * g.row_bytes);
 #pragma unroll 2
             for (int v = tig; v < g.nvec; v += G) {
-                float xv[EPV], tv[EPV], wv[EPV], twv[EPV];
-                Vec<T>::unpack(sx[v], xv);
-                Vec<T>::unpack(st[v], tv);
-                if (has_gamma) Vec<T>::unpack(s_gamma[v], wv);
-                if (has_tgamma) Vec<T>::unpack(s_tgamma[v], twv);
+                float2 xv[NP], tv[NP], wv[NP], twv[NP];
+                Pairs<T>::unpack(sx[v], xv);
+                Pairs<T>::unpack(st[v], tv);
+                if (has_gamma) load_gamma<T>(s_gamma, g.nvec, v, wv);
+                if (has_tgamma) load_gamma<T>(s_tgamma, g.nvec, v, twv);
 #pragma unroll
-                for (int e = 0; e < EPV; ++e) {
-                    const float yh = mul_rn(xv[e], rs);
-                    const float q = mul_rn(tv[e], rs);
-                    float p = mul_rn(yh, dot);
-                    p = mul_rn(p, c);
-                    float o = sub_rn(q, p);
+                for (int e = 0; e < NP; ++e) {
+                    const float2 yh = mul2(xv[e], rs2);
+                    const float2 q = mul2(tv[e], rs2);
+                    float2 p = mul2(yh, dot2);
+                    p = mul2(p, c2);
+                    float2 o = sub2(q, p);
                     if (has_gamma) {
-                        o = mul_rn(o, wv[e]);
-                        if (has_tgamma) o = add_rn(o, mul_rn(yh, twv[e]));
+                        o = mul2(o, wv[e]);
+                        if (has_tgamma) o = add2(o, mul2(yh, twv[e]));
                     }
                     xv[e] = o;
                 }
-                store_vec_streaming(gout + v, Vec<T>::pack(xv));
+                store_vec_streaming(gout + v, Pairs<T>::pack(xv));
             }
         }
     }

@@ -22,6 +22,14 @@ int agb_oracle_num_threads(void) {
 #endif
 }
 
+void agb_oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 float agb_bf16_to_f32(uint16_t b) {
     uint32_t u = (uint32_t)b << 16;
     float f;

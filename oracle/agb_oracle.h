@@ -128,6 +128,7 @@ void agb_oracle_residual_stack(const float* x, const float* r, const float* gamm
 float    agb_bf16_to_f32(uint16_t b);
 uint16_t agb_f32_to_bf16(float f);
 int      agb_oracle_num_threads(void);
+void     agb_oracle_set_num_threads(int n);   /* launchers such as torchrun export OMP_NUM_THREADS=1 */
 
 #ifdef __cplusplus
 }

@@ -175,3 +175,13 @@ def residual_stack(x, r, gammas, g, eps, red=RED_F64):
 
 def num_threads():
     return int(lib().agb_oracle_num_threads())
+
+
+def use_all_cores():
+    """Undo an inherited OMP_NUM_THREADS=1 (torchrun sets it): use every core this process may run on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().agb_oracle_set_num_threads(n)
+    return num_threads()
