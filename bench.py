@@ -128,12 +128,36 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU arm
+def _reference_build():
+    """oracle/_ref (the reference's own sources over a stand-in tensor library) if it was built."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    try:
+        import ref_ffi as REF
+
+        if REF.available():
+            REF.lib()
+            return REF
+    except Exception:
+        pass
+    return None
+
+
+REF_KIND_NOTE = ("the reference's own op builders and autodiff engine (cgadimpl/src/{core,ops,autodiff}, compiled "
+                 "unmodified into oracle/_ref) over a CPU stand-in for its absent OwnTensor library, OpenMP")
+PORT_KIND_NOTE = "op-by-op fp32 restatement of the reference composition (oracle/agb_oracle.c), OpenMP"
+
+
 def cpu_pass(hidden, eps, sample_rows, reps, seed=0):
-    """Times the op-by-op CPU restatement of the reference (all host threads) on a bounded sample
-    of the workload.  Returns (rows/s, threads, seconds per pass)."""
+    """Times the reference's CPU path (all host threads) on a bounded sample of the workload.
+    Returns (rows/s, threads, seconds per pass, kind, note)."""
+    REF = _reference_build()
+    if REF is not None and abs(eps - 1e-5) < 1e-12:     # the reference hard-codes eps = 1e-5
+        cores = REF.use_all_cores()
+        REF.set_reduce_fp64(False)
+        secs = min(REF.time_fwd_bwd(sample_rows, hidden, 1, 1) for _ in range(max(1, reps)))
+        return sample_rows / secs, cores, secs, "reference", REF_KIND_NOTE
     import numpy as np
 
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_ffi as O
 
     O.use_all_cores()
@@ -148,45 +172,53 @@ def cpu_pass(hidden, eps, sample_rows, reps, seed=0):
         O.rmsnorm_fwd_bwd(x, gamma, gy, eps, O.RED_F32)
         ts.append(time.perf_counter() - t0)
     best = min(ts)
-    return sample_rows / best, O.num_threads(), best
+    return sample_rows / best, O.num_threads(), best, "port", PORT_KIND_NOTE
 
 
 def run_reference_arm(args, rank, world):
-    """The reference's own CPU path for this workload.  cgadimpl cannot be built (its tensor
-    library is an absent submodule), so this times the call-by-call CPU restatement of its
-    composition, fp32 reductions, OpenMP over all host cores.  Rank 0 only."""
+    """The reference's own CPU implementation of the path on the host cores: oracle/_ref when it was
+    built (the reference's unmodified graph / op / autodiff sources over a stand-in tensor library),
+    else the C restatement.  cgadimpl's own build cannot run here (OwnTensor, MLIR, Nova absent).
+    Each step is one forward + backward pass over a bounded sample of the workload.  Rank 0 only."""
     if rank != 0:
         return
     rows, hidden, dtype, eps = WORKLOADS[args.workload]
     sample_rows = min(rows, 4096)
-    import numpy as np
+    REF = _reference_build()
+    if REF is not None and abs(eps - 1e-5) < 1e-12:
+        cores = REF.use_all_cores()
+        REF.set_reduce_fp64(False)
+        secs = REF.time_fwd_bwd(sample_rows, hidden, args.steps, max(1, args.warmup))
+        kind, note = "reference", REF_KIND_NOTE
+    else:
+        import numpy as np
 
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import oracle_ffi as O
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import oracle_ffi as O
 
-    O.use_all_cores()
-    rng = np.random.default_rng(0)
-    x = rng.standard_normal((sample_rows, hidden), dtype=np.float32)
-    gy = rng.standard_normal((sample_rows, hidden), dtype=np.float32)
-    gamma = (1 + 0.02 * rng.standard_normal(hidden)).astype(np.float32)
-    for _ in range(max(1, args.warmup)):
-        O.rmsnorm_fwd_bwd(x, gamma, gy, eps, O.RED_F32)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        O.rmsnorm_fwd_bwd(x, gamma, gy, eps, O.RED_F32)
-    dt = time.perf_counter() - t0
-    value = sample_rows * args.steps / dt
+        cores = O.use_all_cores()
+        rng = np.random.default_rng(0)
+        x = rng.standard_normal((sample_rows, hidden), dtype=np.float32)
+        gy = rng.standard_normal((sample_rows, hidden), dtype=np.float32)
+        gamma = (1 + 0.02 * rng.standard_normal(hidden)).astype(np.float32)
+        for _ in range(max(1, args.warmup)):
+            O.rmsnorm_fwd_bwd(x, gamma, gy, eps, O.RED_F32)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            O.rmsnorm_fwd_bwd(x, gamma, gy, eps, O.RED_F32)
+        secs = (time.perf_counter() - t0) / args.steps
+        kind, note = "port", PORT_KIND_NOTE
+    value = sample_rows / secs
     elem = 4 if dtype == "float32" else 2
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "rows_per_gpu": rows, "hidden": hidden, "eps": eps,
                    "io_dtype": dtype, "sample_rows_per_step": sample_rows},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
-                         "sample": f"{sample_rows} of {rows} rows per step, op-by-op restatement of the "
-                                   f"reference composition (cgadimpl itself cannot be built: OwnTensor absent)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": f"{sample_rows} of {rows} rows per step; {note}"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "hbm_gbs": value * bytes_per_row(hidden, elem) / 1e9,
     }
@@ -402,10 +434,9 @@ def main():
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         sample_rows = min(rows, 4096)
-        v, cores, secs = cpu_pass(hidden, eps, sample_rows, reps=8)
-        cpu_baseline = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
-                        "sample": f"{sample_rows} of {rows} rows, best of 8 passes ({secs*1e3:.1f} ms each), "
-                                  f"op-by-op fp32 restatement of the reference composition"}
+        v, cores, secs, kind, note = cpu_pass(hidden, eps, sample_rows, reps=8)
+        cpu_baseline = {"value": v, "unit": UNIT, "cores": cores, "kind": kind,
+                        "sample": f"{sample_rows} of {rows} rows, best of 8 passes ({secs*1e3:.1f} ms each); {note}"}
 
     if rank == 0:
         line = {

@@ -4,17 +4,20 @@
  * This is the checker the CUDA kernels are compared against and the CPU arm of the
  * benchmark.  Nothing in the shipped library links, loads or calls it.
  *
- * PARITY UNPINNED beyond a finite-difference check: every tensor operation of the
- * reference is a call into the third-party OwnTensor library (git submodule `tensor`,
- * url kathir-23s/Tensor-Implementations, pinned commit unknown, directory empty in the
- * reference checkout), so the reference itself cannot be built or run.  What IS pinned is
- * the reference's own composition: which elementwise / reduction calls are made, in which
- * order, and where an fp32 temporary is materialised.  This file follows that composition
- * call by call (citations are paths inside the cgadimpl project) and stands in for each
- * OwnTensor primitive with a plain loop.  The reference's only numeric test of this path,
- * a central finite-difference check on a random [4,10] input at max-abs 1e-3
- * (cgadimpl/Tests/test_core_ops_gpu.cpp:15-84, 262-267), is re-run against this oracle
- * in the test-suite.
+ * What pins it.  The reference cannot be built by its own build system (its tensor library
+ * OwnTensor -- git submodule `tensor`, url kathir-23s/Tensor-Implementations, pinned commit
+ * unknown -- is an empty directory in the reference checkout, and MLIR / Nova are required too)
+ * and it ships no golden vectors.  But its op builders, autodiff engine and rules for this path
+ * compile unmodified over a small stand-in for that library (oracle/ref_shim, oracle/build_ref.py
+ * -> oracle/_ref/libcgadimpl_ref.so), and tests/test_reference_build.py checks that this file
+ * reproduces THAT bit for bit (forward, VJP, the residual stack through the reference's graph
+ * engine, the literal JVP rule, the reductions) in both reduction modes.  So the reference's
+ * COMPOSITION is pinned: which tensor calls are made, in which order, where an fp32 temporary is
+ * materialised.  PARITY REMAINS UNPINNED at one place only: the arithmetic inside the real
+ * OwnTensor (summation order, accumulator width), which no file in the reference shows.
+ * The reference's own numeric test of this path, a central finite-difference check on a random
+ * [4,10] input at max-abs 1e-3 (cgadimpl/Tests/test_core_ops_gpu.cpp:15-84, 262-267), is re-run
+ * against this oracle as well.
  *
  * Reduction modes.  OwnTensor's summation order and accumulator width are unknown, so every
  * reduction exists twice:

@@ -348,3 +348,43 @@ def test_empty_input_and_errors(ops):
         ops.rmsnorm_fwd(x.half(), None, 1e-5)
     with pytest.raises(ValueError):
         ops.rmsnorm_fwd(torch.randn(4, 64), None, 1e-5)          # host tensor: there is no CPU path
+
+
+def test_cuda_matches_the_reference_build(ops):
+    """Against the reference's own code (oracle/_ref: cgadimpl's unmodified op builders and autodiff
+    rules over the stand-in tensor library, fp64 reductions): mul(rms(x), gamma) and its backward,
+    eps = 1e-5 as hard-coded there.  Skipped where that library was not built."""
+    import ref_ffi as REF
+
+    if not REF.available():
+        pytest.skip("reference build not available")
+    REF.set_reduce_fp64(True)
+    for rows, hidden in ((4, 10), (300, 4096), (64, 1000)):
+        x, gamma, gy = make_inputs(rows, hidden, seed=rows)
+        ref = REF.rmsnorm_fwd_bwd(x, gamma, gy)
+        xd, gd, gyd = dev(x), dev(gamma), dev(gy)
+        y, rstd = ops.rmsnorm_fwd(xd, gd, 1e-5)
+        dx, dg = ops.rmsnorm_bwd(xd, gd, rstd, gyd)
+        for k, got in (("y", y), ("rstd", rstd), ("dx", dx), ("dgamma", dg)):
+            assert_close(host(got), ref[k], F32_RTOL, F32_ATOL, f"{k} vs reference build, {rows}x{hidden}")
+            assert frac_bit_equal(host(got), ref[k]) >= 0.99
+    # the residual stack as the reference's graph runs it (add, rms, mul nodes; accumulate_grad)
+    R, H, L = 48, 1024, 4
+    rng = np.random.default_rng(0)
+    x, r, g = (rng.standard_normal((R, H)).astype(np.float32) for _ in range(3))
+    gam = (1 + 0.02 * rng.standard_normal((L, H))).astype(np.float32)
+    ref = REF.residual_stack(x, r, gam, g)
+    xl, rl, gd = dev(x), dev(r), dev(gam)
+    hs, rs = [], []
+    for l in range(L):
+        h, y, rstd = ops.add_rmsnorm_fwd(xl, rl, gd[l], 1e-5)
+        hs.append(h)
+        rs.append(rstd)
+        xl, rl = h, y
+    gh = dev(g)
+    dgs = torch.zeros(L, H, device="cuda")
+    for l in reversed(range(L)):
+        gh, _ = ops.rmsnorm_bwd(hs[l], gd[l], rs[l], gh, dx_add=None if l == L - 1 else gh, dgamma=dgs[l])
+    assert_close(host(y), ref["y"], F32_RTOL, F32_ATOL, "stack y")
+    assert_close(host(gh), ref["dx0"], F32_RTOL, F32_ATOL, "stack dx0")
+    assert_close(host(dgs), ref["dgammas"], F32_RTOL, F32_ATOL, "stack dgammas")
