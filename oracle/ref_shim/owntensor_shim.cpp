@@ -70,6 +70,7 @@ Pool& pool() {
 Tensor::Tensor(const Shape& s, const TensorOptions& o) : shape_(s), numel_(prod(s.dims)), req_(o.requires_grad) {
     const size_t n = static_cast<size_t>(numel_);
     buf_ = std::shared_ptr<float>(pool().get(n), [n](float* p) { pool().put(n, p); });
+    if (n <= 16) std::memset(buf_.get(), 0, n * sizeof(float));  // scalars and empty-shape tensors start defined
 }
 Tensor Tensor::zeros(const Shape& s, const TensorOptions& o) { return full(s, o, 0.0f); }
 Tensor Tensor::ones(const Shape& s, const TensorOptions& o) { return full(s, o, 1.0f); }
