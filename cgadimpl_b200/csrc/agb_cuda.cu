@@ -338,11 +338,17 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
         const float hf = static_cast<float>(hidden);
         agb::BwdArgs a{p.g, x, gy, dx_add, gamma, rstd, dx, want_dg ? partials : nullptr, add_mode, hf, 1.0f / hf};
         P = p.grid;
-#define AGB_LAUNCH_BWD(V, HG, FU, MT)                                                   \
-    do {                                                                                \
-        AGB_TRY(set_smem(agb::rmsnorm_bwd_staged<T, V, HG, FU, MT>, p.smem));           \
-        agb::rmsnorm_bwd_staged<T, V, HG, FU, MT><<<p.grid, p.block, p.smem, st>>>(a);  \
+#define AGB_LAUNCH_BWD2(V, HG, FU, MT, P2)                                                   \
+    do {                                                                                     \
+        AGB_TRY(set_smem(agb::rmsnorm_bwd_staged<T, V, HG, FU, MT, P2>, p.smem));            \
+        agb::rmsnorm_bwd_staged<T, V, HG, FU, MT, P2><<<p.grid, p.block, p.smem, st>>>(a);   \
     } while (0)
+#define AGB_LAUNCH_BWD(V, HG, FU, MT)                     \
+    do {                                                  \
+        if (pow2) AGB_LAUNCH_BWD2(V, HG, FU, MT, true);   \
+        else AGB_LAUNCH_BWD2(V, HG, FU, MT, false);       \
+    } while (0)
+        const bool pow2 = (hidden & (hidden - 1)) == 0;
 #define AGB_BWD_BY_FLAGS(V, MT)                                  \
     do {                                                         \
         if (gamma && p.full) AGB_LAUNCH_BWD(V, true, true, MT);  \
@@ -358,6 +364,7 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
         else AGB_BWD_BY_FLAGS(32 / kEpv, 512);
 #undef AGB_BWD_BY_FLAGS
 #undef AGB_LAUNCH_BWD
+#undef AGB_LAUNCH_BWD2
         AGB_TRY(after_launch("rmsnorm_bwd_staged"));
     }
     if (want_dg) AGB_TRY(launch_dgamma_reduce(partials, P, hidden, dgamma, dgamma_dtype, accumulate_dgamma, st));
@@ -755,6 +762,36 @@ int agb_mul_reduce(const void* g, const void* a, void* out, int64_t rows, int64_
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return dtype == AGB_F32 ? launch_mul_reduce<float>(g, a, out, rows, hidden, out_mode, accumulate, (double*)workspace, st)
                             : launch_mul_reduce<bf16>(g, a, out, rows, hidden, out_mode, accumulate, (double*)workspace, st);
+}
+
+int agb_sgd_step(void* param, const void* grad, int64_t n, float learning_rate, int dtype, agb_stream_t stream) {
+    if (n < 0) return fail(AGB_ERR_INVALID_ARG, "n=%lld", (long long)n);
+    if (dtype != AGB_F32 && dtype != AGB_BF16) return fail(AGB_ERR_UNSUPPORTED, "dtype %d", dtype);
+    if (n == 0) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(param, "param", elem));
+    AGB_TRY(check_ptr(grad, "grad", elem));
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == AGB_F32) agb::sgd_step_kernel<float><<<ew_grid(n, *d), 256, 0, st>>>((float*)param, (const float*)grad, n, -learning_rate);
+    else agb::sgd_step_kernel<bf16><<<ew_grid(n, *d), 256, 0, st>>>((bf16*)param, (const bf16*)grad, n, -learning_rate);
+    return after_launch("sgd_step");
+}
+
+int agb_adam_step(float* param, const float* grad, float* m, float* v, int64_t n, float beta1, float beta2,
+                  float alpha_eff, float eps_eff, agb_stream_t stream) {
+    if (n < 0) return fail(AGB_ERR_INVALID_ARG, "n=%lld", (long long)n);
+    if (n == 0) return AGB_OK;
+    AGB_TRY(check_ptr(param, "param", 4));
+    AGB_TRY(check_ptr(grad, "grad", 4));
+    AGB_TRY(check_ptr(m, "m", 4));
+    AGB_TRY(check_ptr(v, "v", 4));
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    agb::adam_step_kernel<<<ew_grid(n, *d), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        param, grad, m, v, n, beta1, beta2, 1.0f - beta1, 1.0f - beta2, alpha_eff, eps_eff);
+    return after_launch("adam_step");
 }
 
 int agb_row_reduce(int op, const void* x, void* out, int64_t rows, int64_t hidden, int dtype, agb_stream_t stream) {

@@ -307,4 +307,35 @@ __global__ void __launch_bounds__(32) sumall_finish_kernel(const double* __restr
     }
 }
 
+// ---------------------------------------------------------------- optimiser steps on parameters
+// SGD as the reference writes it (cgadimpl/src/optimizer/optim.cpp:12-19):
+//   value += -learning_rate * grad      -> t = (-lr)*g rounded, then p + t rounded
+template <typename T>
+__global__ void __launch_bounds__(256) sgd_step_kernel(T* p, const T* g, long long n, float neg_lr) {
+    const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += nthreads) {
+        const float t = as_stored<T>(mul_rn(neg_lr, Vec<T>::load1(g + i)));
+        Vec<T>::store1(p + i, add_rn(Vec<T>::load1(p + i), t));
+    }
+}
+
+// Adam as the reference writes it (optim.cpp:33-72), one rounding per tensor operation:
+//   m *= b1;  m += (1-b1)*g;  v *= b2;  v += (1-b2)*square(g);
+//   value -= alpha_eff * m / (sqrt(v) + eps_eff)
+__global__ void __launch_bounds__(256) adam_step_kernel(float* p, const float* g, float* m, float* v, long long n,
+                                                        float b1, float b2, float omb1, float omb2, float alpha_eff,
+                                                        float eps_eff) {
+    const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += nthreads) {
+        const float gi = g[i];
+        const float mi = add_rn(mul_rn(m[i], b1), mul_rn(omb1, gi));
+        const float vi = add_rn(mul_rn(v[i], b2), mul_rn(omb2, mul_rn(gi, gi)));
+        m[i] = mi;
+        v[i] = vi;
+        const float num = mul_rn(alpha_eff, mi);
+        const float den = add_rn(__fsqrt_rn(vi), eps_eff);
+        p[i] = sub_rn(p[i], __fdiv_rn(num, den));
+    }
+}
+
 }  // namespace agb

@@ -6,3 +6,5 @@
 #include "ad/detail/autodiff_ops.hpp"
 #include "ad/runtime/cuda_graphs.hpp"
 #include "ad/utils/debug.hpp"
+#include "nn/nn.hpp"
+#include "optim.hpp"

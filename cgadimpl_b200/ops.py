@@ -130,6 +130,17 @@ def scale_lastdim(a, g, out=None):
     return out
 
 
+def sgd_step(param, grad, lr):
+    """param += -lr * grad, as ag::SGD updates a leaf."""
+    check(_lib.lib().agb_sgd_step(_p(param), _p(grad), param.numel(), float(lr), _dt(param), _stream()))
+
+
+def adam_step(param, grad, m, v, beta1, beta2, alpha_eff, eps_eff):
+    """One Adam update of one fp32 parameter (m, v in place); see agb_adam_step."""
+    check(_lib.lib().agb_adam_step(_p(param), _p(grad), _p(m), _p(v), param.numel(), float(beta1), float(beta2),
+                                   float(alpha_eff), float(eps_eff), _stream()))
+
+
 def row_reduce(x, op):
     """op: 'sum' | 'mean' | 'max' over the last axis, keepdim; result has x's dtype."""
     rows, hidden = _rows_hidden(x)

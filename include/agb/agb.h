@@ -182,6 +182,16 @@ size_t agb_mul_reduce_workspace_bytes(int64_t rows, int64_t hidden);
 int agb_mul_reduce(const void* g, const void* a, void* out, int64_t rows, int64_t hidden, int out_mode,
                    int accumulate, void* workspace, size_t workspace_bytes, int dtype, agb_stream_t stream);
 
+/* ---- optimiser steps on the layer's parameters ----
+ * agb_sgd_step: ag::SGD's update of one leaf, `value += -learning_rate * grad`
+ *   (cgadimpl/src/optimizer/optim.cpp:12-19).
+ * agb_adam_step: one Adam::step() for one parameter (optim.cpp:33-72), fp32: the caller passes
+ *   alpha_eff = alpha*sqrt(1-beta2^t)/(1-beta1^t) and eps_eff = epsilon*sqrt(1-beta2^t) as the
+ *   reference computes them on the host.  m and v are updated in place. */
+int agb_sgd_step(void* param, const void* grad, int64_t n, float learning_rate, int dtype, agb_stream_t stream);
+int agb_adam_step(float* param, const float* grad, float* m, float* v, int64_t n, float beta1, float beta2,
+                  float alpha_eff, float eps_eff, agb_stream_t stream);
+
 /* ---- row and global reductions ----
  * rowsum / rowmax (cgadimpl/src/ops/reduction.cpp:25-40) and the reduce_sum / reduce_mean
  * (., {-1}, keepdim) primitive inside the norm: out[r] = op_j x[r,j], out has x's dtype.

@@ -467,3 +467,49 @@ void agb_oracle_residual_stack(const float* x, const float* r, const float* gamm
     for (int l = 0; l < L; ++l) { free(h[l]); free(rs[l]); }
     free(h); free(rs); free(yhat); free(y); free(yprev); free(gh); free(dyhat); free(dx);
 }
+
+/* ag::SGD on one leaf, cgadimpl/src/optimizer/optim.cpp:12-19:  value += -learning_rate * grad */
+void agb_oracle_sgd_step(float* param, const float* grad, int64_t n, float lr) {
+    const float neg = -lr;
+    for (int64_t i = 0; i < n; ++i) {
+        float t = neg * grad[i];
+        param[i] = param[i] + t;
+    }
+}
+
+/* Adam::step() for one parameter, optim.cpp:33-72, one rounding per tensor operation; t is the
+ * step count AFTER the increment at :34. */
+void agb_oracle_adam_step(float* param, const float* grad, float* m, float* v, int64_t n, float alpha, float beta1,
+                          float beta2, float epsilon, int t) {
+    /* std::pow(float, int) promotes to double in C++ (optim.cpp:35-36); the difference is then
+     * narrowed to float by the assignment. */
+    float bias_corr1 = (float)(1.0 - pow((double)beta1, (double)t));
+    float bias_corr2 = (float)(1.0 - pow((double)beta2, (double)t));
+    float alpha_eff = alpha * sqrtf(bias_corr2) / bias_corr1;
+    float eps_eff = epsilon * sqrtf(bias_corr2);
+    float omb1 = 1.0f - beta1, omb2 = 1.0f - beta2;
+    for (int64_t i = 0; i < n; ++i) {
+        float mi = m[i] * beta1;            /* m *= beta1              */
+        float t1 = omb1 * grad[i];          /* (1-beta1) * grad        */
+        mi = mi + t1;                       /* m += .                  */
+        float vi = v[i] * beta2;            /* v *= beta2              */
+        float sq = grad[i] * grad[i];       /* square(grad)            */
+        float t2 = omb2 * sq;               /* (1-beta2) * .           */
+        vi = vi + t2;                       /* v += .                  */
+        m[i] = mi;
+        v[i] = vi;
+        float num = alpha_eff * mi;         /* alpha_eff * m           */
+        float s = sqrtf(vi);                /* sqrt(v)                 */
+        float den = s + eps_eff;            /* . + epsilon*sqrt(bc2)   */
+        float u = num / den;                /* . / .                   */
+        param[i] = param[i] - u;            /* value -= .              */
+    }
+}
+
+/* The host-side scalars of Adam::step(), so callers of the CUDA entry point compute them the same way. */
+void agb_oracle_adam_scalars(float alpha, float beta1, float beta2, float epsilon, int t, float* alpha_eff, float* eps_eff) {
+    float bias_corr1 = (float)(1.0 - pow((double)beta1, (double)t));
+    float bias_corr2 = (float)(1.0 - pow((double)beta2, (double)t));
+    *alpha_eff = alpha * sqrtf(bias_corr2) / bias_corr1;
+    *eps_eff = epsilon * sqrtf(bias_corr2);
+}

@@ -127,6 +127,12 @@ void agb_oracle_residual_stack(const float* x, const float* r, const float* gamm
                                float* y_last, float* dh0, float* dgammas,
                                int64_t R, int64_t H, int L, float eps, int red);
 
+/* Optimiser steps on a parameter: cgadimpl/src/optimizer/optim.cpp:12-19 (SGD), :33-72 (Adam). */
+void agb_oracle_sgd_step(float* param, const float* grad, int64_t n, float lr);
+void agb_oracle_adam_step(float* param, const float* grad, float* m, float* v, int64_t n, float alpha, float beta1,
+                          float beta2, float epsilon, int t);
+void agb_oracle_adam_scalars(float alpha, float beta1, float beta2, float epsilon, int t, float* alpha_eff, float* eps_eff);
+
 /* helpers */
 float    agb_bf16_to_f32(uint16_t b);
 uint16_t agb_f32_to_bf16(float f);

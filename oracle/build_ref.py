@@ -9,6 +9,7 @@ Reference files compiled, unmodified:
     cgadimpl/src/core/{graph,schema,autodiff}.cpp
     cgadimpl/src/ops/{normalization,arithmetic,reduction}.cpp
     cgadimpl/src/autodiff/{autodiff_vjp_ops,autodiff_jvp_ops}.cpp
+    cgadimpl/src/optimizer/optim.cpp
 The reference's own build (CMake + OwnTensor + MLIR + Nova) is not used and cannot run here.
 autodiff.cpp is compiled without -fopenmp: it carries a stray `#pragma omp parallel for` in front of
 a function definition (src/core/autodiff.cpp:32), which is an error once OpenMP is enabled.
@@ -29,6 +30,7 @@ REF_SOURCES = [
     ("src/core/graph.cpp", True), ("src/core/schema.cpp", True), ("src/core/autodiff.cpp", False),
     ("src/ops/normalization.cpp", True), ("src/ops/arithmetic.cpp", True), ("src/ops/reduction.cpp", True),
     ("src/autodiff/autodiff_vjp_ops.cpp", True), ("src/autodiff/autodiff_jvp_ops.cpp", True),
+    ("src/optimizer/optim.cpp", True),
 ]
 SHIM_SOURCES = ["owntensor_shim.cpp", "ref_driver.cpp"]
 FLAGS = ["-std=c++20", "-O2", "-ffp-contract=off", "-fPIC", "-w", "-pthread"]

@@ -94,6 +94,8 @@ public:
     void display(std::ostream& os, int precision = 4) const;
 
     Tensor& operator+=(const Tensor& o);
+    Tensor& operator-=(const Tensor& o);
+    Tensor& operator*=(double s);
 
 private:
     std::shared_ptr<float> buf_;  // uninitialised storage from a size-keyed pool (see owntensor_shim.cpp)
@@ -123,6 +125,7 @@ OWNTENSOR_SHIM_UNARY(acos) OWNTENSOR_SHIM_UNARY(atan) OWNTENSOR_SHIM_UNARY(asinh
 OWNTENSOR_SHIM_UNARY(atanh)
 #undef OWNTENSOR_SHIM_UNARY
 Tensor pow(const Tensor& a, float e, cudaStream_t stream = nullptr);
+Tensor square(const Tensor& a, cudaStream_t stream = nullptr);
 
 Tensor reduce_sum(const Tensor& a, const std::vector<int64_t>& axes = {}, bool keepdim = false);
 Tensor reduce_mean(const Tensor& a, const std::vector<int64_t>& axes = {}, bool keepdim = false);

@@ -239,6 +239,19 @@ Tensor& Tensor::operator+=(const Tensor& o) {
     return *this;
 }
 
+Tensor& Tensor::operator-=(const Tensor& o) {
+    Tensor d = *this - o;
+    if (d.numel() != numel_) throw std::runtime_error("operator-=: result does not fit the left operand");
+    std::memcpy(data<float>(), d.data<float>(), sizeof(float) * numel_);
+    return *this;
+}
+Tensor& Tensor::operator*=(double s) {
+    const float v = static_cast<float>(s);
+    float* a = data<float>();
+    for (int64_t i = 0; i < numel_; ++i) a[i] = a[i] * v;
+    return *this;
+}
+
 #define OWNTENSOR_SHIM_UNARY(name, expr) \
     Tensor name(const Tensor& a, cudaStream_t) { return with_scalar(a, [](float x) { return expr; }); }
 OWNTENSOR_SHIM_UNARY(exp, std::exp(x)) OWNTENSOR_SHIM_UNARY(log, std::log(x)) OWNTENSOR_SHIM_UNARY(sqrt, std::sqrt(x))
@@ -249,6 +262,7 @@ OWNTENSOR_SHIM_UNARY(cosh, std::cosh(x)) OWNTENSOR_SHIM_UNARY(asin, std::asin(x)
 OWNTENSOR_SHIM_UNARY(atan, std::atan(x)) OWNTENSOR_SHIM_UNARY(asinh, std::asinh(x)) OWNTENSOR_SHIM_UNARY(acosh, std::acosh(x))
 OWNTENSOR_SHIM_UNARY(atanh, std::atanh(x))
 #undef OWNTENSOR_SHIM_UNARY
+Tensor square(const Tensor& a, cudaStream_t) { return with_scalar(a, [](float x) { return x * x; }); }
 Tensor pow(const Tensor& a, float e, cudaStream_t) { return with_scalar(a, [e](float x) { return std::pow(x, e); }); }
 
 // ------------------------------------------------------------------ reductions

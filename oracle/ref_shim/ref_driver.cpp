@@ -16,6 +16,7 @@
 #include "ad/detail/autodiff_ops.hpp"
 #include "ad/ops/nodeops.hpp"
 #include "ad/utils/debug.hpp"
+#include "optim.hpp"
 
 // ---- symbols of reference files that are not part of the path ------------------------------
 namespace ag {
@@ -181,6 +182,26 @@ int cgadimpl_ref_reduction(int which, const float* x, float* out, float* dx, int
             backward(Value(loss), nullptr, false);
             to_host(X->grad, dx);
         }
+        return 0;
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "cgadimpl_ref: %s\n", e.what());
+        return 1;
+    }
+}
+
+// `steps` optimiser updates of one parameter vector with given gradients grads[steps, n], through
+// the reference's own ag::SGD / ag::Adam (cgadimpl/src/optimizer/optim.cpp).  which: 0 SGD, 1 Adam.
+int cgadimpl_ref_optimizer(int which, float* param, const float* grads, int64_t n, int steps, float lr_or_alpha) {
+    try {
+        auto P = leaf(from_host(param, {n}, true), "p");
+        auto root = detail::sum_nodeops(P);
+        Adam adam({Value(P)}, lr_or_alpha);
+        for (int s = 0; s < steps; ++s) {
+            std::memcpy(P->grad.data<float>(), grads + static_cast<int64_t>(s) * n, sizeof(float) * n);
+            if (which == 0) SGD(Value(root), nullptr, lr_or_alpha);
+            else adam.step();
+        }
+        to_host(P->value, param);
         return 0;
     } catch (const std::exception& e) {
         std::fprintf(stderr, "cgadimpl_ref: %s\n", e.what());

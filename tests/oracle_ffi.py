@@ -185,3 +185,26 @@ def use_all_cores():
         n = os.cpu_count() or 1
     lib().agb_oracle_set_num_threads(n)
     return num_threads()
+
+
+def sgd_step(param, grad, lr):
+    p = np.ascontiguousarray(param, np.float32).copy()
+    g = _c32(grad)
+    lib().agb_oracle_sgd_step(_f(p), _f(g), C.c_int64(p.size), C.c_float(lr))
+    return p
+
+
+def adam_step(param, grad, m, v, alpha, beta1, beta2, epsilon, t):
+    """Returns new (param, m, v) after step t (1-based)."""
+    p, mm, vv = (np.ascontiguousarray(a, np.float32).copy() for a in (param, m, v))
+    g = _c32(grad)
+    lib().agb_oracle_adam_step(_f(p), _f(g), _f(mm), _f(vv), C.c_int64(p.size), C.c_float(alpha), C.c_float(beta1),
+                               C.c_float(beta2), C.c_float(epsilon), C.c_int(t))
+    return p, mm, vv
+
+
+def adam_scalars(alpha, beta1, beta2, epsilon, t):
+    a, e = C.c_float(0), C.c_float(0)
+    lib().agb_oracle_adam_scalars(C.c_float(alpha), C.c_float(beta1), C.c_float(beta2), C.c_float(epsilon), C.c_int(t),
+                                  C.byref(a), C.byref(e))
+    return a.value, e.value

@@ -96,3 +96,13 @@ def time_fwd_bwd(rows, hidden, iters, warmup=1):
     sec = C.c_double(0.0)
     assert lib().cgadimpl_ref_time_fwd_bwd(C.c_int64(rows), C.c_int64(hidden), C.c_int(iters), C.c_int(warmup), C.byref(sec)) == 0
     return sec.value
+
+
+def optimizer(which, param, grads, lr_or_alpha):
+    """`len(grads)` updates of `param` through the reference's own ag::SGD ('sgd') or ag::Adam ('adam')."""
+    p = np.ascontiguousarray(param, np.float32).copy()
+    g = np.ascontiguousarray(grads, np.float32)
+    rc = lib().cgadimpl_ref_optimizer(C.c_int(0 if which == "sgd" else 1), _p(p), _p(g), C.c_int64(p.size),
+                                      C.c_int(g.shape[0]), C.c_float(lr_or_alpha))
+    assert rc == 0
+    return p

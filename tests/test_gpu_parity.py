@@ -388,3 +388,23 @@ def test_cuda_matches_the_reference_build(ops):
     assert_close(host(y), ref["y"], F32_RTOL, F32_ATOL, "stack y")
     assert_close(host(gh), ref["dx0"], F32_RTOL, F32_ATOL, "stack dx0")
     assert_close(host(dgs), ref["dgammas"], F32_RTOL, F32_ATOL, "stack dgammas")
+
+
+def test_optimizer_steps_match_the_oracle_bitwise(ops):
+    """agb_sgd_step / agb_adam_step against the restatement of cgadimpl/src/optimizer/optim.cpp."""
+    rng = np.random.default_rng(5)
+    n, steps = 4097, 6
+    p0 = (1 + 0.02 * rng.standard_normal(n)).astype(np.float32)
+    grads = rng.standard_normal((steps, n)).astype(np.float32)
+    p, want = dev(p0), p0.copy()
+    for g in grads:
+        ops.sgd_step(p, dev(g), 1e-2)
+        want = O.sgd_step(want, g, 1e-2)
+    assert np.array_equal(host(p), want)
+    p, m, v = dev(p0), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    wp, wm, wv = p0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    for t, g in enumerate(grads, 1):
+        a_eff, e_eff = O.adam_scalars(1e-3, 0.9, 0.999, 1e-8, t)
+        ops.adam_step(p, dev(g), m, v, 0.9, 0.999, a_eff, e_eff)
+        wp, wm, wv = O.adam_step(wp, g, wm, wv, 1e-3, 0.9, 0.999, 1e-8, t)
+    assert np.array_equal(host(p), wp) and np.array_equal(host(m), wm) and np.array_equal(host(v), wv)

@@ -44,3 +44,9 @@ def test_graph_api_parity_on_gpu():
 def test_cuda_graph_capture_of_the_layer_stack():
     out = _run("test_graph_capture_gpu")
     assert "[FAIL]" not in out
+
+
+@pytest.mark.gpu
+def test_nn_module_and_optimizers_on_gpu():
+    out = _run("test_nn_optim_gpu")
+    assert "[FAIL]" not in out

@@ -88,3 +88,20 @@ def test_oracle_reductions_match_reference(fp64):
     out, dx = REF.reduction("mean_all", x)
     assert out[0] == np.float32(O.mean_all(x, red))
     assert np.array_equal(dx, np.full_like(x, np.float32(1.0) / np.float32(x.size)))
+
+
+def test_oracle_optimizer_steps_match_reference_optim_cpp():
+    rng = np.random.default_rng(5)
+    n, steps = 1000, 7
+    p0 = (1 + 0.02 * rng.standard_normal(n)).astype(np.float32)
+    grads = rng.standard_normal((steps, n)).astype(np.float32)
+    want = REF.optimizer("sgd", p0, grads, 1e-2)
+    p = p0.copy()
+    for g in grads:
+        p = O.sgd_step(p, g, 1e-2)
+    assert np.array_equal(p, want)
+    want = REF.optimizer("adam", p0, grads, 1e-3)
+    p, m, v = p0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    for t, g in enumerate(grads, 1):
+        p, m, v = O.adam_step(p, g, m, v, 1e-3, 0.9, 0.999, 1e-8, t)
+    assert np.array_equal(p, want)
