@@ -213,7 +213,7 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_staged(const __grid_const
         // pass 1: sum of squares (each square rounded to fp32, summed in fp64); the (x+r) vectors
         // stay in registers for pass 2
         uint4 keep[VPT];
-        double ss0 = 0.0, ss1 = 0.0;
+        double ss[4] = {0.0, 0.0, 0.0, 0.0};
         if (valid) {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
@@ -235,14 +235,14 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_staged(const __grid_const
 #pragma unroll
                     for (int e = 0; e < NP; ++e) {
                         const float2 q = mul2(xv[e], xv[e]);
-                        ss0 += static_cast<double>(q.x);
-                        ss1 += static_cast<double>(q.y);
+                        ss[(2 * e) & 3] += static_cast<double>(q.x);
+                        ss[(2 * e + 1) & 3] += static_cast<double>(q.y);
                     }
                 }
             }
         }
-        const double ss = warp_sum(ss0 + ss1);
-        if (lane == 0) s_red[(k & 1) * nwarps + warp] = ss;
+        const double ssum = warp_sum((ss[0] + ss[1]) + (ss[2] + ss[3]));
+        if (lane == 0) s_red[(k & 1) * nwarps + warp] = ssum;
         __syncthreads();
         if (*s_abort) { aborted = true; break; }
         // every thread has its vectors in registers: the slot can be refilled right away
@@ -363,7 +363,8 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
         const uint4* sa = reinterpret_cast<const uint4*>(base + 2 * static_cast<size_t>(g.tile_stride));
 
         // pass 1: dot = sum(dy*x), products rounded to fp32, summed in fp64
-        double d0 = 0.0, d1 = 0.0;
+        // (four independent fp64 chains: a dependent DADD chain of 16 would cost more than the loads)
+        double d[4] = {0.0, 0.0, 0.0, 0.0};
         if (valid) {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
@@ -381,13 +382,13 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
 #pragma unroll
                     for (int e = 0; e < NP; ++e) {
                         const float2 p = mul2(gv[e], xv[e]);
-                        d0 += static_cast<double>(p.x);
-                        d1 += static_cast<double>(p.y);
+                        d[(2 * e) & 3] += static_cast<double>(p.x);
+                        d[(2 * e + 1) & 3] += static_cast<double>(p.y);
                     }
                 }
             }
         }
-        const double dsum = warp_sum(d0 + d1);
+        const double dsum = warp_sum((d[0] + d[1]) + (d[2] + d[3]));
         if (lane == 0) s_red[(k & 1) * nwarps + warp] = dsum;
         __syncthreads();
         if (*s_abort) { aborted = true; break; }
