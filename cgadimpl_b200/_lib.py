@@ -37,6 +37,8 @@ SIGNATURES = {
     "agb_accumulate_broadcast": (_i, [_vp, _vp, _i64, _i64, _i, _f, _i, _vp]),
     "agb_mul_reduce_workspace_bytes": (_sz, [_i64, _i64]),
     "agb_mul_reduce": (_i, [_vp, _vp, _vp, _i64, _i64, _i, _i, _vp, _sz, _i, _vp]),
+    "agb_layernorm_fwd": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _vp]),
+    "agb_layernorm_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _vp]),
     "agb_sgd_step": (_i, [_vp, _vp, _i64, _f, _i, _vp]),
     "agb_adam_step": (_i, [_vp, _vp, _vp, _vp, _i64, _f, _f, _f, _f, _vp]),
     "agb_row_reduce": (_i, [_i, _vp, _vp, _i64, _i64, _i, _vp]),

@@ -17,6 +17,9 @@ LIB = os.path.join(PKG, "libagb_cuda.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
+    # No implicit multiply-add contraction: the kernels keep the reference's rounding points.  (This does
+    # not cover the packed __fmul2_rn -> __fadd2_rn pair; see the caution in rmsnorm_staged.cuh.)
+    "--fmad=false",
     "--shared", "-Xcompiler", "-fPIC",
 ]
 

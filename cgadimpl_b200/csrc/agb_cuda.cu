@@ -12,6 +12,7 @@
 #include "elementwise.cuh"
 #include "rmsnorm_generic.cuh"
 #include "rmsnorm_staged.cuh"
+#include "layernorm_staged.cuh"
 
 namespace {
 
@@ -143,7 +144,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     auto tile_stride_of = [&](int rpt) { return round_up(rpt * row_bytes, 128); };
     auto stages_for = [&](int rpt, int c) {
         const int nw = rpt * G / 32;
-        const int fixed = ngamma * gamma_bytes + 2 * nw * 8 + 8 * 16 /*barriers*/ + 16 /*flag*/ + 128 /*slack*/;
+        const int fixed = ngamma * gamma_bytes + 8 * nw * 8 /*reduction scratch*/ + 8 * 16 /*barriers*/ + 16 /*flag*/ + 128 /*slack*/;
         int avail = d.smem_per_sm / c - 1024;  // the runtime reserves 1 KB per resident CTA
         if (avail > d.smem_optin) avail = d.smem_optin;
         const int s = (avail - fixed) / (narr * tile_stride_of(rpt));
@@ -198,7 +199,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     off += gamma_bytes * (ngamma > 1 ? 1 : 0);
     off = round_up(off, 16);
     g.off_red = off;
-    off += 2 * nwarps * 8;
+    off += 8 * nwarps * 8;
     g.off_bar = off;
     off += 8 * 16;
     g.off_flag = off;
@@ -390,6 +391,60 @@ int launch_jvp(const void* x, const void* gamma, const float* rstd, const void* 
     AGB_TRY(set_smem(agb::rmsnorm_jvp_staged<T>, p.smem));
     agb::rmsnorm_jvp_staged<T><<<p.grid, p.block, p.smem, st>>>(a);
     return after_launch("rmsnorm_jvp_staged");
+}
+
+template <typename T>
+int launch_ln_fwd(const void* x, void* y, float* mean, float* var, int64_t rows, int64_t hidden, float eps,
+                  cudaStream_t st) {
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    Plan p;
+    if (aligned16(x) && aligned16(y)) plan_launch(kFwd, rows, hidden, sizeof(T), 1, 0, *d, &p);
+    if (p.generic) {
+        agb::layernorm_fwd_generic<T><<<generic_grid(rows, *d), agb::kGenericThreads, 0, st>>>(
+            (const T*)x, (T*)y, mean, var, rows, (int)hidden, eps);
+        return after_launch("layernorm_fwd_generic");
+    }
+    agb::LnFwdArgs a{p.g, x, y, mean, var, eps};
+#define AGB_LN_FWD(V, FU)                                                              \
+    do {                                                                               \
+        AGB_TRY(set_smem(agb::layernorm_fwd_staged<T, V, FU>, p.smem));                \
+        agb::layernorm_fwd_staged<T, V, FU><<<p.grid, p.block, p.smem, st>>>(a);       \
+    } while (0)
+    if (p.vpt == 4 && p.full) AGB_LN_FWD(4, true);
+    else if (p.vpt == 4) AGB_LN_FWD(4, false);
+    else AGB_LN_FWD(8, false);
+#undef AGB_LN_FWD
+    return after_launch("layernorm_fwd_staged");
+}
+
+template <typename T>
+int launch_ln_bwd(const void* x, const float* mean, const float* var, const void* gy, const void* dx_add, void* dx,
+                  int64_t rows, int64_t hidden, float eps, cudaStream_t st) {
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    int add_mode = 0;
+    if (dx_add) add_mode = (dx_add == gy) ? 2 : 1;
+    Plan p;
+    if (aligned16(x) && aligned16(gy) && aligned16(dx) && (add_mode != 1 || aligned16(dx_add)))
+        plan_launch(kFwd, rows, hidden, sizeof(T), add_mode == 1 ? 3 : 2, 0, *d, &p);
+    const float hf = static_cast<float>(hidden);
+    if (p.generic) {
+        agb::layernorm_bwd_generic<T><<<generic_grid(rows, *d), agb::kGenericThreads, 0, st>>>(
+            (const T*)x, mean, var, (const T*)gy, (const T*)dx_add, (T*)dx, rows, (int)hidden, eps, hf, 2.0f / hf);
+        return after_launch("layernorm_bwd_generic");
+    }
+    agb::LnBwdArgs a{p.g, x, gy, dx_add, mean, var, dx, add_mode, eps, hf, 2.0f / hf};
+#define AGB_LN_BWD(V, FU)                                                              \
+    do {                                                                               \
+        AGB_TRY(set_smem(agb::layernorm_bwd_staged<T, V, FU>, p.smem));                \
+        agb::layernorm_bwd_staged<T, V, FU><<<p.grid, p.block, p.smem, st>>>(a);       \
+    } while (0)
+    if (p.vpt == 4 && p.full) AGB_LN_BWD(4, true);
+    else if (p.vpt == 4) AGB_LN_BWD(4, false);
+    else AGB_LN_BWD(8, false);
+#undef AGB_LN_BWD
+    return after_launch("layernorm_bwd_staged");
 }
 
 inline int ew_grid(int64_t work_items, const DevInfo& d) {
@@ -762,6 +817,36 @@ int agb_mul_reduce(const void* g, const void* a, void* out, int64_t rows, int64_
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return dtype == AGB_F32 ? launch_mul_reduce<float>(g, a, out, rows, hidden, out_mode, accumulate, (double*)workspace, st)
                             : launch_mul_reduce<bf16>(g, a, out, rows, hidden, out_mode, accumulate, (double*)workspace, st);
+}
+
+int agb_layernorm_fwd(const void* x, void* y, float* mean, float* var, int64_t rows, int64_t hidden, float eps,
+                      int dtype, agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    if (rows == 0) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(x, "x", elem));
+    AGB_TRY(check_ptr(y, "y", elem));
+    AGB_TRY(check_ptr(mean, "mean", 4));
+    AGB_TRY(check_ptr(var, "var", 4));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == AGB_F32 ? launch_ln_fwd<float>(x, y, mean, var, rows, hidden, eps, st)
+                            : launch_ln_fwd<bf16>(x, y, mean, var, rows, hidden, eps, st);
+}
+
+int agb_layernorm_bwd(const void* x, const float* mean, const float* var, const void* gy, const void* dx_add, void* dx,
+                      int64_t rows, int64_t hidden, float eps, int dtype, agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    if (rows == 0) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(x, "x", elem));
+    AGB_TRY(check_ptr(gy, "gy", elem));
+    AGB_TRY(check_ptr(dx, "dx", elem));
+    AGB_TRY(check_ptr(mean, "mean", 4));
+    AGB_TRY(check_ptr(var, "var", 4));
+    AGB_TRY(check_ptr(dx_add, "dx_add", elem, false));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == AGB_F32 ? launch_ln_bwd<float>(x, mean, var, gy, dx_add, dx, rows, hidden, eps, st)
+                            : launch_ln_bwd<bf16>(x, mean, var, gy, dx_add, dx, rows, hidden, eps, st);
 }
 
 int agb_sgd_step(void* param, const void* grad, int64_t n, float learning_rate, int dtype, agb_stream_t stream) {

@@ -41,8 +41,20 @@ struct PipeGeom {
 };
 
 // ---------------------------------------------------------------- packed fp32 helpers
+// CAUTION.  The packed intrinsics are documented to behave per lane like __fmul_rn / __fadd_rn, but
+// unlike those a __fmul2_rn feeding a __fadd2_rn WAS observed to become one FFMA2 (measured: 24 % of
+// the results off by one rounding; neither --fmad=false nor an optimisation barrier between the two
+// prevents it).  Rule in these kernels: add2 / sub2 only where NO operand is a product; an addition
+// or subtraction that consumes a product uses add2_after_mul / sub2_after_mul, built from the scalar
+// intrinsics, which are never fused.
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
 __device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 add2_after_mul(float2 a, float2 b) {
+    return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y));
+}
+__device__ __forceinline__ float2 sub2_after_mul(float2 a, float2 b) {
+    return make_float2(__fsub_rn(a.x, b.x), __fsub_rn(a.y, b.y));
+}
 // a - b, one rounding (an FMA with multiplier -1 is exact up to that rounding)
 __device__ __forceinline__ float2 sub2(float2 a, float2 b) { return __ffma2_rn(b, make_float2(-1.0f, -1.0f), a); }
 __device__ __forceinline__ float2 splat(float v) { return make_float2(v, v); }
@@ -417,7 +429,7 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
                         float2 t = mul2(xv[e], r22);
                         t = mul2(t, dot2);
                         t = POW2 ? mul2(t, div_h.dinv) : div_h(t);
-                        t = sub2(dy, t);
+                        t = sub2_after_mul(dy, t);
                         ov[e] = mul2(rs2, t);
                         if (HAS_GAMMA) {
                             const float2 q = mul2(gv[e], mul2(xv[e], rs2));
@@ -427,12 +439,12 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
                     }
                     if (a.add_mode == 2) {
 #pragma unroll
-                        for (int e = 0; e < NP; ++e) ov[e] = add2(ov[e], gv[e]);
+                        for (int e = 0; e < NP; ++e) ov[e] = add2_after_mul(ov[e], gv[e]);
                     } else if (staged_add) {
                         float2 av[NP];
                         Pairs<T>::unpack(sa[v], av);
 #pragma unroll
-                        for (int e = 0; e < NP; ++e) ov[e] = add2(ov[e], av[e]);
+                        for (int e = 0; e < NP; ++e) ov[e] = add2_after_mul(ov[e], av[e]);
                     }
                     store_vec_streaming(gdx + v, Pairs<T>::pack(ov));
                 }
@@ -633,10 +645,10 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_jvp_staged(const __grid_const
                     const float2 q = mul2(tv[e], rs2);
                     float2 p = mul2(yh, dot2);
                     p = mul2(p, c2);
-                    float2 o = sub2(q, p);
+                    float2 o = sub2_after_mul(q, p);
                     if (has_gamma) {
                         o = mul2(o, wv[e]);
-                        if (has_tgamma) o = add2(o, mul2(yh, twv[e]));
+                        if (has_tgamma) o = add2_after_mul(o, mul2(yh, twv[e]));
                     }
                     xv[e] = o;
                 }

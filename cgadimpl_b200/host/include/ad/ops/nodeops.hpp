@@ -14,6 +14,7 @@ std::shared_ptr<Node> mul_nodeops(const std::shared_ptr<Node>& a, const std::sha
 inline std::shared_ptr<Node> operator+(const std::shared_ptr<Node>& a, const std::shared_ptr<Node>& b) { return add_nodeops(a, b); }
 inline std::shared_ptr<Node> operator*(const std::shared_ptr<Node>& a, const std::shared_ptr<Node>& b) { return mul_nodeops(a, b); }
 
+std::shared_ptr<Node> laynor_nodeops(const std::shared_ptr<Node>& x);
 std::shared_ptr<Node> rms_nodeops(const std::shared_ptr<Node>& x);
 std::shared_ptr<Node> realrms_nodeops(const std::shared_ptr<Node>& x, float& g);
 

@@ -8,6 +8,7 @@ namespace ag {
 Value add(const Value& a, const Value& b);
 Value mul(const Value& a, const Value& b);
 
+Value laynor(const Value& x);              // (x - mean) / sqrt(var + 1e-5), no affine parameters
 Value rms(const Value& x);                 // x / sqrt(mean(x^2) + 1e-5), no gamma
 Value realrms(const Value& x, float g);    // scalar gain
 

@@ -134,6 +134,33 @@ void check_gamma(const Tensor& x, const Tensor& gamma) {
 }
 }  // namespace
 
+// normalization.cpp:10-22 -- tape = {variance, mean}, both [.., 1] fp32.
+std::shared_ptr<Node> laynor_nodeops(const std::shared_ptr<Node>& x) {
+    const Tensor& xv = x->value;
+    require_cuda(xv, "laynor");
+    const auto rh = rows_hidden(xv);
+    Tensor y, mean, var;
+    {
+        StreamGuard g(current_stream());
+        y = Tensor(xv.shape(), ag::options(xv).with_req_grad(false));
+        Shape rs = xv.shape();
+        if (rs.dims.empty()) rs.dims.push_back(1);
+        rs.dims.back() = 1;
+        const auto f32 = TensorOptions().with_dtype(Dtype::Float32).with_device(xv.device());
+        mean = Tensor(rs, f32);
+        var = Tensor(rs, f32);
+        check_status(agb_layernorm_fwd(xv.raw(), y.raw(), mean.data<float>(), var.data<float>(), rh.rows, rh.hidden, 1e-5f,
+                                       agb_dtype(xv), current_stream()),
+                     "laynor forward");
+    }
+    auto n = std::make_shared<Node>(y, Op::LayerNorm, x->requires_grad(), "layernor");
+    n->eps = 1e-5f;
+    n->tape.push_back(std::make_shared<Tensor>(var));
+    n->tape.push_back(std::make_shared<Tensor>(mean));
+    link(n, {x});
+    return n;
+}
+
 // normalization.cpp:23-35 -- eps is fixed at 1e-5 there; tape = {rstd, y}.
 std::shared_ptr<Node> rms_nodeops(const std::shared_ptr<Node>& x) {
     NormOut o = norm_forward(x->value, nullptr, 1e-5f);
@@ -265,6 +292,7 @@ std::shared_ptr<Node> rowmax_nodeops(const std::shared_ptr<Node>& x) {
 
 Value add(const Value& a, const Value& b) { return Value(detail::add_nodeops(a.node, b.node)); }
 Value mul(const Value& a, const Value& b) { return Value(detail::mul_nodeops(a.node, b.node)); }
+Value laynor(const Value& x) { return Value(detail::laynor_nodeops(x.node)); }
 Value rms(const Value& x) { return Value(detail::rms_nodeops(x.node)); }
 Value realrms(const Value& x, float g) { return Value(detail::realrms_nodeops(x.node, g)); }
 Value sum(const Value& x) { return Value(detail::sum_nodeops(x.node)); }

@@ -64,6 +64,8 @@ Tensor jvp_Mul(Node* n, const TangentOf& t) {
     Tensor r = binary_op(1, A->value, tangent(t, B), current_stream());
     return binary_op(0, l, r, current_stream());
 }
+// autodiff_jvp_ops.cpp:361-363 throws as well
+Tensor jvp_LayerNorm(Node*, const TangentOf&) { throw std::runtime_error("JVP for LayerNorm not implemented yet!"); }
 // autodiff_jvp_ops.cpp:366-379, corrected
 Tensor jvp_RMSNorm(Node* n, const TangentOf& t) {
     Node* X = n->inputs[0].get();
@@ -113,7 +115,7 @@ AG_NOT_ON_PATH(Acos) AG_NOT_ON_PATH(Atan) AG_NOT_ON_PATH(ASinh) AG_NOT_ON_PATH(A
 AG_NOT_ON_PATH(Relu) AG_NOT_ON_PATH(Sigmoid) AG_NOT_ON_PATH(Tanh) AG_NOT_ON_PATH(Softplus) AG_NOT_ON_PATH(GELU)
 AG_NOT_ON_PATH(SiLU) AG_NOT_ON_PATH(Mish) AG_NOT_ON_PATH(LeakyRelu) AG_NOT_ON_PATH(Gaus) AG_NOT_ON_PATH(Parcon)
 AG_NOT_ON_PATH(LiSHT) AG_NOT_ON_PATH(SoftmaxRow) AG_NOT_ON_PATH(LogSumExpRow) AG_NOT_ON_PATH(MatMul)
-AG_NOT_ON_PATH(Transpose) AG_NOT_ON_PATH(Linear) AG_NOT_ON_PATH(FMA) AG_NOT_ON_PATH(LayerNorm) AG_NOT_ON_PATH(Dyntanh)
+AG_NOT_ON_PATH(Transpose) AG_NOT_ON_PATH(Linear) AG_NOT_ON_PATH(FMA) AG_NOT_ON_PATH(Dyntanh)
 AG_NOT_ON_PATH(Attention) AG_NOT_ON_PATH(SWIGLU) AG_NOT_ON_PATH(CeWithLogits) AG_NOT_ON_PATH(KLDivergence)
 AG_NOT_ON_PATH(MSELoss) AG_NOT_ON_PATH(MAELoss)
 #undef AG_NOT_ON_PATH

@@ -93,6 +93,19 @@ void vjp_Mul(Node* n, const Tensor& gy) {
     }
 }
 
+// autodiff_vjp_ops.cpp:351-365; X.grad += dx fused through dx_add == dx == X.grad
+void vjp_LayerNorm(Node* n, const Tensor& gy) {
+    StreamGuard g(rule_stream(n));
+    Node* X = n->inputs[0].get();
+    if (!X->requires_grad()) return;
+    const auto rh = rows_hidden(X->value);
+    std::lock_guard<std::mutex> lock(X->grad_mutex);
+    check_status(agb_layernorm_bwd(X->value.raw(), n->tape[1]->data<float>(), n->tape[0]->data<float>(), gy.raw(),
+                                   X->grad.raw(), X->grad.raw(), rh.rows, rh.hidden, n->eps, agb_dtype(X->value),
+                                   rule_stream(n)),
+                 "laynor backward");
+}
+
 // autodiff_vjp_ops.cpp:368-377
 void vjp_RMSNorm(Node* n, const Tensor& gy) {
     StreamGuard g(rule_stream(n));
@@ -154,7 +167,7 @@ AG_NOT_ON_PATH(Acos) AG_NOT_ON_PATH(Atan) AG_NOT_ON_PATH(ASinh) AG_NOT_ON_PATH(A
 AG_NOT_ON_PATH(Relu) AG_NOT_ON_PATH(Sigmoid) AG_NOT_ON_PATH(Tanh) AG_NOT_ON_PATH(Softplus) AG_NOT_ON_PATH(GELU)
 AG_NOT_ON_PATH(SiLU) AG_NOT_ON_PATH(Mish) AG_NOT_ON_PATH(LeakyRelu) AG_NOT_ON_PATH(Gaus) AG_NOT_ON_PATH(Parcon)
 AG_NOT_ON_PATH(LiSHT) AG_NOT_ON_PATH(SoftmaxRow) AG_NOT_ON_PATH(LogSumExpRow) AG_NOT_ON_PATH(MatMul)
-AG_NOT_ON_PATH(Transpose) AG_NOT_ON_PATH(Linear) AG_NOT_ON_PATH(FMA) AG_NOT_ON_PATH(LayerNorm) AG_NOT_ON_PATH(Dyntanh)
+AG_NOT_ON_PATH(Transpose) AG_NOT_ON_PATH(Linear) AG_NOT_ON_PATH(FMA) AG_NOT_ON_PATH(Dyntanh)
 AG_NOT_ON_PATH(Attention) AG_NOT_ON_PATH(SWIGLU) AG_NOT_ON_PATH(CeWithLogits) AG_NOT_ON_PATH(KLDivergence)
 AG_NOT_ON_PATH(MSELoss) AG_NOT_ON_PATH(MAELoss)
 #undef AG_NOT_ON_PATH

@@ -105,6 +105,19 @@ int main() {
         try { backward(sum(rowmax(a))); } catch (const std::runtime_error&) { threw = true; }
         CHECK(threw);
     });
+    run_test("LayerNorm", [&] {                                   // test_core_ops_gpu.cpp:256-261
+        Value a = make_tensor(Tensor::randn(Shape{{4, 10}}, opts));
+        auto f = [&] { return laynor(a); };
+        // sum(laynor(a)) is identically zero, so weight the outputs to get a non-trivial gradient
+        Value w = make_tensor(Tensor::randn(Shape{{4, 10}}, opts.with_req_grad(false)));
+        auto fw = [&] { return laynor(a) * w; };
+        backward(sum(fw()));
+        CHECK(check_grad(a.grad(), numerical_gradient(a, fw)));
+        zero_grad(sum(f()));
+        bool threw = false;
+        try { jvp(f(), {}); } catch (const std::runtime_error&) { threw = true; }
+        CHECK(threw);                                             // jvp_LayerNorm throws, as in the reference
+    });
     run_test("RMSNorm", [&] {
         Value a = make_tensor(Tensor::randn(Shape{{4, 10}}, opts));
         auto f = [&] { return rms(a); };

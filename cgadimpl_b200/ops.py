@@ -130,6 +130,24 @@ def scale_lastdim(a, g, out=None):
     return out
 
 
+def layernorm_fwd(x, eps=1e-5, out=None):
+    """cgadimpl's laynor: y = (x - mean) / sqrt(var + eps); returns (y, mean[rows], var[rows])."""
+    rows, hidden = _rows_hidden(x)
+    y = torch.empty_like(x) if out is None else out
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+    var = torch.empty(rows, dtype=torch.float32, device=x.device)
+    check(_lib.lib().agb_layernorm_fwd(_p(x), _p(y), _p(mean), _p(var), rows, hidden, eps, _dt(x), _stream()))
+    return y, mean, var
+
+
+def layernorm_bwd(x, mean, var, gy, eps=1e-5, dx_add=None, dx=None):
+    rows, hidden = _rows_hidden(x)
+    dx = torch.empty_like(x) if dx is None else dx
+    check(_lib.lib().agb_layernorm_bwd(_p(x), _p(mean), _p(var), _p(gy), _p(dx_add), _p(dx), rows, hidden, eps, _dt(x),
+                                       _stream()))
+    return dx
+
+
 def sgd_step(param, grad, lr):
     """param += -lr * grad, as ag::SGD updates a leaf."""
     check(_lib.lib().agb_sgd_step(_p(param), _p(grad), param.numel(), float(lr), _dt(param), _stream()))

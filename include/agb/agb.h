@@ -182,6 +182,17 @@ size_t agb_mul_reduce_workspace_bytes(int64_t rows, int64_t hidden);
 int agb_mul_reduce(const void* g, const void* a, void* out, int64_t rows, int64_t hidden, int out_mode,
                    int accumulate, void* workspace, size_t workspace_bytes, int dtype, agb_stream_t stream);
 
+/* ---- LayerNorm without affine parameters (cgadimpl's `laynor`) ----
+ * Forward replaces laynor_nodeops (cgadimpl/src/ops/normalization.cpp:10-22):
+ *   mean = mean_j x; xm = x - mean; var = mean_j xm^2; y = xm / sqrt(var + eps)
+ * and saves var and mean ([rows] fp32: tape[0], tape[1]).  eps is 1e-5 in the reference.
+ * Backward replaces vjp_LayerNorm (cgadimpl/src/autodiff/autodiff_vjp_ops.cpp:351-365), with the
+ * same dx_add convention as agb_rmsnorm_bwd.  (The reference's jvp_LayerNorm throws.) */
+int agb_layernorm_fwd(const void* x, void* y, float* mean, float* var, int64_t rows, int64_t hidden, float eps,
+                      int dtype, agb_stream_t stream);
+int agb_layernorm_bwd(const void* x, const float* mean, const float* var, const void* gy, const void* dx_add,
+                      void* dx, int64_t rows, int64_t hidden, float eps, int dtype, agb_stream_t stream);
+
 /* ---- optimiser steps on the layer's parameters ----
  * agb_sgd_step: ag::SGD's update of one leaf, `value += -learning_rate * grad`
  *   (cgadimpl/src/optimizer/optim.cpp:12-19).

@@ -513,3 +513,93 @@ void agb_oracle_adam_scalars(float alpha, float beta1, float beta2, float epsilo
     *alpha_eff = alpha * sqrtf(bias_corr2) / bias_corr1;
     *eps_eff = epsilon * sqrtf(bias_corr2);
 }
+
+/* ------------------------------------------------------------------ LayerNorm (no affine)
+ * laynor_nodeops, cgadimpl/src/ops/normalization.cpp:10-22:
+ *   mean = reduce_mean(x,{-1},true); xm = x - mean; variance = reduce_mean(xm*xm,{-1},true);
+ *   y = xm / sqrt(variance + 1e-5f);   tape = {variance, mean}                                   */
+void agb_oracle_layernorm_forward(const float* x, float* y, float* mean, float* var,
+                                  int64_t R, int64_t H, float eps, int red) {
+    float* xm = falloc(R * H);
+    float* sq = falloc(R * H);
+    float* s = falloc(R);
+    ot_reduce_mean_last(x, mean, R, H, red);
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r)
+        for (int64_t j = 0; j < H; ++j) xm[r * H + j] = x[r * H + j] - mean[r];
+    ot_mul(xm, xm, sq, R * H);
+    ot_reduce_mean_last(sq, var, R, H, red);
+    ot_add_scalar(var, eps, s, R);
+    ot_sqrt(s, s, R);
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r)
+        for (int64_t j = 0; j < H; ++j) y[r * H + j] = xm[r * H + j] / s[r];
+    free(xm); free(sq); free(s);
+}
+
+/* vjp_LayerNorm, cgadimpl/src/autodiff/autodiff_vjp_ops.cpp:351-365, call by call:
+ *   std_inv = 1.0f / sqrt(var + 1e-5f)
+ *   d_xhat  = gy * std_inv
+ *   d_var   = reduce_sum(gy * (x - mean) * -0.5f * (std_inv*std_inv*std_inv), {-1}, true)
+ *   d_mean  = reduce_sum(gy * (std_inv * -1.0f), {-1}, true)
+ *             + d_var * reduce_sum((x - mean) * -2.0f, {-1}, true) / float(D)
+ *   dx      = d_xhat + d_var * (x - mean) * (2.0f / float(D)) + d_mean / float(D)               */
+void agb_oracle_layernorm_vjp(const float* x, const float* mean, const float* var, const float* gy, float* dx,
+                              int64_t R, int64_t H, float eps, int red) {
+    const int64_t n = R * H;
+    float* xm = falloc(n);
+    float* t = falloc(n);
+    float* std_inv = falloc(R);
+    float* c3 = falloc(R);
+    float* d_var = falloc(R);
+    float* s1 = falloc(R);
+    float* s2 = falloc(R);
+    float* d_mean = falloc(R);
+    const float D = (float)H;
+    const float k2 = 2.0f / D;
+    for (int64_t r = 0; r < R; ++r) {
+        float v = var[r] + eps;
+        std_inv[r] = 1.0f / sqrtf(v);
+        float q = std_inv[r] * std_inv[r];
+        c3[r] = q * std_inv[r];
+    }
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r)
+        for (int64_t j = 0; j < H; ++j) xm[r * H + j] = x[r * H + j] - mean[r];
+    /* d_var */
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r)
+        for (int64_t j = 0; j < H; ++j) {
+            float a = gy[r * H + j] * xm[r * H + j];
+            a = a * -0.5f;
+            t[r * H + j] = a * c3[r];
+        }
+    ot_reduce_sum_last(t, d_var, R, H, red);
+    /* reduce_sum(gy * (std_inv * -1.0f)) */
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r) {
+        const float nsi = std_inv[r] * -1.0f;
+        for (int64_t j = 0; j < H; ++j) t[r * H + j] = gy[r * H + j] * nsi;
+    }
+    ot_reduce_sum_last(t, s1, R, H, red);
+    /* reduce_sum((x - mean) * -2.0f) */
+    ot_mul_scalar(xm, -2.0f, t, n);
+    ot_reduce_sum_last(t, s2, R, H, red);
+    for (int64_t r = 0; r < R; ++r) {
+        float term = d_var[r] * s2[r];
+        term = term / D;
+        d_mean[r] = s1[r] + term;
+    }
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r) {
+        const float md = d_mean[r] / D;
+        for (int64_t j = 0; j < H; ++j) {
+            float dxh = gy[r * H + j] * std_inv[r];   /* d_xhat                  */
+            float u = d_var[r] * xm[r * H + j];       /* d_var * (x - mean)      */
+            u = u * k2;                               /* . * (2.0f / D)          */
+            float v1 = dxh + u;
+            dx[r * H + j] = v1 + md;
+        }
+    }
+    free(xm); free(t); free(std_inv); free(c3); free(d_var); free(s1); free(s2); free(d_mean);
+}

@@ -127,6 +127,13 @@ void agb_oracle_residual_stack(const float* x, const float* r, const float* gamm
                                float* y_last, float* dh0, float* dgammas,
                                int64_t R, int64_t H, int L, float eps, int red);
 
+/* LayerNorm without affine parameters: laynor_nodeops cgadimpl/src/ops/normalization.cpp:10-22 and
+ * vjp_LayerNorm cgadimpl/src/autodiff/autodiff_vjp_ops.cpp:351-365 (its JVP throws in the reference). */
+void agb_oracle_layernorm_forward(const float* x, float* y, float* mean, float* var,
+                                  int64_t R, int64_t H, float eps, int red);
+void agb_oracle_layernorm_vjp(const float* x, const float* mean, const float* var, const float* gy, float* dx,
+                              int64_t R, int64_t H, float eps, int red);
+
 /* Optimiser steps on a parameter: cgadimpl/src/optimizer/optim.cpp:12-19 (SGD), :33-72 (Adam). */
 void agb_oracle_sgd_step(float* param, const float* grad, int64_t n, float lr);
 void agb_oracle_adam_step(float* param, const float* grad, float* m, float* v, int64_t n, float alpha, float beta1,

@@ -189,6 +189,25 @@ int cgadimpl_ref_reduction(int which, const float* x, float* out, float* dx, int
     }
 }
 
+// laynor(x) and its backward through the reference's own laynor_nodeops / vjp_LayerNorm (eps 1e-5).
+int cgadimpl_ref_layernorm_fwd_bwd(const float* x, const float* gy, float* y, float* mean, float* var, float* dx,
+                                   int64_t R, int64_t H) {
+    try {
+        auto X = leaf(from_host(x, {R, H}, true), "x");
+        auto n = detail::laynor_nodeops(X);
+        Tensor seed = from_host(gy, {R, H}, false);
+        backward(Value(n), &seed, false);
+        to_host(n->value, y);
+        to_host(*n->tape[0], var);
+        to_host(*n->tape[1], mean);
+        to_host(X->grad, dx);
+        return 0;
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "cgadimpl_ref: %s\n", e.what());
+        return 1;
+    }
+}
+
 // `steps` optimiser updates of one parameter vector with given gradients grads[steps, n], through
 // the reference's own ag::SGD / ag::Adam (cgadimpl/src/optimizer/optim.cpp).  which: 0 SGD, 1 Adam.
 int cgadimpl_ref_optimizer(int which, float* param, const float* grads, int64_t n, int steps, float lr_or_alpha) {

@@ -208,3 +208,14 @@ def adam_scalars(alpha, beta1, beta2, epsilon, t):
     lib().agb_oracle_adam_scalars(C.c_float(alpha), C.c_float(beta1), C.c_float(beta2), C.c_float(epsilon), C.c_int(t),
                                   C.byref(a), C.byref(e))
     return a.value, e.value
+
+
+def layernorm_fwd_bwd(x, gy, eps, red=RED_F64):
+    """laynor(x) and its VJP: dict(y, mean, var, dx)."""
+    x, gy = _c32(x), _c32(gy)
+    R, H = x.shape
+    y, dx = np.empty_like(x), np.empty_like(x)
+    mean, var = np.empty(R, np.float32), np.empty(R, np.float32)
+    lib().agb_oracle_layernorm_forward(_f(x), _f(y), _f(mean), _f(var), C.c_int64(R), C.c_int64(H), C.c_float(eps), C.c_int(red))
+    lib().agb_oracle_layernorm_vjp(_f(x), _f(mean), _f(var), _f(gy), _f(dx), C.c_int64(R), C.c_int64(H), C.c_float(eps), C.c_int(red))
+    return dict(y=y, mean=mean, var=var, dx=dx)

@@ -106,3 +106,13 @@ def optimizer(which, param, grads, lr_or_alpha):
                                       C.c_int(g.shape[0]), C.c_float(lr_or_alpha))
     assert rc == 0
     return p
+
+
+def layernorm_fwd_bwd(x, gy):
+    x, gy = _c(x), _c(gy)
+    R, H = x.shape
+    y, dx = np.empty_like(x), np.empty_like(x)
+    mean, var = np.empty(R, np.float32), np.empty(R, np.float32)
+    rc = lib().cgadimpl_ref_layernorm_fwd_bwd(_p(x), _p(gy), _p(y), _p(mean), _p(var), _p(dx), C.c_int64(R), C.c_int64(H))
+    assert rc == 0
+    return dict(y=y, mean=mean, var=var, dx=dx)

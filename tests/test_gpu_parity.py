@@ -285,6 +285,7 @@ def test_jvp_corrected_form(ops, rows, hidden, dtype):
     ty = ops.rmsnorm_jvp(xd, gd, rstd, txd, tgd)
     if dtype == torch.float32:
         assert_close(host(ty), ref, F32_RTOL, F32_ATOL, "jvp")
+        assert frac_bit_equal(host(ty), ref) >= 0.999          # same rounding points as the oracle
         # adjoint identity <gy, J t> == <J^T gy, t> (gamma tangent zero)
         ty0 = ops.rmsnorm_jvp(xd, gd, rstd, txd, None)
         dx, _ = ops.rmsnorm_bwd(xd, gd, rstd, dev(gy))
@@ -408,3 +409,34 @@ def test_optimizer_steps_match_the_oracle_bitwise(ops):
         ops.adam_step(p, dev(g), m, v, 0.9, 0.999, a_eff, e_eff)
         wp, wm, wv = O.adam_step(wp, g, wm, wv, 1e-3, 0.9, 0.999, 1e-8, t)
     assert np.array_equal(host(p), wp) and np.array_equal(host(m), wm) and np.array_equal(host(v), wv)
+
+
+@pytest.mark.parametrize("rows,hidden,dtype", [(4, 10, torch.float32), (2048, 4096, torch.float32), (33, 1000, torch.float32),
+                                               (65, 20000, torch.float32), (300, 8192, torch.bfloat16),
+                                               (129, 1000, torch.bfloat16)])
+def test_layernorm_forward_and_vjp(ops, rows, hidden, dtype):
+    """cgadimpl's laynor (no affine parameters, eps 1e-5) against the oracle, which tests/test_reference_build.py
+    pins bit for bit to the reference's own laynor_nodeops / vjp_LayerNorm."""
+    eps = 1e-5
+    x, _, gy = make_inputs(rows, hidden, seed=rows + hidden, x_std=1.5)
+    x = x + np.float32(0.25)
+    if dtype == torch.bfloat16:
+        x, gy = (O.bf16_bits_to_f32(O.f32_to_bf16_bits(a)) for a in (x, gy))
+    ref = O.layernorm_fwd_bwd(x, gy, eps)
+    xd, gyd = dev(x, dtype), dev(gy, dtype)
+    y, mean, var = ops.layernorm_fwd(xd, eps)
+    dx = ops.layernorm_bwd(xd, mean, var, gyd, eps)
+    assert_close(host(mean), ref["mean"], F32_RTOL, F32_ATOL, "mean")
+    assert_close(host(var), ref["var"], F32_RTOL, F32_ATOL, "var")
+    if dtype == torch.float32:
+        assert_close(host(y), ref["y"], F32_RTOL, F32_ATOL, "y")
+        assert_close(host(dx), ref["dx"], F32_RTOL, F32_ATOL, "dx")
+        assert frac_bit_equal(host(y), ref["y"]) >= 0.999 and frac_bit_equal(host(dx), ref["dx"]) >= 0.999
+        extra = dev(gy) * 0.5
+        dx2 = ops.layernorm_bwd(xd, mean, var, gyd, eps, dx_add=extra)
+        assert np.array_equal(host(dx2), host(dx) + host(extra))
+        assert np.array_equal(host(ops.layernorm_bwd(xd, mean, var, gyd, eps, dx_add=gyd)), host(dx) + gy)
+    else:
+        # outputs are rounded to bf16 once; compare at the bf16 tolerance, relative to the row's scale
+        assert_close(host(y), O.bf16_bits_to_f32(O.f32_to_bf16_bits(ref["y"])), BF16_RTOL, 1e-6, "y bf16")
+        assert_close(host(dx), O.bf16_bits_to_f32(O.f32_to_bf16_bits(ref["dx"])), BF16_RTOL, 1e-2, "dx bf16")

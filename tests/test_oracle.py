@@ -201,3 +201,20 @@ def test_residual_stack_matches_torch_fp64():
     assert_close(out["dh0"], xt.grad.numpy(), 1e-5, 1e-5, "dx0")
     assert_close(out["dh0"], rt.grad.numpy(), 1e-5, 1e-5, "dr0")
     assert_close(out["dgammas"], gt.grad.numpy(), 1e-4, 1e-5, "dgammas")
+
+
+def test_layernorm_against_torch_fp64_and_finite_differences():
+    rows, hidden, eps = 37, 1000, 1e-5
+    x, _, gy = make_inputs(rows, hidden, seed=8)
+    x = x * np.float32(1.5) + np.float32(0.3)
+    out = O.layernorm_fwd_bwd(x, gy, eps)
+    xt = torch.tensor(x, dtype=torch.float64, requires_grad=True)
+    y = torch.nn.functional.layer_norm(xt, (hidden,), eps=eps)
+    y.backward(torch.tensor(gy, dtype=torch.float64))
+    assert_close(out["y"], y.detach().numpy(), 2e-6, 2e-6, "y")
+    assert_close(out["dx"], xt.grad.numpy(), 1e-4, 2e-5, "dx")     # the reference's formula cancels heavily
+    # the reference's own check: finite differences on [4,10] at 1e-3 (test_core_ops_gpu.cpp:256-261)
+    a = np.random.default_rng(3).standard_normal((4, 10)).astype(np.float32)
+    ana = O.layernorm_fwd_bwd(a, np.ones_like(a), eps)["dx"]
+    num = _numgrad(lambda v: O.layernorm_fwd_bwd(v, np.ones_like(v), eps)["y"], a)
+    assert np.abs(ana - num).max() <= 1e-3

@@ -105,3 +105,15 @@ def test_oracle_optimizer_steps_match_reference_optim_cpp():
     for t, g in enumerate(grads, 1):
         p, m, v = O.adam_step(p, g, m, v, 1e-3, 0.9, 0.999, 1e-8, t)
     assert np.array_equal(p, want)
+
+
+@pytest.mark.parametrize("fp64", [False, True])
+@pytest.mark.parametrize("rows,hidden", [(4, 10), (64, 1024), (33, 1000)])
+def test_oracle_layernorm_matches_reference_bitwise(fp64, rows, hidden):
+    x, _, gy = make_inputs(rows, hidden, seed=rows * 3 + hidden)
+    x = x + np.float32(0.5)                      # a non-zero mean makes the mean path matter
+    REF.set_reduce_fp64(fp64)
+    ref = REF.layernorm_fwd_bwd(x, gy)
+    mine = O.layernorm_fwd_bwd(x, gy, 1e-5, O.RED_F64 if fp64 else O.RED_F32)
+    for k in ("y", "mean", "var", "dx"):
+        assert np.array_equal(ref[k], mine[k]), k
