@@ -21,6 +21,7 @@ SIGNATURES = {
     "agb_last_error": (C.c_char_p, []),
     "agb_launch_count": (C.c_uint64, []),
     "agb_device_status": (_i, []),
+    "agb_selftest_bounded_wait": (_i, [_i, _vp, _vp]),
     "agb_set_option": (_i, [C.c_char_p, _i64]),
     "agb_describe_launch": (_i, [_i, _i64, _i64, _i, _i, C.POINTER(_i64)]),
     "agb_rmsnorm_fwd": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _vp]),

@@ -512,6 +512,12 @@ int agb_device_status(void) {
     return AGB_OK;
 }
 
+int agb_selftest_bounded_wait(int poll_limit, int* polls_done, agb_stream_t stream) {
+    if (poll_limit < 1 || poll_limit > 100000) return fail(AGB_ERR_INVALID_ARG, "poll_limit %d outside [1, 100000]", poll_limit);
+    agb::bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(poll_limit, polls_done);
+    return after_launch("bounded_wait_selftest");
+}
+
 int agb_set_option(const char* key, int64_t value) {
     if (!key) return fail(AGB_ERR_INVALID_ARG, "key is NULL");
     if (!strcmp(key, "stages")) opt_stages = value;

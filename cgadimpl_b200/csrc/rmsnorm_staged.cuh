@@ -494,6 +494,25 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
     }
 }
 
+// Self-test of the failure path: one CTA waits on a barrier that nothing will ever complete, with a
+// caller-chosen poll limit, and then does exactly what the real kernels do when a wait runs out:
+// raise the status word and return.  Bounded by poll_limit * kWaitSuspendNs; nothing hangs or traps.
+__global__ void __launch_bounds__(32) bounded_wait_selftest_kernel(int poll_limit, int* polls_done) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) {
+        int i = 0;
+        bool done = false;
+        for (; i < poll_limit && !done; ++i) done = mbar_try_wait(&bar, 0);
+        if (polls_done) *polls_done = i;
+        if (!done) atomicExch(&g_device_status, 6 /* AGB_ERR_TIMEOUT */);
+    }
+}
+
 // Stage 2: dgamma[c] = sum over partial rows p = 0..P-1, fixed order, fp64.
 // Block (32, 16): thread (cx, py) sums rows py, py+16, ... of column c with four independent
 // chains, then the 16 sub-sums are added in py order.

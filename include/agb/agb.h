@@ -63,6 +63,13 @@ uint64_t agb_launch_count(void);
  * rest of its work and returned; its outputs are undefined).  Synchronises the device. */
 int agb_device_status(void);
 
+/* Exercises the failure path without any fault: launches one warp that waits, for at most
+ * `poll_limit` polls (each up to 10 us), on a shared-memory barrier nobody completes, then raises the
+ * device status word exactly as a kernel whose bulk copy never arrived would.  The next
+ * agb_device_status() returns AGB_ERR_TIMEOUT and the context stays usable.  polls_done (device
+ * pointer, nullable) receives the number of polls made. */
+int agb_selftest_bounded_wait(int poll_limit, int* polls_done, agb_stream_t stream);
+
 /* Tuning knobs for sweeps ("stages", "ctas_per_sm", "threads", "force_generic"); value 0
  * restores the built-in heuristic.  Returns AGB_ERR_INVALID_ARG for an unknown key. */
 int agb_set_option(const char* key, int64_t value);

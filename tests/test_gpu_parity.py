@@ -440,3 +440,25 @@ def test_layernorm_forward_and_vjp(ops, rows, hidden, dtype):
         # outputs are rounded to bf16 once; compare at the bf16 tolerance, relative to the row's scale
         assert_close(host(y), O.bf16_bits_to_f32(O.f32_to_bf16_bits(ref["y"])), BF16_RTOL, 1e-6, "y bf16")
         assert_close(host(dx), O.bf16_bits_to_f32(O.f32_to_bf16_bits(ref["dx"])), BF16_RTOL, 1e-2, "dx bf16")
+
+
+def test_bounded_wait_expiry_is_reported_and_the_context_survives(ops):
+    """Failure detection without a fault: a wait that nothing will satisfy runs out after a bounded number
+    of polls, the kernel returns, the host reads AGB_ERR_TIMEOUT, and the next kernels run normally."""
+    from cgadimpl_b200 import AgbError, _lib
+
+    lib = _lib.lib()
+    ops.device_status()                                         # clean before
+    polls = torch.zeros(1, dtype=torch.int32, device="cuda")
+    import ctypes as C
+    assert lib.agb_selftest_bounded_wait(200, C.c_void_p(polls.data_ptr()), None) == 0
+    with pytest.raises(AgbError) as ei:
+        ops.device_status()
+    assert ei.value.status == 6                                 # AGB_ERR_TIMEOUT
+    assert int(polls.item()) == 200                             # it really waited out its budget
+    ops.device_status()                                         # the status word was cleared by the read
+    x = torch.randn(64, 1024, device="cuda")
+    y, rstd = ops.rmsnorm_fwd(x, None, 1e-5)                    # the context is still usable
+    want = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-5)
+    assert torch.allclose(y, want, rtol=1e-5, atol=1e-6)
+    assert lib.agb_selftest_bounded_wait(0, None, None) == 1    # argument validation
