@@ -1,6 +1,7 @@
 // graph.hpp -- Value / Node / topo_from with the members and signatures of
-// cgadimpl/include/ad/core/graph.hpp:18-86.  Checkpointing and version-tracking members are kept
-// as plain fields (unused here) so code that touches them still compiles.
+// cgadimpl/include/ad/core/graph.hpp:18-86.  The checkpointing members are used by
+// ad/autodiff/checkpoint.hpp; the RNG and version-tracking members are kept as plain fields so code
+// that touches them still compiles.
 #pragma once
 #include <atomic>
 #include <functional>
@@ -64,7 +65,12 @@ struct Node : std::enable_shared_from_this<Node> {
 
     bool requires_grad_flag_{false};
     bool requires_grad() const { return requires_grad_flag_; }
-    const std::vector<int64_t>& shape() const { return value.shape().dims; }
+    // What the value looked like before careful deletion dropped it (zero_grad and the rules that
+    // only need a shape keep working on a node whose activation is gone).
+    bool value_released{false};
+    Shape released_shape;
+    TensorOptions released_options;
+    const std::vector<int64_t>& shape() const { return value_released && value.numel() == 0 ? released_shape.dims : value.shape().dims; }
 
     // grad += contribution under grad_mutex; the contribution may be broadcast ([rows,1], [hidden]
     // or [1] against [rows, hidden]), as `grad += gy` is in the reference's row-reduction rules.

@@ -25,6 +25,11 @@ Value rmsnorm(const Value& x, const Value& gamma, float eps = 1e-5f);           
 Value add_rmsnorm(const Value& x, const Value& r, const Value& gamma, float eps = 1e-5f);
 Value residual_of(const Value& add_rmsnorm_out);
 
+// Recompute of one node from its inputs (value returned, tape restored in place); used by
+// checkpointing.  cgadimpl/include/ad/ops/ops.hpp:121-125.
+Tensor forward_eval_node(const std::shared_ptr<Node>& node);
+Tensor forward_eval_node(Node* node);
+
 inline Value operator+(const Value& a, const Value& b) { return ag::add(a, b); }
 inline Value operator*(const Value& a, const Value& b) { return ag::mul(a, b); }
 

@@ -9,6 +9,8 @@
 #include <exception>
 #include <thread>
 
+#include "ad/autodiff/careful_deletion.hpp"
+#include "ad/autodiff/checkpoint.hpp"
 #include "ad/detail/autodiff_ops.hpp"
 #include "ad/detail/host_util.hpp"
 
@@ -18,8 +20,10 @@ void zero_grad(const Value& root) {
     for (Node* n : topo_from(root.node.get()))
         if (n->requires_grad()) {
             detail::StreamGuard g(n->creation_context.stream);
-            if (n->grad.defined() && n->grad.numel() == n->value.numel()) n->grad.zero_();
-            else n->grad = Tensor::zeros(n->value.shape(), ag::options(n->value));
+            const bool gone = n->value_released && n->value.numel() == 0;  // activation dropped: use what it looked like
+            const Shape& shape = gone ? n->released_shape : n->value.shape();
+            if (n->grad.defined() && n->grad.numel() == shape.numel()) n->grad.zero_();
+            else n->grad = Tensor::zeros(shape, gone ? n->released_options : ag::options(n->value));
         }
 }
 
@@ -55,6 +59,34 @@ void run_hooks(Node* n) {
     for (auto& h : n->post_acc_grad_hooks) h(n);
 }
 
+// Which activations a rule reads.  Add / Sum / MeanAll / RowSum only move gy along; Mul and the
+// norm rules read their inputs' values; the norm rules also read their own tape (rstd, mean, var).
+bool rule_reads_inputs(Op op) {
+    return op == Op::Mul || op == Op::RMSNorm || op == Op::RMSNormAffine || op == Op::RealRMSNorm || op == Op::LayerNorm;
+}
+bool rule_reads_own_tape(Op op) {
+    return op == Op::RMSNorm || op == Op::RMSNormAffine || op == Op::RealRMSNorm || op == Op::LayerNorm;
+}
+
+// Runs n's rule with every activation it reads present: dropped ones are recomputed first
+// (cgadimpl/src/core/autodiff.cpp:82-86 restores only the node's own value), and a node that had to
+// be recomputed is dropped again afterwards -- all its children have run by then, so nothing reads
+// it any more.
+void run_rule(Node* n) {
+    VjpFn fn = vjp_lookup(n->op);
+    if (!fn) return;
+    if (n->is_checkpoint && rule_reads_own_tape(n->op) && !checkpoint_impl::ensure_value_present(n->shared_from_this()))
+        throw std::runtime_error("autodiff: failed to recompute checkpointed node during backward");
+    if (rule_reads_inputs(n->op))
+        for (auto& p : n->inputs)
+            if (!checkpoint_impl::ensure_value_present(p))
+                throw std::runtime_error("autodiff: an input activation is gone and cannot be recomputed");
+    fn(n, n->grad);
+    // `value_released` means careful deletion dropped this activation once: whoever brought it back
+    // (this rule or a child's) no longer needs it
+    if (n->is_checkpoint && n->value_released) memory::try_delete_node(n, memory::DeletePolicy::ForwardPass);
+}
+
 }  // namespace
 
 void backward(const Value& root, const Tensor* grad_seed, bool enable_parallel) {
@@ -82,7 +114,7 @@ void backward(const Value& root, const Tensor* grad_seed, bool enable_parallel) 
             Node* n = *it;
             if (!n->requires_grad()) continue;
             debug::on_backprop_step(n, n->grad);
-            if (VjpFn fn = vjp_lookup(n->op)) fn(n, n->grad);
+            run_rule(n);
             run_hooks(n);
         }
         return;
@@ -126,7 +158,7 @@ void backward(const Value& root, const Tensor* grad_seed, bool enable_parallel) 
     auto worker = [&] {
         while (Node* n = rq.pop()) {
             try {
-                if (VjpFn fn = vjp_lookup(n->op)) fn(n, n->grad);
+                run_rule(n);
                 for (auto& pp : n->inputs) {
                     Node* p = pp.get();
                     if (!p || !p->requires_grad()) continue;

@@ -21,7 +21,9 @@ Node::Node(const Tensor& v, Op op_, bool req_grad, const char* nm)
 
 void Node::accumulate_grad(const Tensor& c) {
     std::lock_guard<std::mutex> lock(grad_mutex);
-    if (!grad.defined() || grad.numel() != value.numel()) grad = Tensor::zeros(value.shape(), ag::options(value));
+    const bool gone = value_released && value.numel() == 0;  // activation dropped by careful deletion
+    const Shape& want = gone ? released_shape : value.shape();
+    if (!grad.defined() || grad.numel() != want.numel()) grad = Tensor::zeros(want, gone ? released_options : ag::options(value));
     if (c.numel() == 0) return;
     if (!grad.is_cuda()) {
         // CPU nodes are scalar literals and tiny test inputs: plain loop, fp32 only
@@ -54,9 +56,9 @@ Value::Value(std::shared_ptr<Node> n) : node(std::move(n)) {}
 Value::Value(float v) {
     node = std::make_shared<Node>(Tensor::full(Shape{{1}}, TensorOptions(), v), Op::Leaf, false, "scalar_literal");
 }
-const std::vector<int64_t>& Value::shape() const { return node->value.shape().dims; }
+const std::vector<int64_t>& Value::shape() const { return node->shape(); }
 std::pair<int, int> Value::shape_2d() const {
-    const auto& d = node->value.shape().dims;
+    const auto& d = node->shape();
     if (d.empty()) return {0, 0};
     if (d.size() == 1) return {1, static_cast<int>(d[0])};
     return {static_cast<int>(d[0]), static_cast<int>(d[1])};

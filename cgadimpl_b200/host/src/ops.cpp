@@ -134,29 +134,36 @@ void check_gamma(const Tensor& x, const Tensor& gamma) {
 }
 }  // namespace
 
-// normalization.cpp:10-22 -- tape = {variance, mean}, both [.., 1] fp32.
-std::shared_ptr<Node> laynor_nodeops(const std::shared_ptr<Node>& x) {
-    const Tensor& xv = x->value;
+namespace {
+struct LayerNormOut {
+    Tensor y, mean, var;
+};
+LayerNormOut layernorm_forward(const Tensor& xv, float eps) {
     require_cuda(xv, "laynor");
     const auto rh = rows_hidden(xv);
-    Tensor y, mean, var;
-    {
-        StreamGuard g(current_stream());
-        y = Tensor(xv.shape(), ag::options(xv).with_req_grad(false));
-        Shape rs = xv.shape();
-        if (rs.dims.empty()) rs.dims.push_back(1);
-        rs.dims.back() = 1;
-        const auto f32 = TensorOptions().with_dtype(Dtype::Float32).with_device(xv.device());
-        mean = Tensor(rs, f32);
-        var = Tensor(rs, f32);
-        check_status(agb_layernorm_fwd(xv.raw(), y.raw(), mean.data<float>(), var.data<float>(), rh.rows, rh.hidden, 1e-5f,
-                                       agb_dtype(xv), current_stream()),
-                     "laynor forward");
-    }
-    auto n = std::make_shared<Node>(y, Op::LayerNorm, x->requires_grad(), "layernor");
+    StreamGuard g(current_stream());
+    LayerNormOut o;
+    o.y = Tensor(xv.shape(), ag::options(xv).with_req_grad(false));
+    Shape rs = xv.shape();
+    if (rs.dims.empty()) rs.dims.push_back(1);
+    rs.dims.back() = 1;
+    const auto f32 = TensorOptions().with_dtype(Dtype::Float32).with_device(xv.device());
+    o.mean = Tensor(rs, f32);
+    o.var = Tensor(rs, f32);
+    check_status(agb_layernorm_fwd(xv.raw(), o.y.raw(), o.mean.data<float>(), o.var.data<float>(), rh.rows, rh.hidden, eps,
+                                   agb_dtype(xv), current_stream()),
+                 "laynor forward");
+    return o;
+}
+}  // namespace
+
+// normalization.cpp:10-22 -- tape = {variance, mean}, both [.., 1] fp32.
+std::shared_ptr<Node> laynor_nodeops(const std::shared_ptr<Node>& x) {
+    LayerNormOut o = layernorm_forward(x->value, 1e-5f);
+    auto n = std::make_shared<Node>(o.y, Op::LayerNorm, x->requires_grad(), "layernor");
     n->eps = 1e-5f;
-    n->tape.push_back(std::make_shared<Tensor>(var));
-    n->tape.push_back(std::make_shared<Tensor>(mean));
+    n->tape.push_back(std::make_shared<Tensor>(o.var));
+    n->tape.push_back(std::make_shared<Tensor>(o.mean));
     link(n, {x});
     return n;
 }
@@ -289,6 +296,61 @@ std::shared_ptr<Node> rowmax_nodeops(const std::shared_ptr<Node>& x) {
 }
 
 }  // namespace detail
+
+// Recomputes a node's value from its inputs' values -- and its tape, which the rules of the norm
+// ops read -- with the same kernels and the same stream the forward used, so the recomputed bits
+// equal the originals.  Covers every op of this library's path; cgadimpl/src/ops/ops.cpp:300-386
+// covers the elementwise ops and MatMul / Linear and throws for the normalisation ops.
+Tensor forward_eval_node(Node* node) {
+    using namespace detail;
+    if (!node) throw std::runtime_error("forward_eval_node: null node");
+    if (node->op == Op::Leaf) return node->value;
+    for (auto& p : node->inputs)
+        if (!p || p->value.numel() == 0) throw std::runtime_error("forward_eval_node: an input of the node has no value");
+    // the builders launch on the thread's current stream: make that the node's stream for the call
+    struct CurrentStreamGuard {
+        ag_cuda_stream_t prev;
+        explicit CurrentStreamGuard(ag_cuda_stream_t s) : prev(current_stream()) { set_current_stream(s); }
+        ~CurrentStreamGuard() { set_current_stream(prev); }
+    } cs(node->creation_context.stream);
+    StreamGuard g(node->creation_context.stream);
+    auto in = [&](size_t i) -> const Tensor& { return node->inputs.at(i)->value; };
+    auto set_tape = [&](std::initializer_list<Tensor> ts) {
+        node->tape.clear();
+        for (auto& t : ts) node->tape.push_back(std::make_shared<Tensor>(t));
+    };
+    switch (node->op) {
+        case Op::Add: return binary(0, in(0), in(1));
+        case Op::Mul: return binary(1, in(0), in(1));
+        case Op::RMSNorm: {
+            NormOut o = norm_forward(in(0), nullptr, node->eps);
+            set_tape({o.rstd, o.y});
+            return o.y;
+        }
+        case Op::RealRMSNorm: {
+            NormOut o = norm_forward(in(0), nullptr, node->eps);
+            set_tape({o.rstd, o.y});
+            return binary(1, o.y, in(1));
+        }
+        case Op::RMSNormAffine: {
+            NormOut o = norm_forward(in(0), &in(1), node->eps);
+            set_tape({o.rstd});
+            return o.y;
+        }
+        case Op::LayerNorm: {
+            LayerNormOut o = layernorm_forward(in(0), node->eps);
+            set_tape({o.var, o.mean});
+            return o.y;
+        }
+        case Op::Sum: return reduce_all(in(0), AGB_REDUCE_SUM);
+        case Op::MeanAll: return reduce_all(in(0), AGB_REDUCE_MEAN);
+        case Op::RowSum: return reduce_axis1(in(0), AGB_REDUCE_SUM);
+        case Op::RowMax: return reduce_axis1(in(0), AGB_REDUCE_MAX);
+        default:
+            throw std::runtime_error(std::string("forward_eval_node: unsupported op for recompute: ") + op_name(node->op));
+    }
+}
+Tensor forward_eval_node(const std::shared_ptr<Node>& node) { return forward_eval_node(node.get()); }
 
 Value add(const Value& a, const Value& b) { return Value(detail::add_nodeops(a.node, b.node)); }
 Value mul(const Value& a, const Value& b) { return Value(detail::mul_nodeops(a.node, b.node)); }

@@ -15,12 +15,13 @@ ag_cuda_stream_t rule_stream(Node* n) { return n->creation_context.stream; }
 // P.grad += reduce_for_broadcast(g * a, P.value)   (a may be null: plain g)
 // autodiff_vjp_ops.cpp:15-35 picks the axes to sum from the shapes; here the shape class does.
 void accumulate_reduced(Node* P, const Tensor& g, const Tensor* a, ag_cuda_stream_t st) {
-    const int mode = classify_broadcast(g, P->value);
+    // classified against P's grad, which has P's shape: P's value may have been dropped
+    const int mode = classify_broadcast(g, P->grad);
     if (mode == AGB_BCAST_FULL) {
         P->accumulate_grad(a ? binary_op(1, g, *a, st) : g);
         return;
     }
-    require_cuda(P->value, "broadcast gradient");
+    require_cuda(P->grad, "broadcast gradient");
     const auto rh = rows_hidden(g);
     const size_t wsb = agb_mul_reduce_workspace_bytes(rh.rows, rh.hidden);
     void* ws = workspace(wsb, g, st);
@@ -141,12 +142,12 @@ void vjp_MeanAll(Node* n, const Tensor& gy) {
     StreamGuard g(rule_stream(n));
     Node* X = n->inputs[0].get();
     if (!X->requires_grad()) return;
-    const float scale = 1.0f / static_cast<float>(X->value.numel());
-    const auto rh = rows_hidden(X->value);
-    const Tensor src = on_device_of(gy, X->value);
+    const float scale = 1.0f / static_cast<float>(X->grad.numel());
+    const auto rh = rows_hidden(X->grad);
+    const Tensor src = on_device_of(gy, X->grad);
     std::lock_guard<std::mutex> lock(X->grad_mutex);
     check_status(agb_accumulate_broadcast(X->grad.raw(), src.raw(), rh.rows, rh.hidden, AGB_BCAST_SCALAR, scale,
-                                          agb_dtype(X->value), rule_stream(n)),
+                                          agb_dtype(X->grad), rule_stream(n)),
                  "vjp_MeanAll");
 }
 // autodiff_vjp_ops.cpp:411-414: X.grad += gy ([B,1] broadcast)

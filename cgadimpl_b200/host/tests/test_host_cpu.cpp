@@ -4,6 +4,8 @@
 // behaviour of ops given CPU tensors (there is no CPU implementation of the path).
 #include "ad/ag_all.hpp"
 #include "ad/detail/host_util.hpp"
+#include <unordered_set>
+
 #include "check.hpp"
 
 using namespace ag;
@@ -130,6 +132,42 @@ int main() {
         set_current_stream(nullptr);
         Node n(Tensor::zeros(Shape{{1}}), Op::Leaf, false, "ctx");
         CHECK(n.creation_context.stream == nullptr && !n.creation_context.device.is_cuda());
+    });
+
+    run_test("checkpoint marking and deletion policies (no kernels)", [] {
+        // a hand-built chain leaf -> n1 -> n2 -> n3 -> root of Add nodes over CPU tensors
+        Value a = make_tensor(Tensor::zeros(Shape{{2, 3}}, TensorOptions().with_req_grad(true)), "a");
+        auto mk = [](std::shared_ptr<Node> in) {
+            auto n = std::make_shared<Node>(Tensor::zeros(Shape{{2, 3}}), Op::Add, true, "n");
+            n->inputs = {in, in};
+            return n;
+        };
+        auto n1 = mk(a.node), n2 = mk(n1), n3 = mk(n2), root = mk(n3);
+        reset_checkpoint_stats();
+        memory::reset_deletion_stats();
+        auto_checkpoint_every_n(Value(root), 2);           // breadth-first: root(1) n3(2) n2(3) n1(4) a(5)
+        CHECK(n3->is_checkpoint && n1->is_checkpoint && !n2->is_checkpoint && !root->is_checkpoint && !a.node->is_checkpoint);
+        CHECK(n3->saved_inputs.size() == 2 && n3->saved_inputs[0].node == n2);
+        CHECK(checkpoint_stats().total_checkpoints == 2 && checkpoint_stats().total_memory_saved == 2 * 24);
+        auto_checkpoint_by_depth(Value(root), 2);          // n2 (depth 2) and n1 (depth 3, already marked); never the leaf
+        CHECK(n2->is_checkpoint && !a.node->is_checkpoint && checkpoint_stats().total_checkpoints == 3);
+        checkpoint_impl::mark_node_checkpoint(a.node);     // a leaf cannot be recomputed from anything
+        CHECK(!a.node->is_checkpoint);
+        CHECK(checkpoint_impl::is_checkpointed(n1) && !checkpoint_impl::is_checkpointed(root) && !checkpoint_impl::is_checkpointed(nullptr));
+
+        std::unordered_set<Node*> keep{n2.get()};
+        CHECK(memory::sweep_safe_nodes(Value(root), memory::DeletePolicy::AlwaysSafe, keep) == 0);   // checkpoints, pending grads
+        CHECK(memory::sweep_safe_nodes(Value(root), memory::DeletePolicy::ForwardPass, keep) == 2);  // n1 and n3
+        CHECK(n1->value.numel() == 0 && n3->value.numel() == 0 && n2->value.numel() == 6 && root->value.numel() == 6);
+        CHECK(n1->shape() == std::vector<int64_t>({2, 3}) && n1->value_released);
+        CHECK(n1->grad.numel() == 6);                      // ForwardPass keeps gradients
+        CHECK(memory::deletion_stats().nodes_deleted == 2 && memory::deletion_stats().memory_freed == 2 * 24);
+        zero_grad(Value(root));                            // works on dropped nodes: the shape is remembered
+        CHECK(n3->grad.numel() == 6);
+        // recompute needs kernels, so on CPU it fails cleanly and is counted
+        CHECK(!checkpoint_impl::recompute_subgraph(n3));
+        CHECK(checkpoint_stats().failed_recomputes >= 1 && checkpoint_stats().successful_recomputes == 0);
+        CHECK(checkpoint_impl::ensure_value_present(n2) && !checkpoint_impl::ensure_value_present(n3));
     });
 
     return finish("test_host_cpu");

@@ -25,7 +25,7 @@ def _run(name, timeout=600):
 
 def test_host_layer_without_gpu():
     out = _run("test_host_cpu")
-    assert out.count("[PASS]") >= 8 and "[FAIL]" not in out
+    assert out.count("[PASS]") >= 9 and "[FAIL]" not in out
 
 
 @pytest.mark.gpu
@@ -50,3 +50,9 @@ def test_cuda_graph_capture_of_the_layer_stack():
 def test_nn_module_and_optimizers_on_gpu():
     out = _run("test_nn_optim_gpu")
     assert "[FAIL]" not in out
+
+
+@pytest.mark.gpu
+def test_activation_checkpointing_across_the_stack():
+    out = _run("test_checkpoint_gpu")
+    assert "[FAIL]" not in out and out.count("[PASS]") >= 6
