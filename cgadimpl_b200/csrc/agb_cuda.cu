@@ -13,6 +13,7 @@
 #include "rmsnorm_generic.cuh"
 #include "rmsnorm_staged.cuh"
 #include "layernorm_staged.cuh"
+#include "softmax_staged.cuh"
 
 namespace {
 
@@ -88,7 +89,7 @@ struct Plan {
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-enum Which { kFwd = 0, kBwd = 1, kJvp = 2 };
+enum Which { kFwd = 0, kBwd = 1, kJvp = 2, kSoftmax = 3 };  // kSoftmax: planned like kJvp, never "light"
 
 // Backward variants by elements per thread (= fp64 column sums held in registers): the launch
 // bound caps the registers the compiler may use, and with them the threads an SM can hold.
@@ -98,8 +99,9 @@ struct BwdVariant {
 constexpr BwdVariant kBwdVariants[3] = {{8, 1024, 64}, {16, 768, 80}, {32, 512, 128}};
 
 // narr: arrays staged per tile; ngamma: [hidden] fp32 vectors kept in shared memory.
+// extra_static: statically declared shared memory of the kernel, charged against the per-CTA limit.
 void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, int ngamma, const DevInfo& d,
-                 Plan* p) {
+                 Plan* p, int extra_static = 0) {
     p->generic = true;
     if (opt_force_generic.load() || rows <= 0) return;
     const int64_t row_bytes64 = hidden * elem;
@@ -144,7 +146,8 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     auto tile_stride_of = [&](int rpt) { return round_up(rpt * row_bytes, 128); };
     auto stages_for = [&](int rpt, int c) {
         const int nw = rpt * G / 32;
-        const int fixed = ngamma * gamma_bytes + 8 * nw * 8 /*reduction scratch*/ + 8 * 16 /*barriers*/ + 16 /*flag*/ + 128 /*slack*/;
+        const int fixed = ngamma * gamma_bytes + 8 * nw * 8 /*reduction scratch*/ + 8 * 16 /*barriers*/ + 16 /*flag*/ + 128 /*slack*/ +
+                          extra_static;
         int avail = d.smem_per_sm / c - 1024;  // the runtime reserves 1 KB per resident CTA
         if (avail > d.smem_optin) avail = d.smem_optin;
         const int s = (avail - fixed) / (narr * tile_stride_of(rpt));
@@ -158,7 +161,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     if (target <= 0) target = max_threads;
     if (target > max_threads) target = max_threads;
     const int want_ctas = static_cast<int>(opt_ctas_per_sm.load());
-    const bool light = which != kBwd && elem == 4;
+    const bool light = (which == kFwd || which == kJvp) && elem == 4;
     const int max_resident = light && !want_ctas && !opt_threads.load() ? 512 : 2048;
     int rpt = 0, ctas = 0, S = 0, best = 0;
     for (int c = (want_ctas ? want_ctas : 1); c <= (want_ctas ? want_ctas : 4); ++c)
@@ -391,6 +394,63 @@ int launch_jvp(const void* x, const void* gamma, const float* rstd, const void* 
     AGB_TRY(set_smem(agb::rmsnorm_jvp_staged<T>, p.smem));
     agb::rmsnorm_jvp_staged<T><<<p.grid, p.block, p.smem, st>>>(a);
     return after_launch("rmsnorm_jvp_staged");
+}
+
+// mode: the MODE of softmax_fwd_staged / softmax_fwd_generic.
+template <typename T>
+int launch_softmax_fwd(int mode, const void* z, const void* t, const void* rowscale, const void* add, void* out,
+                       void* out_row, int64_t rows, int64_t hidden, cudaStream_t st) {
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    Plan p;
+    const bool al = aligned16(z) && (!t || aligned16(t)) && (!out || aligned16(out)) && (!add || aligned16(add));
+    // arrays per stage: z [, t] [, fp32 scratch = two bf16 row-widths]; fp32 parks e in place over z
+    const bool scratch = mode != 1 && sizeof(T) == 2;
+    const int narr = (mode == 3 ? 2 : 1) + (scratch ? 2 : 0);
+    if (al) plan_launch(kSoftmax, rows, hidden, sizeof(T), narr, 0, *d, &p, agb::kExpTableSize * 8);
+    if (p.generic) {
+        const int grid = generic_grid(rows, *d);
+#define AGB_SM_GENERIC(M)                                                                                         \
+    agb::softmax_fwd_generic<T, M><<<grid, agb::kGenericThreads, 0, st>>>((const T*)z, (const T*)t, (const T*)rowscale, \
+                                                                         (const T*)add, (T*)out, (T*)out_row, rows, (int)hidden)
+        if (mode == 0) AGB_SM_GENERIC(0);
+        else if (mode == 1) AGB_SM_GENERIC(1);
+        else if (mode == 2) AGB_SM_GENERIC(2);
+        else AGB_SM_GENERIC(3);
+#undef AGB_SM_GENERIC
+        return after_launch("softmax_fwd_generic");
+    }
+    agb::SoftmaxArgs a{p.g, z, t, rowscale, add, out, out_row, scratch ? (mode == 3 ? 2 : 1) * p.g.tile_stride : 0};
+#define AGB_SM_STAGED(M)                                                       \
+    do {                                                                       \
+        AGB_TRY(set_smem(agb::softmax_fwd_staged<T, M>, p.smem));              \
+        agb::softmax_fwd_staged<T, M><<<p.grid, p.block, p.smem, st>>>(a);     \
+    } while (0)
+    if (mode == 0) AGB_SM_STAGED(0);
+    else if (mode == 1) AGB_SM_STAGED(1);
+    else if (mode == 2) AGB_SM_STAGED(2);
+    else AGB_SM_STAGED(3);
+#undef AGB_SM_STAGED
+    return after_launch("softmax_fwd_staged");
+}
+
+template <typename T>
+int launch_softmax_bwd(const void* y, const void* g, const void* add, void* out, int64_t rows, int64_t hidden,
+                       cudaStream_t st) {
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    Plan p;
+    if (aligned16(y) && aligned16(g) && aligned16(out) && (!add || aligned16(add)))
+        plan_launch(kSoftmax, rows, hidden, sizeof(T), 2, 0, *d, &p);
+    if (p.generic) {
+        agb::softmax_bwd_generic<T><<<generic_grid(rows, *d), agb::kGenericThreads, 0, st>>>(
+            (const T*)y, (const T*)g, (const T*)add, (T*)out, rows, (int)hidden);
+        return after_launch("softmax_bwd_generic");
+    }
+    agb::SoftmaxBwdArgs a{p.g, y, g, add, out};
+    AGB_TRY(set_smem(agb::softmax_bwd_staged<T>, p.smem));
+    agb::softmax_bwd_staged<T><<<p.grid, p.block, p.smem, st>>>(a);
+    return after_launch("softmax_bwd_staged");
 }
 
 template <typename T>
@@ -669,6 +729,52 @@ int agb_rmsnorm_jvp(const void* x, const void* gamma, const float* rstd, const v
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return dtype == AGB_F32 ? launch_jvp<float>(x, gamma, rstd, tx, tgamma, ty, rows, hidden, st)
                             : launch_jvp<bf16>(x, gamma, rstd, tx, tgamma, ty, rows, hidden, st);
+}
+
+namespace {
+int softmax_family(int mode, const void* z, const void* t, const void* rowscale, const void* add, void* out, void* out_row,
+                   int64_t rows, int64_t hidden, int dtype, agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    if (rows == 0) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(z, "z", elem));
+    AGB_TRY(check_ptr(t, "t", elem, mode == 3));
+    AGB_TRY(check_ptr(rowscale, "gy", elem, mode == 2));
+    AGB_TRY(check_ptr(add, "add", elem, false));
+    AGB_TRY(check_ptr(out, "out", elem, mode == 0 || mode == 2));
+    AGB_TRY(check_ptr(out_row, "out", elem, mode == 1 || mode == 3));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == AGB_F32 ? launch_softmax_fwd<float>(mode, z, t, rowscale, add, out, out_row, rows, hidden, st)
+                            : launch_softmax_fwd<bf16>(mode, z, t, rowscale, add, out, out_row, rows, hidden, st);
+}
+}  // namespace
+
+int agb_softmax_row_fwd(const void* z, void* y, int64_t rows, int64_t hidden, int dtype, agb_stream_t stream) {
+    return softmax_family(0, z, nullptr, nullptr, nullptr, y, nullptr, rows, hidden, dtype, stream);
+}
+int agb_logsumexp_row_fwd(const void* z, void* out, int64_t rows, int64_t hidden, int dtype, agb_stream_t stream) {
+    return softmax_family(1, z, nullptr, nullptr, nullptr, nullptr, out, rows, hidden, dtype, stream);
+}
+int agb_logsumexp_row_bwd(const void* z, const void* gy, const void* dz_add, void* dz, int64_t rows, int64_t hidden,
+                          int dtype, agb_stream_t stream) {
+    return softmax_family(2, z, nullptr, gy, dz_add, dz, nullptr, rows, hidden, dtype, stream);
+}
+int agb_logsumexp_row_jvp(const void* z, const void* tz, void* out, int64_t rows, int64_t hidden, int dtype,
+                          agb_stream_t stream) {
+    return softmax_family(3, z, tz, nullptr, nullptr, nullptr, out, rows, hidden, dtype, stream);
+}
+int agb_softmax_row_bwd(const void* y, const void* g, const void* dz_add, void* dz, int64_t rows, int64_t hidden,
+                        int dtype, agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    if (rows == 0) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(y, "y", elem));
+    AGB_TRY(check_ptr(g, "g", elem));
+    AGB_TRY(check_ptr(dz, "dz", elem));
+    AGB_TRY(check_ptr(dz_add, "dz_add", elem, false));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == AGB_F32 ? launch_softmax_bwd<float>(y, g, dz_add, dz, rows, hidden, st)
+                            : launch_softmax_bwd<bf16>(y, g, dz_add, dz, rows, hidden, st);
 }
 
 int agb_residual_add(const void* a, const void* b, void* out, int64_t n, int dtype, agb_stream_t stream) {

@@ -1,0 +1,430 @@
+// softmax_staged.cuh -- row softmax / logsumexp over the last axis and their rules, on the same
+// skeleton as the RMSNorm kernels: persistent CTAs, rows brought into a shared-memory ring by the bulk
+// asynchronous copy engine (no multicast), bounded mbarrier waits, fp64 reductions rounded once, 16-byte
+// streaming stores.
+//
+// Rounding follows the reference's composition op by op (cgadimpl/src/ops/reduction.cpp:42-66):
+//   m = max(z) ; zs = z - m (fp32) ; e = exp(zs) (fp32) ; s = (float)sum_fp64(e) ; y = e / s (IEEE fp32)
+//   logsumexp = log(s) + m
+// exp and log are evaluated in fp64 and rounded to fp32 once, i.e. correctly rounded except for
+// astronomically rare double-rounding ties; a correctly rounded C library expf gives the same bits.
+#pragma once
+#include <math.h>
+
+#include "rmsnorm_staged.cuh"
+
+namespace agb {
+
+// ---------------------------------------------------------------- exp / log, fp64 inside
+// exp(x) for x <= 0 as a float: x = (k/32) ln2 + r, |r| <= ln2/64; exp(r) by a degree-5 Taylor
+// polynomial (truncation 2e-15 relative), 2^(j/32) from a 32-entry table, 2^(k>>5) by an exponent add.
+constexpr int kExpTableSize = 32;
+__device__ __forceinline__ void init_exp_table(double* tab) {
+    if (threadIdx.x < kExpTableSize) tab[threadIdx.x] = exp2(static_cast<double>(threadIdx.x) / kExpTableSize);
+}
+__device__ __forceinline__ float exp_nonpositive(float x, const double* tab) {
+    // below -104 the result is under half the smallest subnormal float: exactly 0 after rounding
+    const double xd = static_cast<double>(fmaxf(x, -104.0f));
+    const double kMagic = 6755399441055744.0;  // 1.5 * 2^52: adding it rounds to an integer in the low word
+    const double t = fma(xd, 0x1.71547652b82fep+5 /* 32/ln2 */, kMagic);
+    const int ki = __double2loint(t);
+    const double kd = t - kMagic;
+    double r = fma(kd, -0x1.62e42fe000000p-6 /* ln2/32, high 28 bits: kd * this is exact */, xd);
+    r = fma(kd, -0x1.f473de6af278fp-35 /* ln2/32, rest */, r);
+    double p = fma(r, 1.0 / 120.0, 1.0 / 24.0);
+    p = fma(p, r, 1.0 / 6.0);
+    p = fma(p, r, 0.5);
+    p = fma(p, r, 1.0);
+    p = fma(p, r, 1.0);
+    const double s = p * tab[ki & (kExpTableSize - 1)];
+    // times 2^(ki >> 5): the double stays normal (exponent >= -151), the float conversion does the rest
+    const double scaled = __hiloint2double(__double2hiint(s) + (ki >> 5) * (1 << 20), __double2loint(s));
+    return static_cast<float>(scaled);
+}
+__device__ __forceinline__ float log_rounded(float s) { return static_cast<float>(log(static_cast<double>(s))); }
+
+// a / d for one divisor per row.  Three instructions (see DivConst) while the quotient is safely
+// normal; the general division otherwise (subnormal quotients of masked logits).
+struct RowDiv {
+    float d, dinv;
+    __device__ __forceinline__ float operator()(float a) const {
+        const float q0 = __fmul_rn(a, dinv);
+        if (!(q0 > 1e-30f && q0 < 1e30f)) return __fdiv_rn(a, d);
+        const float r = __fmaf_rn(-q0, d, a);
+        return __fmaf_rn(r, dinv, q0);
+    }
+};
+
+__device__ __forceinline__ RowDiv make_row_div(float divisor) { return RowDiv{divisor, __frcp_rn(divisor)}; }
+
+__device__ __forceinline__ void fence_generic_to_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ float group_max(const float* s_red, int wpr, int lane) {
+    return warp_max(lane < wpr ? s_red[lane] : -INFINITY);
+}
+
+// ------------------------------------------------------------------------------------------
+// Forward family.  MODE 0: out = softmax(z).  1: out_row = logsumexp(z).  2: out = rowscale * softmax(z)
+// [+ add]  (the logsumexp VJP).  3: out_row = sum(softmax(z) * t)  (the logsumexp JVP; t is staged next
+// to z).  e is parked in shared memory between the passes: in place over z for fp32, in a scratch
+// region of the stage (two row-widths) for bf16.
+// ------------------------------------------------------------------------------------------
+struct SoftmaxArgs {
+    PipeGeom g;
+    const void* z;
+    const void* t;         // MODE 3
+    const void* rowscale;  // MODE 2: [rows] of T
+    const void* add;       // MODE 2, nullable: [rows, hidden] added to the result (gradient accumulation)
+    void* out;             // [rows, hidden]
+    void* out_row;         // [rows] of T
+    int scratch_offset;    // bytes from the start of a stage to the fp32 scratch (0: in place over z)
+};
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_constant__ SoftmaxArgs a) {
+    constexpr int EPV = Vec<T>::EPV;
+    constexpr int NARR = MODE == 3 ? 2 : 1;
+    constexpr bool kThreePasses = MODE != 1;
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ double s_exp[kExpTableSize];
+    const PipeGeom& g = a.g;
+    unsigned char* ring = smem;
+    double* s_red = reinterpret_cast<double*>(smem + g.off_red);
+    uint64_t* s_full = reinterpret_cast<uint64_t*>(smem + g.off_bar);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + g.off_flag);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const int G = g.group_threads, wpr = G >> 5;
+    const int grp = tid / G, tig = tid - grp * G;
+    const int S = g.stages;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) mbar_init(&s_full[s], 1);
+        *s_abort = 0;
+        mbar_fence_init();
+    }
+    init_exp_table(s_exp);
+    __syncthreads();
+
+    const unsigned char* const src2[2] = {reinterpret_cast<const unsigned char*>(a.z),
+                                          reinterpret_cast<const unsigned char*>(a.t)};
+    auto issue = [&](long long tile, int slot) {
+        if (NARR == 2) issue_tile<2>(g, ring, s_full, src2, tile, slot);
+        else issue_tile<1>(g, ring, s_full, reinterpret_cast<const unsigned char* const(&)[1]>(src2), tile, slot);
+    };
+    const long long first = blockIdx.x, stride = gridDim.x;
+    const long long my_tiles = g.ntiles > first ? (g.ntiles - first + stride - 1) / stride : 0;
+    long long issued = 0;
+    if (tid == 0)
+        for (; issued < my_tiles && issued < S; ++issued) issue(first + issued * stride, static_cast<int>(issued));
+
+    long long k = 0;
+    bool aborted = false;
+    for (; k < my_tiles; ++k) {
+        const int slot = static_cast<int>(k % S);
+        const uint32_t parity = static_cast<uint32_t>((k / S) & 1);
+        const long long row = (first + k * stride) * g.rows_per_tile + grp;
+        const bool valid = row < g.rows;
+        if (!mbar_wait_bounded(&s_full[slot], parity)) *s_abort = 1;
+
+        unsigned char* stage = ring + static_cast<size_t>(slot) * g.stage_stride;
+        const uint4* sz = reinterpret_cast<const uint4*>(stage + static_cast<size_t>(grp) * g.row_bytes);
+        const uint4* st = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(sz) + g.tile_stride);
+        // fp32 e of this row: EPV floats (EPV/4 vectors) per input vector
+        float4* se = a.scratch_offset
+                         ? reinterpret_cast<float4*>(stage + a.scratch_offset + static_cast<size_t>(grp) * g.hidden * 4)
+                         : reinterpret_cast<float4*>(stage + static_cast<size_t>(grp) * g.row_bytes);
+        double* red = s_red + (k & 1) * 4 * nwarps;
+        float* redf = reinterpret_cast<float*>(red);
+
+        // pass 1: row maximum
+        float m = -INFINITY;
+        if (valid)
+            for (int v = tig; v < g.nvec; v += G) {
+                float f[EPV];
+                Vec<T>::unpack(sz[v], f);
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) m = fmaxf(m, f[e]);
+            }
+        m = warp_max(m);
+        if (lane == 0) redf[warp] = m;
+        __syncthreads();
+        if (*s_abort) { aborted = true; break; }
+        // every thread is past the last pass of the previous tile: its slot can be refilled
+        if (kThreePasses && tid == 0 && k >= 1 && issued < my_tiles) {
+            issue(first + issued * stride, static_cast<int>((k - 1) % S));
+            ++issued;
+        }
+        const float mx = group_max(redf + grp * wpr, wpr, lane);
+
+        // pass 2: e = exp(z - max), its sum in fp64
+        double d0 = 0.0, d1 = 0.0;
+        if (valid)
+            for (int v = tig; v < g.nvec; v += G) {
+                float f[EPV];
+                Vec<T>::unpack(sz[v], f);
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) f[e] = exp_nonpositive(sub_rn(f[e], mx), s_exp);
+#pragma unroll
+                for (int e = 0; e < EPV; e += 2) {
+                    d0 += static_cast<double>(f[e]);
+                    d1 += static_cast<double>(f[e + 1]);
+                }
+                if (kThreePasses) {
+#pragma unroll
+                    for (int q = 0; q < EPV / 4; ++q)
+                        se[v * (EPV / 4) + q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+                }
+            }
+        const double dsum = warp_sum(d0 + d1);
+        if (lane == 0) red[nwarps + warp] = dsum;
+        if (kThreePasses) fence_generic_to_async_smem();  // the slot this thread wrote is refilled by the copy engine later
+        __syncthreads();
+        if (!kThreePasses && tid == 0 && issued < my_tiles) {  // nobody reads the slot again
+            issue(first + issued * stride, slot);
+            ++issued;
+        }
+        const float s = static_cast<float>(group_total(red + nwarps + grp * wpr, wpr, lane));
+
+        if (MODE == 1) {
+            if (valid && tig == 0) Vec<T>::store1(static_cast<T*>(a.out_row) + row, add_rn(log_rounded(s), mx));
+            continue;
+        }
+
+        // pass 3: y = e / s and what the mode makes of it
+        const RowDiv div_s = make_row_div(s);
+        const float scale = (MODE == 2 && valid) ? Vec<T>::load1(static_cast<const T*>(a.rowscale) + row) : 0.0f;
+        double j0 = 0.0, j1 = 0.0;
+        if (valid) {
+            uint4* gout = MODE == 3 ? nullptr : reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.out) + row * g.row_bytes);
+            const uint4* gadd = (MODE == 2 && a.add)
+                                    ? reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(a.add) + row * g.row_bytes)
+                                    : nullptr;
+            for (int v = tig; v < g.nvec; v += G) {
+                float f[EPV];
+#pragma unroll
+                for (int q = 0; q < EPV / 4; ++q) {
+                    const float4 e4 = se[v * (EPV / 4) + q];
+                    f[4 * q] = e4.x; f[4 * q + 1] = e4.y; f[4 * q + 2] = e4.z; f[4 * q + 3] = e4.w;
+                }
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) f[e] = div_s(f[e]);
+                if (MODE == 2) {
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) f[e] = mul_rn(scale, f[e]);
+                    if (gadd) {
+                        float ad[EPV];
+                        Vec<T>::unpack(gadd[v], ad);
+#pragma unroll
+                        for (int e = 0; e < EPV; ++e) f[e] = add_rn(ad[e], f[e]);
+                    }
+                }
+                if (MODE == 3) {
+                    float tv[EPV];
+                    Vec<T>::unpack(st[v], tv);
+#pragma unroll
+                    for (int e = 0; e < EPV; e += 2) {
+                        j0 += static_cast<double>(mul_rn(f[e], tv[e]));
+                        j1 += static_cast<double>(mul_rn(f[e + 1], tv[e + 1]));
+                    }
+                } else {
+                    store_vec_streaming(gout + v, Vec<T>::pack(f));
+                }
+            }
+        }
+        if (MODE == 3) {
+            const double jsum = warp_sum(j0 + j1);
+            if (lane == 0) red[2 * nwarps + warp] = jsum;
+            __syncthreads();
+            const float tot = static_cast<float>(group_total(red + 2 * nwarps + grp * wpr, wpr, lane));
+            if (valid && tig == 0) Vec<T>::store1(static_cast<T*>(a.out_row) + row, tot);
+        }
+    }
+    if (aborted && tid == 0) drain_after_abort(g, s_full, k, issued);
+}
+
+// ------------------------------------------------------------------------------------------
+// out = y * (g - sum(y * g)) [+ add]: the softmax VJP (g = gy) and JVP (g = tangent),
+// cgadimpl/src/autodiff/autodiff_vjp_ops.cpp:421-428 and autodiff_jvp_ops.cpp:411-420.
+// ------------------------------------------------------------------------------------------
+struct SoftmaxBwdArgs {
+    PipeGeom g;
+    const void* y;
+    const void* gr;
+    const void* add;  // nullable
+    void* out;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(1024, 1) softmax_bwd_staged(const __grid_constant__ SoftmaxBwdArgs a) {
+    constexpr int NP = Pairs<T>::NP;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const PipeGeom& g = a.g;
+    unsigned char* ring = smem;
+    double* s_red = reinterpret_cast<double*>(smem + g.off_red);
+    uint64_t* s_full = reinterpret_cast<uint64_t*>(smem + g.off_bar);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + g.off_flag);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const int G = g.group_threads, wpr = G >> 5;
+    const int grp = tid / G, tig = tid - grp * G;
+    const int S = g.stages;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) mbar_init(&s_full[s], 1);
+        *s_abort = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const unsigned char* const src2[2] = {reinterpret_cast<const unsigned char*>(a.y),
+                                          reinterpret_cast<const unsigned char*>(a.gr)};
+    const long long first = blockIdx.x, stride = gridDim.x;
+    const long long my_tiles = g.ntiles > first ? (g.ntiles - first + stride - 1) / stride : 0;
+    long long issued = 0;
+    if (tid == 0)
+        for (; issued < my_tiles && issued < S; ++issued)
+            issue_tile<2>(g, ring, s_full, src2, first + issued * stride, static_cast<int>(issued));
+
+    long long k = 0;
+    bool aborted = false;
+    for (; k < my_tiles; ++k) {
+        const int slot = static_cast<int>(k % S);
+        const uint32_t parity = static_cast<uint32_t>((k / S) & 1);
+        const long long row = (first + k * stride) * g.rows_per_tile + grp;
+        const bool valid = row < g.rows;
+        if (!mbar_wait_bounded(&s_full[slot], parity)) *s_abort = 1;
+        const unsigned char* base = ring + static_cast<size_t>(slot) * g.stage_stride + static_cast<size_t>(grp) * g.row_bytes;
+        const uint4* sy = reinterpret_cast<const uint4*>(base);
+        const uint4* sg = reinterpret_cast<const uint4*>(base + g.tile_stride);
+
+        double d[4] = {0.0, 0.0, 0.0, 0.0};
+        if (valid) {
+#pragma unroll 2
+            for (int v = tig; v < g.nvec; v += G) {
+                float2 yv[NP], gv[NP];
+                Pairs<T>::unpack(sy[v], yv);
+                Pairs<T>::unpack(sg[v], gv);
+#pragma unroll
+                for (int e = 0; e < NP; ++e) {
+                    const float2 p = mul2(yv[e], gv[e]);
+                    d[(2 * e) & 3] += static_cast<double>(p.x);
+                    d[(2 * e + 1) & 3] += static_cast<double>(p.y);
+                }
+            }
+        }
+        const double dsum = warp_sum((d[0] + d[1]) + (d[2] + d[3]));
+        if (lane == 0) s_red[(k & 1) * nwarps + warp] = dsum;
+        __syncthreads();
+        if (*s_abort) { aborted = true; break; }
+        if (tid == 0 && k >= 1 && issued < my_tiles) {
+            issue_tile<2>(g, ring, s_full, src2, first + issued * stride, static_cast<int>((k - 1) % S));
+            ++issued;
+        }
+        const float dot = static_cast<float>(group_total(s_red + (k & 1) * nwarps + grp * wpr, wpr, lane));
+        const float2 dot2 = splat(dot);
+
+        if (valid) {
+            uint4* gout = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.out) + row * g.row_bytes);
+            const uint4* gadd =
+                a.add ? reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(a.add) + row * g.row_bytes) : nullptr;
+#pragma unroll 2
+            for (int v = tig; v < g.nvec; v += G) {
+                float2 yv[NP], gv[NP];
+                Pairs<T>::unpack(sy[v], yv);
+                Pairs<T>::unpack(sg[v], gv);
+#pragma unroll
+                for (int e = 0; e < NP; ++e) yv[e] = mul2(yv[e], sub2(gv[e], dot2));  // g - dot: neither is a product
+                if (gadd) {
+                    float2 av[NP];
+                    Pairs<T>::unpack(gadd[v], av);
+#pragma unroll
+                    for (int e = 0; e < NP; ++e) yv[e] = add2_after_mul(av[e], yv[e]);
+                }
+                store_vec_streaming(gout + v, Pairs<T>::pack(yv));
+            }
+        }
+    }
+    if (aborted && tid == 0) drain_after_abort(g, s_full, k, issued);
+}
+
+// ------------------------------------------------------------------------------------------
+// Unstaged versions: any hidden size, element-aligned pointers.  One CTA of 256 threads per row;
+// e is recomputed in the last pass instead of being parked (same bits: exp is a pure function).
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float block_max_256(float v, float* scratch, int phase) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_max(v);
+    float* s = scratch + (phase & 1) * 8;
+    if (lane == 0) s[warp] = v;
+    __syncthreads();
+    float t = s[0];
+#pragma unroll
+    for (int w = 1; w < kGenericThreads / 32; ++w) t = fmaxf(t, s[w]);
+    return t;
+}
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kGenericThreads) softmax_fwd_generic(const T* __restrict__ z, const T* __restrict__ t,
+                                                                       const T* __restrict__ rowscale, const T* add,
+                                                                       T* out, T* __restrict__ out_row, long long rows,
+                                                                       int hidden) {
+    __shared__ double scratch[32];
+    __shared__ float scratch_f[16];
+    __shared__ double s_exp[kExpTableSize];
+    init_exp_table(s_exp);
+    __syncthreads();
+    int phase = 0;
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x, ++phase) {
+        const T* zr = z + row * hidden;
+        float m = -INFINITY;
+        for (int j = threadIdx.x; j < hidden; j += kGenericThreads) m = fmaxf(m, Vec<T>::load1(zr + j));
+        const float mx = block_max_256(m, scratch_f, phase);
+        double d = 0.0;
+        for (int j = threadIdx.x; j < hidden; j += kGenericThreads)
+            d += static_cast<double>(exp_nonpositive(sub_rn(Vec<T>::load1(zr + j), mx), s_exp));
+        const float s = static_cast<float>(block_sum_256(d, scratch, phase));
+        if (MODE == 1) {
+            if (threadIdx.x == 0) Vec<T>::store1(out_row + row, add_rn(log_rounded(s), mx));
+            continue;
+        }
+        const RowDiv div_s = make_row_div(s);
+        const float scale = MODE == 2 ? Vec<T>::load1(rowscale + row) : 0.0f;
+        double jd = 0.0;
+        for (int j = threadIdx.x; j < hidden; j += kGenericThreads) {
+            float y = div_s(exp_nonpositive(sub_rn(Vec<T>::load1(zr + j), mx), s_exp));
+            if (MODE == 2) {
+                y = mul_rn(scale, y);
+                if (add) y = add_rn(Vec<T>::load1(add + row * hidden + j), y);
+            }
+            if (MODE == 3) jd += static_cast<double>(mul_rn(y, Vec<T>::load1(t + row * hidden + j)));
+            else Vec<T>::store1(out + row * hidden + j, y);
+        }
+        if (MODE == 3) {
+            const float tot = static_cast<float>(block_sum_256(jd, scratch + 16, phase));
+            if (threadIdx.x == 0) Vec<T>::store1(out_row + row, tot);
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kGenericThreads) softmax_bwd_generic(const T* __restrict__ y, const T* __restrict__ gr,
+                                                                       const T* add, T* out, long long rows, int hidden) {
+    __shared__ double scratch[16];
+    int phase = 0;
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x, ++phase) {
+        const T* yr = y + row * hidden;
+        const T* gg = gr + row * hidden;
+        double d = 0.0;
+        for (int j = threadIdx.x; j < hidden; j += kGenericThreads)
+            d += static_cast<double>(mul_rn(Vec<T>::load1(yr + j), Vec<T>::load1(gg + j)));
+        const float dot = static_cast<float>(block_sum_256(d, scratch, phase));
+        for (int j = threadIdx.x; j < hidden; j += kGenericThreads) {
+            float o = mul_rn(Vec<T>::load1(yr + j), sub_rn(Vec<T>::load1(gg + j), dot));
+            if (add) o = add_rn(Vec<T>::load1(add + row * hidden + j), o);
+            Vec<T>::store1(out + row * hidden + j, o);
+        }
+    }
+}
+
+}  // namespace agb

@@ -148,6 +148,45 @@ def layernorm_bwd(x, mean, var, gy, eps=1e-5, dx_add=None, dx=None):
     return dx
 
 
+def softmax_row(z, out=None):
+    """cgadimpl's softmax_row: softmax over the last axis."""
+    rows, hidden = _rows_hidden(z)
+    y = torch.empty_like(z) if out is None else out
+    check(_lib.lib().agb_softmax_row_fwd(_p(z), _p(y), rows, hidden, _dt(z), _stream()))
+    return y
+
+
+def logsumexp_row(z, out=None):
+    """cgadimpl's logsumexp_row: [rows] (same dtype as z)."""
+    rows, hidden = _rows_hidden(z)
+    o = torch.empty(rows, dtype=z.dtype, device=z.device) if out is None else out
+    check(_lib.lib().agb_logsumexp_row_fwd(_p(z), _p(o), rows, hidden, _dt(z), _stream()))
+    return o
+
+
+def softmax_row_bwd(y, g, dz_add=None, dz=None):
+    """y * (g - sum(y*g)) [+ dz_add]: the softmax VJP (g = gy) and JVP (g = tangent)."""
+    rows, hidden = _rows_hidden(y)
+    dz = torch.empty_like(y) if dz is None else dz
+    check(_lib.lib().agb_softmax_row_bwd(_p(y), _p(g), _p(dz_add), _p(dz), rows, hidden, _dt(y), _stream()))
+    return dz
+
+
+def logsumexp_row_bwd(z, gy, dz_add=None, dz=None):
+    """gy[rows] * softmax(z) [+ dz_add]."""
+    rows, hidden = _rows_hidden(z)
+    dz = torch.empty_like(z) if dz is None else dz
+    check(_lib.lib().agb_logsumexp_row_bwd(_p(z), _p(gy), _p(dz_add), _p(dz), rows, hidden, _dt(z), _stream()))
+    return dz
+
+
+def logsumexp_row_jvp(z, tz, out=None):
+    rows, hidden = _rows_hidden(z)
+    o = torch.empty(rows, dtype=z.dtype, device=z.device) if out is None else out
+    check(_lib.lib().agb_logsumexp_row_jvp(_p(z), _p(tz), _p(o), rows, hidden, _dt(z), _stream()))
+    return o
+
+
 def sgd_step(param, grad, lr):
     """param += -lr * grad, as ag::SGD updates a leaf."""
     check(_lib.lib().agb_sgd_step(_p(param), _p(grad), param.numel(), float(lr), _dt(param), _stream()))

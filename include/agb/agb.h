@@ -200,6 +200,29 @@ int agb_layernorm_fwd(const void* x, void* y, float* mean, float* var, int64_t r
 int agb_layernorm_bwd(const void* x, const float* mean, const float* var, const void* gy, const void* dx_add,
                       void* dx, int64_t rows, int64_t hidden, float eps, int dtype, agb_stream_t stream);
 
+/* ---- row softmax / logsumexp over the last axis and their rules ----
+ * agb_softmax_row_fwd replaces softmax_row_nodeops (cgadimpl/src/ops/reduction.cpp:42-53):
+ *   m = max_j z; e = exp(z - m); s = sum_j e; y = e / s.
+ * agb_logsumexp_row_fwd replaces logsumexp_row_nodeops (reduction.cpp:54-66): out[rows] = log(s) + m.
+ * agb_softmax_row_bwd is vjp_SoftmaxRow (autodiff_vjp_ops.cpp:421-428) with g = gy AND jvp_SoftmaxRow
+ *   (autodiff_jvp_ops.cpp:411-420) with g = the tangent of z -- the same expression:
+ *   dz = y * (g - sum_j y*g)  [+ dz_add; dz_add may alias dz: gradient accumulation in place].
+ * agb_logsumexp_row_bwd replaces vjp_LogSumExpRow (autodiff_vjp_ops.cpp:430-440): softmax(z) is
+ *   recomputed; dz = gy[rows] * softmax(z) [+ dz_add].
+ * agb_logsumexp_row_jvp replaces jvp_LogSumExpRow (autodiff_jvp_ops.cpp:421-434):
+ *   out[rows] = sum_j softmax(z) * tz.
+ * Row statistics ([rows] arrays: out, gy) have the element type of z.  exp and log are evaluated in
+ * fp64 and rounded to fp32 once; every other step rounds where the reference materialises a tensor,
+ * and the sums are carried in fp64. */
+int agb_softmax_row_fwd(const void* z, void* y, int64_t rows, int64_t hidden, int dtype, agb_stream_t stream);
+int agb_logsumexp_row_fwd(const void* z, void* out, int64_t rows, int64_t hidden, int dtype, agb_stream_t stream);
+int agb_softmax_row_bwd(const void* y, const void* g, const void* dz_add, void* dz, int64_t rows, int64_t hidden,
+                        int dtype, agb_stream_t stream);
+int agb_logsumexp_row_bwd(const void* z, const void* gy, const void* dz_add, void* dz, int64_t rows, int64_t hidden,
+                          int dtype, agb_stream_t stream);
+int agb_logsumexp_row_jvp(const void* z, const void* tz, void* out, int64_t rows, int64_t hidden, int dtype,
+                          agb_stream_t stream);
+
 /* ---- optimiser steps on the layer's parameters ----
  * agb_sgd_step: ag::SGD's update of one leaf, `value += -learning_rate * grad`
  *   (cgadimpl/src/optimizer/optim.cpp:12-19).

@@ -603,3 +603,87 @@ void agb_oracle_layernorm_vjp(const float* x, const float* mean, const float* va
     }
     free(xm); free(t); free(std_inv); free(c3); free(d_var); free(s1); free(s2); free(d_mean);
 }
+
+/* ------------------------------------------------------------------ row softmax / logsumexp */
+
+void ot_exp(const float* a, float* out, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = expf(a[i]);
+}
+void ot_log(const float* a, float* out, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = logf(a[i]);
+}
+void ot_sub_rowstat(const float* a, const float* s, float* out, int64_t R, int64_t H) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r)
+        for (int64_t j = 0; j < H; ++j) out[r * H + j] = a[r * H + j] - s[r];
+}
+void ot_div_rowstat(const float* a, const float* s, float* out, int64_t R, int64_t H) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r)
+        for (int64_t j = 0; j < H; ++j) out[r * H + j] = a[r * H + j] / s[r];
+}
+
+/* The shared opening of softmax_row_nodeops / logsumexp_row_nodeops (and of the two logsumexp rules):
+ *   max = reduce_max(z,{-1},true); zs = z - max; e = exp(zs); s = reduce_sum(e,{-1},true)            */
+static void softmax_parts(const float* z, float* e, float* mx, float* s, int64_t R, int64_t H, int red) {
+    float* zs = falloc(R * H);
+    ot_reduce_max_last(z, mx, R, H);
+    ot_sub_rowstat(z, mx, zs, R, H);
+    ot_exp(zs, e, R * H);
+    ot_reduce_sum_last(e, s, R, H, red);
+    free(zs);
+}
+
+/* softmax_row_nodeops, cgadimpl/src/ops/reduction.cpp:42-53: y = e / s */
+void agb_oracle_softmax_row_forward(const float* z, float* y, int64_t R, int64_t H, int red) {
+    float* e = falloc(R * H);
+    float* mx = falloc(R);
+    float* s = falloc(R);
+    softmax_parts(z, e, mx, s, R, H, red);
+    ot_div_rowstat(e, s, y, R, H);
+    free(e); free(mx); free(s);
+}
+
+/* logsumexp_row_nodeops, cgadimpl/src/ops/reduction.cpp:54-66: y[R] = log(s) + max */
+void agb_oracle_logsumexp_row_forward(const float* z, float* out, int64_t R, int64_t H, int red) {
+    float* e = falloc(R * H);
+    float* mx = falloc(R);
+    float* s = falloc(R);
+    softmax_parts(z, e, mx, s, R, H, red);
+    ot_log(s, s, R);
+    ot_add(s, mx, out, R);
+    free(e); free(mx); free(s);
+}
+
+/* vjp_SoftmaxRow, autodiff_vjp_ops.cpp:421-428, and jvp_SoftmaxRow, autodiff_jvp_ops.cpp:411-420, are
+ * the same expression in (y, gy) and (y, tZ):  dot = reduce_sum(y * g, {-1}, true);  out = y * (g - dot) */
+void agb_oracle_softmax_row_vjp(const float* y, const float* g, float* out, int64_t R, int64_t H, int red) {
+    float* p = falloc(R * H);
+    float* dot = falloc(R);
+    ot_mul(y, g, p, R * H);
+    ot_reduce_sum_last(p, dot, R, H, red);
+    ot_sub_rowstat(g, dot, p, R, H);
+    ot_mul(y, p, out, R * H);
+    free(p); free(dot);
+}
+
+/* vjp_LogSumExpRow, autodiff_vjp_ops.cpp:430-440: softmax recomputed from z; dz = gy[R,1] * softmax */
+void agb_oracle_logsumexp_row_vjp(const float* z, const float* gy, float* dz, int64_t R, int64_t H, int red) {
+    float* y = falloc(R * H);
+    agb_oracle_softmax_row_forward(z, y, R, H, red);
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r)
+        for (int64_t j = 0; j < H; ++j) dz[r * H + j] = gy[r] * y[r * H + j];
+    free(y);
+}
+
+/* jvp_LogSumExpRow, autodiff_jvp_ops.cpp:421-434: softmax recomputed; out[R] = reduce_sum(softmax * tZ) */
+void agb_oracle_logsumexp_row_jvp(const float* z, const float* tz, float* out, int64_t R, int64_t H, int red) {
+    float* y = falloc(R * H);
+    agb_oracle_softmax_row_forward(z, y, R, H, red);
+    ot_mul(y, tz, y, R * H);
+    ot_reduce_sum_last(y, out, R, H, red);
+    free(y);
+}

@@ -134,6 +134,20 @@ void agb_oracle_layernorm_forward(const float* x, float* y, float* mean, float* 
 void agb_oracle_layernorm_vjp(const float* x, const float* mean, const float* var, const float* gy, float* dx,
                               int64_t R, int64_t H, float eps, int red);
 
+/* Row softmax / logsumexp over the last axis: cgadimpl/src/ops/reduction.cpp:42-66, rules
+ * autodiff_vjp_ops.cpp:421-440 and autodiff_jvp_ops.cpp:411-434.  exp / log are the C library's expf /
+ * logf, as in the stand-in tensor library the reference is compiled over.  softmax_row_vjp is also
+ * the JVP (same expression with the tangent in place of gy).  gy / out of the logsumexp rules are [R]. */
+void ot_exp(const float* a, float* out, int64_t n);
+void ot_log(const float* a, float* out, int64_t n);
+void ot_sub_rowstat(const float* a, const float* s, float* out, int64_t R, int64_t H);
+void ot_div_rowstat(const float* a, const float* s, float* out, int64_t R, int64_t H);
+void agb_oracle_softmax_row_forward(const float* z, float* y, int64_t R, int64_t H, int red);
+void agb_oracle_logsumexp_row_forward(const float* z, float* out, int64_t R, int64_t H, int red);
+void agb_oracle_softmax_row_vjp(const float* y, const float* g, float* out, int64_t R, int64_t H, int red);
+void agb_oracle_logsumexp_row_vjp(const float* z, const float* gy, float* dz, int64_t R, int64_t H, int red);
+void agb_oracle_logsumexp_row_jvp(const float* z, const float* tz, float* out, int64_t R, int64_t H, int red);
+
 /* Optimiser steps on a parameter: cgadimpl/src/optimizer/optim.cpp:12-19 (SGD), :33-72 (Adam). */
 void agb_oracle_sgd_step(float* param, const float* grad, int64_t n, float lr);
 void agb_oracle_adam_step(float* param, const float* grad, float* m, float* v, int64_t n, float alpha, float beta1,

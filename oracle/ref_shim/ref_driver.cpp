@@ -208,6 +208,29 @@ int cgadimpl_ref_layernorm_fwd_bwd(const float* x, const float* gy, float* y, fl
     }
 }
 
+// softmax_row (which 0) / logsumexp_row (which 1) through the reference's own builders and rules.
+// gy and t are [R,H] for softmax and [R] / [R,H] for logsumexp; y, ty are [R,H] or [R] accordingly.
+// The JVP rule is called directly (the engine overwrites leaf seeds, see cgadimpl_ref_rms_jvp).
+int cgadimpl_ref_softmax_family(int which, const float* z, const float* gy, const float* t, float* y, float* dz, float* ty,
+                                int64_t R, int64_t H) {
+    try {
+        auto Z = leaf(from_host(z, {R, H}, true), "z");
+        auto n = which == 0 ? detail::softmax_row_nodeops(Z) : detail::logsumexp_row_nodeops(Z);
+        Tensor seed = which == 0 ? from_host(gy, {R, H}, false) : from_host(gy, {R, 1}, false);
+        backward(Value(n), &seed, false);
+        to_host(n->value, y);
+        to_host(Z->grad, dz);
+        Tensor tangent = from_host(t, {R, H}, false);
+        std::function<const Tensor&(Node*)> tangent_of = [&](Node*) -> const Tensor& { return tangent; };
+        Tensor tv = jvp_lookup(which == 0 ? Op::SoftmaxRow : Op::LogSumExpRow)(n.get(), tangent_of);
+        to_host(tv, ty);
+        return 0;
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "cgadimpl_ref: %s\n", e.what());
+        return 1;
+    }
+}
+
 // `steps` optimiser updates of one parameter vector with given gradients grads[steps, n], through
 // the reference's own ag::SGD / ag::Adam (cgadimpl/src/optimizer/optim.cpp).  which: 0 SGD, 1 Adam.
 int cgadimpl_ref_optimizer(int which, float* param, const float* grads, int64_t n, int steps, float lr_or_alpha) {

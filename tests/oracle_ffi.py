@@ -219,3 +219,44 @@ def layernorm_fwd_bwd(x, gy, eps, red=RED_F64):
     lib().agb_oracle_layernorm_forward(_f(x), _f(y), _f(mean), _f(var), C.c_int64(R), C.c_int64(H), C.c_float(eps), C.c_int(red))
     lib().agb_oracle_layernorm_vjp(_f(x), _f(mean), _f(var), _f(gy), _f(dx), C.c_int64(R), C.c_int64(H), C.c_float(eps), C.c_int(red))
     return dict(y=y, mean=mean, var=var, dx=dx)
+
+
+def softmax_row(z, red=RED_F64):
+    z = np.ascontiguousarray(z, np.float32)
+    R, H = z.shape
+    y = np.empty_like(z)
+    lib().agb_oracle_softmax_row_forward(_f(z), _f(y), C.c_int64(R), C.c_int64(H), C.c_int(red))
+    return y
+
+
+def logsumexp_row(z, red=RED_F64):
+    z = np.ascontiguousarray(z, np.float32)
+    R, H = z.shape
+    out = np.empty(R, np.float32)
+    lib().agb_oracle_logsumexp_row_forward(_f(z), _f(out), C.c_int64(R), C.c_int64(H), C.c_int(red))
+    return out
+
+
+def softmax_row_vjp(y, g, red=RED_F64):
+    """Also the JVP: the same expression with the tangent in place of gy."""
+    y, g = np.ascontiguousarray(y, np.float32), np.ascontiguousarray(g, np.float32)
+    R, H = y.shape
+    out = np.empty_like(y)
+    lib().agb_oracle_softmax_row_vjp(_f(y), _f(g), _f(out), C.c_int64(R), C.c_int64(H), C.c_int(red))
+    return out
+
+
+def logsumexp_row_vjp(z, gy, red=RED_F64):
+    z, gy = np.ascontiguousarray(z, np.float32), np.ascontiguousarray(gy, np.float32)
+    R, H = z.shape
+    dz = np.empty_like(z)
+    lib().agb_oracle_logsumexp_row_vjp(_f(z), _f(gy), _f(dz), C.c_int64(R), C.c_int64(H), C.c_int(red))
+    return dz
+
+
+def logsumexp_row_jvp(z, tz, red=RED_F64):
+    z, tz = np.ascontiguousarray(z, np.float32), np.ascontiguousarray(tz, np.float32)
+    R, H = z.shape
+    out = np.empty(R, np.float32)
+    lib().agb_oracle_logsumexp_row_jvp(_f(z), _f(tz), _f(out), C.c_int64(R), C.c_int64(H), C.c_int(red))
+    return out

@@ -116,3 +116,18 @@ def layernorm_fwd_bwd(x, gy):
     rc = lib().cgadimpl_ref_layernorm_fwd_bwd(_p(x), _p(gy), _p(y), _p(mean), _p(var), _p(dx), C.c_int64(R), C.c_int64(H))
     assert rc == 0
     return dict(y=y, mean=mean, var=var, dx=dx)
+
+
+def softmax_family(which, z, gy, t):
+    """softmax_row ('softmax') or logsumexp_row ('logsumexp') forward, VJP and JVP through the reference's
+    own builders and rules.  gy is [R,H] / [R]; returns y, dz, ty."""
+    z, gy, t = _c(z), _c(gy), _c(t)
+    R, H = z.shape
+    lse = which == "logsumexp"
+    y = np.empty(R if lse else (R, H), np.float32)
+    ty = np.empty(R if lse else (R, H), np.float32)
+    dz = np.empty_like(z)
+    rc = lib().cgadimpl_ref_softmax_family(C.c_int(1 if lse else 0), _p(z), _p(gy), _p(t), _p(y), _p(dz), _p(ty),
+                                           C.c_int64(R), C.c_int64(H))
+    assert rc == 0
+    return dict(y=y, dz=dz, ty=ty)

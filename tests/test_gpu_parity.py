@@ -462,3 +462,94 @@ def test_bounded_wait_expiry_is_reported_and_the_context_survives(ops):
     want = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-5)
     assert torch.allclose(y, want, rtol=1e-5, atol=1e-6)
     assert lib.agb_selftest_bounded_wait(0, None, None) == 1    # argument validation
+
+
+def _logits(rows, hidden, seed):
+    """Logit-like rows: N(0, 3), some rows with a masked tail (-1e4), some with one dominant entry."""
+    rng = np.random.default_rng(seed)
+    z = (3.0 * rng.standard_normal((rows, hidden))).astype(np.float32)
+    z[::3, hidden // 2:] = np.float32(-1e4)
+    z[1::5, 0] = np.float32(60.0)
+    return z
+
+
+@pytest.mark.parametrize("rows,hidden,dtype", [(4, 10, torch.float32), (2048, 4096, torch.float32), (33, 1000, torch.float32),
+                                               (9, 70000, torch.float32), (1024, 32000, torch.float32),
+                                               (300, 8192, torch.bfloat16), (129, 1000, torch.bfloat16),
+                                               (64, 50257, torch.bfloat16)])
+def test_softmax_and_logsumexp_rows(ops, rows, hidden, dtype):
+    """cgadimpl's softmax_row / logsumexp_row with their VJP and JVP rules against the oracle, which
+    tests/test_reference_build.py pins bit for bit to the reference's own builders and rules.  The only
+    place the CUDA path may differ from the oracle beyond rare double-rounding ties is exp / log: fp64
+    evaluation rounded once here, the C library's expf / logf (< 1 ulp, not always correctly rounded) there."""
+    z = _logits(rows, hidden, seed=rows + hidden)
+    rng = np.random.default_rng(11)
+    gy = rng.standard_normal((rows, hidden)).astype(np.float32)
+    gy_row = rng.standard_normal(rows).astype(np.float32)
+    t = rng.standard_normal((rows, hidden)).astype(np.float32)
+    bf = dtype == torch.bfloat16
+    rb = (lambda a: O.bf16_bits_to_f32(O.f32_to_bf16_bits(a))) if bf else (lambda a: a)
+    z, gy, gy_row, t = rb(z), rb(gy), rb(gy_row), rb(t)
+
+    y_ref = O.softmax_row(z)
+    lse_ref = O.logsumexp_row(z)
+    zd, gyd, gyrd, td = dev(z, dtype), dev(gy, dtype), dev(gy_row, dtype), dev(t, dtype)
+    y = ops.softmax_row(zd)
+    lse = ops.logsumexp_row(zd)
+    yh = host(y)
+    assert np.all(np.isfinite(yh)) and np.all(yh >= 0)
+    np.testing.assert_allclose(yh.astype(np.float64).sum(-1), 1.0, atol=2e-2 if bf else 1e-5)   # rows sum to one
+    if not bf:
+        assert_close(yh, y_ref, F32_RTOL, 1e-30, "softmax")          # relative even for the tiny masked entries
+        assert frac_bit_equal(yh, y_ref) >= 0.99
+        assert_close(host(lse), lse_ref, F32_RTOL, F32_ATOL, "logsumexp")
+        assert frac_bit_equal(host(lse), lse_ref) >= 0.99
+        # the rules, fed with the oracle's y so that only the rule itself is compared
+        yd = dev(y_ref)
+        dz = ops.softmax_row_bwd(yd, gyd)
+        want = O.softmax_row_vjp(y_ref, gy)
+        assert_close(host(dz), want, F32_RTOL, F32_ATOL, "softmax vjp")
+        assert frac_bit_equal(host(dz), want) >= 0.999
+        assert np.array_equal(host(ops.softmax_row_bwd(yd, td)), O.softmax_row_vjp(y_ref, t)) or \
+            frac_bit_equal(host(ops.softmax_row_bwd(yd, td)), O.softmax_row_vjp(y_ref, t)) >= 0.999      # the JVP
+        acc = dev(gy) * 0.5
+        assert np.array_equal(host(ops.softmax_row_bwd(yd, gyd, dz_add=acc)), host(acc) + host(dz))
+        inplace = acc.clone()
+        ops.softmax_row_bwd(yd, gyd, dz_add=inplace, dz=inplace)                                         # grad += in place
+        assert np.array_equal(host(inplace), host(acc) + host(dz))
+        dl = ops.logsumexp_row_bwd(zd, gyrd)
+        want = O.logsumexp_row_vjp(z, gy_row)
+        assert_close(host(dl), want, F32_RTOL, 1e-30, "logsumexp vjp")
+        assert frac_bit_equal(host(dl), want) >= 0.99
+        assert np.array_equal(host(ops.logsumexp_row_bwd(zd, gyrd, dz_add=acc)), host(acc) + host(dl))
+        jl = ops.logsumexp_row_jvp(zd, td)
+        assert_close(host(jl), O.logsumexp_row_jvp(z, t), F32_RTOL, F32_ATOL, "logsumexp jvp")
+        # softmax is the gradient of logsumexp: the VJP with gy = 1 is the forward
+        ones = torch.ones(rows, device="cuda")
+        assert np.array_equal(host(ops.logsumexp_row_bwd(zd, ones)), yh)
+    else:
+        assert_close(yh, rb(y_ref), BF16_RTOL, 1e-30, "softmax bf16")
+        assert_close(host(lse), rb(lse_ref), BF16_RTOL, 1e-6, "logsumexp bf16")
+        yd = dev(rb(y_ref), dtype)
+        assert_close(host(ops.softmax_row_bwd(yd, gyd)), rb(O.softmax_row_vjp(rb(y_ref), gy)), BF16_RTOL, 1e-3, "vjp bf16")
+        assert_close(host(ops.logsumexp_row_bwd(zd, gyrd)), rb(O.logsumexp_row_vjp(z, gy_row)), BF16_RTOL, 1e-30, "lse vjp bf16")
+        assert_close(host(ops.logsumexp_row_jvp(zd, td)), rb(O.logsumexp_row_jvp(z, t)), BF16_RTOL, 2e-2, "lse jvp bf16")
+    ops.device_status()
+
+
+def test_softmax_generic_kernels_agree_bitwise_with_staged(ops):
+    z = _logits(257, 2048, seed=3)
+    rng = np.random.default_rng(4)
+    g = rng.standard_normal(z.shape).astype(np.float32)
+    gr = rng.standard_normal(z.shape[0]).astype(np.float32)
+    zd, gd, grd = dev(z), dev(g), dev(gr)
+    staged = [ops.softmax_row(zd), ops.logsumexp_row(zd), ops.logsumexp_row_bwd(zd, grd), ops.logsumexp_row_jvp(zd, gd)]
+    staged.append(ops.softmax_row_bwd(staged[0], gd))
+    ops.set_option("force_generic", 1)
+    try:
+        generic = [ops.softmax_row(zd), ops.logsumexp_row(zd), ops.logsumexp_row_bwd(zd, grd), ops.logsumexp_row_jvp(zd, gd)]
+        generic.append(ops.softmax_row_bwd(staged[0], gd))
+    finally:
+        ops.set_option("force_generic", 0)
+    for a, b in zip(staged, generic):
+        assert np.array_equal(host(a), host(b))

@@ -117,3 +117,38 @@ def test_oracle_layernorm_matches_reference_bitwise(fp64, rows, hidden):
     mine = O.layernorm_fwd_bwd(x, gy, 1e-5, O.RED_F64 if fp64 else O.RED_F32)
     for k in ("y", "mean", "var", "dx"):
         assert np.array_equal(ref[k], mine[k]), k
+
+
+def _logits(rows, hidden, seed):
+    """Logit-like rows: N(0, 3) with a masked tail (-1e4) on some rows and one dominant entry on others."""
+    rng = np.random.default_rng(seed)
+    z = (3.0 * rng.standard_normal((rows, hidden))).astype(np.float32)
+    z[::3, hidden // 2:] = np.float32(-1e4)
+    z[1::5, 0] = np.float32(60.0)
+    return z
+
+
+@pytest.mark.parametrize("fp64", [False, True])
+@pytest.mark.parametrize("rows,hidden", [(4, 10), (64, 1024), (33, 1000)])
+def test_oracle_softmax_and_logsumexp_match_reference_bitwise(fp64, rows, hidden):
+    z = _logits(rows, hidden, seed=rows + hidden)
+    rng = np.random.default_rng(5)
+    gy = rng.standard_normal((rows, hidden)).astype(np.float32)
+    gy_row = rng.standard_normal(rows).astype(np.float32)
+    t = rng.standard_normal((rows, hidden)).astype(np.float32)
+    REF.set_reduce_fp64(fp64)
+    red = O.RED_F64 if fp64 else O.RED_F32
+    ref = REF.softmax_family("softmax", z, gy, t)
+    y = O.softmax_row(z, red)
+    assert np.array_equal(ref["y"], y)
+    assert np.array_equal(ref["dz"], O.softmax_row_vjp(y, gy, red))
+    assert np.array_equal(ref["ty"], O.softmax_row_vjp(y, t, red))
+    ref = REF.softmax_family("logsumexp", z, gy_row, t)
+    assert np.array_equal(ref["y"], O.logsumexp_row(z, red))
+    assert np.array_equal(ref["dz"], O.logsumexp_row_vjp(z, gy_row, red))
+    assert np.array_equal(ref["ty"], O.logsumexp_row_jvp(z, t, red))
+    # sanity against a float64 computation
+    z64 = z.astype(np.float64)
+    e = np.exp(z64 - z64.max(-1, keepdims=True))
+    np.testing.assert_allclose(y, e / e.sum(-1, keepdims=True), rtol=2e-6, atol=1e-9)
+    np.testing.assert_allclose(ref["y"], np.log(e.sum(-1)) + z64.max(-1), rtol=1e-6, atol=1e-6)
