@@ -130,7 +130,8 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
             }
         if (!found) return;
     } else {
-        vpt = 4;
+        // the softmax kernels pay two or three reductions per row: 32 elements per thread amortise them
+        vpt = (which == kSoftmax && elem == 4) ? 8 : 4;
         G = round_up((nvec + vpt - 1) / vpt, 32);
         if (G > 1024) {
             vpt = 8;

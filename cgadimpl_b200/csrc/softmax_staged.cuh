@@ -43,11 +43,19 @@ __device__ __forceinline__ float exp_nonpositive(float x, const double* tab) {
 }
 __device__ __forceinline__ float log_rounded(float s) { return static_cast<float>(log(static_cast<double>(s))); }
 
-// a / d for one divisor per row.  Three instructions (see DivConst) while the quotient is safely
-// normal; the general division otherwise (subnormal quotients of masked logits).
+// a / d for one divisor per row (1 <= d <= 2^24, 0 <= a <= 1).  `fast` is the three-instruction exact
+// division of DivConst; it needs the residual a - q0*d to be free of underflow, which holds for
+// a == 0 and for a >= exp(-40) (q0 >= 2^-82: the residual's granule 2^-128 is representable).  Rows
+// that contain smaller non-zero numerators (masked logits) go through `guarded`, element by element.
+constexpr float kRowDivSafeShift = -40.0f;  // z - max below this makes the row take the guarded path
 struct RowDiv {
     float d, dinv;
-    __device__ __forceinline__ float operator()(float a) const {
+    __device__ __forceinline__ float fast(float a) const {
+        const float q0 = __fmul_rn(a, dinv);
+        const float r = __fmaf_rn(-q0, d, a);
+        return __fmaf_rn(r, dinv, q0);
+    }
+    __device__ __forceinline__ float guarded(float a) const {
         const float q0 = __fmul_rn(a, dinv);
         if (!(q0 > 1e-30f && q0 < 1e30f)) return __fdiv_rn(a, d);
         const float r = __fmaf_rn(-q0, d, a);
@@ -55,6 +63,8 @@ struct RowDiv {
     }
 };
 
+struct TrueTag { static constexpr bool value = true; };
+struct FalseTag { static constexpr bool value = false; };
 __device__ __forceinline__ RowDiv make_row_div(float divisor) { return RowDiv{divisor, __frcp_rn(divisor)}; }
 
 __device__ __forceinline__ void fence_generic_to_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -157,14 +167,20 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
         }
         const float mx = group_max(redf + grp * wpr, wpr, lane);
 
-        // pass 2: e = exp(z - max), its sum in fp64
+        // pass 2: e = exp(z - max), its sum in fp64; `tiny`: some z - max is so low that the fast
+        // division of pass 3 would not be exact
         double d0 = 0.0, d1 = 0.0;
+        bool tiny = false;
         if (valid)
             for (int v = tig; v < g.nvec; v += G) {
                 float f[EPV];
                 Vec<T>::unpack(sz[v], f);
 #pragma unroll
-                for (int e = 0; e < EPV; ++e) f[e] = exp_nonpositive(sub_rn(f[e], mx), s_exp);
+                for (int e = 0; e < EPV; ++e) {
+                    f[e] = sub_rn(f[e], mx);
+                    tiny |= f[e] < kRowDivSafeShift;
+                    f[e] = exp_nonpositive(f[e], s_exp);
+                }
 #pragma unroll
                 for (int e = 0; e < EPV; e += 2) {
                     d0 += static_cast<double>(f[e]);
@@ -177,7 +193,11 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
                 }
             }
         const double dsum = warp_sum(d0 + d1);
-        if (lane == 0) red[nwarps + warp] = dsum;
+        const bool warp_tiny = __any_sync(0xffffffffu, tiny);
+        if (lane == 0) {
+            red[nwarps + warp] = dsum;
+            redf[nwarps + warp] = warp_tiny ? 1.0f : 0.0f;  // second half of the max region
+        }
         if (kThreePasses) fence_generic_to_async_smem();  // the slot this thread wrote is refilled by the copy engine later
         __syncthreads();
         if (!kThreePasses && tid == 0 && issued < my_tiles) {  // nobody reads the slot again
@@ -185,6 +205,7 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
             ++issued;
         }
         const float s = static_cast<float>(group_total(red + nwarps + grp * wpr, wpr, lane));
+        const bool row_tiny = __any_sync(0xffffffffu, lane < wpr && redf[nwarps + grp * wpr + lane] != 0.0f);
 
         if (MODE == 1) {
             if (valid && tig == 0) Vec<T>::store1(static_cast<T*>(a.out_row) + row, add_rn(log_rounded(s), mx));
@@ -200,37 +221,42 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
             const uint4* gadd = (MODE == 2 && a.add)
                                     ? reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(a.add) + row * g.row_bytes)
                                     : nullptr;
-            for (int v = tig; v < g.nvec; v += G) {
-                float f[EPV];
+            auto pass3 = [&](auto guarded_tag) {
+                constexpr bool kGuarded = decltype(guarded_tag)::value;
+                for (int v = tig; v < g.nvec; v += G) {
+                    float f[EPV];
 #pragma unroll
-                for (int q = 0; q < EPV / 4; ++q) {
-                    const float4 e4 = se[v * (EPV / 4) + q];
-                    f[4 * q] = e4.x; f[4 * q + 1] = e4.y; f[4 * q + 2] = e4.z; f[4 * q + 3] = e4.w;
-                }
+                    for (int q = 0; q < EPV / 4; ++q) {
+                        const float4 e4 = se[v * (EPV / 4) + q];
+                        f[4 * q] = e4.x; f[4 * q + 1] = e4.y; f[4 * q + 2] = e4.z; f[4 * q + 3] = e4.w;
+                    }
 #pragma unroll
-                for (int e = 0; e < EPV; ++e) f[e] = div_s(f[e]);
-                if (MODE == 2) {
+                    for (int e = 0; e < EPV; ++e) f[e] = kGuarded ? div_s.guarded(f[e]) : div_s.fast(f[e]);
+                    if (MODE == 2) {
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) f[e] = mul_rn(scale, f[e]);
-                    if (gadd) {
-                        float ad[EPV];
-                        Vec<T>::unpack(gadd[v], ad);
+                        for (int e = 0; e < EPV; ++e) f[e] = mul_rn(scale, f[e]);
+                        if (gadd) {
+                            float ad[EPV];
+                            Vec<T>::unpack(gadd[v], ad);
 #pragma unroll
-                        for (int e = 0; e < EPV; ++e) f[e] = add_rn(ad[e], f[e]);
+                            for (int e = 0; e < EPV; ++e) f[e] = add_rn(ad[e], f[e]);
+                        }
+                    }
+                    if (MODE == 3) {
+                        float tv[EPV];
+                        Vec<T>::unpack(st[v], tv);
+#pragma unroll
+                        for (int e = 0; e < EPV; e += 2) {
+                            j0 += static_cast<double>(mul_rn(f[e], tv[e]));
+                            j1 += static_cast<double>(mul_rn(f[e + 1], tv[e + 1]));
+                        }
+                    } else {
+                        store_vec_streaming(gout + v, Vec<T>::pack(f));
                     }
                 }
-                if (MODE == 3) {
-                    float tv[EPV];
-                    Vec<T>::unpack(st[v], tv);
-#pragma unroll
-                    for (int e = 0; e < EPV; e += 2) {
-                        j0 += static_cast<double>(mul_rn(f[e], tv[e]));
-                        j1 += static_cast<double>(mul_rn(f[e + 1], tv[e + 1]));
-                    }
-                } else {
-                    store_vec_streaming(gout + v, Vec<T>::pack(f));
-                }
-            }
+            };
+            if (row_tiny) pass3(TrueTag{});
+            else pass3(FalseTag{});
         }
         if (MODE == 3) {
             const double jsum = warp_sum(j0 + j1);
@@ -392,7 +418,7 @@ __global__ void __launch_bounds__(kGenericThreads) softmax_fwd_generic(const T* 
         const float scale = MODE == 2 ? Vec<T>::load1(rowscale + row) : 0.0f;
         double jd = 0.0;
         for (int j = threadIdx.x; j < hidden; j += kGenericThreads) {
-            float y = div_s(exp_nonpositive(sub_rn(Vec<T>::load1(zr + j), mx), s_exp));
+            float y = div_s.guarded(exp_nonpositive(sub_rn(Vec<T>::load1(zr + j), mx), s_exp));
             if (MODE == 2) {
                 y = mul_rn(scale, y);
                 if (add) y = add_rn(Vec<T>::load1(add + row * hidden + j), y);

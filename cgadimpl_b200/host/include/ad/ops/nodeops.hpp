@@ -22,6 +22,8 @@ std::shared_ptr<Node> sum_nodeops(const std::shared_ptr<Node>& x);
 std::shared_ptr<Node> mean_all_nodeops(const std::shared_ptr<Node>& x);
 std::shared_ptr<Node> rowsum_nodeops(const std::shared_ptr<Node>& x);
 std::shared_ptr<Node> rowmax_nodeops(const std::shared_ptr<Node>& x);
+std::shared_ptr<Node> softmax_row_nodeops(const std::shared_ptr<Node>& z);
+std::shared_ptr<Node> logsumexp_row_nodeops(const std::shared_ptr<Node>& z);
 
 // additions: the per-channel layer as one node, with and without the residual add
 std::shared_ptr<Node> rmsnorm_nodeops(const std::shared_ptr<Node>& x, const std::shared_ptr<Node>& gamma, float eps);

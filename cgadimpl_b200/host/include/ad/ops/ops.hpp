@@ -16,6 +16,8 @@ Value sum(const Value& x);
 Value mean_all(const Value& x);
 Value rowsum(const Value& x);              // [B,C] -> [B,1]
 Value rowmax(const Value& x);              // [B,C] -> [B,1]
+Value softmax_row(const Value& z);         // softmax over the last axis
+Value logsumexp_row(const Value& z);       // [.., C] -> [.., 1]
 
 // additions
 Value rmsnorm(const Value& x, const Value& gamma, float eps = 1e-5f);                    // == mul(rms(x), gamma), fused

@@ -59,13 +59,16 @@ void run_hooks(Node* n) {
     for (auto& h : n->post_acc_grad_hooks) h(n);
 }
 
-// Which activations a rule reads.  Add / Sum / MeanAll / RowSum only move gy along; Mul and the
-// norm rules read their inputs' values; the norm rules also read their own tape (rstd, mean, var).
+// Which activations a rule reads.  Add / Sum / MeanAll / RowSum only move gy along; Mul, the norm
+// rules and logsumexp read their inputs' values; the norm rules also read their own tape (rstd,
+// mean, var) and softmax its own value.
 bool rule_reads_inputs(Op op) {
-    return op == Op::Mul || op == Op::RMSNorm || op == Op::RMSNormAffine || op == Op::RealRMSNorm || op == Op::LayerNorm;
+    return op == Op::Mul || op == Op::RMSNorm || op == Op::RMSNormAffine || op == Op::RealRMSNorm || op == Op::LayerNorm ||
+           op == Op::LogSumExpRow;
 }
 bool rule_reads_own_tape(Op op) {
-    return op == Op::RMSNorm || op == Op::RMSNormAffine || op == Op::RealRMSNorm || op == Op::LayerNorm;
+    return op == Op::RMSNorm || op == Op::RMSNormAffine || op == Op::RealRMSNorm || op == Op::LayerNorm ||
+           op == Op::SoftmaxRow;
 }
 
 // Runs n's rule with every activation it reads present: dropped ones are recomputed first

@@ -295,6 +295,36 @@ std::shared_ptr<Node> rowmax_nodeops(const std::shared_ptr<Node>& x) {
     return n;
 }
 
+namespace {
+Tensor softmax_family_forward(const Tensor& z, bool lse) {
+    require_cuda(z, lse ? "logsumexp_row" : "softmax_row");
+    StreamGuard g(current_stream());
+    const auto rh = rows_hidden(z);
+    Shape os = z.shape();
+    if (lse) {
+        if (os.dims.empty()) os.dims.push_back(1);
+        os.dims.back() = 1;
+    }
+    Tensor out(os, ag::options(z).with_req_grad(false));
+    if (lse) check_status(agb_logsumexp_row_fwd(z.raw(), out.raw(), rh.rows, rh.hidden, agb_dtype(z), current_stream()), "logsumexp_row");
+    else check_status(agb_softmax_row_fwd(z.raw(), out.raw(), rh.rows, rh.hidden, agb_dtype(z), current_stream()), "softmax_row");
+    return out;
+}
+}  // namespace
+
+// reduction.cpp:42-53
+std::shared_ptr<Node> softmax_row_nodeops(const std::shared_ptr<Node>& z) {
+    auto n = std::make_shared<Node>(softmax_family_forward(z->value, false), Op::SoftmaxRow, z->requires_grad(), "softmax_row");
+    link(n, {z});
+    return n;
+}
+// reduction.cpp:54-66: [.., 1]
+std::shared_ptr<Node> logsumexp_row_nodeops(const std::shared_ptr<Node>& z) {
+    auto n = std::make_shared<Node>(softmax_family_forward(z->value, true), Op::LogSumExpRow, z->requires_grad(), "logsumexp_row");
+    link(n, {z});
+    return n;
+}
+
 }  // namespace detail
 
 // Recomputes a node's value from its inputs' values -- and its tape, which the rules of the norm
@@ -342,6 +372,8 @@ Tensor forward_eval_node(Node* node) {
             set_tape({o.var, o.mean});
             return o.y;
         }
+        case Op::SoftmaxRow: return softmax_family_forward(in(0), false);
+        case Op::LogSumExpRow: return softmax_family_forward(in(0), true);
         case Op::Sum: return reduce_all(in(0), AGB_REDUCE_SUM);
         case Op::MeanAll: return reduce_all(in(0), AGB_REDUCE_MEAN);
         case Op::RowSum: return reduce_axis1(in(0), AGB_REDUCE_SUM);
@@ -361,6 +393,8 @@ Value sum(const Value& x) { return Value(detail::sum_nodeops(x.node)); }
 Value mean_all(const Value& x) { return Value(detail::mean_all_nodeops(x.node)); }
 Value rowsum(const Value& x) { return Value(detail::rowsum_nodeops(x.node)); }
 Value rowmax(const Value& x) { return Value(detail::rowmax_nodeops(x.node)); }
+Value softmax_row(const Value& z) { return Value(detail::softmax_row_nodeops(z.node)); }
+Value logsumexp_row(const Value& z) { return Value(detail::logsumexp_row_nodeops(z.node)); }
 Value rmsnorm(const Value& x, const Value& gamma, float eps) { return Value(detail::rmsnorm_nodeops(x.node, gamma.node, eps)); }
 Value add_rmsnorm(const Value& x, const Value& r, const Value& gamma, float eps) {
     return Value(detail::add_rmsnorm_nodeops(x.node, r.node, gamma.node, eps));

@@ -106,6 +106,30 @@ Tensor jvp_RowMax(Node*, const TangentOf&) {
     throw std::runtime_error("JVP for RowMax cannot be implemented without argmax or comparison ops in the tensor library.");
 }
 
+// autodiff_jvp_ops.cpp:411-420: y * (tZ - sum(y*tZ))
+Tensor jvp_SoftmaxRow(Node* n, const TangentOf& t) {
+    const Tensor tz = tangent(t, n->inputs[0].get());
+    StreamGuard g(current_stream());
+    const auto rh = rows_hidden(n->value);
+    Tensor out(n->value.shape(), ag::options(n->value).with_req_grad(false));
+    check_status(agb_softmax_row_bwd(n->value.raw(), tz.raw(), nullptr, out.raw(), rh.rows, rh.hidden, agb_dtype(n->value),
+                                     current_stream()),
+                 "jvp_SoftmaxRow");
+    return out;
+}
+// autodiff_jvp_ops.cpp:421-434: sum(softmax(z) * tZ) per row, [.., 1]
+Tensor jvp_LogSumExpRow(Node* n, const TangentOf& t) {
+    Node* Z = n->inputs[0].get();
+    const Tensor tz = tangent(t, Z);
+    StreamGuard g(current_stream());
+    const auto rh = rows_hidden(Z->value);
+    Tensor out(n->value.shape(), ag::options(Z->value).with_req_grad(false));
+    check_status(agb_logsumexp_row_jvp(Z->value.raw(), tz.raw(), out.raw(), rh.rows, rh.hidden, agb_dtype(Z->value),
+                                       current_stream()),
+                 "jvp_LogSumExpRow");
+    return out;
+}
+
 #define AG_NOT_ON_PATH(name) \
     Tensor jvp_##name(Node*, const TangentOf&) { not_on_path(#name); }
 AG_NOT_ON_PATH(Sub) AG_NOT_ON_PATH(Div) AG_NOT_ON_PATH(Exp) AG_NOT_ON_PATH(Log) AG_NOT_ON_PATH(Sqrt)
@@ -114,7 +138,7 @@ AG_NOT_ON_PATH(Cos) AG_NOT_ON_PATH(Tan) AG_NOT_ON_PATH(Sinh) AG_NOT_ON_PATH(Cosh
 AG_NOT_ON_PATH(Acos) AG_NOT_ON_PATH(Atan) AG_NOT_ON_PATH(ASinh) AG_NOT_ON_PATH(ACosh) AG_NOT_ON_PATH(ATanh)
 AG_NOT_ON_PATH(Relu) AG_NOT_ON_PATH(Sigmoid) AG_NOT_ON_PATH(Tanh) AG_NOT_ON_PATH(Softplus) AG_NOT_ON_PATH(GELU)
 AG_NOT_ON_PATH(SiLU) AG_NOT_ON_PATH(Mish) AG_NOT_ON_PATH(LeakyRelu) AG_NOT_ON_PATH(Gaus) AG_NOT_ON_PATH(Parcon)
-AG_NOT_ON_PATH(LiSHT) AG_NOT_ON_PATH(SoftmaxRow) AG_NOT_ON_PATH(LogSumExpRow) AG_NOT_ON_PATH(MatMul)
+AG_NOT_ON_PATH(LiSHT) AG_NOT_ON_PATH(MatMul)
 AG_NOT_ON_PATH(Transpose) AG_NOT_ON_PATH(Linear) AG_NOT_ON_PATH(FMA) AG_NOT_ON_PATH(Dyntanh)
 AG_NOT_ON_PATH(Attention) AG_NOT_ON_PATH(SWIGLU) AG_NOT_ON_PATH(CeWithLogits) AG_NOT_ON_PATH(KLDivergence)
 AG_NOT_ON_PATH(MSELoss) AG_NOT_ON_PATH(MAELoss)

@@ -159,6 +159,30 @@ void vjp_RowSum(Node* n, const Tensor& gy) {
 // autodiff_vjp_ops.cpp:416-418 throws as well
 void vjp_RowMax(Node*, const Tensor&) { throw std::runtime_error("VJP for RowMax not implemented yet!"); }
 
+// autodiff_vjp_ops.cpp:421-428: Z.grad += y * (gy - sum(y*gy)); the `+=` is fused (dz_add == dz == Z.grad)
+void vjp_SoftmaxRow(Node* n, const Tensor& gy) {
+    StreamGuard g(rule_stream(n));
+    Node* Z = n->inputs[0].get();
+    if (!Z->requires_grad()) return;
+    const auto rh = rows_hidden(n->value);
+    std::lock_guard<std::mutex> lock(Z->grad_mutex);
+    check_status(agb_softmax_row_bwd(n->value.raw(), gy.raw(), Z->grad.raw(), Z->grad.raw(), rh.rows, rh.hidden,
+                                     agb_dtype(n->value), rule_stream(n)),
+                 "vjp_SoftmaxRow");
+}
+// autodiff_vjp_ops.cpp:430-440: softmax(z) recomputed from Z.value; Z.grad += gy[.., 1] * softmax(z)
+void vjp_LogSumExpRow(Node* n, const Tensor& gy) {
+    StreamGuard g(rule_stream(n));
+    Node* Z = n->inputs[0].get();
+    if (!Z->requires_grad()) return;
+    const auto rh = rows_hidden(Z->value);
+    if (gy.numel() != rh.rows) throw std::runtime_error("vjp_LogSumExpRow: gy must have one entry per row");
+    std::lock_guard<std::mutex> lock(Z->grad_mutex);
+    check_status(agb_logsumexp_row_bwd(Z->value.raw(), gy.raw(), Z->grad.raw(), Z->grad.raw(), rh.rows, rh.hidden,
+                                       agb_dtype(Z->value), rule_stream(n)),
+                 "vjp_LogSumExpRow");
+}
+
 #define AG_NOT_ON_PATH(name) \
     void vjp_##name(Node*, const Tensor&) { not_on_path("VJP", #name); }
 AG_NOT_ON_PATH(Sub) AG_NOT_ON_PATH(Div) AG_NOT_ON_PATH(Exp) AG_NOT_ON_PATH(Log) AG_NOT_ON_PATH(Sqrt)
@@ -167,7 +191,7 @@ AG_NOT_ON_PATH(Cos) AG_NOT_ON_PATH(Tan) AG_NOT_ON_PATH(Sinh) AG_NOT_ON_PATH(Cosh
 AG_NOT_ON_PATH(Acos) AG_NOT_ON_PATH(Atan) AG_NOT_ON_PATH(ASinh) AG_NOT_ON_PATH(ACosh) AG_NOT_ON_PATH(ATanh)
 AG_NOT_ON_PATH(Relu) AG_NOT_ON_PATH(Sigmoid) AG_NOT_ON_PATH(Tanh) AG_NOT_ON_PATH(Softplus) AG_NOT_ON_PATH(GELU)
 AG_NOT_ON_PATH(SiLU) AG_NOT_ON_PATH(Mish) AG_NOT_ON_PATH(LeakyRelu) AG_NOT_ON_PATH(Gaus) AG_NOT_ON_PATH(Parcon)
-AG_NOT_ON_PATH(LiSHT) AG_NOT_ON_PATH(SoftmaxRow) AG_NOT_ON_PATH(LogSumExpRow) AG_NOT_ON_PATH(MatMul)
+AG_NOT_ON_PATH(LiSHT) AG_NOT_ON_PATH(MatMul)
 AG_NOT_ON_PATH(Transpose) AG_NOT_ON_PATH(Linear) AG_NOT_ON_PATH(FMA) AG_NOT_ON_PATH(Dyntanh)
 AG_NOT_ON_PATH(Attention) AG_NOT_ON_PATH(SWIGLU) AG_NOT_ON_PATH(CeWithLogits) AG_NOT_ON_PATH(KLDivergence)
 AG_NOT_ON_PATH(MSELoss) AG_NOT_ON_PATH(MAELoss)

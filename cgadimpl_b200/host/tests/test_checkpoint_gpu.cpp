@@ -137,7 +137,7 @@ int main() {
         Value x = leaf(randv(R * H, 21), {R, H}), g = leaf(randv(H, 22, 0.05f, 1.0f), {H});
         Value g2 = leaf(randv(H, 22, 0.05f, 1.0f), {1, H});
         std::vector<Value> nodes = {add(x, x), mul(x, g2), rms(x), realrms(x, 1.5f), rmsnorm(x, g), laynor(x),
-                                    sum(x), mean_all(x), rowsum(x), rowmax(x)};
+                                    sum(x), mean_all(x), rowsum(x), rowmax(x), softmax_row(x), logsumexp_row(x)};
         for (auto& v : nodes) {
             const auto val = v.val().to_vector();
             std::vector<std::vector<float>> tape;

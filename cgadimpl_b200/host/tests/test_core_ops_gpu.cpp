@@ -144,6 +144,49 @@ int main() {
         const double want = host_sum(rms(a));
         CHECK(std::fabs(G->grad.to_vector()[0] - want) <= 1e-3);
     });
+    run_test("SoftmaxRow", [&] {
+        Value a = make_tensor(Tensor::randn(Shape{{4, 10}}, opts));
+        // sum(softmax(a)) is identically 4, so weight the outputs to get a non-trivial gradient
+        Value w = make_tensor(Tensor::randn(Shape{{4, 10}}, opts.with_req_grad(false)));
+        auto f = [&] { return softmax_row(a) * w; };
+        backward(sum(f()));
+        CHECK(check_grad(a.grad(), numerical_gradient(a, f)));
+        // forward-mode against the same finite differences: J t for a tangent t on `a`
+        Value y = softmax_row(a);
+        Tensor t = Tensor::randn(Shape{{4, 10}}, opts.with_req_grad(false));
+        Tensor jt = jvp(y, {{a.node.get(), t}});
+        const auto tv = t.to_vector(), base = a.val().to_vector();
+        std::vector<float> plus(base), minus(base);
+        for (size_t i = 0; i < base.size(); ++i) { plus[i] = float(base[i] + 1e-2 * tv[i]); minus[i] = float(base[i] - 1e-2 * tv[i]); }
+        const Tensor keep = a.val().clone();
+        a.val() = Tensor::from_host(plus.data(), keep.shape(), ag::options(keep)).to(keep.device());
+        const auto yp = softmax_row(a).val().to_vector();
+        a.val() = Tensor::from_host(minus.data(), keep.shape(), ag::options(keep)).to(keep.device());
+        const auto ym = softmax_row(a).val().to_vector();
+        a.val() = keep;
+        std::vector<float> fd(yp.size());
+        for (size_t i = 0; i < fd.size(); ++i) fd[i] = float((double(yp[i]) - double(ym[i])) / 2e-2);
+        CHECK(check_grad(jt, fd));
+    });
+    run_test("LogSumExpRow", [&] {
+        Value a = make_tensor(Tensor::randn(Shape{{4, 10}}, opts));
+        auto f = [&] { return logsumexp_row(a); };
+        Value y = f();
+        CHECK(y.shape() == std::vector<int64_t>({4, 1}));
+        backward(sum(y));
+        CHECK(check_grad(a.grad(), numerical_gradient(a, f)));
+        // d logsumexp / dz = softmax(z): with the all-ones seed the gradient IS the softmax, bit for bit
+        CHECK(a.grad().to_vector() == softmax_row(a).val().to_vector());
+        Tensor t = Tensor::randn(Shape{{4, 10}}, opts.with_req_grad(false));
+        Tensor jt = jvp(y, {{a.node.get(), t}});
+        CHECK(jt.shape().dims == std::vector<int64_t>({4, 1}));
+        const auto sm = softmax_row(a).val().to_vector(), tv = t.to_vector(), got = jt.to_vector();
+        for (int r = 0; r < 4; ++r) {
+            double want = 0;
+            for (int j = 0; j < 10; ++j) want += double(sm[r * 10 + j]) * tv[r * 10 + j];
+            CHECK(std::fabs(got[r] - want) <= 1e-5);
+        }
+    });
     cudaDeviceSynchronize();
     return finish("test_core_ops_gpu");
 }
