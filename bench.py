@@ -42,6 +42,15 @@ WORKLOADS = {
 STRONG_SCALING = {"rmsnorm_fwd_vjp_bf16_sharded_64x8192x8192"}
 # configuration 4: 32 fused residual-add + RMSNorm layers, forward + VJP as one CUDA graph (C++ host layer)
 STACK_WORKLOADS = {"residual_stack_fp32_32x4x4096x4096": (32, 4 * 4096, 4096, 0)}
+# Next rows of the path, same bar: one forward + VJP pass per step, per-kernel CUDA events.
+OP_WORKLOADS = {
+    # name: (op, rows, hidden, dtype)
+    "layernorm_fwd_vjp_fp32_32768x4096": ("layernorm", 32768, 4096, "float32"),
+    "layernorm_fwd_vjp_bf16_65536x8192": ("layernorm", 65536, 8192, "bfloat16"),
+    "softmax_fwd_vjp_fp32_32768x4096": ("softmax", 32768, 4096, "float32"),
+    "softmax_fwd_vjp_bf16_65536x8192": ("softmax", 65536, 8192, "bfloat16"),
+    "logsumexp_fwd_vjp_fp32_32768x4096": ("logsumexp", 32768, 4096, "float32"),
+}
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one backward launch, from the ncu
 # captures summarised under profiles/ (taken on a smaller case of the same kernel and scaled by rows).
 NCU_TRAFFIC = {
@@ -258,6 +267,72 @@ def run_stack(args, rank):
     }), flush=True)
 
 
+def run_op(args, rank):
+    """LayerNorm / softmax / logsumexp rows: forward + VJP per step on one GPU, each kernel timed with
+    CUDA events on the launching stream; roofline per kernel from its algorithmic bytes."""
+    if rank != 0:
+        return
+    import torch
+
+    from cgadimpl_b200 import ops
+
+    op, rows, hidden, dtype_name = OP_WORKLOADS[args.workload]
+    dtype = getattr(torch, dtype_name)
+    elem = 4 if dtype == torch.float32 else 2
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    x = (torch.randn(rows, hidden, device="cuda", generator=gen) * (3.0 if op != "layernorm" else 1.0)).to(dtype)
+    gy = torch.randn(rows, hidden, device="cuda", generator=gen).to(dtype)
+    gyr = torch.randn(rows, device="cuda", generator=gen).to(dtype)
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    orow = torch.empty(rows, device="cuda", dtype=dtype)
+    B = rows * hidden * elem
+    if op == "layernorm":
+        _, mean, var = ops.layernorm_fwd(x, 1e-5, out=y)
+        fwd, bwd = (lambda: ops.layernorm_fwd(x, 1e-5, out=y)), (lambda: ops.layernorm_bwd(x, mean, var, gy, 1e-5, dx=dx))
+        fwd_bytes, bwd_bytes, names = 2 * B + 8 * rows, 3 * B + 8 * rows, ("layernorm_fwd_staged", "layernorm_bwd_staged")
+    elif op == "softmax":
+        fwd, bwd = (lambda: ops.softmax_row(x, out=y)), (lambda: ops.softmax_row_bwd(y, gy, dz=dx))
+        fwd_bytes, bwd_bytes, names = 2 * B, 3 * B, ("softmax_fwd_staged<0>", "softmax_bwd_staged")
+    else:
+        fwd, bwd = (lambda: ops.logsumexp_row(x, out=orow)), (lambda: ops.logsumexp_row_bwd(x, gyr, dz=dx))
+        fwd_bytes, bwd_bytes, names = B + rows * elem, 2 * B + rows * elem, ("softmax_fwd_staged<1>", "softmax_fwd_staged<2>")
+    warm = max(3, args.warmup)
+    for _ in range(warm):
+        fwd(); bwd()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    time.sleep(0.3)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    l0 = ops.launch_count()
+    torch.cuda.synchronize()
+    for k in range(args.steps):
+        ev[k][0].record(); fwd(); ev[k][1].record(); bwd(); ev[k][2].record()
+    torch.cuda.synchronize()
+    launches = ops.launch_count() - l0
+    clocks = sampler.stop()
+    ops.device_status()
+    total_ms = ev[0][0].elapsed_time(ev[-1][2])
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    peak, peak_kind = measured_peak()
+    fa, ba = fwd_bytes / fwd_ms / 1e6, bwd_bytes / bwd_ms / 1e6
+    dom = ("bwd", names[1], ba, bwd_bytes, bwd_ms) if bwd_ms >= fwd_ms else ("fwd", names[0], fa, fwd_bytes, fwd_ms)
+    print(json.dumps({
+        "metric": f"{op}_fwd_vjp_rows_per_s", "value": rows * args.steps / (total_ms / 1e3), "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": warm, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "rows": rows, "hidden": hidden, "io_dtype": dtype_name,
+                   "l2": "inputs + outputs per step exceed the 126 MB L2; no flush needed"},
+        "gpu_launches": launches, "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": dom[1], "achieved": dom[2], "peak": peak, "unit": "GB/s",
+                     "frac": dom[2] / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "algorithmic_bytes_per_launch": dom[3], "avg_launch_ms": dom[4],
+                     "fwd": {"kernel": names[0], "achieved": fa, "frac": fa / peak, "avg_launch_ms": fwd_ms},
+                     "bwd": {"kernel": names[1], "achieved": ba, "frac": ba / peak, "avg_launch_ms": bwd_ms}},
+    }), flush=True)
+
+
 # --------------------------------------------------------------------------- GPU arm
 def main():
     ap = argparse.ArgumentParser()
@@ -265,7 +340,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(STACK_WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(STACK_WORKLOADS) + sorted(OP_WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -279,6 +354,9 @@ def main():
 
     if args.workload in STACK_WORKLOADS:
         run_stack(args, rank)
+        return
+    if args.workload in OP_WORKLOADS:
+        run_op(args, rank)
         return
     if args.impl == "reference":
         run_reference_arm(args, rank, world)

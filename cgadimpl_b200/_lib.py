@@ -40,6 +40,7 @@ SIGNATURES = {
     "agb_mul_reduce": (_i, [_vp, _vp, _vp, _i64, _i64, _i, _i, _vp, _sz, _i, _vp]),
     "agb_layernorm_fwd": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _vp]),
     "agb_layernorm_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _vp]),
+    "agb_layernorm_jvp": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _vp]),
     "agb_softmax_row_fwd": (_i, [_vp, _vp, _i64, _i64, _i, _vp]),
     "agb_logsumexp_row_fwd": (_i, [_vp, _vp, _i64, _i64, _i, _vp]),
     "agb_softmax_row_bwd": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i, _vp]),

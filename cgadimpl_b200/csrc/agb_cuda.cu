@@ -397,6 +397,24 @@ int launch_jvp(const void* x, const void* gamma, const float* rstd, const void* 
     return after_launch("rmsnorm_jvp_staged");
 }
 
+template <typename T>
+int launch_ln_jvp(const void* y, const void* t, const float* var, void* ty, int64_t rows, int64_t hidden, float eps,
+                  cudaStream_t st) {
+    const DevInfo* d;
+    AGB_TRY(device_info(&d));
+    Plan p;
+    if (aligned16(y) && aligned16(t) && aligned16(ty)) plan_launch(kJvp, rows, hidden, sizeof(T), 2, 0, *d, &p);
+    if (p.generic) {
+        agb::layernorm_jvp_generic<T><<<generic_grid(rows, *d), agb::kGenericThreads, 0, st>>>(
+            (const T*)y, (const T*)t, var, (T*)ty, rows, (int)hidden, eps);
+        return after_launch("layernorm_jvp_generic");
+    }
+    agb::LnJvpArgs a{p.g, y, t, var, ty, eps};
+    AGB_TRY(set_smem(agb::layernorm_jvp_staged<T>, p.smem));
+    agb::layernorm_jvp_staged<T><<<p.grid, p.block, p.smem, st>>>(a);
+    return after_launch("layernorm_jvp_staged");
+}
+
 // mode: the MODE of softmax_fwd_staged / softmax_fwd_generic.
 template <typename T>
 int launch_softmax_fwd(int mode, const void* z, const void* t, const void* rowscale, const void* add, void* out,
@@ -749,6 +767,20 @@ int softmax_family(int mode, const void* z, const void* t, const void* rowscale,
                             : launch_softmax_fwd<bf16>(mode, z, t, rowscale, add, out, out_row, rows, hidden, st);
 }
 }  // namespace
+
+int agb_layernorm_jvp(const void* y, const void* t, const float* var, void* ty, int64_t rows, int64_t hidden, float eps,
+                      int dtype, agb_stream_t stream) {
+    AGB_TRY(check_common(rows, hidden, dtype));
+    if (rows == 0) return AGB_OK;
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    AGB_TRY(check_ptr(y, "y", elem));
+    AGB_TRY(check_ptr(t, "t", elem));
+    AGB_TRY(check_ptr(ty, "ty", elem));
+    AGB_TRY(check_ptr(var, "var", 4));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == AGB_F32 ? launch_ln_jvp<float>(y, t, var, ty, rows, hidden, eps, st)
+                            : launch_ln_jvp<bf16>(y, t, var, ty, rows, hidden, eps, st);
+}
 
 int agb_softmax_row_fwd(const void* z, void* y, int64_t rows, int64_t hidden, int dtype, agb_stream_t stream) {
     return softmax_family(0, z, nullptr, nullptr, nullptr, y, nullptr, rows, hidden, dtype, stream);

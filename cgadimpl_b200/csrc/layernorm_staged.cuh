@@ -370,4 +370,155 @@ __global__ void __launch_bounds__(kGenericThreads) layernorm_bwd_generic(const T
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// JVP of laynor (the reference's jvp_LayerNorm throws, cgadimpl/src/autodiff/autodiff_jvp_ops.cpp:361-363).
+// With y = (x - mean) / sqrt(var + eps) saved by the forward and t the tangent of x:
+//   tmean = sum(t) / H ;  d = (sum(y*t) - tmean * sum(y)) / H      (= mean(y * (t - tmean)); fp64, rounded once)
+//   ty = std_inv * ((t - tmean) - y * d) ,  std_inv = 1 / sqrt(var + eps)
+// Every elementwise step rounds to fp32 once, like the other rules of this library.
+// ------------------------------------------------------------------------------------------
+struct LnJvpArgs {
+    PipeGeom g;
+    const void* y;
+    const void* t;
+    const float* var;
+    void* ty;
+    float eps;
+};
+
+__device__ __forceinline__ void ln_jvp_stats(double st, double sy, double syt, int hidden, float* tmean, float* d) {
+    const double tm = st / static_cast<double>(hidden);
+    *tmean = static_cast<float>(tm);
+    *d = static_cast<float>((syt - tm * sy) / static_cast<double>(hidden));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024, 1) layernorm_jvp_staged(const __grid_constant__ LnJvpArgs a) {
+    constexpr int NP = Pairs<T>::NP;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const PipeGeom& g = a.g;
+    unsigned char* ring = smem;
+    double* s_red = reinterpret_cast<double*>(smem + g.off_red);
+    uint64_t* s_full = reinterpret_cast<uint64_t*>(smem + g.off_bar);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + g.off_flag);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const int G = g.group_threads, wpr = G >> 5;
+    const int grp = tid / G, tig = tid - grp * G;
+    const int S = g.stages;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) mbar_init(&s_full[s], 1);
+        *s_abort = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const unsigned char* const src2[2] = {reinterpret_cast<const unsigned char*>(a.y),
+                                          reinterpret_cast<const unsigned char*>(a.t)};
+    const long long first = blockIdx.x, stride = gridDim.x;
+    const long long my_tiles = g.ntiles > first ? (g.ntiles - first + stride - 1) / stride : 0;
+    long long issued = 0;
+    if (tid == 0)
+        for (; issued < my_tiles && issued < S; ++issued)
+            issue_tile<2>(g, ring, s_full, src2, first + issued * stride, static_cast<int>(issued));
+
+    long long k = 0;
+    bool aborted = false;
+    for (; k < my_tiles; ++k) {
+        const int slot = static_cast<int>(k % S);
+        const uint32_t parity = static_cast<uint32_t>((k / S) & 1);
+        const long long row = (first + k * stride) * g.rows_per_tile + grp;
+        const bool valid = row < g.rows;
+        const float var = valid ? a.var[row] : 1.0f;
+        if (!mbar_wait_bounded(&s_full[slot], parity)) *s_abort = 1;
+        const unsigned char* base = ring + static_cast<size_t>(slot) * g.stage_stride + static_cast<size_t>(grp) * g.row_bytes;
+        const uint4* sy = reinterpret_cast<const uint4*>(base);
+        const uint4* st = reinterpret_cast<const uint4*>(base + g.tile_stride);
+
+        double at = 0.0, ay = 0.0, ayt0 = 0.0, ayt1 = 0.0;
+        if (valid) {
+#pragma unroll 2
+            for (int v = tig; v < g.nvec; v += G) {
+                float2 yv[NP], tv[NP];
+                Pairs<T>::unpack(sy[v], yv);
+                Pairs<T>::unpack(st[v], tv);
+#pragma unroll
+                for (int e = 0; e < NP; ++e) {
+                    const float2 p = mul2(yv[e], tv[e]);
+                    at += static_cast<double>(tv[e].x) + static_cast<double>(tv[e].y);
+                    ay += static_cast<double>(yv[e].x) + static_cast<double>(yv[e].y);
+                    ayt0 += static_cast<double>(p.x);
+                    ayt1 += static_cast<double>(p.y);
+                }
+            }
+        }
+        double* red = s_red + (k & 1) * 3 * nwarps;
+        const double wt = warp_sum(at), wy = warp_sum(ay), wyt = warp_sum(ayt0 + ayt1);
+        if (lane == 0) {
+            red[warp] = wt;
+            red[nwarps + warp] = wy;
+            red[2 * nwarps + warp] = wyt;
+        }
+        __syncthreads();
+        if (*s_abort) { aborted = true; break; }
+        if (tid == 0 && k >= 1 && issued < my_tiles) {
+            issue_tile<2>(g, ring, s_full, src2, first + issued * stride, static_cast<int>((k - 1) % S));
+            ++issued;
+        }
+        float tmean, d;
+        ln_jvp_stats(group_total(red + grp * wpr, wpr, lane), group_total(red + nwarps + grp * wpr, wpr, lane),
+                     group_total(red + 2 * nwarps + grp * wpr, wpr, lane), g.hidden, &tmean, &d);
+        const float std_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, a.eps)));
+        const float2 tm2 = splat(tmean), d2 = splat(d), si2 = splat(std_inv);
+
+        if (valid) {
+            uint4* gout = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.ty) + row * g.row_bytes);
+#pragma unroll 2
+            for (int v = tig; v < g.nvec; v += G) {
+                float2 yv[NP], tv[NP];
+                Pairs<T>::unpack(sy[v], yv);
+                Pairs<T>::unpack(st[v], tv);
+#pragma unroll
+                for (int e = 0; e < NP; ++e) {
+                    const float2 tc = sub2(tv[e], tm2);                  // neither operand is a product
+                    yv[e] = mul2(si2, sub2_after_mul(tc, mul2(yv[e], d2)));
+                }
+                store_vec_streaming(gout + v, Pairs<T>::pack(yv));
+            }
+        }
+    }
+    if (aborted && tid == 0) drain_after_abort(g, s_full, k, issued);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kGenericThreads) layernorm_jvp_generic(const T* __restrict__ y, const T* __restrict__ t,
+                                                                         const float* __restrict__ var_in, T* __restrict__ ty,
+                                                                         long long rows, int hidden, float eps) {
+    __shared__ double scratch[16];
+    int phase = 0;
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* yr = y + row * hidden;
+        const T* tr = t + row * hidden;
+        double at = 0.0, ay = 0.0, ayt = 0.0;
+        for (int j = threadIdx.x; j < hidden; j += kGenericThreads) {
+            const float yv = Vec<T>::load1(yr + j), tv = Vec<T>::load1(tr + j);
+            at += static_cast<double>(tv);
+            ay += static_cast<double>(yv);
+            ayt += static_cast<double>(mul_rn(yv, tv));
+        }
+        const double st = block_sum_256(at, scratch, phase++);
+        const double sy = block_sum_256(ay, scratch, phase++);
+        const double syt = block_sum_256(ayt, scratch, phase++);
+        float tmean, d;
+        ln_jvp_stats(st, sy, syt, hidden, &tmean, &d);
+        const float std_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var_in[row], eps)));
+        for (int j = threadIdx.x; j < hidden; j += kGenericThreads) {
+            const float yv = Vec<T>::load1(yr + j);
+            const float tc = sub_rn(Vec<T>::load1(tr + j), tmean);
+            Vec<T>::store1(ty + row * hidden + j, mul_rn(std_inv, sub_rn(tc, mul_rn(yv, d))));
+        }
+    }
+}
+
 }  // namespace agb

@@ -262,7 +262,8 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_staged(const __grid_const
             issue(first + issued * stride, slot);
             ++issued;
         }
-        const double tot = group_total(s_red + (k & 1) * nwarps + grp * wpr, wpr, lane);
+        // a row owned by one warp needs no second step: the shuffle sum is already the row's total
+        const double tot = wpr == 1 ? ssum : group_total(s_red + (k & 1) * nwarps + grp * wpr, wpr, lane);
         const float rs = rstd_from_sumsq(tot, g.hidden, a.eps);
         const float2 rs2 = splat(rs);
 
@@ -409,7 +410,7 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
             issue(first + issued * stride, static_cast<int>((k - 1) % S));
             ++issued;
         }
-        const float dot = static_cast<float>(group_total(s_red + (k & 1) * nwarps + grp * wpr, wpr, lane));
+        const float dot = static_cast<float>(wpr == 1 ? dsum : group_total(s_red + (k & 1) * nwarps + grp * wpr, wpr, lane));
         const float2 dot2 = splat(dot), rs2 = splat(rs), r22 = splat(mul_rn(rs, rs));
 
         // pass 2: dx and the dgamma terms
@@ -646,7 +647,7 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_jvp_staged(const __grid_const
             issue_tile<2>(g, ring, s_full, src2, first + issued * stride, static_cast<int>((k - 1) % S));
             ++issued;
         }
-        const float dot = static_cast<float>(group_total(s_red + (k & 1) * nwarps + grp * wpr, wpr, lane));
+        const float dot = static_cast<float>(wpr == 1 ? dsum : group_total(s_red + (k & 1) * nwarps + grp * wpr, wpr, lane));
         const float2 dot2 = splat(dot), c2 = splat(__fdiv_rn(rs, a.hidden_f));
 
         if (valid) {

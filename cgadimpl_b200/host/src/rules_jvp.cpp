@@ -64,8 +64,19 @@ Tensor jvp_Mul(Node* n, const TangentOf& t) {
     Tensor r = binary_op(1, A->value, tangent(t, B), current_stream());
     return binary_op(0, l, r, current_stream());
 }
-// autodiff_jvp_ops.cpp:361-363 throws as well
-Tensor jvp_LayerNorm(Node*, const TangentOf&) { throw std::runtime_error("JVP for LayerNorm not implemented yet!"); }
+// The reference throws here (autodiff_jvp_ops.cpp:361-363).  ty = std_inv * ((t - mean t) - y * mean(y * (t - mean t)))
+// from the node's own value y and tape[0] = variance.
+Tensor jvp_LayerNorm(Node* n, const TangentOf& t) {
+    const Tensor tx = tangent(t, n->inputs[0].get());
+    require_cuda(n->value, "laynor jvp");
+    StreamGuard g(current_stream());
+    const auto rh = rows_hidden(n->value);
+    Tensor out(n->value.shape(), ag::options(n->value).with_req_grad(false));
+    check_status(agb_layernorm_jvp(n->value.raw(), tx.raw(), n->tape[0]->data<float>(), out.raw(), rh.rows, rh.hidden, n->eps,
+                                   agb_dtype(n->value), current_stream()),
+                 "laynor jvp");
+    return out;
+}
 // autodiff_jvp_ops.cpp:366-379, corrected
 Tensor jvp_RMSNorm(Node* n, const TangentOf& t) {
     Node* X = n->inputs[0].get();

@@ -113,10 +113,22 @@ int main() {
         auto fw = [&] { return laynor(a) * w; };
         backward(sum(fw()));
         CHECK(check_grad(a.grad(), numerical_gradient(a, fw)));
-        zero_grad(sum(f()));
-        bool threw = false;
-        try { jvp(f(), {}); } catch (const std::runtime_error&) { threw = true; }
-        CHECK(threw);                                             // jvp_LayerNorm throws, as in the reference
+        // forward mode (the reference's jvp_LayerNorm throws; implemented here): central differences along t
+        Value y = f();
+        Tensor t = Tensor::randn(Shape{{4, 10}}, opts.with_req_grad(false));
+        Tensor jt = jvp(y, {{a.node.get(), t}});
+        const auto tv = t.to_vector(), base = a.val().to_vector();
+        std::vector<float> plus(base), minus(base);
+        for (size_t i = 0; i < base.size(); ++i) { plus[i] = float(base[i] + 1e-2 * tv[i]); minus[i] = float(base[i] - 1e-2 * tv[i]); }
+        const Tensor keep = a.val().clone();
+        a.val() = Tensor::from_host(plus.data(), keep.shape(), ag::options(keep)).to(keep.device());
+        const auto yp = f().val().to_vector();
+        a.val() = Tensor::from_host(minus.data(), keep.shape(), ag::options(keep)).to(keep.device());
+        const auto ym = f().val().to_vector();
+        a.val() = keep;
+        std::vector<float> fd(yp.size());
+        for (size_t i = 0; i < fd.size(); ++i) fd[i] = float((double(yp[i]) - double(ym[i])) / 2e-2);
+        CHECK(check_grad(jt, fd));
     });
     run_test("RMSNorm", [&] {
         Value a = make_tensor(Tensor::randn(Shape{{4, 10}}, opts));

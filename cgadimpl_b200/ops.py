@@ -148,6 +148,14 @@ def layernorm_bwd(x, mean, var, gy, eps=1e-5, dx_add=None, dx=None):
     return dx
 
 
+def layernorm_jvp(y, t, var, eps=1e-5, out=None):
+    """Tangent of laynor's output for a tangent t of its input (y, var from layernorm_fwd)."""
+    rows, hidden = _rows_hidden(y)
+    ty = torch.empty_like(y) if out is None else out
+    check(_lib.lib().agb_layernorm_jvp(_p(y), _p(t), _p(var), _p(ty), rows, hidden, eps, _dt(y), _stream()))
+    return ty
+
+
 def softmax_row(z, out=None):
     """cgadimpl's softmax_row: softmax over the last axis."""
     rows, hidden = _rows_hidden(z)

@@ -199,6 +199,11 @@ int agb_layernorm_fwd(const void* x, void* y, float* mean, float* var, int64_t r
                       int dtype, agb_stream_t stream);
 int agb_layernorm_bwd(const void* x, const float* mean, const float* var, const void* gy, const void* dx_add,
                       void* dx, int64_t rows, int64_t hidden, float eps, int dtype, agb_stream_t stream);
+/* The JVP the reference leaves unimplemented (jvp_LayerNorm throws, autodiff_jvp_ops.cpp:361-363).
+ * y is the forward's output, t the tangent of x, var the saved variance:
+ *   tmean = mean_j t;  d = mean_j y*(t - tmean);  ty = (1/sqrt(var+eps)) * ((t - tmean) - y*d). */
+int agb_layernorm_jvp(const void* y, const void* t, const float* var, void* ty, int64_t rows, int64_t hidden, float eps,
+                      int dtype, agb_stream_t stream);
 
 /* ---- row softmax / logsumexp over the last axis and their rules ----
  * agb_softmax_row_fwd replaces softmax_row_nodeops (cgadimpl/src/ops/reduction.cpp:42-53):

@@ -687,3 +687,32 @@ void agb_oracle_logsumexp_row_jvp(const float* z, const float* tz, float* out, i
     ot_reduce_sum_last(y, out, R, H, red);
     free(y);
 }
+
+/* JVP of laynor.  The reference has none (jvp_LayerNorm throws, autodiff_jvp_ops.cpp:361-363), so this is a
+ * definition, not a restatement -- parity unpinned; it is checked against finite differences of the pinned
+ * forward and against the adjoint identity with the pinned VJP:
+ *   tmean = sum(t)/H ; d = (sum(y*t) - tmean*sum(y))/H  (fp64, rounded once) ;
+ *   ty = std_inv * ((t - tmean) - y*d) ,  std_inv = 1/sqrt(var + eps)                                   */
+void agb_oracle_layernorm_jvp(const float* y, const float* t, const float* var, float* ty, int64_t R, int64_t H, float eps) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r) {
+        const float* yr = y + r * H;
+        const float* tr = t + r * H;
+        double st = 0.0, sy = 0.0, syt = 0.0;
+        for (int64_t j = 0; j < H; ++j) {
+            const float p = yr[j] * tr[j];
+            st += tr[j]; sy += yr[j]; syt += p;
+        }
+        const double tm = st / (double)H;
+        const float tmean = (float)tm;
+        const float d = (float)((syt - tm * sy) / (double)H);
+        const float v = var[r] + eps;
+        const float std_inv = 1.0f / sqrtf(v);
+        for (int64_t j = 0; j < H; ++j) {
+            const float tc = tr[j] - tmean;
+            const float p = yr[j] * d;
+            const float u = tc - p;
+            ty[r * H + j] = std_inv * u;
+        }
+    }
+}

@@ -134,6 +134,9 @@ void agb_oracle_layernorm_forward(const float* x, float* y, float* mean, float* 
 void agb_oracle_layernorm_vjp(const float* x, const float* mean, const float* var, const float* gy, float* dx,
                               int64_t R, int64_t H, float eps, int red);
 
+/* JVP of laynor: a definition of this library (the reference's rule throws); y, var from the forward. */
+void agb_oracle_layernorm_jvp(const float* y, const float* t, const float* var, float* ty, int64_t R, int64_t H, float eps);
+
 /* Row softmax / logsumexp over the last axis: cgadimpl/src/ops/reduction.cpp:42-66, rules
  * autodiff_vjp_ops.cpp:421-440 and autodiff_jvp_ops.cpp:411-434.  exp / log are the C library's expf /
  * logf, as in the stand-in tensor library the reference is compiled over.  softmax_row_vjp is also

@@ -260,3 +260,11 @@ def logsumexp_row_jvp(z, tz, red=RED_F64):
     out = np.empty(R, np.float32)
     lib().agb_oracle_logsumexp_row_jvp(_f(z), _f(tz), _f(out), C.c_int64(R), C.c_int64(H), C.c_int(red))
     return out
+
+
+def layernorm_jvp(y, t, var, eps):
+    y, t, var = (np.ascontiguousarray(a, np.float32) for a in (y, t, var))
+    R, H = y.shape
+    ty = np.empty_like(y)
+    lib().agb_oracle_layernorm_jvp(_f(y), _f(t), _f(var), _f(ty), C.c_int64(R), C.c_int64(H), C.c_float(eps))
+    return ty

@@ -436,10 +436,28 @@ def test_layernorm_forward_and_vjp(ops, rows, hidden, dtype):
         dx2 = ops.layernorm_bwd(xd, mean, var, gyd, eps, dx_add=extra)
         assert np.array_equal(host(dx2), host(dx) + host(extra))
         assert np.array_equal(host(ops.layernorm_bwd(xd, mean, var, gyd, eps, dx_add=gyd)), host(dx) + gy)
+        # the JVP (this library's definition; the reference's rule throws): oracle bits and the adjoint identity
+        t = np.random.default_rng(rows).standard_normal((rows, hidden)).astype(np.float32)
+        ty = ops.layernorm_jvp(y, dev(t), var, eps)
+        want = O.layernorm_jvp(host(y), t, host(var), eps)
+        assert_close(host(ty), want, F32_RTOL, F32_ATOL, "ty")
+        assert frac_bit_equal(host(ty), want) >= 0.999
+        lhs = float((gy.astype(np.float64) * host(ty)).sum())
+        rhs = float((host(dx).astype(np.float64) * t).sum())
+        assert abs(lhs - rhs) <= 1e-4 * max(1.0, abs(lhs), float(np.abs(gy.astype(np.float64) * host(ty)).sum()) * 1e-2)
+        ops.set_option("force_generic", 1)
+        try:
+            assert np.array_equal(host(ops.layernorm_jvp(y, dev(t), var, eps)), host(ty))
+        finally:
+            ops.set_option("force_generic", 0)
     else:
         # outputs are rounded to bf16 once; compare at the bf16 tolerance, relative to the row's scale
         assert_close(host(y), O.bf16_bits_to_f32(O.f32_to_bf16_bits(ref["y"])), BF16_RTOL, 1e-6, "y bf16")
         assert_close(host(dx), O.bf16_bits_to_f32(O.f32_to_bf16_bits(ref["dx"])), BF16_RTOL, 1e-2, "dx bf16")
+        t = O.bf16_bits_to_f32(O.f32_to_bf16_bits(np.random.default_rng(rows).standard_normal((rows, hidden)).astype(np.float32)))
+        ty = ops.layernorm_jvp(y, dev(t, dtype), var, eps)
+        want = O.layernorm_jvp(host(y), t, host(var), eps)
+        assert_close(host(ty), O.bf16_bits_to_f32(O.f32_to_bf16_bits(want)), BF16_RTOL, 1e-2, "ty bf16")
 
 
 def test_bounded_wait_expiry_is_reported_and_the_context_survives(ops):

@@ -218,3 +218,21 @@ def test_layernorm_against_torch_fp64_and_finite_differences():
     ana = O.layernorm_fwd_bwd(a, np.ones_like(a), eps)["dx"]
     num = _numgrad(lambda v: O.layernorm_fwd_bwd(v, np.ones_like(v), eps)["y"], a)
     assert np.abs(ana - num).max() <= 1e-3
+
+
+def test_layernorm_jvp_definition_against_torch_fp64_and_the_adjoint_identity():
+    """The reference's jvp_LayerNorm throws, so the JVP is this library's own definition: it must be the
+    directional derivative of the pinned forward and the adjoint of the pinned VJP."""
+    rows, hidden, eps = 29, 1000, 1e-5
+    x, _, gy = make_inputs(rows, hidden, seed=12)
+    x = x * np.float32(1.5) + np.float32(0.3)
+    t = np.random.default_rng(13).standard_normal((rows, hidden)).astype(np.float32)
+    out = O.layernorm_fwd_bwd(x, gy, eps)
+    ty = O.layernorm_jvp(out["y"], t, out["var"], eps)
+    xt = torch.tensor(x, dtype=torch.float64)
+    _, want = torch.func.jvp(lambda v: torch.nn.functional.layer_norm(v, (hidden,), eps=eps), (xt,),
+                             (torch.tensor(t, dtype=torch.float64),))
+    assert_close(ty, want.numpy(), 1e-5, 2e-6, "ty")
+    lhs = float((gy.astype(np.float64) * ty).sum())
+    rhs = float((out["dx"].astype(np.float64) * t).sum())
+    assert abs(lhs - rhs) <= 1e-4 * max(1.0, abs(lhs))
