@@ -50,6 +50,8 @@ OP_WORKLOADS = {
     "softmax_fwd_vjp_fp32_32768x4096": ("softmax", 32768, 4096, "float32"),
     "softmax_fwd_vjp_bf16_65536x8192": ("softmax", 65536, 8192, "bfloat16"),
     "logsumexp_fwd_vjp_fp32_32768x4096": ("logsumexp", 32768, 4096, "float32"),
+    "layernorm_fwd_vjp_fp32_8192x4096": ("layernorm", 8192, 4096, "float32"),     # small cases for ncu captures
+    "softmax_fwd_vjp_fp32_8192x4096": ("softmax", 8192, 4096, "float32"),
 }
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one backward launch, from the ncu
 # captures summarised under profiles/ (taken on a smaller case of the same kernel and scaled by rows).
@@ -400,7 +402,7 @@ def main():
     ex = RowShardedRMSNorm(hidden, dtype, eps)
 
     def step():
-        ex.fwd_bwd(x, gy, gamma, y=y, rstd=rstd, dx=dx, dgamma=dgamma)
+        ex.fwd_bwd(x, gy, gamma, y=y, rstd=rstd, dx=dx, dgamma=dgamma, wait=False)
 
     def sync_all():
         if dist is not None:
@@ -430,10 +432,12 @@ def main():
             ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=dgamma, workspace=ex._workspace(x))
             ev[k][2].record()
         else:
-            ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=ex._dg64, workspace=ex._workspace(x))
+            # backward on this stream; the 8*H-byte all-reduce and the final rounding run on the executor's
+            # side stream and overlap the next step's kernels (dgamma buffers alternate)
+            ex.bwd_and_exchange(x, gamma, rstd, gy, dx, dgamma)
             ev[k][2].record()
-            dist.all_reduce(ex._dg64, op=dist.ReduceOp.SUM)
-            ops.dgamma_finalize(ex._dg64, dgamma)
+    if world > 1:
+        ex.wait_dgamma()          # the timed region ends when the last dgamma is final
     t_end.record()
     sync_all()
     launches = ops.launch_count() - launches0

@@ -7,6 +7,10 @@ NCCL (NVLink / NVSwitch) and rounded to fp32 once afterwards.  Reducing in fp64 
 N-GPU dgamma equal to the 1-GPU result up to fp64 rounding, i.e. the same fp32 bits in all
 but rare tie cases.
 
+The all-reduce carries 8 * hidden bytes and is latency-bound, so with overlap=True (default) it
+runs on a side stream and overlaps whatever the caller enqueues next (the next step's kernels);
+`wait_dgamma()` makes the current stream wait for the newest dgamma before it is read.
+
 Two entry points:
   fwd_bwd(x, gy, gamma)           device tensors of this rank's shard
   fwd_bwd_host(...)               pinned HOST buffers; chunks of rows are copied in, processed
@@ -37,7 +41,7 @@ def allreduce_dgamma_f64(dg64, group=None):
 
 
 class RowShardedRMSNorm:
-    def __init__(self, hidden, dtype=torch.float32, eps=1e-5, device=None, group=None, chunk_rows=None):
+    def __init__(self, hidden, dtype=torch.float32, eps=1e-5, device=None, group=None, chunk_rows=None, overlap=True):
         self.hidden = int(hidden)
         self.dtype = dtype
         self.eps = float(eps)
@@ -48,6 +52,12 @@ class RowShardedRMSNorm:
             self.world = torch.distributed.get_world_size(group)
         self._ws = None
         self._dg64 = torch.zeros(self.hidden, dtype=torch.float64, device=self.device)
+        # overlapped exchange: two fp64 buffers used in turn, a side stream, one "reduced" event per buffer
+        self.overlap = bool(overlap) and self.world > 1
+        self._dg64_ring = [self._dg64, torch.zeros_like(self._dg64)] if self.overlap else [self._dg64]
+        self._side = torch.cuda.Stream(self.device) if self.overlap else None
+        self._reduced = [None, None]
+        self._turn = 0
         self._chunk_rows = chunk_rows
         self._slots = None
         self._streams = None
@@ -58,9 +68,10 @@ class RowShardedRMSNorm:
             self._ws = ops.bwd_workspace(x)
         return self._ws
 
-    def fwd_bwd(self, x, gy, gamma, y=None, rstd=None, dx=None, dgamma=None):
+    def fwd_bwd(self, x, gy, gamma, y=None, rstd=None, dx=None, dgamma=None, wait=True):
         """One pass over this rank's rows.  Returns (y, rstd, dx, dgamma); dgamma is the sum over
-        ALL ranks' rows (fp32 [hidden])."""
+        ALL ranks' rows (fp32 [hidden]).  wait=False leaves the exchange running on the side stream
+        (call wait_dgamma() before dgamma is read) so that it overlaps the next step."""
         y, rstd = ops.rmsnorm_fwd(x, gamma, self.eps, out=y, rstd=rstd)
         if gamma is None:
             dx, _ = ops.rmsnorm_bwd(x, None, rstd, gy, dx=dx)
@@ -68,10 +79,42 @@ class RowShardedRMSNorm:
         if self.world == 1:
             dx, dgamma = ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=dgamma, workspace=self._workspace(x))
             return y, rstd, dx, dgamma
-        dx, _ = ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=self._dg64, workspace=self._workspace(x))
-        allreduce_dgamma_f64(self._dg64, self.group)
-        dgamma = ops.dgamma_finalize(self._dg64, dgamma)
+        if dgamma is None:
+            dgamma = torch.empty(self.hidden, dtype=torch.float32, device=self.device)
+        if not self.overlap:
+            dx, _ = ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=self._dg64, workspace=self._workspace(x))
+            allreduce_dgamma_f64(self._dg64, self.group)
+            ops.dgamma_finalize(self._dg64, dgamma)
+            return y, rstd, dx, dgamma
+        dx = self.bwd_and_exchange(x, gamma, rstd, gy, dx, dgamma)
+        if wait:
+            self.wait_dgamma()
         return y, rstd, dx, dgamma
+
+    def bwd_and_exchange(self, x, gamma, rstd, gy, dx, dgamma):
+        """Backward on the current stream; all-reduce + rounding of dgamma on the side stream.  The
+        caller's stream does not wait for the exchange: call wait_dgamma() before reading dgamma."""
+        cur = torch.cuda.current_stream(self.device)
+        slot = self._turn
+        self._turn ^= 1
+        buf = self._dg64_ring[slot]
+        if self._reduced[slot] is not None:
+            cur.wait_event(self._reduced[slot])          # the exchange that last used this buffer
+        dx, _ = ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=buf, workspace=self._workspace(x))
+        self._side.wait_stream(cur)
+        with torch.cuda.stream(self._side):
+            allreduce_dgamma_f64(buf, self.group)
+            ops.dgamma_finalize(buf, dgamma)
+            ev = torch.cuda.Event()
+            ev.record()
+        self._reduced[slot] = ev
+        self._newest = ev
+        return dx
+
+    def wait_dgamma(self):
+        """Orders the current stream after the newest dgamma exchange (no-op without overlap)."""
+        if self.overlap and getattr(self, "_newest", None) is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._newest)
 
     # ------------------------------------------------------------------ host-buffer path
     def _ensure_slots(self, chunk_rows, nslots=3):

@@ -45,6 +45,17 @@ def _rank_main(rank, world, port, rows, hidden, dtype_name, q):
         ok = bool(torch.equal(y, ys[a:b]) and torch.equal(dx, dxs[a:b]) and torch.equal(rstd, rs[a:b]))
         same = float((dg == dgs).float().mean())
         maxulp = int((dg.view(torch.int32) - dgs.view(torch.int32)).abs().max())
+        # overlapped exchange: several steps back to back with alternating upstream gradients, the
+        # all-reduce of step k running beside the kernels of step k+1; every dgamma must be its own step's
+        xs, gs, gam = x[a:b].cuda().contiguous(), gy[a:b].cuda().contiguous(), gamma.cuda()
+        outs = [torch.empty(hidden, device="cuda") for _ in range(5)]
+        for k in range(5):
+            ex.fwd_bwd(xs, gs * float(k + 1), gam, dgamma=outs[k], wait=False)
+        ex.wait_dgamma()
+        torch.cuda.synchronize()
+        for k in range(5):
+            _, want = ops.rmsnorm_bwd(x.cuda(), gam, rs, gy.cuda() * float(k + 1))
+            ok = ok and int((outs[k].view(torch.int32) - want.view(torch.int32)).abs().max()) <= 1
         q.put((rank, ok, same, maxulp))
     finally:
         dist.destroy_process_group()
