@@ -57,10 +57,10 @@ OP_WORKLOADS = {
 # captures summarised under profiles/ (taken on a smaller case of the same kernel and scaled by rows).
 NCU_TRAFFIC = {
     "rmsnorm_fwd_vjp_fp32_16x2048x4096": {
-        "bwd_dram_bytes_per_launch": 1479438336,
+        "bwd_dram_bytes_per_launch": 1475391488,
         "source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on the 8192 x 4096 case (profiles/rmsnorm_bwd_staged_fp32_8192x4096.md), scaled x4 by rows; writes still dirty in L2 at kernel end are not counted by the DRAM counter"},
     "rmsnorm_fwd_vjp_bf16_sharded_64x8192x8192": {
-        "bwd_dram_bytes_per_launch": 25118081024,
+        "bwd_dram_bytes_per_launch": 24952111104,
         "source": "ncu capture on the 16384 x 8192 bf16 case (profiles/rmsnorm_bwd_staged_bf16_16384x8192.md), scaled x32 by rows (per rank at N=1)"},
 }
 DEFAULT_WORKLOAD = "rmsnorm_fwd_vjp_fp32_16x2048x4096"
