@@ -101,7 +101,7 @@ constexpr BwdVariant kBwdVariants[3] = {{8, 1024, 64}, {16, 768, 80}, {32, 512, 
 // narr: arrays staged per tile; ngamma: [hidden] fp32 vectors kept in shared memory.
 // extra_static: statically declared shared memory of the kernel, charged against the per-CTA limit.
 void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, int ngamma, const DevInfo& d,
-                 Plan* p, int extra_static = 0) {
+                 Plan* p, int extra_static = 0, bool heavy = false) {
     p->generic = true;
     if (opt_force_generic.load() || rows <= 0) return;
     const int64_t row_bytes64 = hidden * elem;
@@ -156,13 +156,16 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     };
     // Rows per tile and CTAs per SM: maximise resident threads subject to the ring depth (2 tiles
     // per CTA when several CTAs share the SM, 3 for a lone CTA), the register file and the thread
-    // limit; on a tie prefer more, smaller CTAs.  The fp32 forward / jvp have so few instructions
-    // per byte that 512 threads per SM in one CTA are enough, and measurably better than more.
+    // limit; on a tie prefer more, smaller CTAs.  The fp32 RMSNorm forward has so few instructions
+    // per byte that 512 threads per SM in one CTA are enough, and measurably better than more (6.5
+    // against 5.5 TB/s); its jvp, two arrays wide, is the other way round (5.9 -> 6.6 TB/s).
     int target = static_cast<int>(opt_threads.load());
     if (target <= 0) target = max_threads;
     if (target > max_threads) target = max_threads;
     const int want_ctas = static_cast<int>(opt_ctas_per_sm.load());
-    const bool light = (which == kFwd || which == kJvp) && elem == 4;
+    // heavy: the caller's kernel has several times the instructions per byte of the RMSNorm forward (LayerNorm:
+    // measured 4.5 -> 5.4-6.4 TB/s in fp32 when it gets the full thread count)
+    const bool light = !heavy && which == kFwd && elem == 4;
     const int max_resident = light && !want_ctas && !opt_threads.load() ? 512 : 2048;
     int rpt = 0, ctas = 0, S = 0, best = 0;
     for (int c = (want_ctas ? want_ctas : 1); c <= (want_ctas ? want_ctas : 4); ++c)
@@ -403,7 +406,7 @@ int launch_ln_jvp(const void* y, const void* t, const float* var, void* ty, int6
     const DevInfo* d;
     AGB_TRY(device_info(&d));
     Plan p;
-    if (aligned16(y) && aligned16(t) && aligned16(ty)) plan_launch(kJvp, rows, hidden, sizeof(T), 2, 0, *d, &p);
+    if (aligned16(y) && aligned16(t) && aligned16(ty)) plan_launch(kJvp, rows, hidden, sizeof(T), 2, 0, *d, &p, 0, true);
     if (p.generic) {
         agb::layernorm_jvp_generic<T><<<generic_grid(rows, *d), agb::kGenericThreads, 0, st>>>(
             (const T*)y, (const T*)t, var, (T*)ty, rows, (int)hidden, eps);
@@ -478,7 +481,7 @@ int launch_ln_fwd(const void* x, void* y, float* mean, float* var, int64_t rows,
     const DevInfo* d;
     AGB_TRY(device_info(&d));
     Plan p;
-    if (aligned16(x) && aligned16(y)) plan_launch(kFwd, rows, hidden, sizeof(T), 1, 0, *d, &p);
+    if (aligned16(x) && aligned16(y)) plan_launch(kFwd, rows, hidden, sizeof(T), 1, 0, *d, &p, 0, true);
     if (p.generic) {
         agb::layernorm_fwd_generic<T><<<generic_grid(rows, *d), agb::kGenericThreads, 0, st>>>(
             (const T*)x, (T*)y, mean, var, rows, (int)hidden, eps);
@@ -506,7 +509,7 @@ int launch_ln_bwd(const void* x, const float* mean, const float* var, const void
     if (dx_add) add_mode = (dx_add == gy) ? 2 : 1;
     Plan p;
     if (aligned16(x) && aligned16(gy) && aligned16(dx) && (add_mode != 1 || aligned16(dx_add)))
-        plan_launch(kFwd, rows, hidden, sizeof(T), add_mode == 1 ? 3 : 2, 0, *d, &p);
+        plan_launch(kFwd, rows, hidden, sizeof(T), add_mode == 1 ? 3 : 2, 0, *d, &p, 0, true);
     const float hf = static_cast<float>(hidden);
     if (p.generic) {
         agb::layernorm_bwd_generic<T><<<generic_grid(rows, *d), agb::kGenericThreads, 0, st>>>(
