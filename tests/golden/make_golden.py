@@ -2,9 +2,10 @@
 
     python tests/golden/make_golden.py
 
-The reference ships no golden vectors and cannot be built or imported here (its tensor library is an
-absent submodule), so these files pin the ORACLE, not the reference: a later change to the oracle or
-to the kernels that alters any bit of these outputs fails tests/test_golden.py.  Inputs are seeded
+The reference ships no golden vectors.  These files pin the ORACLE at configurations the reference's own
+code cannot run (eps 1e-6, bf16 I/O, the corrected JVP): a later change to the oracle or to the kernels
+that alters any bit of these outputs fails tests/test_golden.py.  Vectors produced by the reference's
+own code (eps 1e-5, fp32) are the ref_*.npz files made by make_reference_golden.py.  Inputs are seeded
 numpy draws with the distributions of the benchmark configurations, kept tiny (R <= 64).
 """
 import os

@@ -22,7 +22,9 @@ def load(name):
 
 def test_fixture_set_is_complete():
     names = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN, "*.npz")))
-    assert names == ["bf16_16x256_outliers", "fp32_4x10_plain", "fp32_5x1000", "fp32_8x64", "jvp_8x64", "stack_6x32x3"]
+    assert names == ["bf16_16x256_outliers", "fp32_4x10_plain", "fp32_5x1000", "fp32_8x64", "jvp_8x64",
+                     "ref_layernorm_6x48", "ref_logsumexp_6x40", "ref_optim_64", "ref_rms_plain_6x48", "ref_rmsnorm_6x48",
+                     "ref_softmax_6x40", "ref_stack_5x32x3", "stack_6x32x3"]
 
 
 @pytest.mark.parametrize("name", ["fp32_8x64", "fp32_4x10_plain", "fp32_5x1000"])
@@ -52,6 +54,45 @@ def test_oracle_reproduces_other_golden():
     out = O.residual_stack(c["x"], c["r"], c["gammas"], c["g"], float(c["eps"]))
     assert np.array_equal(out["y"], c["y"]) and np.array_equal(out["dh0"], c["dh0"])
     assert np.array_equal(out["dgammas"], c["dgammas"])
+
+
+def test_oracle_reproduces_the_reference_builds_vectors_bitwise():
+    """ref_*.npz hold outputs of the reference's own code (tests/golden/make_reference_golden.py); they pin the
+    oracle on machines without the reference tree."""
+    eps = 1e-5
+    c = load("ref_rmsnorm_6x48")
+    out = O.rmsnorm_fwd_bwd(c["x"], c["gamma"], c["gy"], eps)
+    for k in ("y", "rstd", "dx", "dgamma"):
+        assert np.array_equal(out[k], c[k]), k
+    c = load("ref_rms_plain_6x48")
+    out = O.rmsnorm_fwd_bwd(c["x"], None, c["gy"], eps)
+    for k in ("y", "rstd", "dx"):
+        assert np.array_equal(out[k], c[k]), k
+    c = load("ref_stack_5x32x3")
+    out = O.residual_stack(c["x"], c["r"], c["gammas"], c["g"], eps)
+    assert np.array_equal(out["y"], c["y"]) and np.array_equal(out["dgammas"], c["dgammas"])
+    assert np.array_equal(out["dh0"], c["dx0"]) and np.array_equal(out["dh0"], c["dr0"])
+    c = load("ref_layernorm_6x48")
+    out = O.layernorm_fwd_bwd(c["x"], c["gy"], eps)
+    for k in ("y", "mean", "var", "dx"):
+        assert np.array_equal(out[k], c[k]), k
+    c = load("ref_softmax_6x40")
+    y = O.softmax_row(c["z"])
+    assert np.array_equal(y, c["y"])
+    assert np.array_equal(O.softmax_row_vjp(y, c["gy"]), c["dz"]) and np.array_equal(O.softmax_row_vjp(y, c["t"]), c["ty"])
+    c = load("ref_logsumexp_6x40")
+    assert np.array_equal(O.logsumexp_row(c["z"]), c["y"])
+    assert np.array_equal(O.logsumexp_row_vjp(c["z"], c["gy"]), c["dz"])
+    assert np.array_equal(O.logsumexp_row_jvp(c["z"], c["t"]), c["ty"])
+    c = load("ref_optim_64")
+    p = c["p0"].copy()
+    for g in c["grads"]:
+        p = O.sgd_step(p, g, 1e-2)
+    assert np.array_equal(p, c["sgd"])
+    p, m, v = c["p0"].copy(), np.zeros(64, np.float32), np.zeros(64, np.float32)
+    for t, g in enumerate(c["grads"], 1):
+        p, m, v = O.adam_step(p, g, m, v, 1e-3, 0.9, 0.999, 1e-8, t)
+    assert np.array_equal(p, c["adam"])
 
 
 def _dev(a, dtype=None):
@@ -108,3 +149,46 @@ def test_cuda_reproduces_bf16_jvp_and_stack_golden():
         gh, _ = ops.rmsnorm_bwd(hs[l], gam[l], rs[l], gh, dx_add=None if l == L - 1 else gh, dgamma=dgs[l])
     assert_close(gh.cpu().numpy(), c["dh0"], 1e-5, 1e-6, "dh0")
     assert_close(dgs.cpu().numpy(), c["dgammas"], 1e-5, 1e-6, "dgammas")
+
+
+@pytest.mark.gpu
+def test_cuda_reproduces_the_reference_builds_vectors():
+    """The CUDA path against outputs of the reference's own code, carried here as fixtures."""
+    from cgadimpl_b200 import ops
+
+    eps = 1e-5
+    host = lambda t: t.cpu().numpy()  # noqa: E731
+    for name in ("ref_rmsnorm_6x48", "ref_rms_plain_6x48"):
+        c = load(name)
+        gamma = _dev(c["gamma"]) if "gamma" in c else None
+        y, rstd = ops.rmsnorm_fwd(_dev(c["x"]), gamma, eps)
+        dx, dg = ops.rmsnorm_bwd(_dev(c["x"]), gamma, rstd, _dev(c["gy"]))
+        for k, got in (("y", y), ("rstd", rstd), ("dx", dx)) + ((("dgamma", dg),) if gamma is not None else ()):
+            assert_close(host(got), c[k], 1e-5, 1e-6, f"{name} {k}")
+            assert np.array_equal(host(got), c[k]), f"{name} {k}: not bit-identical on a tiny case"
+    c = load("ref_layernorm_6x48")
+    y, mean, var = ops.layernorm_fwd(_dev(c["x"]), eps)
+    dx = ops.layernorm_bwd(_dev(c["x"]), mean, var, _dev(c["gy"]), eps)
+    for k, got in (("y", y), ("mean", mean), ("var", var), ("dx", dx)):
+        assert_close(host(got), c[k], 1e-5, 1e-6, f"layernorm {k}")
+    c = load("ref_softmax_6x40")
+    y = ops.softmax_row(_dev(c["z"]))
+    assert_close(host(y), c["y"], 1e-5, 1e-30, "softmax")
+    yd = _dev(c["y"])
+    assert_close(host(ops.softmax_row_bwd(yd, _dev(c["gy"]))), c["dz"], 1e-5, 1e-6, "softmax vjp")
+    assert_close(host(ops.softmax_row_bwd(yd, _dev(c["t"]))), c["ty"], 1e-5, 1e-6, "softmax jvp")
+    c = load("ref_logsumexp_6x40")
+    z = _dev(c["z"])
+    assert_close(host(ops.logsumexp_row(z)), c["y"], 1e-5, 1e-6, "logsumexp")
+    assert_close(host(ops.logsumexp_row_bwd(z, _dev(c["gy"]))), c["dz"], 1e-5, 1e-30, "logsumexp vjp")
+    assert_close(host(ops.logsumexp_row_jvp(z, _dev(c["t"]))), c["ty"], 1e-5, 1e-6, "logsumexp jvp")
+    c = load("ref_optim_64")
+    p = _dev(c["p0"]).clone()
+    for g in c["grads"]:
+        ops.sgd_step(p, _dev(g), 1e-2)
+    assert np.array_equal(host(p), c["sgd"])
+    p, m, v = _dev(c["p0"]).clone(), torch.zeros(64, device="cuda"), torch.zeros(64, device="cuda")
+    for t, g in enumerate(c["grads"], 1):
+        a_eff, e_eff = O.adam_scalars(1e-3, 0.9, 0.999, 1e-8, t)
+        ops.adam_step(p, _dev(g), m, v, 0.9, 0.999, a_eff, e_eff)
+    assert np.array_equal(host(p), c["adam"])
