@@ -1,5 +1,5 @@
 """Builds oracle/_ref/libcgadimpl_ref.so: the REFERENCE's own sources for the RMSNorm path, compiled
-from where they lie under /root/reference (nothing is copied), over the CPU stand-in for its absent
+from where they lie in the reference checkout (nothing is copied; location: $CGADIMPL_REFERENCE), over the CPU stand-in for its absent
 tensor library in oracle/ref_shim/.  Test infrastructure; needs the reference tree, so it runs in
 the development container only -- the built library travels with the repository snapshot.
 
