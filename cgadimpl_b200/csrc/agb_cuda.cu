@@ -429,7 +429,22 @@ int launch_softmax_fwd(int mode, const void* z, const void* t, const void* rowsc
     // arrays per stage: z [, t] [, fp32 scratch = two bf16 row-widths]; fp32 parks e in place over z
     const bool scratch = mode != 1 && sizeof(T) == 2;
     const int narr = (mode == 3 ? 2 : 1) + (scratch ? 2 : 0);
-    if (al) plan_launch(kSoftmax, rows, hidden, sizeof(T), narr, 0, *d, &p, agb::kExpTableSize * 8);
+    if (al) plan_launch(kSoftmax, rows, hidden, sizeof(T), narr, 0, *d, &p, agb::kExpTableSize * 8 + agb::kExp32Size * 8);
+    if (p.generic && al && (hidden * static_cast<int64_t>(sizeof(T))) % 16 == 0 && !opt_force_generic.load()) {
+        // too wide for the ring, but vectorisable: one 1024-thread CTA per row
+        agb::SoftmaxArgs a{};
+        a.g.rows = rows; a.g.hidden = static_cast<int>(hidden); a.g.row_bytes = static_cast<int>(hidden * sizeof(T));
+        a.g.nvec = a.g.row_bytes / 16;
+        a.z = z; a.t = t; a.rowscale = rowscale; a.add = add; a.out = out; a.out_row = out_row;
+        const int grid = static_cast<int>(rows < d->sms ? rows : d->sms);   // one 1024-thread CTA per SM
+#define AGB_SM_WIDE(M) agb::softmax_fwd_wide<T, M><<<grid, agb::kWideThreads, 0, st>>>(a)
+        if (mode == 0) AGB_SM_WIDE(0);
+        else if (mode == 1) AGB_SM_WIDE(1);
+        else if (mode == 2) AGB_SM_WIDE(2);
+        else AGB_SM_WIDE(3);
+#undef AGB_SM_WIDE
+        return after_launch("softmax_fwd_wide");
+    }
     if (p.generic) {
         const int grid = generic_grid(rows, *d);
 #define AGB_SM_GENERIC(M)                                                                                         \
@@ -464,6 +479,16 @@ int launch_softmax_bwd(const void* y, const void* g, const void* add, void* out,
     Plan p;
     if (aligned16(y) && aligned16(g) && aligned16(out) && (!add || aligned16(add)))
         plan_launch(kSoftmax, rows, hidden, sizeof(T), 2, 0, *d, &p);
+    const bool al = aligned16(y) && aligned16(g) && aligned16(out) && (!add || aligned16(add));
+    if (p.generic && al && (hidden * static_cast<int64_t>(sizeof(T))) % 16 == 0 && !opt_force_generic.load()) {
+        agb::SoftmaxBwdArgs a{};
+        a.g.rows = rows; a.g.hidden = static_cast<int>(hidden); a.g.row_bytes = static_cast<int>(hidden * sizeof(T));
+        a.g.nvec = a.g.row_bytes / 16;
+        a.y = y; a.gr = g; a.add = add; a.out = out;
+        const int grid = static_cast<int>(rows < d->sms ? rows : d->sms);
+        agb::softmax_bwd_wide<T><<<grid, agb::kWideThreads, 0, st>>>(a);
+        return after_launch("softmax_bwd_wide");
+    }
     if (p.generic) {
         agb::softmax_bwd_generic<T><<<generic_grid(rows, *d), agb::kGenericThreads, 0, st>>>(
             (const T*)y, (const T*)g, (const T*)add, (T*)out, rows, (int)hidden);

@@ -6,8 +6,10 @@
 // Rounding follows the reference's composition op by op (cgadimpl/src/ops/reduction.cpp:42-66):
 //   m = max(z) ; zs = z - m (fp32) ; e = exp(zs) (fp32) ; s = (float)sum_fp64(e) ; y = e / s (IEEE fp32)
 //   logsumexp = log(s) + m
-// exp and log are evaluated in fp64 and rounded to fp32 once, i.e. correctly rounded except for
-// astronomically rare double-rounding ties; a correctly rounded C library expf gives the same bits.
+// exp is evaluated to ~2^-33 relative before its one rounding to fp32 (double-word fp32 arithmetic: a
+// 256-entry table of 2^(j/256) as hi + lo, an exact Cody-Waite reduction, a cubic in r), log in fp64:
+// the results are the correctly rounded ones except in ~0.1 % of the cases -- the same order as a C
+// library expf, whose < 1 ulp error shows up equally rarely.
 #pragma once
 #include <math.h>
 
@@ -41,6 +43,51 @@ __device__ __forceinline__ float exp_nonpositive(float x, const double* tab) {
     const double scaled = __hiloint2double(__double2hiint(s) + (ki >> 5) * (1 << 20), __double2loint(s));
     return static_cast<float>(scaled);
 }
+// The fast form for -86 <= x <= 0, all in fp32 (about 16 instructions against 27 for the fp64 route, and no
+// use of the fp64 / conversion pipes):
+//   k = rint(x * 256/ln2);  r = (x - k*C1) - k*C2  (C1 + C2 = ln2/256; the first step is EXACT: both terms
+//   are multiples of 2^-32 and their difference is below 2^-9)
+//   exp(r) - 1 = w = r + r^2 (1/2 + r/6)          (|r| <= 1.36e-3; the r^4 term is 2^-43)
+//   2^(j/256) = Th + Tl, j = k mod 256;  result = (Th + (Tl + Th*w)) * 2^(k div 256)
+// Every rounding before the last addition is 2^-25 of a term of size 1.4e-3, i.e. ~2^-34 of the result.
+constexpr int kExp32Size = 256;
+__device__ __forceinline__ void init_exp32_table(float2* tab) {
+    for (int j = threadIdx.x; j < kExp32Size; j += blockDim.x) {
+        const double t = exp2(static_cast<double>(j) / kExp32Size);
+        const float hi = static_cast<float>(t);
+        tab[j] = make_float2(hi, static_cast<float>(t - static_cast<double>(hi)));
+    }
+}
+__device__ __forceinline__ float exp_fast_range(float x, const float2* tab32) {   // -86 <= x <= 0
+    const float kMagic = 12582912.0f;                    // 1.5 * 2^23, bit pattern 0x4B400000
+    const float t = __fmaf_rn(x, 0x1.715476p+8f /* 256/ln2 */, kMagic);
+    const int k = __float_as_int(t) - 0x4B400000;
+    const float kf = __fsub_rn(t, kMagic);
+    float r = __fmaf_rn(kf, -0x1.62e430p-9f /* C1 */, x);
+    r = __fmaf_rn(kf, 0x1.05c610p-37f /* -C2 */, r);
+    const float p = __fmaf_rn(r, 0x1.555556p-3f /* 1/6 */, 0.5f);
+    const float w = __fmaf_rn(__fmul_rn(r, r), p, r);
+    const float2 T = tab32[k & (kExp32Size - 1)];
+    const float y = __fadd_rn(T.x, __fmaf_rn(T.x, w, T.y));
+    return __int_as_float(__float_as_int(y) + (k >> 8) * (1 << 23));
+}
+__device__ __forceinline__ float exp_nonpositive32(float x, const float2* tab32, const double* tab64) {
+    if (x < -86.0f) return exp_nonpositive(x, tab64);   // results next to or below the normal range
+    return exp_fast_range(x, tab32);
+}
+// N values at once: one test (on their minimum) decides between the fast form for all and the fp64 route
+// for all, so the common case carries one branch per vector instead of one per element.
+template <int N>
+__device__ __forceinline__ void exp_nonpositive32_vec(float (&f)[N], float vmin, const float2* tab32, const double* tab64) {
+    if (vmin < -86.0f) {
+#pragma unroll
+        for (int e = 0; e < N; ++e) f[e] = exp_nonpositive(f[e], tab64);
+    } else {
+#pragma unroll
+        for (int e = 0; e < N; ++e) f[e] = exp_fast_range(f[e], tab32);
+    }
+}
+
 __device__ __forceinline__ float log_rounded(float s) { return static_cast<float>(log(static_cast<double>(s))); }
 
 // a / d for one divisor per row (1 <= d <= 2^24, 0 <= a <= 1).  `fast` is the three-instruction exact
@@ -97,6 +144,7 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
     constexpr bool kThreePasses = MODE != 1;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ double s_exp[kExpTableSize];
+    __shared__ float2 s_exp32[kExp32Size];
     const PipeGeom& g = a.g;
     unsigned char* ring = smem;
     double* s_red = reinterpret_cast<double*>(smem + g.off_red);
@@ -114,6 +162,7 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
         mbar_fence_init();
     }
     init_exp_table(s_exp);
+    init_exp32_table(s_exp32);
     __syncthreads();
 
     const unsigned char* const src2[2] = {reinterpret_cast<const unsigned char*>(a.z),
@@ -175,12 +224,14 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
             for (int v = tig; v < g.nvec; v += G) {
                 float f[EPV];
                 Vec<T>::unpack(sz[v], f);
+                float vmin = 0.0f;
 #pragma unroll
                 for (int e = 0; e < EPV; ++e) {
                     f[e] = sub_rn(f[e], mx);
-                    tiny |= f[e] < kRowDivSafeShift;
-                    f[e] = exp_nonpositive(f[e], s_exp);
+                    vmin = fminf(vmin, f[e]);
                 }
+                tiny |= vmin < kRowDivSafeShift;
+                exp_nonpositive32_vec<EPV>(f, vmin, s_exp32, s_exp);
 #pragma unroll
                 for (int e = 0; e < EPV; e += 2) {
                     d0 += static_cast<double>(f[e]);
@@ -375,6 +426,184 @@ __global__ void __launch_bounds__(1024, 1) softmax_bwd_staged(const __grid_const
 }
 
 // ------------------------------------------------------------------------------------------
+// Rows too wide for the shared-memory ring (vocabulary-sized logits) but 16-byte aligned: one CTA of
+// 1024 threads per row, 16-byte loads, three passes over the row of which only the first comes from DRAM
+// (a row is at most 1 MB and stays in L2); e is recomputed in the last pass instead of being parked.
+// Same modes and the same bits as softmax_fwd_staged.
+// ------------------------------------------------------------------------------------------
+constexpr int kWideThreads = 1024;
+__device__ __forceinline__ uint4 ldg128(const uint4* p) { return __ldg(p); }
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kWideThreads, 1) softmax_fwd_wide(const __grid_constant__ SoftmaxArgs a) {
+    constexpr int EPV = Vec<T>::EPV;
+    __shared__ double s_exp[kExpTableSize];
+    __shared__ float2 s_exp32[kExp32Size];
+    __shared__ double s_redd[2][32];
+    __shared__ float s_redf[2][64];
+    const PipeGeom& g = a.g;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int nwarps = kWideThreads / 32;
+    init_exp_table(s_exp);
+    init_exp32_table(s_exp32);
+    __syncthreads();
+    int phase = 0;
+    for (long long row = blockIdx.x; row < g.rows; row += gridDim.x, phase ^= 1) {
+        const uint4* zr = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(a.z) + row * g.row_bytes);
+        // pass 1: maximum
+        float m = -INFINITY;
+#pragma unroll 4
+        for (int v = tid; v < g.nvec; v += kWideThreads) {   // unrolled: several 16-byte loads in flight per thread
+            float f[EPV];
+            Vec<T>::unpack(ldg128(zr + v), f);
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) m = fmaxf(m, f[e]);
+        }
+        m = warp_max(m);
+        if (lane == 0) s_redf[phase][warp] = m;
+        __syncthreads();
+        const float mx = warp_max(s_redf[phase][lane]);   // nwarps == 32
+        // pass 2: sum of exp, and whether the fast division is exact for this row
+        double d0 = 0.0, d1 = 0.0;
+        bool tiny = false;
+#pragma unroll 2
+        for (int v = tid; v < g.nvec; v += kWideThreads) {
+            float f[EPV];
+            Vec<T>::unpack(ldg128(zr + v), f);
+            float vmin = 0.0f;
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) {
+                f[e] = sub_rn(f[e], mx);
+                vmin = fminf(vmin, f[e]);
+            }
+            tiny |= vmin < kRowDivSafeShift;
+            exp_nonpositive32_vec<EPV>(f, vmin, s_exp32, s_exp);
+#pragma unroll
+            for (int e = 0; e < EPV; e += 2) {
+                d0 += static_cast<double>(f[e]);
+                d1 += static_cast<double>(f[e + 1]);
+            }
+        }
+        const double dsum = warp_sum(d0 + d1);
+        const bool warp_tiny = __any_sync(0xffffffffu, tiny);
+        if (lane == 0) {
+            s_redd[phase][warp] = dsum;
+            s_redf[phase][32 + warp] = warp_tiny ? 1.0f : 0.0f;
+        }
+        __syncthreads();
+        const float s = static_cast<float>(warp_sum(s_redd[phase][lane]));
+        const bool row_tiny = __any_sync(0xffffffffu, s_redf[phase][32 + lane] != 0.0f);
+        if (MODE == 1) {
+            if (tid == 0) Vec<T>::store1(static_cast<T*>(a.out_row) + row, add_rn(log_rounded(s), mx));
+            continue;
+        }
+        // pass 3
+        const RowDiv div_s = make_row_div(s);
+        const float scale = MODE == 2 ? Vec<T>::load1(static_cast<const T*>(a.rowscale) + row) : 0.0f;
+        uint4* gout = MODE == 3 ? nullptr : reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.out) + row * g.row_bytes);
+        const uint4* gadd = (MODE == 2 && a.add) ? reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(a.add) + row * g.row_bytes) : nullptr;
+        const uint4* tr = MODE == 3 ? reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(a.t) + row * g.row_bytes) : nullptr;
+        double j0 = 0.0, j1 = 0.0;
+#pragma unroll 2
+        for (int v = tid; v < g.nvec; v += kWideThreads) {
+            float f[EPV];
+            Vec<T>::unpack(ldg128(zr + v), f);
+            float vmin = 0.0f;
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) {
+                f[e] = sub_rn(f[e], mx);
+                vmin = fminf(vmin, f[e]);
+            }
+            exp_nonpositive32_vec<EPV>(f, vmin, s_exp32, s_exp);
+            if (row_tiny) {
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) f[e] = div_s.guarded(f[e]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) f[e] = div_s.fast(f[e]);
+            }
+            if (MODE == 2) {
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) f[e] = mul_rn(scale, f[e]);
+                if (gadd) {
+                    float ad[EPV];
+                    Vec<T>::unpack(gadd[v], ad);   // may alias the output: plain load
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) f[e] = add_rn(ad[e], f[e]);
+                }
+            }
+            if (MODE == 3) {
+                float tv[EPV];
+                Vec<T>::unpack(ldg128(tr + v), tv);
+#pragma unroll
+                for (int e = 0; e < EPV; e += 2) {
+                    j0 += static_cast<double>(mul_rn(f[e], tv[e]));
+                    j1 += static_cast<double>(mul_rn(f[e + 1], tv[e + 1]));
+                }
+            } else {
+                store_vec_streaming(gout + v, Vec<T>::pack(f));
+            }
+        }
+        if (MODE == 3) {
+            const double jsum = warp_sum(j0 + j1);
+            __syncthreads();   // everyone has read s_redd[phase] of pass 2
+            if (lane == 0) s_redd[phase][warp] = jsum;
+            __syncthreads();
+            const float tot = static_cast<float>(warp_sum(s_redd[phase][lane]));
+            if (tid == 0) Vec<T>::store1(static_cast<T*>(a.out_row) + row, tot);
+        }
+    }
+}
+
+// The same for out = y * (g - sum(y*g)) [+ add].
+template <typename T>
+__global__ void __launch_bounds__(kWideThreads, 1) softmax_bwd_wide(const __grid_constant__ SoftmaxBwdArgs a) {
+    constexpr int NP = Pairs<T>::NP;
+    __shared__ double s_redd[2][32];
+    const PipeGeom& g = a.g;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int phase = 0;
+    for (long long row = blockIdx.x; row < g.rows; row += gridDim.x, phase ^= 1) {
+        const uint4* yr = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(a.y) + row * g.row_bytes);
+        const uint4* gr = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(a.gr) + row * g.row_bytes);
+        double d[4] = {0.0, 0.0, 0.0, 0.0};
+#pragma unroll 2
+        for (int v = tid; v < g.nvec; v += kWideThreads) {
+            float2 yv[NP], gv[NP];
+            Pairs<T>::unpack(ldg128(yr + v), yv);
+            Pairs<T>::unpack(ldg128(gr + v), gv);
+#pragma unroll
+            for (int e = 0; e < NP; ++e) {
+                const float2 p = mul2(yv[e], gv[e]);
+                d[(2 * e) & 3] += static_cast<double>(p.x);
+                d[(2 * e + 1) & 3] += static_cast<double>(p.y);
+            }
+        }
+        const double dsum = warp_sum((d[0] + d[1]) + (d[2] + d[3]));
+        if (lane == 0) s_redd[phase][warp] = dsum;
+        __syncthreads();
+        const float2 dot2 = splat(static_cast<float>(warp_sum(s_redd[phase][lane])));
+        uint4* gout = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.out) + row * g.row_bytes);
+        const uint4* gadd = a.add ? reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(a.add) + row * g.row_bytes) : nullptr;
+#pragma unroll 2
+        for (int v = tid; v < g.nvec; v += kWideThreads) {
+            float2 yv[NP], gv[NP];
+            Pairs<T>::unpack(ldg128(yr + v), yv);
+            Pairs<T>::unpack(ldg128(gr + v), gv);
+#pragma unroll
+            for (int e = 0; e < NP; ++e) yv[e] = mul2(yv[e], sub2(gv[e], dot2));
+            if (gadd) {
+                float2 av[NP];
+                Pairs<T>::unpack(gadd[v], av);   // may alias the output: plain load
+#pragma unroll
+                for (int e = 0; e < NP; ++e) yv[e] = add2_after_mul(av[e], yv[e]);
+            }
+            store_vec_streaming(gout + v, Pairs<T>::pack(yv));
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // Unstaged versions: any hidden size, element-aligned pointers.  One CTA of 256 threads per row;
 // e is recomputed in the last pass instead of being parked (same bits: exp is a pure function).
 // ------------------------------------------------------------------------------------------
@@ -398,7 +627,9 @@ __global__ void __launch_bounds__(kGenericThreads) softmax_fwd_generic(const T* 
     __shared__ double scratch[32];
     __shared__ float scratch_f[16];
     __shared__ double s_exp[kExpTableSize];
+    __shared__ float2 s_exp32[kExp32Size];
     init_exp_table(s_exp);
+    init_exp32_table(s_exp32);
     __syncthreads();
     int phase = 0;
     for (long long row = blockIdx.x; row < rows; row += gridDim.x, ++phase) {
@@ -408,7 +639,7 @@ __global__ void __launch_bounds__(kGenericThreads) softmax_fwd_generic(const T* 
         const float mx = block_max_256(m, scratch_f, phase);
         double d = 0.0;
         for (int j = threadIdx.x; j < hidden; j += kGenericThreads)
-            d += static_cast<double>(exp_nonpositive(sub_rn(Vec<T>::load1(zr + j), mx), s_exp));
+            d += static_cast<double>(exp_nonpositive32(sub_rn(Vec<T>::load1(zr + j), mx), s_exp32, s_exp));
         const float s = static_cast<float>(block_sum_256(d, scratch, phase));
         if (MODE == 1) {
             if (threadIdx.x == 0) Vec<T>::store1(out_row + row, add_rn(log_rounded(s), mx));
@@ -418,7 +649,7 @@ __global__ void __launch_bounds__(kGenericThreads) softmax_fwd_generic(const T* 
         const float scale = MODE == 2 ? Vec<T>::load1(rowscale + row) : 0.0f;
         double jd = 0.0;
         for (int j = threadIdx.x; j < hidden; j += kGenericThreads) {
-            float y = div_s.guarded(exp_nonpositive(sub_rn(Vec<T>::load1(zr + j), mx), s_exp));
+            float y = div_s.guarded(exp_nonpositive32(sub_rn(Vec<T>::load1(zr + j), mx), s_exp32, s_exp));
             if (MODE == 2) {
                 y = mul_rn(scale, y);
                 if (add) y = add_rn(Vec<T>::load1(add + row * hidden + j), y);

@@ -494,7 +494,7 @@ def _logits(rows, hidden, seed):
 @pytest.mark.parametrize("rows,hidden,dtype", [(4, 10, torch.float32), (2048, 4096, torch.float32), (33, 1000, torch.float32),
                                                (9, 70000, torch.float32), (1024, 32000, torch.float32),
                                                (300, 8192, torch.bfloat16), (129, 1000, torch.bfloat16),
-                                               (64, 50257, torch.bfloat16)])
+                                               (64, 50257, torch.bfloat16), (32, 50304, torch.bfloat16)])
 def test_softmax_and_logsumexp_rows(ops, rows, hidden, dtype):
     """cgadimpl's softmax_row / logsumexp_row with their VJP and JVP rules against the oracle, which
     tests/test_reference_build.py pins bit for bit to the reference's own builders and rules.  The only
@@ -570,4 +570,19 @@ def test_softmax_generic_kernels_agree_bitwise_with_staged(ops):
     finally:
         ops.set_option("force_generic", 0)
     for a, b in zip(staged, generic):
+        assert np.array_equal(host(a), host(b))
+    # rows too wide for the shared-memory ring take the one-CTA-per-row kernels: same bits as the unstaged ones
+    z = _logits(21, 40000, seed=5)
+    g = np.random.default_rng(6).standard_normal(z.shape).astype(np.float32)
+    gr = np.random.default_rng(7).standard_normal(z.shape[0]).astype(np.float32)
+    zd, gd, grd = dev(z), dev(g), dev(gr)
+    wide = [ops.softmax_row(zd), ops.logsumexp_row(zd), ops.logsumexp_row_bwd(zd, grd, dz_add=gd), ops.logsumexp_row_jvp(zd, gd)]
+    wide.append(ops.softmax_row_bwd(wide[0], gd, dz_add=gd))
+    ops.set_option("force_generic", 1)
+    try:
+        generic = [ops.softmax_row(zd), ops.logsumexp_row(zd), ops.logsumexp_row_bwd(zd, grd, dz_add=gd), ops.logsumexp_row_jvp(zd, gd)]
+        generic.append(ops.softmax_row_bwd(wide[0], gd, dz_add=gd))
+    finally:
+        ops.set_option("force_generic", 0)
+    for a, b in zip(wide, generic):
         assert np.array_equal(host(a), host(b))
