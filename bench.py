@@ -186,6 +186,28 @@ def cpu_pass(hidden, eps, sample_rows, reps, seed=0):
     return sample_rows / best, O.num_threads(), best, "port", PORT_KIND_NOTE
 
 
+def cpu_fused_pass(hidden, eps, sample_rows, reps, seed=0):
+    """The row-fused CPU variant of the same arithmetic (one read of each input per pass), all host threads."""
+    import numpy as np
+
+    if os.path.join(ROOT, "tests") not in sys.path:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_ffi as O
+
+    O.use_all_cores()
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((sample_rows, hidden), dtype=np.float32)
+    gy = rng.standard_normal((sample_rows, hidden), dtype=np.float32)
+    gamma = (1 + 0.02 * rng.standard_normal(hidden)).astype(np.float32)
+    O.rmsnorm_fwd_bwd(x, gamma, gy, eps, fused=True)
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        O.rmsnorm_fwd_bwd(x, gamma, gy, eps, fused=True)
+        ts.append(time.perf_counter() - t0)
+    return sample_rows / min(ts), O.num_threads(), min(ts)
+
+
 def run_reference_arm(args, rank, world):
     """The reference's own CPU implementation of the path on the host cores: oracle/_ref when it was
     built (the reference's unmodified graph / op / autodiff sources over a stand-in tensor library),
@@ -528,6 +550,11 @@ def main():
         v, cores, secs, kind, note = cpu_pass(hidden, eps, sample_rows, reps=8)
         cpu_baseline = {"value": v, "unit": UNIT, "cores": cores, "kind": kind,
                         "sample": f"{sample_rows} of {rows} rows, best of 8 passes ({secs*1e3:.1f} ms each); {note}"}
+        # the same arithmetic as ONE pass per row over memory, so that the comparison is not flattered by the
+        # reference's many passes and temporaries
+        fv, fcores, fsecs = cpu_fused_pass(hidden, eps, sample_rows, reps=8)
+        cpu_baseline["fused_single_pass"] = {"value": fv, "unit": UNIT, "cores": fcores,
+                                             "note": f"row-fused C restatement (oracle/agb_oracle.c), best of 8 passes ({fsecs*1e3:.1f} ms each)"}
 
     if rank == 0:
         line = {
