@@ -76,6 +76,7 @@ public:
     static DeviceAllocator& instance();
     void* allocate(size_t bytes, int device, cudaStream_t stream);
     void release(void* ptr);                       // returns the block to its stream's cache
+    bool owns(void* ptr) const;                    // true for a live block handed out by allocate()
     void reserve(size_t bytes, int device, cudaStream_t stream);  // pre-populates the cache with one block
     void empty_cache();                            // cudaFree of every cached (not in-use) block
     void set_memory_limit(size_t bytes);           // 0 = unlimited; exceeding it throws (never calls cudaMalloc)

@@ -152,6 +152,11 @@ void DeviceAllocator::release(void* ptr) {
     impl_->st.bytes_cached += b.size;
 }
 
+bool DeviceAllocator::owns(void* ptr) const {
+    std::lock_guard<std::mutex> lk(impl_->mu);
+    return impl_->live.count(ptr) != 0;
+}
+
 void DeviceAllocator::reserve(size_t bytes, int device, cudaStream_t stream) { release(allocate(bytes, device, stream)); }
 
 void DeviceAllocator::empty_cache() {
