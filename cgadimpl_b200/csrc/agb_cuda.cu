@@ -250,6 +250,10 @@ inline int generic_grid(int64_t rows, const DevInfo& d) {
     int64_t g = static_cast<int64_t>(d.sms) * 8;
     return static_cast<int>(rows < g ? rows : g);
 }
+// dgamma partial rows ([hidden] fp64 each, one per CTA of the backward): a caller workspace must hold at
+// least max_partials() rows; the staged backward may run up to kMaxCtasPerSm CTAs per SM and is given as
+// many of them as the workspace has rows for (agb_rmsnorm_bwd_workspace_bytes() asks for all of them).
+constexpr int kMaxCtasPerSm = 4;
 inline int max_partials(const DevInfo& d) { return 2 * d.sms; }
 
 // ------------------------------------------------------------------ typed launchers
@@ -325,6 +329,11 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
     const bool al = aligned16(x) && aligned16(gy) && aligned16(dx) && (!gamma || aligned16(gamma)) &&
                     (add_mode != 1 || aligned16(dx_add));
     if (al) plan_launch(kBwd, rows, hidden, sizeof(T), add_mode == 1 ? 3 : 2, gamma ? 1 : 0, *d, &p);
+    if (want_dg && !p.generic) {
+        // every CTA writes the partial row of its block index: never launch more CTAs than the workspace has rows
+        const size_t cap = workspace_bytes / (static_cast<size_t>(hidden) * sizeof(double));
+        if (static_cast<size_t>(p.grid) > cap) p.grid = static_cast<int>(cap);
+    }
     double* partials = static_cast<double*>(workspace);
     int P = 0;
     if (p.generic) {
@@ -688,7 +697,7 @@ size_t agb_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t hidden, int dtype) 
     (void)dtype;
     const DevInfo* d;
     if (hidden <= 0 || device_info(&d) != AGB_OK) return 0;
-    return static_cast<size_t>(max_partials(*d)) * hidden * sizeof(double);
+    return static_cast<size_t>(kMaxCtasPerSm) * d->sms * hidden * sizeof(double);
 }
 
 int agb_rmsnorm_bwd(const void* x, const void* gamma, const float* rstd, const void* gy, const void* dx_add, void* dx,

@@ -104,8 +104,11 @@ int agb_add_rmsnorm_fwd(const void* x, const void* r, const void* gamma, void* h
  * dx_add (nullable) is added to dx: it fuses Node::accumulate_grad's `grad +=`
  * (cgadimpl/src/core/graph.cpp:44-47) and the second parent of vjp_Add (:40-45).  dx_add may
  * alias gy or dx (in-place accumulation).
- * dgamma is produced in two deterministic stages: per-CTA fp64 partials in `workspace`
- * (agb_rmsnorm_bwd_workspace_bytes), then a fixed-order column reduction.  `dgamma_dtype`:
+ * dgamma is produced in two deterministic stages: per-CTA fp64 partials in `workspace`, then a
+ * fixed-order column reduction.  The workspace must hold at least 2 * SMs rows of `hidden` doubles;
+ * agb_rmsnorm_bwd_workspace_bytes returns the 4 * SMs rows the largest launch uses, and a smaller
+ * workspace only means fewer CTAs (one partial row each).  For a given workspace size the result is
+ * bit-reproducible.  `dgamma_dtype`:
  * AGB_F32 writes the final fp32 [hidden]; AGB_F64 writes the un-rounded fp64 [hidden] sum, for
  * a cross-device all-reduce or for accumulation over row chunks, to be finished with
  * agb_dgamma_finalize.  With accumulate_dgamma the result is added to the old contents.

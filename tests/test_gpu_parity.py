@@ -133,6 +133,36 @@ def test_plain_rms_is_the_reference_op(ops):
     assert np.array_equal(host(y), ref["y"]) and np.array_equal(host(dx), ref["dx"])
 
 
+@pytest.mark.parametrize("rows,hidden,dtype", [(4096, 1024, torch.float32), (2048, 1000, torch.bfloat16),
+                                               (1024, 4096, torch.float32), (512, 8192, torch.bfloat16)])
+def test_backward_stays_inside_its_workspace(ops, rows, hidden, dtype):
+    """The dgamma partial rows (one per CTA) must fit the caller's workspace whatever grid the launch
+    heuristic picks: a guard area behind the workspace stays untouched, both with the size the library asks
+    for and with the smallest size it accepts (2 * SMs rows), and dgamma agrees between the two."""
+    from cgadimpl_b200 import _lib
+
+    x, gamma, gy = make_inputs(rows, hidden, seed=1)
+    xd, gd, gyd = dev(x, dtype), dev(gamma, dtype), dev(gy, dtype)
+    _, rstd = ops.rmsnorm_fwd(xd, gd, 1e-5)
+    full = int(_lib.lib().agb_rmsnorm_bwd_workspace_bytes(rows, hidden, 0))
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    smallest = 2 * sms * hidden * 8
+    assert full >= smallest
+    guard = 4 << 20
+    results = []
+    for nbytes in (full, smallest):
+        buf = torch.full((nbytes + guard,), 0x5A, dtype=torch.uint8, device="cuda")
+        dx, dg = ops.rmsnorm_bwd(xd, gd, rstd, gyd, workspace=buf[:nbytes])
+        torch.cuda.synchronize()
+        assert bool((buf[nbytes:] == 0x5A).all()), f"wrote past a {nbytes}-byte workspace"
+        results.append((host(dx), host(dg)))
+    assert np.array_equal(results[0][0], results[1][0])
+    assert frac_bit_equal(results[0][1], results[1][1]) >= 0.99
+    with pytest.raises(Exception):
+        ops.rmsnorm_bwd(xd, gd, rstd, gyd, workspace=torch.empty(smallest - 8, dtype=torch.uint8, device="cuda"))
+    ops.device_status()
+
+
 def test_dx_add_and_accumulate_dgamma(ops):
     rows, hidden = 130, 2048
     x, gamma, gy = make_inputs(rows, hidden, seed=3)
