@@ -57,6 +57,7 @@ class RowShardedRMSNorm:
         self._dg64_ring = [self._dg64, torch.zeros_like(self._dg64)] if self.overlap else [self._dg64]
         self._side = torch.cuda.Stream(self.device) if self.overlap else None
         self._reduced = [None, None]
+        self._newest = None
         self._turn = 0
         self._chunk_rows = chunk_rows
         self._slots = None
@@ -113,7 +114,7 @@ class RowShardedRMSNorm:
 
     def wait_dgamma(self):
         """Orders the current stream after the newest dgamma exchange (no-op without overlap)."""
-        if self.overlap and getattr(self, "_newest", None) is not None:
+        if self.overlap and self._newest is not None:
             torch.cuda.current_stream(self.device).wait_event(self._newest)
 
     # ------------------------------------------------------------------ host-buffer path

@@ -4,6 +4,7 @@
 #include "ad/ops/ops.hpp"
 
 #include <map>
+#include <vector>
 
 #include "ad/detail/host_util.hpp"
 
@@ -30,8 +31,11 @@ int classify_broadcast(const Tensor& full, const Tensor& b) {
 
 void* workspace(size_t bytes, const Tensor& like, ag_cuda_stream_t stream) {
     thread_local std::map<std::pair<int, ag_cuda_stream_t>, Tensor> pool;
+    // a workspace that is outgrown is retired, not freed: a captured CUDA graph may still point at it
+    thread_local std::vector<Tensor> retired;
     Tensor& t = pool[{like.device().index, stream}];
     if (!t.defined() || t.nbytes() < bytes) {
+        if (t.defined()) retired.push_back(t);
         StreamGuard g(stream);
         t = Tensor(Shape{{static_cast<int64_t>((bytes + 7) / 8)}},
                    TensorOptions().with_dtype(Dtype::Float64).with_device(like.device()));
