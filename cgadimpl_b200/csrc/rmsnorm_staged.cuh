@@ -185,14 +185,6 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_staged(const __grid_const
     const int grp = tid / G, tig = tid - grp * G;
     const int S = g.stages;
 
-    if (tid == 0) {
-        for (int s = 0; s < S; ++s) mbar_init(&s_full[s], 1);
-        *s_abort = 0;
-        mbar_fence_init();
-    }
-    if (HAS_GAMMA) stage_gamma<T>(s_gamma, a.gamma, g.nvec);
-    __syncthreads();
-
     const unsigned char* const src2[2] = {reinterpret_cast<const unsigned char*>(a.x),
                                           reinterpret_cast<const unsigned char*>(a.r)};
     auto issue = [&](long long tile, int slot) {
@@ -201,12 +193,20 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_staged(const __grid_const
         else
             issue_tile<1>(g, ring, s_full, reinterpret_cast<const unsigned char* const(&)[1]>(src2), tile, slot);
     };
-
     const long long first = blockIdx.x, stride = gridDim.x;
     const long long my_tiles = g.ntiles > first ? (g.ntiles - first + stride - 1) / stride : 0;
     long long issued = 0;
-    if (tid == 0)
+    // The first tiles are requested before gamma is staged, so that their latency overlaps it.  The thread
+    // that initialised the barriers issues the copies itself (program order + the init fence suffice); the
+    // others touch the barriers only after the __syncthreads below.
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) mbar_init(&s_full[s], 1);
+        *s_abort = 0;
+        mbar_fence_init();
         for (; issued < my_tiles && issued < S; ++issued) issue(first + issued * stride, static_cast<int>(issued));
+    }
+    if (HAS_GAMMA) stage_gamma<T>(s_gamma, a.gamma, g.nvec);
+    __syncthreads();
 
     long long k = 0;
     bool aborted = false;
@@ -332,14 +332,6 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
     const bool staged_add = a.add_mode == 1;
     const DivConst2 div_h{splat(a.hidden_f), splat(a.hidden_inv)};
 
-    if (tid == 0) {
-        for (int s = 0; s < S; ++s) mbar_init(&s_full[s], 1);
-        *s_abort = 0;
-        mbar_fence_init();
-    }
-    if (HAS_GAMMA) stage_gamma<T>(s_gamma, a.gamma, g.nvec);
-    __syncthreads();
-
     const unsigned char* const src3[3] = {reinterpret_cast<const unsigned char*>(a.x),
                                           reinterpret_cast<const unsigned char*>(a.gy),
                                           reinterpret_cast<const unsigned char*>(a.add)};
@@ -349,12 +341,18 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
         else
             issue_tile<2>(g, ring, s_full, reinterpret_cast<const unsigned char* const(&)[2]>(src3), tile, slot);
     };
-
     const long long first = blockIdx.x, stride = gridDim.x;
     const long long my_tiles = g.ntiles > first ? (g.ntiles - first + stride - 1) / stride : 0;
     long long issued = 0;
-    if (tid == 0)
+    // first tiles requested before gamma is staged (see the forward kernel)
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) mbar_init(&s_full[s], 1);
+        *s_abort = 0;
+        mbar_fence_init();
         for (; issued < my_tiles && issued < S; ++issued) issue(first + issued * stride, static_cast<int>(issued));
+    }
+    if (HAS_GAMMA) stage_gamma<T>(s_gamma, a.gamma, g.nvec);
+    __syncthreads();
 
     double acc[HAS_GAMMA ? VPT * EPV : 1];
 #pragma unroll
