@@ -37,11 +37,34 @@ def _rows_hidden(x):
     return x.numel() // hidden if hidden else 0, hidden
 
 
+def _same(x, *others):
+    """Operands that must match x in shape, dtype and device and be contiguous (None is skipped)."""
+    for t in others:
+        if t is None:
+            continue
+        if t.shape != x.shape or t.dtype != x.dtype or t.device != x.device or not t.is_contiguous():
+            raise ValueError(f"operand {tuple(t.shape)} {t.dtype} on {t.device} does not match "
+                             f"{tuple(x.shape)} {x.dtype} on {x.device} (or is not contiguous)")
+
+
+def _vec(x, n, dtype, *others):
+    """Per-row or per-column vectors: n elements of dtype on x's device, contiguous (None is skipped)."""
+    for t in others:
+        if t is None:
+            continue
+        if t.numel() != n or t.dtype != dtype or t.device != x.device or not t.is_contiguous():
+            raise ValueError(f"operand {tuple(t.shape)} {t.dtype} on {t.device}: expected {n} contiguous elements of "
+                             f"{dtype} on {x.device}")
+
+
 def rmsnorm_fwd(x, gamma=None, eps=1e-5, out=None, rstd=None):
     """y = (x * rstd) * gamma; returns (y, rstd[rows] fp32).  gamma=None is cgadimpl's `rms(x)`."""
     rows, hidden = _rows_hidden(x)
     y = torch.empty_like(x) if out is None else out
     rstd = torch.empty(rows, dtype=torch.float32, device=x.device) if rstd is None else rstd
+    _same(x, y)
+    _vec(x, hidden, x.dtype, gamma)
+    _vec(x, rows, torch.float32, rstd)
     check(_lib.lib().agb_rmsnorm_fwd(_p(x), _p(gamma), _p(y), _p(rstd), rows, hidden, eps, _dt(x), _stream()))
     return y, rstd
 
@@ -52,6 +75,9 @@ def add_rmsnorm_fwd(x, r, gamma=None, eps=1e-5, h=None, out=None, rstd=None):
     h = torch.empty_like(x) if h is None else h
     y = torch.empty_like(x) if out is None else out
     rstd = torch.empty(rows, dtype=torch.float32, device=x.device) if rstd is None else rstd
+    _same(x, r, h, y)
+    _vec(x, hidden, x.dtype, gamma)
+    _vec(x, rows, torch.float32, rstd)
     check(_lib.lib().agb_add_rmsnorm_fwd(_p(x), _p(r), _p(gamma), _p(h), _p(y), _p(rstd), rows, hidden, eps,
                                          _dt(x), _stream()))
     return h, y, rstd
@@ -78,6 +104,11 @@ def rmsnorm_bwd(x, gamma, rstd, gy, dx_add=None, dx=None, dgamma=None, accumulat
         if workspace is None:
             workspace = bwd_workspace(x)
         ws_bytes = workspace.numel() * workspace.element_size()
+    _same(x, gy, dx_add, dx)
+    _vec(x, hidden, x.dtype, gamma)
+    _vec(x, rows, torch.float32, rstd)
+    if dgamma is not None and dgamma.numel() != hidden:
+        raise ValueError("dgamma must have `hidden` elements")
     check(_lib.lib().agb_rmsnorm_bwd(_p(x), _p(gamma), _p(rstd), _p(gy), _p(dx_add), _p(dx), _p(dgamma), dg_dtype,
                                      int(bool(accumulate_dgamma)), _p(workspace), ws_bytes, rows, hidden, _dt(x),
                                      _stream()))
@@ -92,6 +123,10 @@ def rmsnorm_bwd_static(x, gamma, rstd, gy, dx_add=None, dx=None, dgamma=None, ac
     dx = torch.empty_like(x) if dx is None else dx
     if gamma is not None and dgamma is None:
         dgamma = torch.zeros(hidden, dtype=torch.float32, device=x.device)
+    _same(x, gy, dx_add, dx)
+    _vec(x, hidden, x.dtype, gamma)
+    _vec(x, rows, torch.float32, rstd)
+    _vec(x, hidden, torch.float32, dgamma)
     check(_lib.lib().agb_rmsnorm_bwd_static(_p(x), _p(gamma), _p(rstd), _p(gy), _p(dx_add), _p(dx), _p(dgamma),
                                             int(bool(accumulate_dgamma)), rows, hidden, _dt(x), _stream()))
     return dx, dgamma
@@ -107,6 +142,9 @@ def dgamma_finalize(sum_f64, dgamma=None, accumulate=False):
 def rmsnorm_jvp(x, gamma, rstd, tx, tgamma=None, out=None):
     rows, hidden = _rows_hidden(x)
     ty = torch.empty_like(x) if out is None else out
+    _same(x, tx, ty)
+    _vec(x, hidden, x.dtype, gamma, tgamma)
+    _vec(x, rows, torch.float32, rstd)
     check(_lib.lib().agb_rmsnorm_jvp(_p(x), _p(gamma), _p(rstd), _p(tx), _p(tgamma), _p(ty), rows, hidden, _dt(x),
                                      _stream()))
     return ty
@@ -114,6 +152,8 @@ def rmsnorm_jvp(x, gamma, rstd, tx, tgamma=None, out=None):
 
 def residual_add(a, b, out=None):
     out = torch.empty_like(a) if out is None else out
+    _rows_hidden(a)
+    _same(a, b, out)
     check(_lib.lib().agb_residual_add(_p(a), _p(b), _p(out), a.numel(), _dt(a), _stream()))
     return out
 
@@ -136,6 +176,7 @@ def layernorm_fwd(x, eps=1e-5, out=None):
     y = torch.empty_like(x) if out is None else out
     mean = torch.empty(rows, dtype=torch.float32, device=x.device)
     var = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _same(x, y)
     check(_lib.lib().agb_layernorm_fwd(_p(x), _p(y), _p(mean), _p(var), rows, hidden, eps, _dt(x), _stream()))
     return y, mean, var
 
@@ -143,6 +184,8 @@ def layernorm_fwd(x, eps=1e-5, out=None):
 def layernorm_bwd(x, mean, var, gy, eps=1e-5, dx_add=None, dx=None):
     rows, hidden = _rows_hidden(x)
     dx = torch.empty_like(x) if dx is None else dx
+    _same(x, gy, dx_add, dx)
+    _vec(x, rows, torch.float32, mean, var)
     check(_lib.lib().agb_layernorm_bwd(_p(x), _p(mean), _p(var), _p(gy), _p(dx_add), _p(dx), rows, hidden, eps, _dt(x),
                                        _stream()))
     return dx
@@ -152,6 +195,8 @@ def layernorm_jvp(y, t, var, eps=1e-5, out=None):
     """Tangent of laynor's output for a tangent t of its input (y, var from layernorm_fwd)."""
     rows, hidden = _rows_hidden(y)
     ty = torch.empty_like(y) if out is None else out
+    _same(y, t, ty)
+    _vec(y, rows, torch.float32, var)
     check(_lib.lib().agb_layernorm_jvp(_p(y), _p(t), _p(var), _p(ty), rows, hidden, eps, _dt(y), _stream()))
     return ty
 
@@ -160,6 +205,7 @@ def softmax_row(z, out=None):
     """cgadimpl's softmax_row: softmax over the last axis."""
     rows, hidden = _rows_hidden(z)
     y = torch.empty_like(z) if out is None else out
+    _same(z, y)
     check(_lib.lib().agb_softmax_row_fwd(_p(z), _p(y), rows, hidden, _dt(z), _stream()))
     return y
 
@@ -168,6 +214,7 @@ def logsumexp_row(z, out=None):
     """cgadimpl's logsumexp_row: [rows] (same dtype as z)."""
     rows, hidden = _rows_hidden(z)
     o = torch.empty(rows, dtype=z.dtype, device=z.device) if out is None else out
+    _vec(z, rows, z.dtype, o)
     check(_lib.lib().agb_logsumexp_row_fwd(_p(z), _p(o), rows, hidden, _dt(z), _stream()))
     return o
 
@@ -176,6 +223,7 @@ def softmax_row_bwd(y, g, dz_add=None, dz=None):
     """y * (g - sum(y*g)) [+ dz_add]: the softmax VJP (g = gy) and JVP (g = tangent)."""
     rows, hidden = _rows_hidden(y)
     dz = torch.empty_like(y) if dz is None else dz
+    _same(y, g, dz_add, dz)
     check(_lib.lib().agb_softmax_row_bwd(_p(y), _p(g), _p(dz_add), _p(dz), rows, hidden, _dt(y), _stream()))
     return dz
 
@@ -184,6 +232,8 @@ def logsumexp_row_bwd(z, gy, dz_add=None, dz=None):
     """gy[rows] * softmax(z) [+ dz_add]."""
     rows, hidden = _rows_hidden(z)
     dz = torch.empty_like(z) if dz is None else dz
+    _same(z, dz_add, dz)
+    _vec(z, rows, z.dtype, gy)
     check(_lib.lib().agb_logsumexp_row_bwd(_p(z), _p(gy), _p(dz_add), _p(dz), rows, hidden, _dt(z), _stream()))
     return dz
 
@@ -191,6 +241,8 @@ def logsumexp_row_bwd(z, gy, dz_add=None, dz=None):
 def logsumexp_row_jvp(z, tz, out=None):
     rows, hidden = _rows_hidden(z)
     o = torch.empty(rows, dtype=z.dtype, device=z.device) if out is None else out
+    _same(z, tz)
+    _vec(z, rows, z.dtype, o)
     check(_lib.lib().agb_logsumexp_row_jvp(_p(z), _p(tz), _p(o), rows, hidden, _dt(z), _stream()))
     return o
 

@@ -379,6 +379,15 @@ def test_empty_input_and_errors(ops):
         ops.rmsnorm_fwd(x.half(), None, 1e-5)
     with pytest.raises(ValueError):
         ops.rmsnorm_fwd(torch.randn(4, 64), None, 1e-5)          # host tensor: there is no CPU path
+    # operands that do not match are refused before any pointer reaches the library
+    with pytest.raises(ValueError):
+        ops.rmsnorm_bwd(x, gamma, rstd, torch.randn(4, 32, device="cuda"))
+    with pytest.raises(ValueError):
+        ops.rmsnorm_fwd(x, torch.ones(32, device="cuda"), 1e-5)
+    with pytest.raises(ValueError):
+        ops.rmsnorm_bwd(x, gamma, rstd, x.t().contiguous().t())  # same shape, not contiguous
+    with pytest.raises(ValueError):
+        ops.softmax_row_bwd(x, x.double())
 
 
 def test_cuda_matches_the_reference_build(ops):
