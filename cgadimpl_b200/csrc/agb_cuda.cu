@@ -76,7 +76,7 @@ int device_info(const DevInfo** out) {
 }
 
 // ------------------------------------------------------------------ options
-std::atomic<int64_t> opt_stages{0}, opt_ctas_per_sm{0}, opt_threads{0}, opt_force_generic{0}, opt_ept{0};
+std::atomic<int64_t> opt_stages{0}, opt_ctas_per_sm{0}, opt_threads{0}, opt_force_generic{0}, opt_ept{0}, opt_rpw{0};
 
 // ------------------------------------------------------------------ launch planning
 struct Plan {
@@ -185,6 +185,27 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     if (want_stages >= 2 && want_stages < S) S = want_stages;
     const int block = rpt * G;
     const int nwarps = block / 32;
+    // Backward with rows that one warp owns (G == 32, hidden <= 32 elements-per-thread): let every warp
+    // take several rows of a tile back to back, so the block-wide barrier is paid once per tile, as long
+    // as the ring stays three tiles deep.
+    int rpw = 1;
+    if (which == kBwd && G == 32) {
+        const int want_rpw = static_cast<int>(opt_rpw.load());
+        for (int cand = (want_rpw > 0 ? want_rpw : 4); cand >= 2; --cand) {
+            if (static_cast<int64_t>(rpt) * cand > rows) continue;
+            int avail = d.smem_per_sm / ctas - 1024;
+            if (avail > d.smem_optin) avail = d.smem_optin;
+            const int fixed = ngamma * gamma_bytes + 8 * nwarps * 8 + 8 * 16 + 16 + 128 + extra_static;
+            const int st = (avail - fixed) / (narr * tile_stride_of(rpt * cand));
+            if (st >= 3 || (want_rpw > 0 && st >= 2)) {
+                rpw = cand;
+                if (st < S) S = st;
+                break;
+            }
+        }
+        if (want_rpw == 1) rpw = 1;
+    }
+    rpt *= rpw;
     const int tile_stride = tile_stride_of(rpt);
     const int stage_stride = narr * tile_stride;
 
@@ -194,6 +215,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     g.nvec = nvec;
     g.row_bytes = row_bytes;
     g.rows_per_tile = rpt;
+    g.rows_per_warp = rpw;
     g.group_threads = G;
     g.stages = S;
     g.tile_stride = tile_stride;
@@ -641,6 +663,7 @@ int agb_set_option(const char* key, int64_t value) {
     else if (!strcmp(key, "threads")) opt_threads = value;
     else if (!strcmp(key, "force_generic")) opt_force_generic = value;
     else if (!strcmp(key, "ept")) opt_ept = value;
+    else if (!strcmp(key, "rows_per_warp")) opt_rpw = value;   // backward, one-warp rows: 0 auto, 1 off, 2..4 forced
     else return fail(AGB_ERR_INVALID_ARG, "unknown option '%s'", key);
     return AGB_OK;
 }

@@ -28,7 +28,8 @@ struct PipeGeom {
     int hidden;
     int nvec;           // 16-byte vectors per row
     int row_bytes;
-    int rows_per_tile;  // row groups per CTA
+    int rows_per_tile;  // rows per tile (= row groups per CTA, times rows_per_warp)
+    int rows_per_warp;  // > 1 only in the backward with one-warp rows: rows a warp handles per tile (else 1)
     int group_threads;  // threads per row, multiple of 32
     int stages;
     int tile_stride;    // bytes between the staged arrays inside one stage
@@ -360,7 +361,94 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
 
     long long k = 0;
     bool aborted = false;
-    for (; k < my_tiles; ++k) {
+    const int RW = g.rows_per_warp > 1 ? g.rows_per_warp : 1;
+    if (RW > 1) {
+        // Short rows owned by ONE warp each (G == 32): a warp takes RW consecutive rows of the tile one after
+        // the other with no block-wide step in between -- its shuffle sum is already the row's total -- so the
+        // barrier, the wait and the refill are paid once per tile of nwarps * RW rows instead of once per row.
+        for (; k < my_tiles; ++k) {
+            const int slot = static_cast<int>(k % S);
+            const uint32_t parity = static_cast<uint32_t>((k / S) & 1);
+            if (!mbar_wait_bounded(&s_full[slot], parity)) *s_abort = 1;
+            const long long row0 = (first + k * stride) * g.rows_per_tile + static_cast<long long>(warp) * RW;
+            const unsigned char* tile_base = ring + static_cast<size_t>(slot) * g.stage_stride +
+                                             static_cast<size_t>(warp) * RW * g.row_bytes;
+            for (int j = 0; j < RW; ++j) {
+                const long long row = row0 + j;
+                if (row >= g.rows) break;
+                const float rs = a.rstd[row];
+                const uint4* sx = reinterpret_cast<const uint4*>(tile_base + static_cast<size_t>(j) * g.row_bytes);
+                const uint4* sg = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(sx) + g.tile_stride);
+                const uint4* sa = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(sx) + 2 * static_cast<size_t>(g.tile_stride));
+                double d[4] = {0.0, 0.0, 0.0, 0.0};
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const int v = lane + i * 32;
+                    if (FULL || v < g.nvec) {
+                        float2 xv[NP], gv[NP];
+                        Pairs<T>::unpack(sx[v], xv);
+                        Pairs<T>::unpack(sg[v], gv);
+                        if (HAS_GAMMA) {
+                            float2 wv[NP];
+                            load_gamma<T>(s_gamma, g.nvec, v, wv);
+#pragma unroll
+                            for (int e = 0; e < NP; ++e) gv[e] = mul2(gv[e], wv[e]);
+                        }
+#pragma unroll
+                        for (int e = 0; e < NP; ++e) {
+                            const float2 p = mul2(gv[e], xv[e]);
+                            d[(2 * e) & 3] += static_cast<double>(p.x);
+                            d[(2 * e + 1) & 3] += static_cast<double>(p.y);
+                        }
+                    }
+                }
+                const float dot = static_cast<float>(warp_sum((d[0] + d[1]) + (d[2] + d[3])));
+                const float2 dot2 = splat(dot), rs2 = splat(rs), r22 = splat(mul_rn(rs, rs));
+                uint4* gdx = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.dx) + row * g.row_bytes);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const int v = lane + i * 32;
+                    if (FULL || v < g.nvec) {
+                        float2 xv[NP], gv[NP], ov[NP], wv[NP];
+                        Pairs<T>::unpack(sx[v], xv);
+                        Pairs<T>::unpack(sg[v], gv);
+                        if (HAS_GAMMA) load_gamma<T>(s_gamma, g.nvec, v, wv);
+#pragma unroll
+                        for (int e = 0; e < NP; ++e) {
+                            const float2 dy = HAS_GAMMA ? mul2(gv[e], wv[e]) : gv[e];
+                            float2 t = mul2(xv[e], r22);
+                            t = mul2(t, dot2);
+                            t = POW2 ? mul2(t, div_h.dinv) : div_h(t);
+                            t = sub2_after_mul(dy, t);
+                            ov[e] = mul2(rs2, t);
+                            if (HAS_GAMMA) {
+                                const float2 q = mul2(gv[e], mul2(xv[e], rs2));
+                                acc[i * EPV + 2 * e] += static_cast<double>(q.x);
+                                acc[i * EPV + 2 * e + 1] += static_cast<double>(q.y);
+                            }
+                        }
+                        if (a.add_mode == 2) {
+#pragma unroll
+                            for (int e = 0; e < NP; ++e) ov[e] = add2_after_mul(ov[e], gv[e]);
+                        } else if (staged_add) {
+                            float2 av[NP];
+                            Pairs<T>::unpack(sa[v], av);
+#pragma unroll
+                            for (int e = 0; e < NP; ++e) ov[e] = add2_after_mul(ov[e], av[e]);
+                        }
+                        store_vec_streaming(gdx + v, Pairs<T>::pack(ov));
+                    }
+                }
+            }
+            __syncthreads();   // every warp is done with the slot
+            if (*s_abort) { aborted = true; break; }
+            if (tid == 0 && issued < my_tiles) {
+                issue(first + issued * stride, slot);
+                ++issued;
+            }
+        }
+    }
+    for (; RW == 1 && k < my_tiles; ++k) {
         const int slot = static_cast<int>(k % S);
         const uint32_t parity = static_cast<uint32_t>((k / S) & 1);
         const long long row = (first + k * stride) * g.rows_per_tile + grp;
@@ -457,7 +545,8 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
 
     if (HAS_GAMMA && a.partials != nullptr) {
         double* prow = a.partials + static_cast<size_t>(blockIdx.x) * g.hidden;
-        if (g.rows_per_tile == 1) {
+        const int ngroups = blockDim.x / G;   // row groups of this CTA, each with its own column sums
+        if (ngroups == 1) {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int v = tig + i * G;
@@ -472,7 +561,7 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
             // combine the row groups of this CTA in group order, through the (now idle) ring
             __syncthreads();
             double* s_acc = reinterpret_cast<double*>(ring);
-            for (int gi = 0; gi < g.rows_per_tile; ++gi) {
+            for (int gi = 0; gi < ngroups; ++gi) {
                 if (grp == gi) {
 #pragma unroll
                     for (int i = 0; i < VPT; ++i) {
