@@ -2,7 +2,8 @@
 
     python -m cgadimpl_b200.build [--force] [--verbose]
 
-Output: cgadimpl_b200/libagb_cuda.so (in-tree, git-ignored).
+Output: cgadimpl_b200/libagb_cuda.so and, next to it, libagb_cuda.ptxas.log with ptxas' resource usage
+of every kernel (registers, spills, shared memory); both in-tree and git-ignored.
 """
 import os
 import shutil
@@ -13,6 +14,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libagb_cuda.so")
+PTXAS_LOG = os.path.join(PKG, "libagb_cuda.ptxas.log")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -42,16 +44,42 @@ def _sources():
 
 def build(force: bool = False, verbose: bool = False) -> str:
     srcs = _sources()
-    if not force and os.path.exists(LIB) and all(os.path.getmtime(LIB) >= os.path.getmtime(s) for s in srcs):
+    if not force and os.path.exists(LIB) and os.path.exists(PTXAS_LOG) and \
+            all(os.path.getmtime(LIB) >= os.path.getmtime(s) for s in srcs):
         return LIB
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [
-        "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-o", LIB, os.path.join(CSRC, "agb_cuda.cu")]
+    cmd = [_nvcc()] + NVCC_FLAGS + ["-Xptxas", "-v", "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-o", LIB,
+                                    os.path.join(CSRC, "agb_cuda.cu")]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if verbose:
         sys.stderr.write(r.stderr)
     if r.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+    with open(PTXAS_LOG, "w") as f:
+        f.write(r.stderr)
     return LIB
+
+
+def kernel_resources():
+    """{mangled kernel name: {"registers": n, "spill_stores": bytes, "spill_loads": bytes}} from the last build."""
+    import re
+
+    build()
+    out, name = {}, None
+    for line in open(PTXAS_LOG):
+        m = re.search(r"Compiling entry function '(\S+)'", line)
+        if m:
+            name = m.group(1)
+            out[name] = {}
+            continue
+        if name is None:
+            continue
+        m = re.search(r"(\d+) bytes spill stores, (\d+) bytes spill loads", line)
+        if m:
+            out[name]["spill_stores"], out[name]["spill_loads"] = int(m.group(1)), int(m.group(2))
+        m = re.search(r"Used (\d+) registers", line)
+        if m:
+            out[name]["registers"] = int(m.group(1))
+    return out
 
 
 if __name__ == "__main__":

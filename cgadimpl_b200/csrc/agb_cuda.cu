@@ -189,7 +189,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     // take several rows of a tile back to back, so the block-wide barrier is paid once per tile, as long
     // as the ring stays three tiles deep.
     int rpw = 1;
-    if (which == kBwd && G == 32) {
+    if (which == kBwd && G == 32 && vpt * epv == 32) {
         const int want_rpw = static_cast<int>(opt_rpw.load());
         for (int cand = (want_rpw > 0 ? want_rpw : 4); cand >= 2; --cand) {
             if (static_cast<int64_t>(rpt) * cand > rows) continue;
@@ -398,7 +398,25 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
         // elements per thread 8 / 16 / 32  <->  launch bound 1024 / 768 / 512 threads
         constexpr int kEpv = 16 / static_cast<int>(sizeof(T));
         const int ept = p.vpt * kEpv;
-        if (ept == 8) AGB_BWD_BY_FLAGS(8 / kEpv, 1024);
+        if (p.g.rows_per_warp > 1) {
+            // rows-per-warp form (planned only for 32 elements per thread and one-warp rows)
+#define AGB_LAUNCH_MULTI(HG, FU, P2)                                                                              \
+    do {                                                                                                          \
+        AGB_TRY(set_smem(agb::rmsnorm_bwd_staged<T, 32 / kEpv, HG, FU, 512, P2, true>, p.smem));                  \
+        agb::rmsnorm_bwd_staged<T, 32 / kEpv, HG, FU, 512, P2, true><<<p.grid, p.block, p.smem, st>>>(a);         \
+    } while (0)
+#define AGB_MULTI_P2(HG, FU)                        \
+    do {                                            \
+        if (pow2) AGB_LAUNCH_MULTI(HG, FU, true);   \
+        else AGB_LAUNCH_MULTI(HG, FU, false);       \
+    } while (0)
+            if (gamma && p.full) AGB_MULTI_P2(true, true);
+            else if (gamma) AGB_MULTI_P2(true, false);
+            else if (p.full) AGB_MULTI_P2(false, true);
+            else AGB_MULTI_P2(false, false);
+#undef AGB_MULTI_P2
+#undef AGB_LAUNCH_MULTI
+        } else if (ept == 8) AGB_BWD_BY_FLAGS(8 / kEpv, 1024);
         else if (ept == 16) AGB_BWD_BY_FLAGS(16 / kEpv, 768);
         else AGB_BWD_BY_FLAGS(32 / kEpv, 512);
 #undef AGB_BWD_BY_FLAGS

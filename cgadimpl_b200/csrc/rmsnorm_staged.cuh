@@ -314,7 +314,9 @@ struct BwdArgs {
 
 // POW2: hidden is a power of two, so `/ hidden` is an exact multiplication by 2^-k (one
 // instruction instead of the three of the general exact division).
-template <typename T, int VPT, bool HAS_GAMMA, bool FULL, int MAXT, bool POW2>
+// MULTI: the rows-per-warp form for short rows (see the first loop below); a separate instantiation, because
+// two loop bodies in one kernel cost the main one its registers (measured: 800 bytes of spills).
+template <typename T, int VPT, bool HAS_GAMMA, bool FULL, int MAXT, bool POW2, bool MULTI = false>
 __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_constant__ BwdArgs a) {
     constexpr int NP = Pairs<T>::NP;
     constexpr int EPV = 2 * NP;
@@ -361,8 +363,8 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
 
     long long k = 0;
     bool aborted = false;
-    const int RW = g.rows_per_warp > 1 ? g.rows_per_warp : 1;
-    if (RW > 1) {
+    const int RW = MULTI ? g.rows_per_warp : 1;
+    if constexpr (MULTI) {
         // Short rows owned by ONE warp each (G == 32): a warp takes RW consecutive rows of the tile one after
         // the other with no block-wide step in between -- its shuffle sum is already the row's total -- so the
         // barrier, the wait and the refill are paid once per tile of nwarps * RW rows instead of once per row.
@@ -448,7 +450,7 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
             }
         }
     }
-    for (; RW == 1 && k < my_tiles; ++k) {
+    for (; !MULTI && k < my_tiles; ++k) {
         const int slot = static_cast<int>(k % S);
         const uint32_t parity = static_cast<uint32_t>((k / S) & 1);
         const long long row = (first + k * stride) * g.rows_per_tile + grp;
