@@ -167,8 +167,13 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     // measured 4.5 -> 5.4-6.4 TB/s in fp32 when it gets the full thread count)
     const bool light = !heavy && which == kFwd && elem == 4;
     const int max_resident = light && !want_ctas && !opt_threads.load() ? 512 : 2048;
+    // The forward with the fused residual add (two arrays in, two out) is an exception, measured on the
+    // 32-layer stack shape: ONE CTA per SM streams best -- bf16 with the usual tile (6.4 against 6.2 TB/s),
+    // fp32 with a single row group and a two-slot ring (6.45-6.55 against 5.9 TB/s; a third slot brings it
+    // back down).
+    const bool fused_fwd = which == kFwd && narr == 2 && !want_ctas && (elem == 2 || G >= 256);
     int rpt = 0, ctas = 0, S = 0, best = 0;
-    for (int c = (want_ctas ? want_ctas : 1); c <= (want_ctas ? want_ctas : 4); ++c)
+    for (int c = (want_ctas ? want_ctas : 1); c <= (want_ctas ? want_ctas : (fused_fwd ? 1 : 4)); ++c)
         for (int r = target / G > 0 ? target / G : 1; r >= 1; --r) {
             if (r > rows && r > 1) continue;
             const int blk = r * G;
@@ -180,6 +185,10 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
             if (better) { best = blk * c; rpt = r; ctas = c; S = st; }
             break;  // the largest tile that fits for this CTA count
         }
+    // (fused-add forward, fp32, wide rows: a single row group and a two-slot ring, see above)
+    if (fused_fwd && elem == 4 && G >= 256 && !opt_threads.load() && stages_for(1, 1) >= 2) {
+        rpt = 1; ctas = 1; S = 2;
+    }
     if (rpt == 0) return;
     const int want_stages = static_cast<int>(opt_stages.load());
     if (want_stages >= 2 && want_stages < S) S = want_stages;
