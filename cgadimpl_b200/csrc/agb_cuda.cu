@@ -171,7 +171,8 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     // 32-layer stack shape: ONE CTA per SM streams best -- bf16 with the usual tile (6.4 against 6.2 TB/s),
     // fp32 with a single row group and a two-slot ring (6.45-6.55 against 5.9 TB/s; a third slot brings it
     // back down).
-    const bool fused_fwd = which == kFwd && narr == 2 && !want_ctas && (elem == 2 || G >= 256);
+    // (!heavy: the LayerNorm backward also plans as kFwd with two arrays, and one CTA per SM halves it)
+    const bool fused_fwd = !heavy && which == kFwd && narr == 2 && !want_ctas && (elem == 2 || G >= 256);
     int rpt = 0, ctas = 0, S = 0, best = 0;
     for (int c = (want_ctas ? want_ctas : 1); c <= (want_ctas ? want_ctas : (fused_fwd ? 1 : 4)); ++c)
         for (int r = target / G > 0 ? target / G : 1; r >= 1; --r) {
@@ -703,13 +704,21 @@ int agb_set_option(const char* key, int64_t value) {
 
 int agb_describe_launch(int which, int64_t rows, int64_t hidden, int dtype, int fused_add, int64_t out[6]) {
     AGB_TRY(check_common(rows, hidden, dtype));
-    if (!out || which < 0 || which > 2) return fail(AGB_ERR_INVALID_ARG, "bad arguments");
+    if (!out || which < 0 || which > 5) return fail(AGB_ERR_INVALID_ARG, "bad arguments");
     const DevInfo* d;
     AGB_TRY(device_info(&d));
     Plan p;
     const int elem = dtype == AGB_F32 ? 4 : 2;
-    const int narr = which == kFwd ? (fused_add ? 2 : 1) : (which == kBwd ? (fused_add == 1 ? 3 : 2) : 2);
-    plan_launch(static_cast<Which>(which), rows, hidden, elem, narr, 1, *d, &p);
+    if (which <= 2) {
+        const int narr = which == kFwd ? (fused_add ? 2 : 1) : (which == kBwd ? (fused_add == 1 ? 3 : 2) : 2);
+        plan_launch(static_cast<Which>(which), rows, hidden, elem, narr, 1, *d, &p);
+    } else if (which == 3) {   // the same calls as launch_ln_fwd / launch_ln_bwd / launch_ln_jvp
+        plan_launch(kFwd, rows, hidden, elem, 1, 0, *d, &p, 0, true);
+    } else if (which == 4) {
+        plan_launch(kFwd, rows, hidden, elem, fused_add == 1 ? 3 : 2, 0, *d, &p, 0, true);
+    } else {
+        plan_launch(kJvp, rows, hidden, elem, 2, 0, *d, &p, 0, true);
+    }
     if (p.generic) {
         out[0] = generic_grid(rows, *d); out[1] = agb::kGenericThreads; out[2] = 0; out[3] = 0; out[4] = 1; out[5] = 1;
     } else {

@@ -292,7 +292,7 @@ def set_option(key, value):
 
 def describe_launch(which, rows, hidden, dtype, fused_add=0):
     out = (C.c_int64 * 6)()
-    code = {"fwd": 0, "bwd": 1, "jvp": 2}[which]
+    code = {"fwd": 0, "bwd": 1, "jvp": 2, "ln_fwd": 3, "ln_bwd": 4, "ln_jvp": 5}[which]
     check(_lib.lib().agb_describe_launch(code, rows, hidden, _DT[dtype], fused_add, out))
     keys = ("grid", "block", "smem", "stages", "rows_per_tile", "generic")
     return dict(zip(keys, [int(v) for v in out]))

@@ -76,7 +76,8 @@ int agb_set_option(const char* key, int64_t value);
 
 /* Describes the launch the heuristic would make: out[0]=grid, out[1]=block, out[2]=dynamic
  * shared bytes, out[3]=pipeline stages, out[4]=rows per tile, out[5]=1 if the generic
- * (unstaged) kernel is used.  `which`: 0 = forward, 1 = backward, 2 = jvp. */
+ * (unstaged) kernel is used.  `which`: 0 = forward, 1 = backward, 2 = jvp of the RMSNorm layer;
+ * 3, 4, 5 = the same three of LayerNorm. */
 int agb_describe_launch(int which, int64_t rows, int64_t hidden, int dtype, int fused_add, int64_t out[6]);
 
 /* ---- RMSNorm forward ----
