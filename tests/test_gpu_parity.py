@@ -625,3 +625,18 @@ def test_softmax_generic_kernels_agree_bitwise_with_staged(ops):
         ops.set_option("force_generic", 0)
     for a, b in zip(wide, generic):
         assert np.array_equal(host(a), host(b))
+
+
+def test_launch_plans_keep_the_sm_filled(ops):
+    """The launch heuristic's special cases must stay on the kernels they were measured on: the
+    one-CTA-per-SM rule belongs to the fused-add RMSNorm forward; the LayerNorm kernels (planned
+    through the same routine) run several CTAs per SM on the headline shapes."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    for dt, rows, hidden in ((torch.float32, 32768, 4096), (torch.bfloat16, 65536, 8192)):
+        fused = ops.describe_launch("fwd", rows, hidden, dt, fused_add=1)
+        assert fused["generic"] == 0 and fused["grid"] == sms
+        for which in ("ln_fwd", "ln_bwd", "ln_jvp", "bwd", "jvp"):
+            plan = ops.describe_launch(which, rows, hidden, dt)
+            assert plan["generic"] == 0, (which, plan)
+            assert plan["grid"] >= 2 * sms and plan["grid"] % sms == 0, (which, dt, plan)
+            assert plan["grid"] * plan["block"] >= 512 * sms, (which, dt, plan)
