@@ -173,8 +173,13 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     // back down).
     // (!heavy: the LayerNorm backward also plans as kFwd with two arrays, and one CTA per SM halves it)
     const bool fused_fwd = !heavy && which == kFwd && narr == 2 && !want_ctas && (elem == 2 || G >= 256);
+    // The fp32 LayerNorm forward (heavy, one array): two 512-thread CTAs with a two-slot ring beat four
+    // 256-thread ones on every fp32 shape measured (6.1-6.2 against 5.25 TB/s at 32768 x 4096, 5.7 against
+    // 5.1 at hidden 1024); in bf16, where the kernel is bound by instruction issue, four stay ahead.
+    const bool ln_fwd32 = heavy && which == kFwd && narr == 1 && elem == 4;
+    const int c_hi = want_ctas ? want_ctas : (fused_fwd ? 1 : (ln_fwd32 ? 2 : 4));
     int rpt = 0, ctas = 0, S = 0, best = 0;
-    for (int c = (want_ctas ? want_ctas : 1); c <= (want_ctas ? want_ctas : (fused_fwd ? 1 : 4)); ++c)
+    for (int c = (want_ctas ? want_ctas : 1); c <= c_hi; ++c)
         for (int r = target / G > 0 ? target / G : 1; r >= 1; --r) {
             if (r > rows && r > 1) continue;
             const int blk = r * G;
@@ -197,6 +202,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
         const int cap = elem == 4 ? 3 : 2;
         if (S > cap) S = cap;
     }
+    if (ln_fwd32 && ctas > 1 && S > 2) S = 2;
     const int want_stages = static_cast<int>(opt_stages.load());
     if (want_stages >= 2 && want_stages < S) S = want_stages;
     const int block = rpt * G;

@@ -639,4 +639,5 @@ def test_launch_plans_keep_the_sm_filled(ops):
             plan = ops.describe_launch(which, rows, hidden, dt)
             assert plan["generic"] == 0, (which, plan)
             assert plan["grid"] >= 2 * sms and plan["grid"] % sms == 0, (which, dt, plan)
-            assert plan["grid"] * plan["block"] >= 512 * sms, (which, dt, plan)
+            # (the backward holds 32 elements per thread: 128-thread row groups)
+            assert plan["grid"] * plan["block"] >= (256 if which == "bwd" else 512) * sms, (which, dt, plan)
