@@ -358,6 +358,78 @@ def run_op(args, rank):
 
 
 # --------------------------------------------------------------------------- GPU arm
+def run_single_process(args):
+    """--single-process --gpus N: ONE host process drives N GPUs through the C-ABI executor of
+    include/agb/agb_shard.h (weak scaling, the default workload's rows on every GPU); the dgamma
+    exchange is the executor's peer-sum kernel instead of an NCCL all-reduce.  Device-timed per shard
+    stream, max over shards.  Kernel-only line: no e2e, no CPU leg."""
+    import torch
+
+    from cgadimpl_b200 import ops
+    from cgadimpl_b200.shard_executor import ShardExecutor
+
+    n = args.gpus
+    if torch.cuda.device_count() < n:
+        raise SystemExit(f"--single-process --gpus {n}: only {torch.cuda.device_count()} device(s) visible")
+    rows, hidden, dtype_name, eps = WORKLOADS[args.workload]
+    dtype = getattr(torch, dtype_name)
+    elem = 4 if dtype == torch.float32 else 2
+    xs, gys, gammas, ys, dxs, rstds, dgs = [], [], [], [], [], [], []
+    for d in range(n):
+        dev = torch.device("cuda", d)
+        gen = torch.Generator(device=dev).manual_seed(1000 * d)
+        xs.append(torch.randn(rows, hidden, device=dev, generator=gen, dtype=torch.float32).to(dtype))
+        gys.append(torch.randn(rows, hidden, device=dev, generator=gen, dtype=torch.float32).to(dtype))
+        ggen = torch.Generator(device=dev).manual_seed(7)
+        gammas.append((1 + 0.02 * torch.randn(hidden, device=dev, generator=ggen)).to(dtype))
+        ys.append(torch.empty_like(xs[-1]))
+        dxs.append(torch.empty_like(xs[-1]))
+        rstds.append(torch.empty(rows, dtype=torch.float32, device=dev))
+        dgs.append(torch.empty(hidden, dtype=torch.float32, device=dev))
+    for d in range(n):
+        torch.cuda.synchronize(d)
+    with ShardExecutor(list(range(n)), hidden) as ex:
+        io, h, dt = ex.prepare(xs, gammas, gys, ys, rstds, dxs, dgs)
+        for _ in range(args.warmup):
+            ex.run_prepared(io, h, eps, dt)
+        ex.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        time.sleep(0.3)
+        t0 = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+        t1 = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+        launches0 = ops.launch_count()
+        for d in range(n):
+            t0[d].record(ex.stream(d))
+        for _ in range(args.steps):
+            ex.run_prepared(io, h, eps, dt)
+        for d in range(n):
+            t1[d].record(ex.stream(d))
+        ex.synchronize()
+        launches = ops.launch_count() - launches0
+        elapsed_ms = max(t0[d].elapsed_time(t1[d]) for d in range(n))
+        time.sleep(0.2)
+        clocks = sampler.stop()
+    for d in dgs[1:]:
+        assert torch.equal(d.cpu(), dgs[0].cpu()), "shards disagree on dgamma"
+    value = rows * n * args.steps / (elapsed_ms / 1e3)
+    bpr = bytes_per_row(hidden, elem)
+    peak, peak_kind = measured_peak()
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "rows_per_gpu": rows, "global_rows": rows * n, "hidden": hidden,
+                   "io_dtype": dtype_name, "eps": eps,
+                   "parallelism": f"rows{n}, one host process (agb_shard_run_fwd_bwd, peer-sum dgamma exchange)",
+                   "l2": "inputs+outputs per step (>= 2 GB per GPU) exceed the 126 MB L2; no flush needed"},
+        "hbm_gbs": value / n * bpr / 1e9, "bytes_per_row": bpr, "gpu_launches": launches, "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": value / n * bpr / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": value / n * bpr / 1e9 / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "kernel": "whole step per GPU (forward + backward + dgamma reduce + peer sum)"},
+        "e2e": None, "cpu_baseline": None}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -368,6 +440,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--single-process", action="store_true",
+                    help="drive --gpus N devices from this one process through the C-ABI shard executor")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
@@ -384,6 +458,11 @@ def main():
         return
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
+        return
+    if args.single_process:
+        if world > 1:
+            raise SystemExit("--single-process is for a plain `python bench.py` launch, not torchrun")
+        run_single_process(args)
         return
 
     import torch

@@ -54,6 +54,25 @@ SIGNATURES = {
 }
 
 
+class ShardIO(C.Structure):
+    """agb_shard_io_t of include/agb/agb_shard.h."""
+    _fields_ = [("x", _vp), ("gamma", _vp), ("gy", _vp), ("dx_add", _vp), ("y", _vp), ("rstd", _vp), ("dx", _vp),
+                ("dgamma", _vp), ("rows", _i64)]
+
+
+# every symbol include/agb/agb_shard.h declares (same library)
+SHARD_SIGNATURES = {
+    "agb_shard_create": (_i, [C.POINTER(_i), _i, _i64, C.POINTER(_vp)]),
+    "agb_shard_count": (_i, [_vp]),
+    "agb_shard_stream": (_i, [_vp, _i, C.POINTER(_vp)]),
+    "agb_shard_run_fwd_bwd": (_i, [_vp, C.POINTER(ShardIO), _i64, _f, _i, _i]),
+    "agb_shard_run_fwd": (_i, [_vp, C.POINTER(ShardIO), _i64, _f, _i]),
+    "agb_shard_run_bwd": (_i, [_vp, C.POINTER(ShardIO), _i64, _i, _i]),
+    "agb_shard_synchronize": (_i, [_vp]),
+    "agb_shard_destroy": (_i, [_vp]),
+}
+
+
 class AgbError(RuntimeError):
     def __init__(self, status, message):
         super().__init__(f"agb status {status}: {message}")
@@ -72,7 +91,7 @@ def lib():
                 f"{LIB_PATH} is missing: build it with `python -m cgadimpl_b200.build` "
                 "(there is no CPU or PyTorch fallback)")
         h = C.CDLL(LIB_PATH)
-        for name, (res, args) in SIGNATURES.items():
+        for name, (res, args) in list(SIGNATURES.items()) + list(SHARD_SIGNATURES.items()):
             fn = getattr(h, name)
             fn.restype = res
             fn.argtypes = args

@@ -1201,3 +1201,4 @@ int agb_reduce_all(int op, const void* x, void* out, int64_t n, int dtype, void*
 }
 
 }  // extern "C"
+#include "agb_shard.cuh"

@@ -1,0 +1,83 @@
+/*
+ * agb_shard.h -- row-sharded RMSNorm forward + VJP over several GPUs of one node, driven from ONE
+ * host process (exported by libagb_cuda.so).
+ *
+ * The path shards by rows: the forward and dx need nothing from other rows; only dgamma, the column
+ * sum of gy * xhat over ALL rows, couples the shards (in cgadimpl it is reduce_for_broadcast inside
+ * vjp_Mul, cgadimpl/src/autodiff/autodiff_vjp_ops.cpp:15-35 and :54-59, over the whole tensor).
+ * Each shard runs agb_rmsnorm_fwd / agb_rmsnorm_bwd on its own device and stream and leaves its
+ * un-rounded fp64 [hidden] column sums in a buffer of the executor.  The exchange is ONE small kernel
+ * per shard that reads every shard's sums with ordinary loads -- over NVLink peer mappings when the
+ * shards sit on different GPUs -- adds them in shard order in fp64 and rounds once to fp32, so every
+ * shard ends with the bit-identical dgamma and the result does not depend on timing.  The kernels are
+ * ordered by CUDA events recorded and waited on from the calling host thread; no kernel waits on
+ * another kernel, nothing spins, there is no multicast load.
+ *
+ * A caller with one process per GPU (torch.distributed, MPI) does not need this header: it calls
+ * agb_rmsnorm_bwd with dgamma_dtype = AGB_F64, all-reduces the [hidden] doubles with its own
+ * collective and finishes with agb_dgamma_finalize.
+ *
+ * Unlike the entry points of agb.h, agb_shard_create / agb_shard_destroy allocate and free device
+ * memory (streams, events, the backward workspace and two fp64 vectors per shard); the run calls
+ * only enqueue work.  An executor is not thread-safe: one host thread drives it at a time.
+ */
+#ifndef AGB_AGB_SHARD_H
+#define AGB_AGB_SHARD_H
+
+#include "agb/agb.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AGB_SHARD_MAX 16
+
+typedef struct agb_shard agb_shard_t;
+
+/* What one shard works on; every pointer is device memory of that shard's device.
+ *   x, gy, y, dx [rows, hidden]; rstd [rows] fp32; gamma [hidden] (a replica per device; NULL = the
+ *   gamma-less rms(x), then dgamma must be NULL); dx_add nullable, same meaning as in
+ *   agb_rmsnorm_bwd; dgamma [hidden] fp32 receives the sum over ALL shards (nullable).
+ *   rows may differ between shards and may be 0 (the shard then contributes zeros). */
+typedef struct {
+    const void* x;
+    const void* gamma;
+    const void* gy;
+    const void* dx_add;
+    void* y;
+    float* rstd;
+    void* dx;
+    float* dgamma;
+    int64_t rows;
+} agb_shard_io_t;
+
+/* Creates an executor with one shard per entry of `devices` (CUDA ordinals).  An ordinal may be
+ * listed more than once: those shards share the GPU, each on its own stream (useful on a one-GPU
+ * machine and in tests).  Distinct devices must be able to map each other's memory
+ * (cudaDeviceCanAccessPeer), otherwise AGB_ERR_UNSUPPORTED.  max_hidden bounds the `hidden` of later
+ * runs and sizes the workspaces.  The caller's current device is restored before returning. */
+int agb_shard_create(const int* devices, int n, int64_t max_hidden, agb_shard_t** out);
+int agb_shard_count(const agb_shard_t* s);
+/* The stream shard i runs on (a cudaStream_t of devices[i]), so that a caller can order its own
+ * copies and kernels before and after a run with events. */
+int agb_shard_stream(const agb_shard_t* s, int i, agb_stream_t* stream);
+
+/* Enqueues, on every shard: forward, VJP, then the dgamma exchange.  io[i] belongs to shard i.
+ * With accumulate_dgamma the summed dgamma is added to the old contents of each io[i].dgamma.
+ * Returns as soon as everything is enqueued. */
+int agb_shard_run_fwd_bwd(agb_shard_t* s, const agb_shard_io_t* io, int64_t hidden, float eps, int dtype,
+                          int accumulate_dgamma);
+/* The two halves, for callers that run other work in between (the forward uses x, gamma, y, rstd;
+ * the backward x, gamma, rstd, gy, dx_add, dx, dgamma). */
+int agb_shard_run_fwd(agb_shard_t* s, const agb_shard_io_t* io, int64_t hidden, float eps, int dtype);
+int agb_shard_run_bwd(agb_shard_t* s, const agb_shard_io_t* io, int64_t hidden, int dtype, int accumulate_dgamma);
+
+/* Waits for every shard's stream and returns the worst device status (see agb_device_status). */
+int agb_shard_synchronize(agb_shard_t* s);
+/* Synchronises, then frees everything the executor owns.  NULL is accepted. */
+int agb_shard_destroy(agb_shard_t* s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AGB_AGB_SHARD_H */

@@ -17,8 +17,8 @@ def lib():
     return _lib.lib()
 
 
-def _declared_symbols():
-    text = open(os.path.join(ROOT, "include", "agb", "agb.h")).read()
+def _declared_symbols(header="agb.h"):
+    text = open(os.path.join(ROOT, "include", "agb", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(agb_[a-z0-9_]+)\s*\(", text)))
 
@@ -29,6 +29,29 @@ def test_header_and_binding_agree(lib):
     assert sorted(_lib.SIGNATURES) == declared
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in agb.h but not exported"
+
+
+def test_shard_header_and_binding_agree(lib):
+    declared = _declared_symbols("agb_shard.h")
+    assert sorted(_lib.SHARD_SIGNATURES) == declared
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in agb_shard.h but not exported"
+
+
+def test_shard_argument_validation_needs_no_device(lib):
+    out = C.c_void_p()
+    devs = (C.c_int * 2)(0, 0)
+    assert lib.agb_shard_create(None, 2, 4096, C.byref(out)) == 1
+    assert lib.agb_shard_create(devs, 0, 4096, C.byref(out)) == 1
+    assert lib.agb_shard_create(devs, 17, 4096, C.byref(out)) == 1
+    assert lib.agb_shard_create(devs, 2, 0, C.byref(out)) == 1
+    assert lib.agb_shard_create(devs, 2, 4096, None) == 1
+    assert out.value is None
+    assert lib.agb_shard_count(None) == 0
+    assert lib.agb_shard_destroy(None) == 0
+    assert lib.agb_shard_synchronize(None) == 1
+    io = (_lib.ShardIO * 1)()
+    assert lib.agb_shard_run_fwd_bwd(None, io, 4096, 1e-5, 0, 0) == 1
 
 
 def test_version_and_strings(lib):
