@@ -388,11 +388,29 @@ def run_single_process(args):
         dgs.append(torch.empty(hidden, dtype=torch.float32, device=dev))
     for d in range(n):
         torch.cuda.synchronize(d)
-    with ShardExecutor(list(range(n)), hidden) as ex:
-        io, h, dt = ex.prepare(xs, gammas, gys, ys, rstds, dxs, dgs)
+    # --replicas: N independent one-GPU executors (no exchange between GPUs): what each GPU does alone while
+    # the others are busy too -- the yardstick for what the exchange and the lock step cost
+    groups = [[d] for d in range(n)] if args.replicas else [list(range(n))]
+    exs = [ShardExecutor(g, hidden) for g in groups]
+    try:
+        for ex in exs:
+            ex.set_deferred_exchange(args.deferred_exchange)
+        pick = lambda seq, g: [seq[d] for d in g]
+        prepared = [ex.prepare(pick(xs, g), pick(gammas, g), pick(gys, g), pick(ys, g), pick(rstds, g), pick(dxs, g),
+                               pick(dgs, g)) for ex, g in zip(exs, groups)]
+        stream_of = {d: ex.stream(i) for ex, g in zip(exs, groups) for i, d in enumerate(g)}
+
+        def step():
+            for ex, (io, h, dt) in zip(exs, prepared):
+                ex.run_prepared(io, h, eps, dt)
+
+        def sync():
+            for ex in exs:
+                ex.synchronize()
+
         for _ in range(args.warmup):
-            ex.run_prepared(io, h, eps, dt)
-        ex.synchronize()
+            step()
+        sync()
         sampler = ClockSampler(0)
         sampler.start()
         time.sleep(0.3)
@@ -400,18 +418,23 @@ def run_single_process(args):
         t1 = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
         launches0 = ops.launch_count()
         for d in range(n):
-            t0[d].record(ex.stream(d))
+            t0[d].record(stream_of[d])
         for _ in range(args.steps):
-            ex.run_prepared(io, h, eps, dt)
+            step()
         for d in range(n):
-            t1[d].record(ex.stream(d))
-        ex.synchronize()
+            t1[d].record(stream_of[d])
+        sync()
         launches = ops.launch_count() - launches0
-        elapsed_ms = max(t0[d].elapsed_time(t1[d]) for d in range(n))
+        per_gpu_ms = [t0[d].elapsed_time(t1[d]) / args.steps for d in range(n)]
+        elapsed_ms = max(per_gpu_ms) * args.steps
         time.sleep(0.2)
         clocks = sampler.stop()
-    for d in dgs[1:]:
-        assert torch.equal(d.cpu(), dgs[0].cpu()), "shards disagree on dgamma"
+    finally:
+        for ex in exs:
+            ex.close()
+    if not args.replicas:
+        for d in dgs[1:]:
+            assert torch.equal(d.cpu(), dgs[0].cpu()), "shards disagree on dgamma"
     value = rows * n * args.steps / (elapsed_ms / 1e3)
     bpr = bytes_per_row(hidden, elem)
     peak, peak_kind = measured_peak()
@@ -421,7 +444,10 @@ def run_single_process(args):
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "rows_per_gpu": rows, "global_rows": rows * n, "hidden": hidden,
                    "io_dtype": dtype_name, "eps": eps,
-                   "parallelism": f"rows{n}, one host process (agb_shard_run_fwd_bwd, peer-sum dgamma exchange)",
+                   "parallelism": (f"{n} independent replicas, one host process, no exchange" if args.replicas else
+                                   f"rows{n}, one host process (agb_shard_run_fwd_bwd, peer-sum dgamma exchange"
+                                   f"{' on side streams' if args.deferred_exchange else ''})"),
+                   "per_gpu_ms_per_step": per_gpu_ms,
                    "l2": "inputs+outputs per step (>= 2 GB per GPU) exceed the 126 MB L2; no flush needed"},
         "hbm_gbs": value / n * bpr / 1e9, "bytes_per_row": bpr, "gpu_launches": launches, "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": value / n * bpr / 1e9, "peak": peak, "unit": "GB/s",
@@ -442,6 +468,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--single-process", action="store_true",
                     help="drive --gpus N devices from this one process through the C-ABI shard executor")
+    ap.add_argument("--deferred-exchange", action="store_true",
+                    help="with --single-process: dgamma exchange on side streams (agb_shard_set_deferred_exchange)")
+    ap.add_argument("--replicas", action="store_true",
+                    help="with --single-process: N independent one-GPU executors, no exchange (a yardstick)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

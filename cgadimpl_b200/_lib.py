@@ -68,6 +68,8 @@ SHARD_SIGNATURES = {
     "agb_shard_run_fwd_bwd": (_i, [_vp, C.POINTER(ShardIO), _i64, _f, _i, _i]),
     "agb_shard_run_fwd": (_i, [_vp, C.POINTER(ShardIO), _i64, _f, _i]),
     "agb_shard_run_bwd": (_i, [_vp, C.POINTER(ShardIO), _i64, _i, _i]),
+    "agb_shard_set_deferred_exchange": (_i, [_vp, _i]),
+    "agb_shard_wait_dgamma": (_i, [_vp]),
     "agb_shard_synchronize": (_i, [_vp]),
     "agb_shard_destroy": (_i, [_vp]),
 }

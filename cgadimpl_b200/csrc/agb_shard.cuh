@@ -7,6 +7,9 @@
 //              | wait bwd[j] for all j | peer-sum kernel -> record done[i]
 // A wait always follows, in host program order, the record it refers to, so it can never see a
 // stale record.  No kernel polls memory that another kernel writes.
+// Deferred mode moves the last line to a second stream per shard and alternates two sum buffers, so
+// that a shard's main stream goes on with the next step without waiting for the slowest shard; it
+// only waits (for the sums it wrote two runs ago to have been read) before overwriting a buffer.
 #pragma once
 #include "agb/agb_shard.h"
 
@@ -34,12 +37,14 @@ struct agb_shard {
     int n = 0;
     int64_t max_hidden = 0;
     size_t ws_bytes = 0;
-    bool done_pending = false;   // the done[] events of an earlier run have been recorded
+    bool deferred = false;       // exchange on the side streams, two sum buffers in turn
+    bool done_recorded[2] = {false, false};   // the done[][b] events have been recorded by an earlier run
+    int turn = 0, newest = -1;   // buffer of the next run / of the latest exchange
     int dev[AGB_SHARD_MAX] = {};
-    cudaStream_t st[AGB_SHARD_MAX] = {};
-    cudaEvent_t ev_bwd[AGB_SHARD_MAX] = {}, ev_done[AGB_SHARD_MAX] = {};
+    cudaStream_t st[AGB_SHARD_MAX] = {}, side[AGB_SHARD_MAX] = {};
+    cudaEvent_t ev_bwd[AGB_SHARD_MAX] = {}, ev_done[AGB_SHARD_MAX][2] = {};
     void* ws[AGB_SHARD_MAX] = {};
-    double* sums[AGB_SHARD_MAX] = {};
+    double* sums[AGB_SHARD_MAX][2] = {};
 };
 
 namespace {
@@ -67,14 +72,18 @@ void shard_free(agb_shard_t* s) {
     for (int i = 0; i < s->n; ++i) {
         if (cudaSetDevice(s->dev[i]) != cudaSuccess) continue;
         if (s->st[i]) cudaStreamSynchronize(s->st[i]);
+        if (s->side[i]) cudaStreamSynchronize(s->side[i]);
     }
     for (int i = 0; i < s->n; ++i) {
         if (cudaSetDevice(s->dev[i]) != cudaSuccess) continue;
         if (s->ws[i]) cudaFree(s->ws[i]);
-        if (s->sums[i]) cudaFree(s->sums[i]);
         if (s->ev_bwd[i]) cudaEventDestroy(s->ev_bwd[i]);
-        if (s->ev_done[i]) cudaEventDestroy(s->ev_done[i]);
+        for (int b = 0; b < 2; ++b) {
+            if (s->sums[i][b]) cudaFree(s->sums[i][b]);
+            if (s->ev_done[i][b]) cudaEventDestroy(s->ev_done[i][b]);
+        }
         if (s->st[i]) cudaStreamDestroy(s->st[i]);
+        if (s->side[i]) cudaStreamDestroy(s->side[i]);
     }
     delete s;
 }
@@ -102,13 +111,15 @@ int shard_create(const int* devices, int n, int64_t max_hidden, agb_shard_t* s) 
         s->n = i + 1;   // shard_free releases what exists so far
         AGB_CUDA(cudaSetDevice(devices[i]));
         AGB_CUDA(cudaStreamCreateWithFlags(&s->st[i], cudaStreamNonBlocking));
+        AGB_CUDA(cudaStreamCreateWithFlags(&s->side[i], cudaStreamNonBlocking));
         AGB_CUDA(cudaEventCreateWithFlags(&s->ev_bwd[i], cudaEventDisableTiming));
-        AGB_CUDA(cudaEventCreateWithFlags(&s->ev_done[i], cudaEventDisableTiming));
+        for (int b = 0; b < 2; ++b) AGB_CUDA(cudaEventCreateWithFlags(&s->ev_done[i][b], cudaEventDisableTiming));
         const size_t wb = agb_rmsnorm_bwd_workspace_bytes(1, max_hidden, AGB_F32);
         if (wb == 0) return fail(AGB_ERR_CUDA, "no workspace size for device %d: %s", devices[i], t_err);
         if (i == 0 || wb < s->ws_bytes) s->ws_bytes = wb;
         AGB_CUDA(cudaMalloc(&s->ws[i], wb));
-        AGB_CUDA(cudaMalloc(reinterpret_cast<void**>(&s->sums[i]), static_cast<size_t>(max_hidden) * sizeof(double)));
+        for (int b = 0; b < 2; ++b)
+            AGB_CUDA(cudaMalloc(reinterpret_cast<void**>(&s->sums[i][b]), static_cast<size_t>(max_hidden) * sizeof(double)));
     }
     return AGB_OK;
 }
@@ -131,34 +142,38 @@ int shard_bwd(agb_shard_t* s, const agb_shard_io_t* io, int64_t hidden, int dtyp
         if (want_dg && !io[i].gamma) return fail(AGB_ERR_INVALID_ARG, "shard %d: dgamma without gamma", i);
         if (want_dg) AGB_TRY(check_ptr(io[i].dgamma, "dgamma", 4));
     }
+    const int b = s->deferred ? (s->turn & 1) : 0;   // the sum buffer of this run
     for (int i = 0; i < s->n; ++i) {
         AGB_CUDA(cudaSetDevice(s->dev[i]));
-        if (want_dg && s->done_pending)   // the other shards may still be reading this shard's previous sums
+        if (want_dg && s->done_recorded[b])   // shards may still be reading what this shard last wrote into buffer b
             for (int j = 0; j < s->n; ++j)
-                if (j != i) AGB_CUDA(cudaStreamWaitEvent(s->st[i], s->ev_done[j], 0));
+                if (j != i || s->deferred) AGB_CUDA(cudaStreamWaitEvent(s->st[i], s->ev_done[j][b], 0));
         if (io[i].rows > 0) {
             int st = agb_rmsnorm_bwd(io[i].x, io[i].gamma, io[i].rstd, io[i].gy, io[i].dx_add, io[i].dx,
-                                     want_dg ? s->sums[i] : nullptr, AGB_F64, 0, want_dg ? s->ws[i] : nullptr,
+                                     want_dg ? s->sums[i][b] : nullptr, AGB_F64, 0, want_dg ? s->ws[i] : nullptr,
                                      want_dg ? s->ws_bytes : 0, io[i].rows, hidden, dtype, s->st[i]);
             if (st != AGB_OK) return st;
         } else if (want_dg) {
-            AGB_CUDA(cudaMemsetAsync(s->sums[i], 0, static_cast<size_t>(hidden) * sizeof(double), s->st[i]));
+            AGB_CUDA(cudaMemsetAsync(s->sums[i][b], 0, static_cast<size_t>(hidden) * sizeof(double), s->st[i]));
         }
         if (want_dg) AGB_CUDA(cudaEventRecord(s->ev_bwd[i], s->st[i]));
     }
     if (!want_dg) return AGB_OK;
     agb::PeerSums src{};
-    for (int j = 0; j < s->n; ++j) src.p[j] = s->sums[j];
+    for (int j = 0; j < s->n; ++j) src.p[j] = s->sums[j][b];
     for (int i = 0; i < s->n; ++i) {
         AGB_CUDA(cudaSetDevice(s->dev[i]));
+        cudaStream_t q = s->deferred ? s->side[i] : s->st[i];
         for (int j = 0; j < s->n; ++j)
-            if (j != i) AGB_CUDA(cudaStreamWaitEvent(s->st[i], s->ev_bwd[j], 0));
-        agb::dgamma_peer_sum_kernel<<<static_cast<unsigned>((hidden + 255) / 256), 256, 0, s->st[i]>>>(
+            if (j != i || s->deferred) AGB_CUDA(cudaStreamWaitEvent(q, s->ev_bwd[j], 0));
+        agb::dgamma_peer_sum_kernel<<<static_cast<unsigned>((hidden + 255) / 256), 256, 0, q>>>(
             src, s->n, static_cast<int>(hidden), io[i].dgamma, accumulate);
         AGB_TRY(after_launch("dgamma_peer_sum"));
-        AGB_CUDA(cudaEventRecord(s->ev_done[i], s->st[i]));
+        AGB_CUDA(cudaEventRecord(s->ev_done[i][b], q));
     }
-    s->done_pending = true;
+    s->done_recorded[b] = true;
+    s->newest = b;
+    if (s->deferred) ++s->turn;
     return AGB_OK;
 }
 
@@ -210,12 +225,36 @@ int agb_shard_run_fwd_bwd(agb_shard_t* s, const agb_shard_io_t* io, int64_t hidd
     return shard_bwd(s, io, hidden, dtype, accumulate_dgamma);
 }
 
+int agb_shard_set_deferred_exchange(agb_shard_t* s, int on) {
+    if (!s) return fail(AGB_ERR_INVALID_ARG, "executor is NULL");
+    if ((on != 0) == s->deferred) return AGB_OK;
+    // switching modes changes which stream owns the exchange: settle everything in flight first
+    AGB_TRY(agb_shard_synchronize(s));
+    s->deferred = on != 0;
+    s->done_recorded[0] = s->done_recorded[1] = false;
+    s->turn = 0;
+    s->newest = -1;
+    return AGB_OK;
+}
+
+int agb_shard_wait_dgamma(agb_shard_t* s) {
+    if (!s) return fail(AGB_ERR_INVALID_ARG, "executor is NULL");
+    if (!s->deferred || s->newest < 0) return AGB_OK;   // immediate mode: the shard streams already hold it
+    DeviceRestore restore;
+    for (int i = 0; i < s->n; ++i) {
+        AGB_CUDA(cudaSetDevice(s->dev[i]));
+        AGB_CUDA(cudaStreamWaitEvent(s->st[i], s->ev_done[i][s->newest], 0));
+    }
+    return AGB_OK;
+}
+
 int agb_shard_synchronize(agb_shard_t* s) {
     if (!s) return fail(AGB_ERR_INVALID_ARG, "executor is NULL");
     DeviceRestore restore;
     for (int i = 0; i < s->n; ++i) {
         AGB_CUDA(cudaSetDevice(s->dev[i]));
         AGB_CUDA(cudaStreamSynchronize(s->st[i]));
+        AGB_CUDA(cudaStreamSynchronize(s->side[i]));
     }
     int worst = AGB_OK;
     for (int i = 0; i < s->n; ++i) {

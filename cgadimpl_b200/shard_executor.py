@@ -90,6 +90,13 @@ class ShardExecutor:
     def prepare(self, xs, gammas, gys, ys, rstds, dxs, dgammas, dx_adds=None):
         return self._io(xs, gammas, gys, ys, rstds, dxs, dgammas, [None] * len(self.devices) if dx_adds is None else dx_adds)
 
+    def set_deferred_exchange(self, on):
+        """Run the dgamma exchange on side streams (see agb_shard_set_deferred_exchange)."""
+        check(_lib.lib().agb_shard_set_deferred_exchange(self._h, int(bool(on))))
+
+    def wait_dgamma(self):
+        check(_lib.lib().agb_shard_wait_dgamma(self._h))
+
     def synchronize(self):
         check(_lib.lib().agb_shard_synchronize(self._h))
 

@@ -72,6 +72,16 @@ int agb_shard_run_fwd_bwd(agb_shard_t* s, const agb_shard_io_t* io, int64_t hidd
 int agb_shard_run_fwd(agb_shard_t* s, const agb_shard_io_t* io, int64_t hidden, float eps, int dtype);
 int agb_shard_run_bwd(agb_shard_t* s, const agb_shard_io_t* io, int64_t hidden, int dtype, int accumulate_dgamma);
 
+/* Deferred exchange (off by default).  In the default mode the dgamma exchange runs on the shard streams,
+ * so after a run each shard's stream holds its final dgamma -- and every shard waits, in every run, for
+ * the slowest one.  With on != 0 the exchange runs on a second stream per shard with two alternating sum
+ * buffers: a shard's stream goes straight on to the next run and only waits, before its backward, until
+ * the sums it wrote two runs ago have been read.  dgamma is then final on the shard streams only after
+ * agb_shard_wait_dgamma (which makes every shard stream wait for the latest exchange; enqueue-only) or
+ * after agb_shard_synchronize.  Switching modes synchronises the executor. */
+int agb_shard_set_deferred_exchange(agb_shard_t* s, int on);
+int agb_shard_wait_dgamma(agb_shard_t* s);
+
 /* Waits for every shard's stream and returns the worst device status (see agb_device_status). */
 int agb_shard_synchronize(agb_shard_t* s);
 /* Synchronises, then frees everything the executor owns.  NULL is accepted. */

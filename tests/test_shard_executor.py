@@ -35,7 +35,8 @@ def _bounds(rows_per_shard):
     return [(int(edges[i]), int(edges[i + 1])) for i in range(len(rows_per_shard))]
 
 
-def _run_sharded(devices, rows_per_shard, hidden, eps, seed, dtype=torch.float32, steps=1, accumulate=False):
+def _run_sharded(devices, rows_per_shard, hidden, eps, seed, dtype=torch.float32, steps=1, accumulate=False,
+                 deferred=False):
     from cgadimpl_b200.shard_executor import ShardExecutor
 
     rows = int(sum(rows_per_shard))
@@ -48,6 +49,7 @@ def _run_sharded(devices, rows_per_shard, hidden, eps, seed, dtype=torch.float32
         torch.cuda.synchronize(d)
     with ShardExecutor(devices, hidden) as ex:
         assert len(ex) == len(devices)
+        ex.set_deferred_exchange(deferred)
         for _ in range(steps):   # repeated runs reuse the executor's fp64 buffers: the done-event path
             ys, rstds, dxs, dgs = ex.fwd_bwd(xs, gammas, gys, eps, dgammas=dgammas, accumulate_dgamma=accumulate)
         ex.synchronize()
@@ -74,15 +76,46 @@ def test_shards_on_one_gpu_equal_the_single_call_and_the_oracle(ops, rows_per_sh
     assert_close(dx.cpu().numpy(), ref["dx"], F32_RTOL, F32_ATOL, "dx vs oracle")
 
 
-def test_repeated_runs_and_accumulation(ops):
-    hidden, eps, steps = 1024, 1e-6, 3
-    (x, gamma, gy), y, rstd, dx, dgs = _run_sharded([0, 0], (300, 212), hidden, eps, seed=5, steps=steps, accumulate=True)
+@pytest.mark.parametrize("deferred", [False, True])
+def test_repeated_runs_and_accumulation(ops, deferred):
+    """Several runs through one executor: the sum buffers are reused (one in the immediate mode, two in turn
+    with the exchange deferred to the side streams), guarded by the done events."""
+    hidden, eps, steps = 1024, 1e-6, 5
+    (x, gamma, gy), y, rstd, dx, dgs = _run_sharded([0, 0, 0], (300, 112, 100), hidden, eps, seed=5, steps=steps,
+                                                    accumulate=True, deferred=deferred)
     ref = O.rmsnorm_fwd_bwd(x, gamma, gy, eps, O.RED_F64)
     want = np.float32(0.5)
-    for _ in range(steps):   # dgamma started at 0.5 and received the same sum three times, rounded each time
+    for _ in range(steps):   # dgamma started at 0.5 and received the same sum `steps` times, rounded each time
         want = (want + ref["dgamma"]).astype(np.float32)
     assert_close(dgs[0].cpu().numpy(), want, F32_RTOL, 2e-6, "accumulated dgamma")
-    assert torch.equal(dgs[0], dgs[1])
+    assert torch.equal(dgs[0], dgs[1]) and torch.equal(dgs[0], dgs[2])
+
+
+def test_deferred_exchange_is_ordered_by_wait_dgamma(ops):
+    """With the exchange on the side streams, a reader on a shard's own stream is ordered after it by
+    wait_dgamma(): copy dgamma on that stream right after, without a host synchronisation in between."""
+    from cgadimpl_b200.shard_executor import ShardExecutor
+
+    hidden, eps = 2048, 1e-5
+    x, gamma, gy = make_inputs(4096, hidden, seed=8)
+    xs, gys = _split(x, [(0, 3000), (3000, 4096)], [0, 0]), _split(gy, [(0, 3000), (3000, 4096)], [0, 0])
+    gammas = [torch.from_numpy(gamma).cuda() for _ in range(2)]
+    dgs = [torch.zeros(hidden, device="cuda") for _ in range(2)]
+    torch.cuda.synchronize()
+    with ShardExecutor([0, 0], hidden) as ex:
+        ex.set_deferred_exchange(True)
+        ex.fwd_bwd(xs, gammas, gys, eps, dgammas=dgs)
+        ex.wait_dgamma()
+        with torch.cuda.stream(ex.stream(1)):
+            seen = dgs[1].clone()
+        ex.synchronize()
+        ex.set_deferred_exchange(False)      # and back: the immediate mode gives the same bits
+        again = [torch.zeros(hidden, device="cuda") for _ in range(2)]
+        ex.fwd_bwd(xs, gammas, gys, eps, dgammas=again)
+        ex.synchronize()
+    ref = O.rmsnorm_fwd_bwd(x, gamma, gy, eps, O.RED_F64)
+    assert_close(seen.cpu().numpy(), ref["dgamma"], F32_RTOL, F32_ATOL, "dgamma read on the shard stream")
+    assert torch.equal(seen, dgs[0]) and torch.equal(seen, again[0]) and torch.equal(seen, again[1])
 
 
 def test_bf16_shards(ops):
@@ -125,12 +158,14 @@ def test_without_gamma_and_argument_errors(ops):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("deferred", [False, True])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_two_devices_exchange_over_peer_mappings(ops, dtype):
+def test_two_devices_exchange_over_peer_mappings(ops, dtype, deferred):
     hidden, eps = 4096, 1e-5
     n = min(torch.cuda.device_count(), 4)
     rows_per_shard = [1000 + 13 * i for i in range(n)]
-    (x, gamma, gy), y, rstd, dx, dgs = _run_sharded(list(range(n)), rows_per_shard, hidden, eps, seed=21, dtype=dtype, steps=2)
+    (x, gamma, gy), y, rstd, dx, dgs = _run_sharded(list(range(n)), rows_per_shard, hidden, eps, seed=21, dtype=dtype, steps=4,
+                                                    deferred=deferred)
     xd, gd, gyd = (torch.from_numpy(a).cuda().to(dtype) for a in (x, gamma, gy))
     y1, rstd1 = ops.rmsnorm_fwd(xd, gd, eps)
     dx1, dg1 = ops.rmsnorm_bwd(xd, gd, rstd1, gyd)
