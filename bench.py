@@ -466,6 +466,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "collective"],
+                    help="N > 1: how dgamma crosses the ranks (the library's peer-load kernel, or an NCCL all-reduce)")
     ap.add_argument("--single-process", action="store_true",
                     help="drive --gpus N devices from this one process through the C-ABI shard executor")
     ap.add_argument("--deferred-exchange", action="store_true",
@@ -533,7 +535,7 @@ def main():
     dx = torch.empty_like(x)
     rstd = torch.empty(rows, dtype=torch.float32, device="cuda")
     dgamma = torch.empty(hidden, dtype=torch.float32, device="cuda")
-    ex = RowShardedRMSNorm(hidden, dtype, eps)
+    ex = RowShardedRMSNorm(hidden, dtype, eps, exchange=args.exchange)
 
     def step():
         ex.fwd_bwd(x, gy, gamma, y=y, rstd=rstd, dx=dx, dgamma=dgamma, wait=False)
@@ -672,6 +674,7 @@ def main():
             "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "rows_per_gpu": rows, "global_rows": total_rows, "hidden": hidden,
                        "io_dtype": dtype_name, "eps": eps, "parallelism": f"rows{world}",
+                       "dgamma_exchange": ex.exchange,
                        "l2": "inputs+outputs per step (>= 2 GB) exceed the 126 MB L2; no flush needed",
                        "launch": {"fwd": ops.describe_launch("fwd", rows, hidden, dtype),
                                   "bwd": ops.describe_launch("bwd", rows, hidden, dtype)}},
@@ -680,6 +683,7 @@ def main():
             "e2e": e2e, "cpu_baseline": cpu_baseline,
         }
         print(json.dumps(line), flush=True)
+    ex.close()
     if dist is not None:
         dist.destroy_process_group()
 

@@ -72,6 +72,16 @@ SHARD_SIGNATURES = {
     "agb_shard_wait_dgamma": (_i, [_vp]),
     "agb_shard_synchronize": (_i, [_vp]),
     "agb_shard_destroy": (_i, [_vp]),
+    "agb_peer_create": (_i, [_i, _i, _i64, C.POINTER(_vp), C.c_char_p]),
+    "agb_peer_connect": (_i, [_vp, C.c_char_p]),
+    "agb_peer_acquire": (_i, [_vp, _vp, C.POINTER(_vp)]),
+    "agb_peer_exchange": (_i, [_vp, _vp, _i64, _i, _vp, _vp]),
+    "agb_peer_publish": (_i, [_vp, _vp]),
+    "agb_peer_sum": (_i, [_vp, _vp, _i64, _i, _vp]),
+    "agb_peer_block": (_i, [_vp, C.POINTER(_vp)]),
+    "agb_peer_connect_local": (_i, [_vp, C.POINTER(_vp)]),
+    "agb_peer_disconnect": (_i, [_vp]),
+    "agb_peer_destroy": (_i, [_vp]),
 }
 
 

@@ -704,6 +704,10 @@ int agb_set_option(const char* key, int64_t value) {
     else if (!strcmp(key, "force_generic")) opt_force_generic = value;
     else if (!strcmp(key, "ept")) opt_ept = value;
     else if (!strcmp(key, "rows_per_warp")) opt_rpw = value;   // backward, one-warp rows: 0 auto, 1 off, 2..4 forced
+    else if (!strcmp(key, "peer_poll_limit")) {   // polls before a cross-GPU wait gives up (0 = default, ~2 s)
+        const int v = value > 0 ? static_cast<int>(value < (1 << 24) ? value : (1 << 24)) : (1 << 22);
+        AGB_CUDA(cudaMemcpyToSymbol(agb::g_peer_poll_limit, &v, sizeof(int)));
+    }
     else return fail(AGB_ERR_INVALID_ARG, "unknown option '%s'", key);
     return AGB_OK;
 }
@@ -1202,3 +1206,4 @@ int agb_reduce_all(int op, const void* x, void* out, int64_t n, int dtype, void*
 
 }  // extern "C"
 #include "agb_shard.cuh"
+#include "agb_peer.cuh"

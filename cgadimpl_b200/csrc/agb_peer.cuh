@@ -1,0 +1,269 @@
+// agb_peer.cuh -- the dgamma exchange between ranks that are separate PROCESSES (one per GPU, one
+// node), declared in include/agb/agb_shard.h.  Included at the end of agb_cuda.cu.
+//
+// Each rank owns one device block:
+//   [0,16)   ready[2]  step number whose sums are complete in buffer b   (written by the owner)
+//   [16,32)  ack[2]    step number up to which the OWNER has read everybody's buffer b
+//   [128..)  sums[2][max_hidden] fp64
+// and maps every other rank's block through CUDA IPC (plain peer loads over NVLink, no multicast).
+// Step t uses buffer b = t & 1.  Rank r may overwrite its buffer b at step t once every rank has
+// acknowledged step t-2; it publishes with a release store of t; a reader acquires every rank's
+// ready[b] >= t before it loads the sums.  All waits are bounded polls.
+#pragma once
+#include "agb/agb_shard.h"
+
+namespace agb {
+
+constexpr int kPeerHeaderBytes = 128;
+// (g_peer_poll_limit, the bound of every wait below, lives in agb_device.cuh beside the status word)
+
+struct PeerBlocks {
+    unsigned char* base[AGB_SHARD_MAX];
+};
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ bool poll_until_at_least(const unsigned long long* p, unsigned long long want) {
+    const int limit = g_peer_poll_limit;
+    for (int i = 0; i < limit; ++i) {
+        if (ld_acquire_sys(p) >= want) return true;
+        __nanosleep(500);
+    }
+    return false;
+}
+__device__ __forceinline__ unsigned long long* peer_ready(unsigned char* base, int b) {
+    return reinterpret_cast<unsigned long long*>(base) + b;
+}
+__device__ __forceinline__ unsigned long long* peer_ack(unsigned char* base, int b) {
+    return reinterpret_cast<unsigned long long*>(base) + 2 + b;
+}
+
+// One warp: lane j waits until rank j has acknowledged step `need` on buffer b.
+__global__ void peer_wait_ack_kernel(PeerBlocks blk, int n, int b, unsigned long long need) {
+    const int j = threadIdx.x;
+    if (j < n && !poll_until_at_least(peer_ack(blk.base[j], b), need)) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
+}
+
+// The sums of step t are complete in this rank's buffer b (written by earlier kernels of the same
+// stream): make them visible system-wide, then publish the step number.
+__global__ void peer_publish_kernel(unsigned char* own, int b, unsigned long long t) {
+    __threadfence_system();
+    st_release_sys(peer_ready(own, b), t);
+}
+
+// One CTA: wait for every rank's publication of step t, add the sums in rank order, round once,
+// acknowledge.  On a timeout nothing is written and nothing is acknowledged.
+__global__ void __launch_bounds__(1024) peer_sum_kernel(PeerBlocks blk, int n, int self, int b, unsigned long long t,
+                                                        long long max_hidden, int hidden, float* __restrict__ dgamma,
+                                                        int accumulate) {
+    __shared__ int timed_out;
+    if (threadIdx.x == 0) timed_out = 0;
+    __syncthreads();
+    if (threadIdx.x < n && !poll_until_at_least(peer_ready(blk.base[threadIdx.x], b), t)) timed_out = 1;
+    __syncthreads();
+    if (timed_out) {
+        if (threadIdx.x == 0) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
+        return;
+    }
+    const size_t off = kPeerHeaderBytes + static_cast<size_t>(b) * static_cast<size_t>(max_hidden) * sizeof(double);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        double s = __ldcg(reinterpret_cast<const double*>(blk.base[0] + off) + c);
+        for (int r = 1; r < n; ++r) s += __ldcg(reinterpret_cast<const double*>(blk.base[r] + off) + c);
+        const float v = static_cast<float>(s);
+        dgamma[c] = accumulate ? add_rn(dgamma[c], v) : v;
+    }
+    __syncthreads();   // every load of this CTA has returned (its value was used above)
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        st_release_sys(peer_ack(blk.base[self], b), t);
+    }
+}
+
+}  // namespace agb
+
+struct agb_peer {
+    int rank = 0, world = 1, dev = 0;
+    int64_t max_hidden = 0;
+    unsigned long long step = 0;    // steps completed (exchange enqueued)
+    bool connected = false, acquired = false, published = false;
+    bool ipc_opened[AGB_SHARD_MAX] = {};
+    agb::PeerBlocks blk{};          // blk.base[rank] is this rank's own allocation
+    cudaEvent_t ev_pub = nullptr;
+};
+
+namespace {
+
+size_t peer_block_bytes(int64_t max_hidden) {
+    return agb::kPeerHeaderBytes + 2 * static_cast<size_t>(max_hidden) * sizeof(double);
+}
+
+int peer_check(const agb_peer_t* p, bool need_connected) {
+    if (!p) return fail(AGB_ERR_INVALID_ARG, "exchange is NULL");
+    if (need_connected && !p->connected) return fail(AGB_ERR_INVALID_ARG, "agb_peer_connect has not been called");
+    int dev = -1;
+    AGB_CUDA(cudaGetDevice(&dev));
+    if (dev != p->dev) return fail(AGB_ERR_INVALID_ARG, "current device %d, exchange created on %d", dev, p->dev);
+    return AGB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int agb_peer_create(int rank, int world, int64_t max_hidden, agb_peer_t** out, unsigned char handle[AGB_PEER_HANDLE_BYTES]) {
+    if (!out) return fail(AGB_ERR_INVALID_ARG, "out is NULL");
+    *out = nullptr;
+    if (world < 1 || world > AGB_SHARD_MAX || rank < 0 || rank >= world)
+        return fail(AGB_ERR_INVALID_ARG, "rank %d of %d (at most %d ranks)", rank, world, AGB_SHARD_MAX);
+    if (max_hidden <= 0 || max_hidden > (1LL << 30)) return fail(AGB_ERR_INVALID_ARG, "max_hidden=%lld", (long long)max_hidden);
+    static_assert(sizeof(cudaIpcMemHandle_t) <= AGB_PEER_HANDLE_BYTES, "handle does not fit");
+    agb_peer_t* p = new agb_peer();
+    p->rank = rank;
+    p->world = world;
+    p->max_hidden = max_hidden;
+    cudaError_t e = cudaGetDevice(&p->dev);
+    void* mem = nullptr;
+    if (e == cudaSuccess) e = cudaMalloc(&mem, peer_block_bytes(max_hidden));
+    if (e == cudaSuccess) e = cudaMemset(mem, 0, peer_block_bytes(max_hidden));
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->ev_pub, cudaEventDisableTiming);
+    if (e == cudaSuccess && handle) {
+        cudaIpcMemHandle_t h;
+        memset(handle, 0, AGB_PEER_HANDLE_BYTES);
+        e = cudaIpcGetMemHandle(&h, mem);
+        if (e == cudaSuccess) memcpy(handle, &h, sizeof(h));
+    }
+    if (e != cudaSuccess) {
+        if (mem) cudaFree(mem);
+        if (p->ev_pub) cudaEventDestroy(p->ev_pub);
+        delete p;
+        return cuda_fail(e, "agb_peer_create");
+    }
+    p->blk.base[rank] = static_cast<unsigned char*>(mem);
+    *out = p;
+    return AGB_OK;
+}
+
+int agb_peer_connect(agb_peer_t* p, const unsigned char* all_handles) {
+    AGB_TRY(peer_check(p, false));
+    if (p->connected) return fail(AGB_ERR_INVALID_ARG, "already connected");
+    if (!all_handles && p->world > 1) return fail(AGB_ERR_INVALID_ARG, "all_handles is NULL");
+    for (int r = 0; r < p->world; ++r) {
+        if (r == p->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, all_handles + static_cast<size_t>(r) * AGB_PEER_HANDLE_BYTES, sizeof(h));
+        void* ptr = nullptr;
+        AGB_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        p->blk.base[r] = static_cast<unsigned char*>(ptr);
+        p->ipc_opened[r] = true;
+    }
+    p->connected = true;
+    return AGB_OK;
+}
+
+int agb_peer_block(agb_peer_t* p, void** base) {
+    if (!p || !base) return fail(AGB_ERR_INVALID_ARG, "exchange or output is NULL");
+    *base = p->blk.base[p->rank];
+    return AGB_OK;
+}
+
+int agb_peer_connect_local(agb_peer_t* p, void* const* bases) {
+    AGB_TRY(peer_check(p, false));
+    if (p->connected) return fail(AGB_ERR_INVALID_ARG, "already connected");
+    if (!bases) return fail(AGB_ERR_INVALID_ARG, "bases is NULL");
+    for (int r = 0; r < p->world; ++r) {
+        if (r == p->rank) continue;
+        if (!bases[r]) return fail(AGB_ERR_INVALID_ARG, "bases[%d] is NULL", r);
+        p->blk.base[r] = static_cast<unsigned char*>(bases[r]);
+    }
+    p->connected = true;
+    return AGB_OK;
+}
+
+int agb_peer_acquire(agb_peer_t* p, agb_stream_t stream, double** sums) {
+    AGB_TRY(peer_check(p, true));
+    if (!sums) return fail(AGB_ERR_INVALID_ARG, "sums is NULL");
+    if (p->acquired) return fail(AGB_ERR_INVALID_ARG, "agb_peer_acquire called twice without agb_peer_sum in between");
+    const unsigned long long t = p->step + 1;
+    const int b = static_cast<int>(t & 1);
+    if (p->world > 1 && t > 2) {   // everybody must have read what this rank wrote into buffer b at step t-2
+        agb::peer_wait_ack_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p->blk, p->world, b, t - 2);
+        AGB_TRY(after_launch("peer_wait_ack"));
+    }
+    *sums = reinterpret_cast<double*>(p->blk.base[p->rank] + agb::kPeerHeaderBytes +
+                                      static_cast<size_t>(b) * static_cast<size_t>(p->max_hidden) * sizeof(double));
+    p->acquired = true;
+    p->published = false;
+    return AGB_OK;
+}
+
+int agb_peer_publish(agb_peer_t* p, agb_stream_t stream) {
+    AGB_TRY(peer_check(p, true));
+    if (!p->acquired || p->published) return fail(AGB_ERR_INVALID_ARG, "agb_peer_publish needs one agb_peer_acquire before it");
+    const unsigned long long t = p->step + 1;
+    agb::peer_publish_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(p->blk.base[p->rank], static_cast<int>(t & 1), t);
+    AGB_TRY(after_launch("peer_publish"));
+    p->published = true;
+    return AGB_OK;
+}
+
+int agb_peer_sum(agb_peer_t* p, float* dgamma, int64_t hidden, int accumulate, agb_stream_t stream) {
+    AGB_TRY(peer_check(p, true));
+    if (!p->published) return fail(AGB_ERR_INVALID_ARG, "agb_peer_sum needs agb_peer_publish before it");
+    if (hidden <= 0 || hidden > p->max_hidden)
+        return fail(AGB_ERR_WORKSPACE, "hidden %lld outside (0, max_hidden %lld]", (long long)hidden, (long long)p->max_hidden);
+    AGB_TRY(check_ptr(dgamma, "dgamma", 4));
+    const unsigned long long t = p->step + 1;
+    agb::peer_sum_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        p->blk, p->world, p->rank, static_cast<int>(t & 1), t, static_cast<long long>(p->max_hidden),
+        static_cast<int>(hidden), dgamma, accumulate);
+    AGB_TRY(after_launch("peer_sum"));
+    p->step = t;
+    p->acquired = p->published = false;
+    return AGB_OK;
+}
+
+int agb_peer_exchange(agb_peer_t* p, float* dgamma, int64_t hidden, int accumulate, agb_stream_t stream,
+                      agb_stream_t sum_stream) {
+    AGB_TRY(agb_peer_publish(p, stream));
+    if (sum_stream != stream) {
+        AGB_CUDA(cudaEventRecord(p->ev_pub, static_cast<cudaStream_t>(stream)));
+        AGB_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(sum_stream), p->ev_pub, 0));
+    }
+    return agb_peer_sum(p, dgamma, hidden, accumulate, sum_stream);
+}
+
+int agb_peer_disconnect(agb_peer_t* p) {
+    if (!p) return AGB_OK;
+    DeviceRestore restore;
+    AGB_CUDA(cudaSetDevice(p->dev));
+    AGB_CUDA(cudaDeviceSynchronize());
+    for (int r = 0; r < p->world; ++r)
+        if (p->ipc_opened[r]) {
+            AGB_CUDA(cudaIpcCloseMemHandle(p->blk.base[r]));
+            p->ipc_opened[r] = false;
+            p->blk.base[r] = nullptr;
+        }
+    p->connected = false;
+    return AGB_OK;
+}
+
+int agb_peer_destroy(agb_peer_t* p) {
+    if (!p) return AGB_OK;
+    DeviceRestore restore;
+    cudaSetDevice(p->dev);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < p->world; ++r)
+        if (p->ipc_opened[r]) cudaIpcCloseMemHandle(p->blk.base[r]);
+    if (p->blk.base[p->rank]) cudaFree(p->blk.base[p->rank]);
+    if (p->ev_pub) cudaEventDestroy(p->ev_pub);
+    delete p;
+    return AGB_OK;
+}
+
+}  // extern "C"

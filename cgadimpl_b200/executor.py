@@ -41,7 +41,8 @@ def allreduce_dgamma_f64(dg64, group=None):
 
 
 class RowShardedRMSNorm:
-    def __init__(self, hidden, dtype=torch.float32, eps=1e-5, device=None, group=None, chunk_rows=None, overlap=True):
+    def __init__(self, hidden, dtype=torch.float32, eps=1e-5, device=None, group=None, chunk_rows=None, overlap=True,
+                 exchange="auto"):
         self.hidden = int(hidden)
         self.dtype = dtype
         self.eps = float(eps)
@@ -62,6 +63,29 @@ class RowShardedRMSNorm:
         self._chunk_rows = chunk_rows
         self._slots = None
         self._streams = None
+        # How the fp64 dgamma sums cross the ranks: "peer" = the library's own kernel over CUDA-IPC peer
+        # mappings (PeerExchange; CUDA ranks of one node), "collective" = torch.distributed all-reduce
+        # (NCCL, or gloo on CPU), "auto" = peer where it can be set up on every rank, else collective.
+        if exchange not in ("auto", "peer", "collective"):
+            raise ValueError("exchange must be 'auto', 'peer' or 'collective'")
+        self._peer = None
+        if self.world > 1 and exchange != "collective" and self.device.type == "cuda":
+            from .peer_exchange import PeerExchange
+
+            try:
+                self._peer = PeerExchange(self.hidden, group=group, device=self.device)
+            except RuntimeError:
+                if exchange == "peer":
+                    raise
+        elif exchange == "peer" and self.world > 1:
+            raise ValueError("exchange='peer' needs CUDA ranks")
+        self.exchange = "peer" if self._peer is not None else ("collective" if self.world > 1 else "none")
+
+    def close(self):
+        """Collective when the peer exchange is in use: every rank must call it (before the process group goes)."""
+        if self._peer is not None:
+            self._peer.close()
+            self._peer = None
 
     # ------------------------------------------------------------------ device-resident path
     def _workspace(self, x):
@@ -82,6 +106,11 @@ class RowShardedRMSNorm:
             return y, rstd, dx, dgamma
         if dgamma is None:
             dgamma = torch.empty(self.hidden, dtype=torch.float32, device=self.device)
+        if self._peer is not None and not self.overlap:
+            buf = self._peer.acquire()
+            dx, _ = ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma_f64_ptr=buf, workspace=self._workspace(x))
+            self._peer.exchange(dgamma, self.hidden)
+            return y, rstd, dx, dgamma
         if not self.overlap:
             dx, _ = ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=self._dg64, workspace=self._workspace(x))
             allreduce_dgamma_f64(self._dg64, self.group)
@@ -96,6 +125,16 @@ class RowShardedRMSNorm:
         """Backward on the current stream; all-reduce + rounding of dgamma on the side stream.  The
         caller's stream does not wait for the exchange: call wait_dgamma() before reading dgamma."""
         cur = torch.cuda.current_stream(self.device)
+        if self._peer is not None:
+            # the library's own exchange: wait for the buffer (two steps old), backward, publish on this
+            # stream; the summing kernel, which waits for the other ranks, on the side stream
+            buf = self._peer.acquire(cur)
+            dx, _ = ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma_f64_ptr=buf, workspace=self._workspace(x))
+            self._peer.exchange(dgamma, self.hidden, stream=cur, sum_stream=self._side)
+            ev = torch.cuda.Event()
+            ev.record(self._side)
+            self._newest = ev
+            return dx
         slot = self._turn
         self._turn ^= 1
         buf = self._dg64_ring[slot]

@@ -90,13 +90,28 @@ def bwd_workspace(x):
 
 
 def rmsnorm_bwd(x, gamma, rstd, gy, dx_add=None, dx=None, dgamma=None, accumulate_dgamma=False,
-                workspace=None, dgamma_f64=False):
+                workspace=None, dgamma_f64=False, dgamma_f64_ptr=None):
     """Returns (dx, dgamma).  dgamma is fp32 [hidden] (or the un-rounded fp64 sum when
-    dgamma_f64), None when gamma is None.  dx_add is added to dx (may be gy or dx itself)."""
+    dgamma_f64), None when gamma is None.  dx_add is added to dx (may be gy or dx itself).
+    dgamma_f64_ptr: a raw device address of `hidden` doubles that receives the un-rounded sums
+    instead of a tensor (the buffer of a PeerExchange); dgamma is then returned as None."""
     rows, hidden = _rows_hidden(x)
     dx = torch.empty_like(x) if dx is None else dx
     dg_dtype = AGB_F32
     ws_bytes = 0
+    if dgamma_f64_ptr is not None:
+        if gamma is None or dgamma is not None:
+            raise ValueError("dgamma_f64_ptr needs gamma and excludes dgamma")
+        if workspace is None:
+            workspace = bwd_workspace(x)
+        _same(x, gy, dx_add, dx)
+        _vec(x, hidden, x.dtype, gamma)
+        _vec(x, rows, torch.float32, rstd)
+        check(_lib.lib().agb_rmsnorm_bwd(_p(x), _p(gamma), _p(rstd), _p(gy), _p(dx_add), _p(dx),
+                                         C.c_void_p(int(dgamma_f64_ptr)), AGB_F64, int(bool(accumulate_dgamma)),
+                                         _p(workspace), workspace.numel() * workspace.element_size(), rows, hidden,
+                                         _dt(x), _stream()))
+        return dx, None
     if gamma is not None:
         if dgamma is None:
             dgamma = torch.zeros(hidden, dtype=torch.float64 if dgamma_f64 else torch.float32, device=x.device)

@@ -87,6 +87,48 @@ int agb_shard_synchronize(agb_shard_t* s);
 /* Synchronises, then frees everything the executor owns.  NULL is accepted. */
 int agb_shard_destroy(agb_shard_t* s);
 
+/* ---- the same exchange between PROCESSES (one process per GPU, all on one node) ----
+ * Each rank owns one device block (two fp64 [max_hidden] sum buffers used in turn, a "ready" and an
+ * "ack" counter per buffer) and maps the blocks of all other ranks through CUDA IPC.  Per step:
+ *   agb_peer_acquire   enqueues, on `stream`, a wait until every rank has read what this rank put into
+ *                      the buffer two steps ago, and returns where this step's backward must leave its
+ *                      sums (pass it to agb_rmsnorm_bwd as dgamma with dgamma_dtype = AGB_F64);
+ *   agb_peer_exchange  enqueues, on `stream`, the publication of those sums (a release store of the step
+ *                      number, visible to the peers over NVLink) and, on `sum_stream` (may be the same
+ *                      stream; a second one keeps the caller's stream from waiting for the slowest rank),
+ *                      one kernel that waits for every rank's publication of this step, adds all ranks'
+ *                      sums in rank order in fp64, rounds once to fp32 into `dgamma` (+= with accumulate)
+ *                      and acknowledges the read.  Every rank gets the same bits.
+ * Processes cannot order each other's streams with events, so these kernels wait on counters in
+ * device memory that kernels on OTHER GPUs write.  Every such wait is bounded (about two seconds);
+ * when it runs out the kernel raises the device status word (agb_device_status -> AGB_ERR_TIMEOUT),
+ * leaves dgamma untouched and returns.  Never run two ranks on the same GPU.
+ * Setup is collective: every rank calls agb_peer_create, the 64-byte handles are all-gathered by the
+ * caller's own means (rank order), then every rank calls agb_peer_connect.  Before agb_peer_destroy
+ * every rank must have synchronised its device and passed a barrier, so that nobody still reads a
+ * block that is being freed. */
+#define AGB_PEER_HANDLE_BYTES 64
+typedef struct agb_peer agb_peer_t;
+int agb_peer_create(int rank, int world, int64_t max_hidden, agb_peer_t** out, unsigned char handle[AGB_PEER_HANDLE_BYTES]);
+int agb_peer_connect(agb_peer_t* p, const unsigned char* all_handles /* world * AGB_PEER_HANDLE_BYTES */);
+int agb_peer_acquire(agb_peer_t* p, agb_stream_t stream, double** sums);
+int agb_peer_exchange(agb_peer_t* p, float* dgamma, int64_t hidden, int accumulate, agb_stream_t stream,
+                      agb_stream_t sum_stream);
+/* agb_peer_exchange is these two, with an event between them when the streams differ. */
+int agb_peer_publish(agb_peer_t* p, agb_stream_t stream);
+int agb_peer_sum(agb_peer_t* p, float* dgamma, int64_t hidden, int accumulate, agb_stream_t stream);
+/* Ranks that are threads of ONE process (CUDA IPC cannot map a block into the process that made it):
+ * every rank reads its block's address with agb_peer_block and all of them connect with the array of
+ * addresses instead of handles.  Ranks on the same GPU must publish before any of them sums, so that
+ * no kernel waits for a later launch on its own GPU. */
+int agb_peer_block(agb_peer_t* p, void** base);
+int agb_peer_connect_local(agb_peer_t* p, void* const* bases /* world addresses, rank order */);
+/* Tear-down in two collective phases: every rank unmaps the others' blocks (agb_peer_disconnect, which
+ * synchronises the device first), a barrier, then every rank frees its own (agb_peer_destroy) -- a block
+ * must not be freed while another process still has it mapped. */
+int agb_peer_disconnect(agb_peer_t* p);
+int agb_peer_destroy(agb_peer_t* p);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,6 +1,8 @@
-"""Row-sharded forward + VJP on 2 GPUs (one process per GPU, NCCL): every rank's y and dx equal the
-rows of the single-GPU result bit for bit, and the all-reduced dgamma equals the single-GPU dgamma
-(the partials are exchanged in fp64 and rounded once).  Skipped with fewer than 2 GPUs."""
+"""Row-sharded forward + VJP on 2 GPUs (one process per GPU): every rank's y and dx equal the
+rows of the single-GPU result bit for bit, and the exchanged dgamma equals the single-GPU dgamma
+(the partials are exchanged in fp64 and rounded once) -- with the library's own exchange over
+CUDA-IPC peer mappings ("peer") and with the NCCL all-reduce ("collective").  Skipped with fewer
+than 2 GPUs."""
 import os
 import socket
 
@@ -17,7 +19,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank_main(rank, world, port, rows, hidden, dtype_name, q):
+def _rank_main(rank, world, port, rows, hidden, dtype_name, exchange, q):
     import torch.distributed as dist
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -35,7 +37,8 @@ def _rank_main(rank, world, port, rows, hidden, dtype_name, q):
         gy = torch.randn(rows, hidden, generator=g).to(dtype)
         gamma = (1 + 0.02 * torch.randn(hidden, generator=g)).to(dtype)
         a, b = shard_rows(rows, world, rank)
-        ex = RowShardedRMSNorm(hidden, dtype, 1e-6)
+        ex = RowShardedRMSNorm(hidden, dtype, 1e-6, exchange=exchange)
+        assert ex.exchange == exchange, f"asked for {exchange}, got {ex.exchange}"
         y, rstd, dx, dg = ex.fwd_bwd(x[a:b].cuda().contiguous(), gy[a:b].cuda().contiguous(), gamma.cuda())
         torch.cuda.synchronize()
         ops.device_status()
@@ -56,13 +59,23 @@ def _rank_main(rank, world, port, rows, hidden, dtype_name, q):
         for k in range(5):
             _, want = ops.rmsnorm_bwd(x.cuda(), gam, rs, gy.cuda() * float(k + 1))
             ok = ok and int((outs[k].view(torch.int32) - want.view(torch.int32)).abs().max()) <= 1
+        # the exchange without the side stream (every step waits for its dgamma), accumulating over steps
+        ex2 = RowShardedRMSNorm(hidden, dtype, 1e-6, overlap=False, exchange=exchange)
+        for k in range(4):
+            _, _, _, dg2 = ex2.fwd_bwd(xs, gs, gam)
+        torch.cuda.synchronize()
+        ok = ok and int((dg2.view(torch.int32) - dgs.view(torch.int32)).abs().max()) <= 1
+        ops.device_status()
+        ex2.close()
+        ex.close()
         q.put((rank, ok, same, maxulp))
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("exchange", ["peer", "collective"])
 @pytest.mark.parametrize("dtype_name,rows,hidden", [("float32", 3001, 4096), ("bfloat16", 2048, 8192)])
-def test_two_gpu_sharded_fwd_bwd(dtype_name, rows, hidden):
+def test_two_gpu_sharded_fwd_bwd(dtype_name, rows, hidden, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
@@ -71,7 +84,7 @@ def test_two_gpu_sharded_fwd_bwd(dtype_name, rows, hidden):
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, rows, hidden, dtype_name, q)) for r in range(world)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, rows, hidden, dtype_name, exchange, q)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get() for _ in range(world)]
