@@ -41,10 +41,12 @@ class PeerExchange:
             if not all_ok(st == 0):
                 self._drop_local()
                 raise RuntimeError(f"peer exchange: creating the device block failed on some rank ({err or 'not here'})")
-            mine = torch.frombuffer(bytearray(handle.raw), dtype=torch.uint8).to(self.device)
-            gathered = [torch.empty_like(mine) for _ in range(self.world)]
-            dist.all_gather(gathered, mine, group=group)
-            blob = b"".join(t.cpu().numpy().tobytes() for t in gathered)
+            # gather the handles with a SUM all-reduce of a [world, 64] table that is zero outside this rank's
+            # row: unlike all_gather it exists for every algorithm a caller may have pinned NCCL to
+            table = torch.zeros(self.world, HANDLE_BYTES, dtype=torch.int32, device=self.device)
+            table[self.rank] = torch.frombuffer(bytearray(handle.raw), dtype=torch.uint8).to(self.device, torch.int32)
+            dist.all_reduce(table, op=dist.ReduceOp.SUM, group=group)
+            blob = table.to(torch.uint8).cpu().numpy().tobytes()
             st = lib.agb_peer_connect(self._h, blob)
             err = lib.agb_last_error().decode() if st != 0 else ""
             torch.cuda.synchronize(self.device)
