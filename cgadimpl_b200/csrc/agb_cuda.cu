@@ -14,6 +14,7 @@
 #include "rmsnorm_staged.cuh"
 #include "layernorm_staged.cuh"
 #include "softmax_staged.cuh"
+#include "agb_peer_device.cuh"
 
 namespace {
 
@@ -340,11 +341,22 @@ int launch_fwd(const void* x, const void* r, const void* gamma, void* h, void* y
     return after_launch("rmsnorm_fwd_staged");
 }
 
+// Set by agb_peer_rmsnorm_bwd around its own call of the backward (same thread, same call stack): the
+// column reduction of that call then waits for the peers' acknowledgements and publishes the sums itself.
+thread_local const agb::PeerHook* t_reduce_hook = nullptr;
+thread_local bool t_reduce_hook_used = false;
+
 int launch_dgamma_reduce(const double* partials, int P, int64_t hidden, void* dgamma, int dgamma_dtype,
                          int accumulate, cudaStream_t st) {
     const int mode = dgamma_dtype == AGB_F64 ? (accumulate ? 3 : 2) : (accumulate ? 1 : 0);
     dim3 block(32, 16);
     const int grid = static_cast<int>((hidden + 31) / 32);
+    if (t_reduce_hook && mode == 2) {
+        agb::dgamma_reduce_publish_kernel<<<grid, block, 0, st>>>(partials, P, (int)hidden, static_cast<double*>(dgamma),
+                                                                  *t_reduce_hook);
+        t_reduce_hook_used = true;
+        return after_launch("dgamma_reduce_publish");
+    }
     agb::dgamma_reduce_kernel<<<grid, block, 0, st>>>(partials, P, (int)hidden, dgamma, mode);
     return after_launch("dgamma_reduce");
 }

@@ -11,81 +11,8 @@
 // ready[b] >= t before it loads the sums.  All waits are bounded polls.
 #pragma once
 #include "agb/agb_shard.h"
+#include "agb_peer_device.cuh"
 
-namespace agb {
-
-constexpr int kPeerHeaderBytes = 128;
-// (g_peer_poll_limit, the bound of every wait below, lives in agb_device.cuh beside the status word)
-
-struct PeerBlocks {
-    unsigned char* base[AGB_SHARD_MAX];
-};
-
-__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
-    unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
-    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ bool poll_until_at_least(const unsigned long long* p, unsigned long long want) {
-    const int limit = g_peer_poll_limit;
-    for (int i = 0; i < limit; ++i) {
-        if (ld_acquire_sys(p) >= want) return true;
-        __nanosleep(500);
-    }
-    return false;
-}
-__device__ __forceinline__ unsigned long long* peer_ready(unsigned char* base, int b) {
-    return reinterpret_cast<unsigned long long*>(base) + b;
-}
-__device__ __forceinline__ unsigned long long* peer_ack(unsigned char* base, int b) {
-    return reinterpret_cast<unsigned long long*>(base) + 2 + b;
-}
-
-// One warp: lane j waits until rank j has acknowledged step `need` on buffer b.
-__global__ void peer_wait_ack_kernel(PeerBlocks blk, int n, int b, unsigned long long need) {
-    const int j = threadIdx.x;
-    if (j < n && !poll_until_at_least(peer_ack(blk.base[j], b), need)) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
-}
-
-// The sums of step t are complete in this rank's buffer b (written by earlier kernels of the same
-// stream): make them visible system-wide, then publish the step number.
-__global__ void peer_publish_kernel(unsigned char* own, int b, unsigned long long t) {
-    __threadfence_system();
-    st_release_sys(peer_ready(own, b), t);
-}
-
-// One CTA: wait for every rank's publication of step t, add the sums in rank order, round once,
-// acknowledge.  On a timeout nothing is written and nothing is acknowledged.
-__global__ void __launch_bounds__(1024) peer_sum_kernel(PeerBlocks blk, int n, int self, int b, unsigned long long t,
-                                                        long long max_hidden, int hidden, float* __restrict__ dgamma,
-                                                        int accumulate) {
-    __shared__ int timed_out;
-    if (threadIdx.x == 0) timed_out = 0;
-    __syncthreads();
-    if (threadIdx.x < n && !poll_until_at_least(peer_ready(blk.base[threadIdx.x], b), t)) timed_out = 1;
-    __syncthreads();
-    if (timed_out) {
-        if (threadIdx.x == 0) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
-        return;
-    }
-    const size_t off = kPeerHeaderBytes + static_cast<size_t>(b) * static_cast<size_t>(max_hidden) * sizeof(double);
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        double s = __ldcg(reinterpret_cast<const double*>(blk.base[0] + off) + c);
-        for (int r = 1; r < n; ++r) s += __ldcg(reinterpret_cast<const double*>(blk.base[r] + off) + c);
-        const float v = static_cast<float>(s);
-        dgamma[c] = accumulate ? add_rn(dgamma[c], v) : v;
-    }
-    __syncthreads();   // every load of this CTA has returned (its value was used above)
-    if (threadIdx.x == 0) {
-        __threadfence_system();
-        st_release_sys(peer_ack(blk.base[self], b), t);
-    }
-}
-
-}  // namespace agb
 
 struct agb_peer {
     int rank = 0, world = 1, dev = 0;
@@ -202,6 +129,38 @@ int agb_peer_acquire(agb_peer_t* p, agb_stream_t stream, double** sums) {
     return AGB_OK;
 }
 
+int agb_peer_rmsnorm_bwd(agb_peer_t* p, const void* x, const void* gamma, const float* rstd, const void* gy,
+                         const void* dx_add, void* dx, void* workspace, size_t workspace_bytes, int64_t rows,
+                         int64_t hidden, int dtype, agb_stream_t stream) {
+    AGB_TRY(peer_check(p, true));
+    if (p->acquired) return fail(AGB_ERR_INVALID_ARG, "a step is already open (agb_peer_acquire without agb_peer_sum)");
+    if (!gamma) return fail(AGB_ERR_INVALID_ARG, "gamma is NULL: without gamma there is no dgamma to exchange");
+    if (hidden <= 0 || hidden > p->max_hidden)
+        return fail(AGB_ERR_WORKSPACE, "hidden %lld outside (0, max_hidden %lld]", (long long)hidden, (long long)p->max_hidden);
+    if (rows == 0) {   // no reduction kernel runs for an empty shard: the plain sequence
+        double* sums = nullptr;
+        AGB_TRY(agb_peer_acquire(p, stream, &sums));
+        AGB_TRY(agb_rmsnorm_bwd(x, gamma, rstd, gy, dx_add, dx, sums, AGB_F64, 0, workspace, workspace_bytes, rows, hidden,
+                                dtype, stream));
+        return agb_peer_publish(p, stream);
+    }
+    const unsigned long long t = p->step + 1;
+    const int b = static_cast<int>(t & 1);
+    agb::PeerHook hook{p->blk, p->world, p->rank, b, (p->world > 1 && t > 2) ? t - 2 : 0ull, t};
+    double* sums = reinterpret_cast<double*>(p->blk.base[p->rank] + agb::kPeerHeaderBytes +
+                                             static_cast<size_t>(b) * static_cast<size_t>(p->max_hidden) * sizeof(double));
+    t_reduce_hook = &hook;
+    t_reduce_hook_used = false;
+    const int st = agb_rmsnorm_bwd(x, gamma, rstd, gy, dx_add, dx, sums, AGB_F64, 0, workspace, workspace_bytes, rows, hidden,
+                                   dtype, stream);
+    t_reduce_hook = nullptr;
+    if (st != AGB_OK) return st;
+    if (!t_reduce_hook_used) return fail(AGB_ERR_CUDA, "internal: the backward did not run its column reduction");
+    p->acquired = true;
+    p->published = true;
+    return AGB_OK;
+}
+
 int agb_peer_publish(agb_peer_t* p, agb_stream_t stream) {
     AGB_TRY(peer_check(p, true));
     if (!p->acquired || p->published) return fail(AGB_ERR_INVALID_ARG, "agb_peer_publish needs one agb_peer_acquire before it");
@@ -230,7 +189,7 @@ int agb_peer_sum(agb_peer_t* p, float* dgamma, int64_t hidden, int accumulate, a
 
 int agb_peer_exchange(agb_peer_t* p, float* dgamma, int64_t hidden, int accumulate, agb_stream_t stream,
                       agb_stream_t sum_stream) {
-    AGB_TRY(agb_peer_publish(p, stream));
+    if (!p || !p->published) AGB_TRY(agb_peer_publish(p, stream));   // (agb_peer_rmsnorm_bwd has published already)
     if (sum_stream != stream) {
         AGB_CUDA(cudaEventRecord(p->ev_pub, static_cast<cudaStream_t>(stream)));
         AGB_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(sum_stream), p->ev_pub, 0));

@@ -1,0 +1,138 @@
+// agb_peer_device.cuh -- device side of the cross-process dgamma exchange (host side: agb_peer.cuh;
+// block layout and protocol are described there).
+#pragma once
+#include "agb/agb_shard.h"
+#include "agb_device.cuh"
+
+namespace agb {
+
+constexpr int kPeerHeaderBytes = 128;
+constexpr int kPeerCounterOffset = 32;   // an unsigned int used by the fused reduce kernel to find its last CTA
+// (g_peer_poll_limit, the bound of every wait below, lives in agb_device.cuh beside the status word)
+
+struct PeerBlocks {
+    unsigned char* base[AGB_SHARD_MAX];
+};
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ bool poll_until_at_least(const unsigned long long* p, unsigned long long want) {
+    const int limit = g_peer_poll_limit;
+    for (int i = 0; i < limit; ++i) {
+        if (ld_acquire_sys(p) >= want) return true;
+        __nanosleep(500);
+    }
+    return false;
+}
+__device__ __forceinline__ unsigned long long* peer_ready(unsigned char* base, int b) {
+    return reinterpret_cast<unsigned long long*>(base) + b;
+}
+__device__ __forceinline__ unsigned long long* peer_ack(unsigned char* base, int b) {
+    return reinterpret_cast<unsigned long long*>(base) + 2 + b;
+}
+
+// One warp: lane j waits until rank j has acknowledged step `need` on buffer b.
+__global__ void peer_wait_ack_kernel(PeerBlocks blk, int n, int b, unsigned long long need) {
+    const int j = threadIdx.x;
+    if (j < n && !poll_until_at_least(peer_ack(blk.base[j], b), need)) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
+}
+
+// The sums of step t are complete in this rank's buffer b (written by earlier kernels of the same
+// stream): make them visible system-wide, then publish the step number.
+__global__ void peer_publish_kernel(unsigned char* own, int b, unsigned long long t) {
+    __threadfence_system();
+    st_release_sys(peer_ready(own, b), t);
+}
+
+// One CTA: wait for every rank's publication of step t, add the sums in rank order, round once,
+// acknowledge.  On a timeout nothing is written and nothing is acknowledged.
+__global__ void __launch_bounds__(1024) peer_sum_kernel(PeerBlocks blk, int n, int self, int b, unsigned long long t,
+                                                        long long max_hidden, int hidden, float* __restrict__ dgamma,
+                                                        int accumulate) {
+    __shared__ int timed_out;
+    if (threadIdx.x == 0) timed_out = 0;
+    __syncthreads();
+    if (threadIdx.x < n && !poll_until_at_least(peer_ready(blk.base[threadIdx.x], b), t)) timed_out = 1;
+    __syncthreads();
+    if (timed_out) {
+        if (threadIdx.x == 0) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
+        return;
+    }
+    const size_t off = kPeerHeaderBytes + static_cast<size_t>(b) * static_cast<size_t>(max_hidden) * sizeof(double);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        double s = __ldcg(reinterpret_cast<const double*>(blk.base[0] + off) + c);
+        for (int r = 1; r < n; ++r) s += __ldcg(reinterpret_cast<const double*>(blk.base[r] + off) + c);
+        const float v = static_cast<float>(s);
+        dgamma[c] = accumulate ? add_rn(dgamma[c], v) : v;
+    }
+    __syncthreads();   // every load of this CTA has returned (its value was used above)
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        st_release_sys(peer_ack(blk.base[self], b), t);
+    }
+}
+
+
+// What the backward's final column reduction needs to do the exchange's bookkeeping itself: wait until
+// every rank has acknowledged step need_ack (0: nothing to wait for) before it overwrites the sums, and
+// publish step t once the last CTA has written its columns.
+struct PeerHook {
+    PeerBlocks blk;
+    int n, self, b;
+    unsigned long long need_ack, t;
+};
+
+// dgamma_reduce_kernel (fp64 store form) with the wait in front and the publication behind, so that the
+// exchange adds no kernel to the backward's stream.  Same summation order, same bits.
+__global__ void __launch_bounds__(512) dgamma_reduce_publish_kernel(const double* __restrict__ partials, int P, int hidden,
+                                                                    double* __restrict__ out, PeerHook h) {
+    __shared__ double s[16][33];
+    __shared__ int timed_out;
+    const int cx = threadIdx.x, py = threadIdx.y;
+    const int c = blockIdx.x * 32 + cx;
+    if (cx == 0 && py == 0) timed_out = 0;
+    __syncthreads();
+    if (h.need_ack > 0 && py == 0 && cx < h.n && !poll_until_at_least(peer_ack(h.blk.base[cx], h.b), h.need_ack))
+        timed_out = 1;
+    double v0 = 0.0, v1 = 0.0, v2 = 0.0, v3 = 0.0;
+    if (c < hidden) {
+        int p = py;
+        for (; p + 48 < P; p += 64) {
+            v0 += partials[static_cast<size_t>(p) * hidden + c];
+            v1 += partials[static_cast<size_t>(p + 16) * hidden + c];
+            v2 += partials[static_cast<size_t>(p + 32) * hidden + c];
+            v3 += partials[static_cast<size_t>(p + 48) * hidden + c];
+        }
+        for (; p < P; p += 16) v0 += partials[static_cast<size_t>(p) * hidden + c];
+    }
+    s[py][cx] = (v0 + v1) + (v2 + v3);
+    __syncthreads();
+    if (timed_out) {   // somebody may still be reading the old sums: write nothing, publish nothing
+        if (cx == 0 && py == 0) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
+        return;
+    }
+    if (py == 0 && c < hidden) {
+        double t = s[0][cx];
+#pragma unroll
+        for (int j = 1; j < 16; ++j) t += s[j][cx];
+        out[c] = t;
+        __threadfence();
+    }
+    __syncthreads();
+    if (cx == 0 && py == 0) {
+        unsigned int* counter = reinterpret_cast<unsigned int*>(h.blk.base[h.self] + kPeerCounterOffset);
+        if (atomicAdd(counter, 1u) == gridDim.x - 1) {   // the last CTA: every column is written
+            atomicExch(counter, 0u);
+            __threadfence_system();
+            st_release_sys(peer_ready(h.blk.base[h.self], h.b), h.t);
+        }
+    }
+}
+
+}  // namespace agb

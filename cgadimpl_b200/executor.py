@@ -107,8 +107,8 @@ class RowShardedRMSNorm:
         if dgamma is None:
             dgamma = torch.empty(self.hidden, dtype=torch.float32, device=self.device)
         if self._peer is not None and not self.overlap:
-            buf = self._peer.acquire()
-            dx, _ = ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma_f64_ptr=buf, workspace=self._workspace(x))
+            dx = torch.empty_like(x) if dx is None else dx
+            self._peer.rmsnorm_bwd(x, gamma, rstd, gy, dx, self._workspace(x))
             self._peer.exchange(dgamma, self.hidden)
             return y, rstd, dx, dgamma
         if not self.overlap:
@@ -126,10 +126,10 @@ class RowShardedRMSNorm:
         caller's stream does not wait for the exchange: call wait_dgamma() before reading dgamma."""
         cur = torch.cuda.current_stream(self.device)
         if self._peer is not None:
-            # the library's own exchange: wait for the buffer (two steps old), backward, publish on this
-            # stream; the summing kernel, which waits for the other ranks, on the side stream
-            buf = self._peer.acquire(cur)
-            dx, _ = ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma_f64_ptr=buf, workspace=self._workspace(x))
+            # the library's own exchange: the backward's last kernel waits for the buffer (two steps old) and
+            # publishes the sums; the summing kernel, which waits for the other ranks, runs on the side stream
+            dx = torch.empty_like(x) if dx is None else dx
+            self._peer.rmsnorm_bwd(x, gamma, rstd, gy, dx, self._workspace(x), stream=cur)
             self._peer.exchange(dgamma, self.hidden, stream=cur, sum_stream=self._side)
             ev = torch.cuda.Event()
             ev.record(self._side)

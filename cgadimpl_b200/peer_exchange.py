@@ -70,6 +70,22 @@ class PeerExchange:
         check(_lib.lib().agb_peer_acquire(self._h, C.c_void_p(s.cuda_stream), C.byref(out)))
         return out.value
 
+    def rmsnorm_bwd(self, x, gamma, rstd, gy, dx, workspace, dx_add=None, stream=None):
+        """The VJP of this rank's rows with the exchange's bookkeeping fused into its last kernel
+        (agb_peer_rmsnorm_bwd): no extra launch on the backward's stream.  Follow with exchange()."""
+        from . import ops
+
+        rows, hidden = ops._rows_hidden(x)
+        ops._same(x, gy, dx_add, dx)
+        ops._vec(x, hidden, x.dtype, gamma)
+        ops._vec(x, rows, torch.float32, rstd)
+        s = torch.cuda.current_stream(self.device) if stream is None else stream
+        p = ops._p
+        check(_lib.lib().agb_peer_rmsnorm_bwd(self._h, p(x), p(gamma), p(rstd), p(gy), p(dx_add), p(dx), p(workspace),
+                                              workspace.numel() * workspace.element_size(), rows, hidden, ops._dt(x),
+                                              C.c_void_p(s.cuda_stream)))
+        return dx
+
     def exchange(self, dgamma, hidden, accumulate=False, stream=None, sum_stream=None):
         s = torch.cuda.current_stream(self.device) if stream is None else stream
         q = s if sum_stream is None else sum_stream

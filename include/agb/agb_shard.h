@@ -114,6 +114,14 @@ int agb_peer_connect(agb_peer_t* p, const unsigned char* all_handles /* world * 
 int agb_peer_acquire(agb_peer_t* p, agb_stream_t stream, double** sums);
 int agb_peer_exchange(agb_peer_t* p, float* dgamma, int64_t hidden, int accumulate, agb_stream_t stream,
                       agb_stream_t sum_stream);
+/* agb_peer_acquire + agb_rmsnorm_bwd + agb_peer_publish in one call and WITHOUT extra kernels: the
+ * backward's final column reduction itself waits for the acknowledgements before it overwrites the sum
+ * buffer and publishes the step when its last CTA has written.  Follow it with agb_peer_exchange (which
+ * then only orders the streams and enqueues the summing kernel) or agb_peer_sum.  Arguments as in
+ * agb_rmsnorm_bwd; gamma is required. */
+int agb_peer_rmsnorm_bwd(agb_peer_t* p, const void* x, const void* gamma, const float* rstd, const void* gy,
+                         const void* dx_add, void* dx, void* workspace, size_t workspace_bytes, int64_t rows,
+                         int64_t hidden, int dtype, agb_stream_t stream);
 /* agb_peer_exchange is these two, with an event between them when the streams differ. */
 int agb_peer_publish(agb_peer_t* p, agb_stream_t stream);
 int agb_peer_sum(agb_peer_t* p, float* dgamma, int64_t hidden, int accumulate, agb_stream_t stream);

@@ -79,6 +79,47 @@ def test_two_ranks_in_one_process_sum_in_rank_order(ops):
         _destroy(lib, peers)
 
 
+def test_fused_backward_publishes_and_matches_the_unfused_sequence(ops):
+    """agb_peer_rmsnorm_bwd (wait + publish inside the backward's column reduction) against acquire /
+    backward / publish: same dx, same dgamma bits, over enough steps to reuse both buffers."""
+    from cgadimpl_b200 import ops as O2
+    from cgadimpl_b200._lib import check
+
+    hidden, eps, world, steps = 1024, 1e-6, 2, 6
+    x, gamma, gy = make_inputs(777, hidden, seed=12)
+    cut = 300
+    xs = [torch.from_numpy(x[:cut]).cuda(), torch.from_numpy(x[cut:]).cuda()]
+    gys = [torch.from_numpy(gy[:cut]).cuda(), torch.from_numpy(gy[cut:]).cuda()]
+    gd = torch.from_numpy(gamma).cuda()
+    lib, peers = _make_ranks(world, hidden)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = O2._p
+    try:
+        rstds = [ops.rmsnorm_fwd(xs[r], gd, eps)[1] for r in range(world)]
+        ws = ops.bwd_workspace(xs[1])
+        outs = [torch.zeros(hidden, device="cuda") for _ in range(world)]
+        for k in range(steps):
+            scale = float(k + 1)
+            dxs = []
+            for r in range(world):
+                g = gys[r] * scale
+                dx = torch.empty_like(xs[r])
+                check(lib.agb_peer_rmsnorm_bwd(peers[r], p(xs[r]), p(gd), p(rstds[r]), p(g), None, p(dx), p(ws),
+                                               ws.numel(), xs[r].shape[0], hidden, 0, stream))
+                dxs.append(dx)
+            for r in range(world):
+                check(lib.agb_peer_sum(peers[r], C.c_void_p(outs[r].data_ptr()), hidden, 0, stream))
+            torch.cuda.synchronize()
+            xd, gyd = torch.cat(xs), torch.cat(gys) * scale
+            dx1, dg1 = ops.rmsnorm_bwd(xd, gd, torch.cat(rstds), gyd)
+            assert torch.equal(torch.cat(dxs), dx1)
+            assert torch.equal(outs[0], outs[1])
+            assert int((outs[0].view(torch.int32) - dg1.view(torch.int32)).abs().max()) <= 1, f"step {k}"
+        ops.device_status()
+    finally:
+        _destroy(lib, peers)
+
+
 def test_wait_that_runs_out_reports_timeout_and_leaves_dgamma_untouched(ops):
     from cgadimpl_b200._lib import AgbError, check
 
