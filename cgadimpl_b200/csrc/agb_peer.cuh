@@ -178,7 +178,7 @@ int agb_peer_sum(agb_peer_t* p, float* dgamma, int64_t hidden, int accumulate, a
         return fail(AGB_ERR_WORKSPACE, "hidden %lld outside (0, max_hidden %lld]", (long long)hidden, (long long)p->max_hidden);
     AGB_TRY(check_ptr(dgamma, "dgamma", 4));
     const unsigned long long t = p->step + 1;
-    agb::peer_sum_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+    agb::peer_sum_kernel<<<1, agb::kPeerSumThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         p->blk, p->world, p->rank, static_cast<int>(t & 1), t, static_cast<long long>(p->max_hidden),
         static_cast<int>(hidden), dgamma, accumulate);
     AGB_TRY(after_launch("peer_sum"));

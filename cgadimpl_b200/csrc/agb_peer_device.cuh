@@ -50,11 +50,14 @@ __global__ void peer_publish_kernel(unsigned char* own, int b, unsigned long lon
     st_release_sys(peer_ready(own, b), t);
 }
 
-// One CTA: wait for every rank's publication of step t, add the sums in rank order, round once,
-// acknowledge.  On a timeout nothing is written and nothing is acknowledged.
-__global__ void __launch_bounds__(1024) peer_sum_kernel(PeerBlocks blk, int n, int self, int b, unsigned long long t,
-                                                        long long max_hidden, int hidden, float* __restrict__ dgamma,
-                                                        int accumulate) {
+// One small CTA (256 threads, few registers: it must fit beside a resident CTA of the persistent forward
+// or backward kernel instead of taking an SM from it -- a 1024-thread version delayed the next forward by
+// ~10 us per step): wait for every rank's publication of step t, add the sums in rank order, round
+// once, acknowledge.  On a timeout nothing is written and nothing is acknowledged.
+constexpr int kPeerSumThreads = 256;
+__global__ void __launch_bounds__(kPeerSumThreads) peer_sum_kernel(PeerBlocks blk, int n, int self, int b,
+                                                                   unsigned long long t, long long max_hidden, int hidden,
+                                                                   float* __restrict__ dgamma, int accumulate) {
     __shared__ int timed_out;
     if (threadIdx.x == 0) timed_out = 0;
     __syncthreads();
@@ -65,7 +68,20 @@ __global__ void __launch_bounds__(1024) peer_sum_kernel(PeerBlocks blk, int n, i
         return;
     }
     const size_t off = kPeerHeaderBytes + static_cast<size_t>(b) * static_cast<size_t>(max_hidden) * sizeof(double);
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    // two columns per thread and pass (16-byte loads) when the buffers are 16-byte aligned: max_hidden even
+    const int pairs = (max_hidden % 2 == 0) ? hidden / 2 : 0;
+    for (int q = threadIdx.x; q < pairs; q += blockDim.x) {
+        double2 s = __ldcg(reinterpret_cast<const double2*>(blk.base[0] + off) + q);
+        for (int r = 1; r < n; ++r) {
+            const double2 v = __ldcg(reinterpret_cast<const double2*>(blk.base[r] + off) + q);
+            s.x += v.x;
+            s.y += v.y;
+        }
+        const float v0 = static_cast<float>(s.x), v1 = static_cast<float>(s.y);
+        dgamma[2 * q] = accumulate ? add_rn(dgamma[2 * q], v0) : v0;
+        dgamma[2 * q + 1] = accumulate ? add_rn(dgamma[2 * q + 1], v1) : v1;
+    }
+    for (int c = 2 * pairs + threadIdx.x; c < hidden; c += blockDim.x) {
         double s = __ldcg(reinterpret_cast<const double*>(blk.base[0] + off) + c);
         for (int r = 1; r < n; ++r) s += __ldcg(reinterpret_cast<const double*>(blk.base[r] + off) + c);
         const float v = static_cast<float>(s);
@@ -77,7 +93,6 @@ __global__ void __launch_bounds__(1024) peer_sum_kernel(PeerBlocks blk, int n, i
         st_release_sys(peer_ack(blk.base[self], b), t);
     }
 }
-
 
 // What the backward's final column reduction needs to do the exchange's bookkeeping itself: wait until
 // every rank has acknowledged step need_ack (0: nothing to wait for) before it overwrites the sums, and
