@@ -717,7 +717,7 @@ int agb_set_option(const char* key, int64_t value) {
     else if (!strcmp(key, "ept")) opt_ept = value;
     else if (!strcmp(key, "rows_per_warp")) opt_rpw = value;   // backward, one-warp rows: 0 auto, 1 off, 2..4 forced
     else if (!strcmp(key, "peer_poll_limit")) {   // polls before a cross-GPU wait gives up (0 = default, ~2 s)
-        const int v = value > 0 ? static_cast<int>(value < (1 << 24) ? value : (1 << 24)) : (1 << 22);
+        const int v = value > 0 ? static_cast<int>(value < (1 << 22) ? value : (1 << 22)) : (1 << 20);
         AGB_CUDA(cudaMemcpyToSymbol(agb::g_peer_poll_limit, &v, sizeof(int)));
     }
     else return fail(AGB_ERR_INVALID_ARG, "unknown option '%s'", key);

@@ -14,9 +14,9 @@ namespace agb {
 // (defined here: the library is a single translation unit)
 __device__ int g_device_status = 0;
 
-// Polls of a counter in another GPU's memory before a cross-GPU wait gives up (each poll sleeps
-// ~0.5 us: about two seconds); agb_set_option("peer_poll_limit") changes it.
-__device__ int g_peer_poll_limit = 1 << 22;
+// Polls of a counter in another GPU's memory before a cross-GPU wait gives up (a poll sleeps up to
+// 2 us: about two seconds); agb_set_option("peer_poll_limit") changes it.
+__device__ int g_peer_poll_limit = 1 << 20;
 
 // A wait gives up after kWaitPollLimit polls of mbarrier.try_wait, each of which may suspend the
 // thread in hardware for up to kWaitSuspendNs: at most ~2.6 s in total.

@@ -22,11 +22,26 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
 __device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+__device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+// Polls with RELAXED loads and a growing sleep (0.2 -> 2 us), and pays for the acquire once, with a fence,
+// when the value has arrived.  A rank that runs ahead of the others waits here for most of a step, beside
+// the CTAs of the next forward and backward: an acquire load every half microsecond (each one invalidates
+// the SM's L1) slowed the co-resident forward CTA, and with it the whole statically partitioned kernel,
+// by tens of microseconds.
 __device__ __forceinline__ bool poll_until_at_least(const unsigned long long* p, unsigned long long want) {
     const int limit = g_peer_poll_limit;
+    unsigned int ns = 200;
     for (int i = 0; i < limit; ++i) {
-        if (ld_acquire_sys(p) >= want) return true;
-        __nanosleep(500);
+        if (ld_relaxed_sys(p) >= want) {
+            asm volatile("fence.acq_rel.sys;" ::: "memory");
+            return true;
+        }
+        __nanosleep(ns);
+        if (ns < 2000) ns *= 2;
     }
     return false;
 }
