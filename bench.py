@@ -560,6 +560,7 @@ def main():
     sampled = [k for k in range(args.steps) if k % 5 == 0]
     ev = {k: [torch.cuda.Event(enable_timing=True) for _ in range(3)] for k in sampled}
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    prepared = ex.prepare_step(x, gy, gamma, y, rstd, dx, dgamma)   # operands validated once, bare calls per step
     launches0 = ops.launch_count()
     sync_all()
     t_start.record()
@@ -567,15 +568,12 @@ def main():
         e = ev.get(k)
         if e:
             e[0].record()
-        y_, rstd_ = ops.rmsnorm_fwd(x, gamma, eps, out=y, rstd=rstd)
+        prepared.fwd()
         if e:
             e[1].record()
-        if world == 1:
-            ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=dgamma, workspace=ex._workspace(x))
-        else:
-            # backward on this stream; the 8*H-byte all-reduce and the final rounding run on the executor's
-            # side stream and overlap the next step's kernels (dgamma buffers alternate)
-            ex.bwd_and_exchange(x, gamma, rstd, gy, dx, dgamma)
+        # backward on this stream; for N > 1 the exchange of the 8*H-byte fp64 sums and the final rounding
+        # run on the executor's side stream and overlap the next step's kernels (sum buffers alternate)
+        prepared.bwd()
         if e:
             e[2].record()
     if world > 1:

@@ -59,6 +59,15 @@ def _rank_main(rank, world, port, rows, hidden, dtype_name, exchange, q):
         for k in range(5):
             _, want = ops.rmsnorm_bwd(x.cuda(), gam, rs, gy.cuda() * float(k + 1))
             ok = ok and int((outs[k].view(torch.int32) - want.view(torch.int32)).abs().max()) <= 1
+        # the prepared step (operands validated once, bare C-ABI calls per step)
+        st = ex.prepare_step(xs, gs, gam, torch.empty_like(xs), torch.empty(xs.shape[0], device="cuda"),
+                             torch.empty_like(xs), outs[0])
+        for k in range(3):
+            st.fwd()
+            st.bwd()
+        ex.wait_dgamma()
+        torch.cuda.synchronize()
+        ok = ok and int((outs[0].view(torch.int32) - dgs.view(torch.int32)).abs().max()) <= 1
         # the exchange without the side stream (every step waits for its dgamma), accumulating over steps
         ex2 = RowShardedRMSNorm(hidden, dtype, 1e-6, overlap=False, exchange=exchange)
         for k in range(4):
