@@ -2,8 +2,8 @@
 
 Every rank owns a small device block (two fp64 [hidden] sum buffers, a ready and an ack counter each)
 and maps the blocks of the other ranks through CUDA IPC; one kernel per rank then adds all ranks' sums
-in rank order over NVLink peer loads.  torch.distributed is used once, to all-gather the 64-byte IPC
-handles, and at close, for the barrier that must precede freeing a block others have mapped.
+in rank order over NVLink peer loads.  torch.distributed is used at set-up, to collect the 64-byte IPC
+handles of all ranks, and at close, for the barriers that must precede unmapping and freeing the blocks.
 """
 import ctypes as C
 
@@ -63,8 +63,8 @@ class PeerExchange:
             self._h = C.c_void_p()
 
     def acquire(self, stream=None):
-        """Enqueues the wait for the buffer of this step and returns it as a [max_hidden] fp64 tensor view
-        address (int): where this step's backward must leave its sums."""
+        """Enqueues the wait for this step's sum buffer and returns its device address (int): where the
+        backward must leave its fp64 sums (ops.rmsnorm_bwd(..., dgamma_f64_ptr=address))."""
         s = torch.cuda.current_stream(self.device) if stream is None else stream
         out = C.c_void_p()
         check(_lib.lib().agb_peer_acquire(self._h, C.c_void_p(s.cuda_stream), C.byref(out)))
