@@ -4,13 +4,19 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 A "step" is one forward + VJP pass over the workload's rows: rmsnorm_fwd, rmsnorm_bwd (dx fused
-with the dgamma partials), the fixed-order dgamma reduction and, for N > 1, the NCCL all-reduce
-of the fp64 dgamma sums.  N > 1 is launched by torchrun, one rank per GPU; every rank holds the
-same number of rows (weak scaling) and `value` counts the rows of all ranks.
+with the dgamma partials), the fixed-order dgamma reduction and, for N > 1, the all-reduce of the
+fp64 dgamma sums.  N > 1 is launched by torchrun, one rank per GPU.
 
-Workload (default): x [16,2048,4096] fp32 ~ N(0,1), gamma = 1 + 0.02 N(0,1), gy ~ N(0,1),
-eps 1e-5 -- 32768 rows per GPU, synthetic, seed 0.  Inputs (2 x 537 MB) and outputs are far
-larger than the 126 MB L2, so no flush is needed between iterations.
+Workload (default): the row-sharded configuration -- x [64,8192,8192] bf16 ~ N(0,1) (524288 rows),
+gamma = 1 + 0.02 N(0,1), gy ~ N(0,1), eps 1e-6, synthetic, seeded; the rows are split evenly over the
+ranks (strong scaling), `value` counts all 524288 rows.  Inputs and outputs per step (>= 5 GB per GPU at
+N = 8, 43 GB at N = 1) are far larger than the 126 MB L2, so no flush is needed between iterations.
+
+Timing: after W warm-up steps the K-step block is timed with CUDA events, bracketed by a barrier and a
+device synchronize on both sides, max over ranks; the block is repeated until about one second has been
+timed and the MEDIAN block is reported (every block's time is in `timing.block_ms`).
+
+At N = 1 the line also carries the other single-GPU configurations (`other_configs`).
 
 Prints ONE JSON line on rank 0.
 """
@@ -36,10 +42,17 @@ WORKLOADS = {
     "rmsnorm_fwd_vjp_bf16_65536x1000": (65536, 1000, "bfloat16", 1e-6),
     "rmsnorm_fwd_vjp_bf16_65536x5120": (65536, 5120, "bfloat16", 1e-6),
     "rmsnorm_fwd_vjp_bf16_65536x12288": (65536, 12288, "bfloat16", 1e-6),
-    # configuration 5: 524288 rows in total, split evenly over the ranks (strong scaling)
+    # the row-sharded configuration: 524288 rows in total, split evenly over the ranks (strong scaling)
     "rmsnorm_fwd_vjp_bf16_sharded_64x8192x8192": (64 * 8192, 8192, "bfloat16", 1e-6),
 }
 STRONG_SCALING = {"rmsnorm_fwd_vjp_bf16_sharded_64x8192x8192"}
+# input distributions: (std of x, std of gamma - 1, fraction of rows of x multiplied by 100)
+DISTRIBUTIONS = {name: (3.0, 0.1, 0.01) for name in WORKLOADS if "65536x" in name}   # the odd-width bf16 configuration
+DEFAULT_DISTRIBUTION = (1.0, 0.02, 0.0)
+# single-GPU configurations carried in the default line at N = 1
+OTHER_CONFIGS = ["rmsnorm_fwd_vjp_fp32_16x2048x4096", "rmsnorm_fwd_vjp_bf16_65536x1000", "rmsnorm_fwd_vjp_bf16_65536x5120",
+                 "rmsnorm_fwd_vjp_bf16_65536x8192", "rmsnorm_fwd_vjp_bf16_65536x12288"]
+OTHER_STACK = "residual_stack_fp32_32x4x4096x4096"
 # configuration 4: 32 fused residual-add + RMSNorm layers, forward + VJP as one CUDA graph (C++ host layer)
 STACK_WORKLOADS = {"residual_stack_fp32_32x4x4096x4096": (32, 4 * 4096, 4096, 0)}
 # Next rows of the path, same bar: one forward + VJP pass per step, per-kernel CUDA events.
@@ -53,17 +66,19 @@ OP_WORKLOADS = {
     "layernorm_fwd_vjp_fp32_8192x4096": ("layernorm", 8192, 4096, "float32"),     # small cases for ncu captures
     "softmax_fwd_vjp_fp32_8192x4096": ("softmax", 8192, 4096, "float32"),
 }
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one backward launch, from the ncu
-# captures summarised under profiles/ (taken on a smaller case of the same kernel and scaled by rows).
-NCU_TRAFFIC = {
-    "rmsnorm_fwd_vjp_fp32_16x2048x4096": {
-        "bwd_dram_bytes_per_launch": 1475391488,
-        "source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on the 8192 x 4096 case (profiles/rmsnorm_bwd_staged_fp32_8192x4096.md), scaled x4 by rows; writes still dirty in L2 at kernel end are not counted by the DRAM counter"},
-    "rmsnorm_fwd_vjp_bf16_sharded_64x8192x8192": {
-        "bwd_dram_bytes_per_launch": 24952111104,
-        "source": "ncu capture on the 16384 x 8192 bf16 case (profiles/rmsnorm_bwd_staged_bf16_16384x8192.md), scaled x32 by rows (per rank at N=1)"},
-}
-DEFAULT_WORKLOAD = "rmsnorm_fwd_vjp_fp32_16x2048x4096"
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of ONE backward launch at the benchmarked shape,
+# read from profiles/ncu_traffic.json (written from ncu captures of exactly these shapes; see that file's
+# "command" entries).  Absent entry -> roofline.traffic is null.
+def ncu_traffic(rows, hidden, dtype_name):
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+            table = json.load(f)
+    except Exception:
+        return None
+    return table.get(f"rmsnorm_bwd_{dtype_name}_{rows}x{hidden}")
+
+
+DEFAULT_WORKLOAD = "rmsnorm_fwd_vjp_bf16_sharded_64x8192x8192"
 METRIC = "rmsnorm_fwd_vjp_rows_per_s"
 UNIT = "rows/s"
 SPEC_HBM_GBS = 8000.0
@@ -155,18 +170,25 @@ def _reference_build():
 
 REF_KIND_NOTE = ("the reference's own op builders and autodiff engine (cgadimpl/src/{core,ops,autodiff}, compiled "
                  "unmodified into oracle/_ref) over a CPU stand-in for its absent OwnTensor library, OpenMP")
+REF_EPS_NOTE = ("; fp32 on the CPU with the reference's hard-coded eps = 1e-5 (it has no bf16 path and no eps "
+                "argument; the work per row is the same)")
 PORT_KIND_NOTE = "op-by-op fp32 restatement of the reference composition (oracle/agb_oracle.c), OpenMP"
+
+
+def cpu_sample_rows(rows, hidden):
+    """A bounded sample of the workload for the CPU legs: 16 Mi elements per array (4096 rows of 4096)."""
+    return max(1, min(rows, (1 << 24) // hidden))
 
 
 def cpu_pass(hidden, eps, sample_rows, reps, seed=0):
     """Times the reference's CPU path (all host threads) on a bounded sample of the workload.
     Returns (rows/s, threads, seconds per pass, kind, note)."""
     REF = _reference_build()
-    if REF is not None and abs(eps - 1e-5) < 1e-12:     # the reference hard-codes eps = 1e-5
+    if REF is not None:     # the reference hard-codes eps = 1e-5 and computes in fp32; neither changes the work per row
         cores = REF.use_all_cores()
         REF.set_reduce_fp64(False)
         secs = min(REF.time_fwd_bwd(sample_rows, hidden, 1, 1) for _ in range(max(1, reps)))
-        return sample_rows / secs, cores, secs, "reference", REF_KIND_NOTE
+        return sample_rows / secs, cores, secs, "reference", REF_KIND_NOTE + REF_EPS_NOTE
     import numpy as np
 
     import oracle_ffi as O
@@ -216,13 +238,13 @@ def run_reference_arm(args, rank, world):
     if rank != 0:
         return
     rows, hidden, dtype, eps = WORKLOADS[args.workload]
-    sample_rows = min(rows, 4096)
+    sample_rows = cpu_sample_rows(rows, hidden)
     REF = _reference_build()
-    if REF is not None and abs(eps - 1e-5) < 1e-12:
+    if REF is not None:
         cores = REF.use_all_cores()
         REF.set_reduce_fp64(False)
         secs = REF.time_fwd_bwd(sample_rows, hidden, args.steps, max(1, args.warmup))
-        kind, note = "reference", REF_KIND_NOTE
+        kind, note = "reference", REF_KIND_NOTE + REF_EPS_NOTE
     else:
         import numpy as np
 
@@ -242,18 +264,19 @@ def run_reference_arm(args, rank, world):
         secs = (time.perf_counter() - t0) / args.steps
         kind, note = "port", PORT_KIND_NOTE
     value = sample_rows / secs
-    elem = 4 if dtype == "float32" else 2
+    strong = args.workload in STRONG_SCALING
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "rows_per_gpu": rows, "hidden": hidden, "eps": eps,
-                   "io_dtype": dtype, "sample_rows_per_step": sample_rows},
+        "config": {"workload": args.workload, "rows_per_gpu": rows // world if strong else rows,
+                   "global_rows": rows if strong else rows * world, "hidden": hidden, "io_dtype": dtype, "eps": eps,
+                   "parallelism": f"rows{world}"},
+        "sample_rows_per_step": sample_rows,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
                          "sample": f"{sample_rows} of {rows} rows per step; {note}"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "hbm_gbs": value * bytes_per_row(hidden, elem) / 1e9,
     }
     print(json.dumps(line), flush=True)
 
@@ -456,16 +479,239 @@ def run_single_process(args):
         "e2e": None, "cpu_baseline": None}), flush=True)
 
 
+# --------------------------------------------------------------------------- GPU arm: helpers
+def synth(rows, hidden, dtype, seed, std=1.0, outlier_frac=0.0, chunk=16384):
+    """[rows, hidden] ~ N(0, std) on the current device, generated chunk by chunk in fp32 and rounded once;
+    a seeded fraction of rows is multiplied by 100 before rounding (outlier rows)."""
+    import torch
+
+    out = torch.empty(rows, hidden, dtype=dtype, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    scale = None
+    if outlier_frac > 0 and rows > 0:
+        scale = torch.full((rows, 1), std, device="cuda")
+        k = max(1, int(round(rows * outlier_frac)))
+        idx = torch.randperm(rows, generator=gen, device="cuda")[:k]
+        scale[idx] = std * 100.0
+    for r0 in range(0, rows, chunk):
+        n = min(chunk, rows - r0)
+        t = torch.randn(n, hidden, device="cuda", generator=gen)
+        out[r0:r0 + n] = (t * (scale[r0:r0 + n] if scale is not None else std)).to(dtype)
+    return out
+
+
+def make_operands(name, rows, hidden, dtype, seed):
+    import torch
+
+    x_std, g_std, outl = DISTRIBUTIONS.get(name, DEFAULT_DISTRIBUTION)
+    x = synth(rows, hidden, dtype, seed, x_std, outl)
+    gy = synth(rows, hidden, dtype, seed + 1)
+    ggen = torch.Generator(device="cuda").manual_seed(7)
+    gamma = (1 + g_std * torch.randn(hidden, device="cuda", generator=ggen)).to(dtype)
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device="cuda")
+    dgamma = torch.empty(hidden, dtype=torch.float32, device="cuda")
+    return x, gy, gamma, y, dx, rstd, dgamma
+
+
+def time_steps(prepared, ex, steps, warmup, world, dist, target_s, sample_every=5):
+    """W warm-up steps, then blocks of exactly `steps` steps, each bracketed by barrier + synchronize and
+    timed with CUDA events on the launching stream (max over ranks), repeated until ~target_s seconds are
+    timed.  Returns (block times in ms, mean fwd ms, mean bwd ms, kernel launches in all blocks)."""
+    import torch
+
+    from cgadimpl_b200 import ops
+
+    def sync_all():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        prepared.fwd()
+        prepared.bwd()
+    if world > 1:
+        ex.wait_dgamma()
+    sync_all()
+    ops.device_status()
+    # one untimed probe block decides how many blocks make up the target
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
+    for _ in range(min(steps, 5)):
+        prepared.fwd()
+        prepared.bwd()
+    if world > 1:
+        ex.wait_dgamma()
+    p1.record()
+    sync_all()
+    est = p0.elapsed_time(p1) / min(steps, 5) * steps / 1e3
+    nblocks = max(1, min(400, int(target_s / max(est, 1e-6) + 0.999)))
+    if dist is not None:       # every rank must run the same number of blocks
+        t = torch.tensor([nblocks], device="cuda", dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        nblocks = int(t.item())
+    block_ms, fwd_ms, bwd_ms = [], [], []
+    launches0 = ops.launch_count()
+    for b in range(nblocks):
+        # per-kernel events on every `sample_every`-th step only: three event records per step cost a few
+        # microseconds of stream bubbles and keep dependent kernels from being placed early
+        sampled = [k for k in range(steps) if k % sample_every == 0]
+        ev = {k: [torch.cuda.Event(enable_timing=True) for _ in range(3)] for k in sampled}
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync_all()
+        t0.record()
+        for k in range(steps):
+            e = ev.get(k)
+            if e:
+                e[0].record()
+            prepared.fwd()
+            if e:
+                e[1].record()
+            prepared.bwd()
+            if e:
+                e[2].record()
+        if world > 1:
+            ex.wait_dgamma()          # the block ends when its last dgamma is final
+        t1.record()
+        sync_all()
+        block_ms.append(t0.elapsed_time(t1))
+        fwd_ms += [ev[k][0].elapsed_time(ev[k][1]) for k in sampled]
+        bwd_ms += [ev[k][1].elapsed_time(ev[k][2]) for k in sampled]
+    launches = ops.launch_count() - launches0
+    if dist is not None:
+        t = torch.tensor(block_ms, device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        block_ms = [float(v) for v in t.tolist()]
+    ops.device_status()
+    return block_ms, statistics.mean(fwd_ms), statistics.mean(bwd_ms), launches
+
+
+def check_dgamma(x, gy, gamma, rstd, dgamma, dist, rows_total, chunk=8192):
+    """Outside the timed region: the exchanged dgamma against an fp64 column sum of gy * x * rstd over ALL
+    ranks' rows (each rank sums its rows in fp64 with torch, the sums are added over the ranks in fp64)."""
+    import torch
+
+    rows, hidden = x.shape
+    want = torch.zeros(hidden, dtype=torch.float64, device="cuda")
+    for r0 in range(0, rows, chunk):
+        sl = slice(r0, min(rows, r0 + chunk))
+        want += (gy[sl].double() * x[sl].double() * rstd[sl].double()[:, None]).sum(0)
+    if dist is not None:
+        dist.all_reduce(want, op=dist.ReduceOp.SUM)
+    err = (dgamma.double() - want).abs()
+    # fp32-accumulated (16-bit I/O) or fp64-accumulated fp32-rounded products (fp32 I/O): the floor grows like
+    # sqrt(rows) * 2^-24 * a few; typical columns are of size sqrt(rows)
+    rtol = 1e-5
+    atol = (4e-6 if x.element_size() == 2 else 5e-7) * float(rows_total) ** 0.5
+    ok = bool((err <= atol + rtol * want.abs()).all())
+    return {"ok": ok, "max_abs_err": float(err.max()), "rtol": rtol, "atol": atol,
+            "dgamma_rms": float(want.pow(2).mean().sqrt()),
+            "against": "fp64 column sum of gy*x*rstd over all ranks' rows (torch), outside the timed region"}
+
+
+def measure_one(name, steps, warmup, target_s):
+    """One single-GPU configuration for `other_configs`: allocate, time, free."""
+    import torch
+
+    from cgadimpl_b200 import ops
+    from cgadimpl_b200.executor import RowShardedRMSNorm
+
+    rows, hidden, dtype_name, eps = WORKLOADS[name]
+    dtype = getattr(torch, dtype_name)
+    elem = 4 if dtype == torch.float32 else 2
+    x, gy, gamma, y, dx, rstd, dgamma = make_operands(name, rows, hidden, dtype, seed=11)
+    ex = RowShardedRMSNorm(hidden, dtype, eps)
+    prepared = ex.prepare_step(x, gy, gamma, y, rstd, dx, dgamma)
+    block_ms, fwd_ms, bwd_ms, _ = time_steps(prepared, ex, steps, warmup, 1, None, target_s)
+    chk = check_dgamma(x, gy, gamma, rstd, dgamma, None, rows)
+    ms = statistics.median(block_ms) / steps
+    peak, _ = measured_peak()
+    gbs = rows * bytes_per_row(hidden, elem) / (ms / 1e3) / 1e9
+    out = {"workload": name, "rows": rows, "hidden": hidden, "io_dtype": dtype_name, "eps": eps, "ms_per_step": ms,
+           "rows_per_s": rows / (ms / 1e3), "step_gbs": gbs, "frac": gbs / peak, "frac_of_spec_8TBs": gbs / SPEC_HBM_GBS,
+           "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+           "fwd_frac": rows * (2 * hidden * elem + 4) / (fwd_ms / 1e3) / 1e9 / peak,
+           "bwd_frac": rows * (3 * hidden * elem + 4) / (bwd_ms / 1e3) / 1e9 / peak,
+           "blocks": len(block_ms), "dgamma_check_ok": chk["ok"],
+           "launch": {"fwd": ops.describe_launch("fwd", rows, hidden, dtype), "bwd": ops.describe_launch("bwd", rows, hidden, dtype)}}
+    ex.close()
+    del x, gy, gamma, y, dx, rstd, dgamma, prepared
+    torch.cuda.empty_cache()
+    return out
+
+
+def measure_stack(steps, warmup):
+    """The 32-layer residual stack as one CUDA graph, through the C++ host layer (bench_stack)."""
+    from cgadimpl_b200.host import build as host_build
+
+    host_build.build()
+    layers, rows, hidden, bf16 = STACK_WORKLOADS[OTHER_STACK]
+    exe = os.path.join(os.path.dirname(host_build.__file__), "build", "bench_stack")
+    r = subprocess.run([exe, str(layers), str(rows), str(hidden), str(max(steps, 10)), str(max(3, warmup)), str(bf16)],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        return {"workload": OTHER_STACK, "error": (r.stdout + r.stderr)[-400:]}
+    d = json.loads(r.stdout.strip().splitlines()[-1])
+    peak, _ = measured_peak()
+    return {"workload": OTHER_STACK, "layers": layers, "rows": rows, "hidden": hidden, "io_dtype": "float32",
+            "ms_per_step": d["ms_per_replay"], "row_layers_per_s": d["row_layers_per_s"], "step_gbs": d["gbs"],
+            "frac": d["gbs"] / peak, "frac_of_spec_8TBs": d["gbs"] / SPEC_HBM_GBS, "cuda_graph_nodes": d["graph_nodes"],
+            "api": "ag::nn::ResidualRMSNormStack captured by ag::CudaGraphRunner (C++ host layer)"}
+
+
+def copy_probe(dist, nbytes=1 << 30):
+    """Host <-> device copy rate of this rank's GPU with every rank copying at the same time (pinned memory,
+    one direction at a time, then both): what bounds the end-to-end figure.  GB/s, min over ranks."""
+    import torch
+
+    h = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    h2 = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    d = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    d2 = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        fn()
+        torch.cuda.synchronize()
+        return time.perf_counter() - t0
+
+    def both():
+        with torch.cuda.stream(s1):
+            d.copy_(h, non_blocking=True)
+        with torch.cuda.stream(s2):
+            h2.copy_(d2, non_blocking=True)
+
+    res = {"h2d_gbs": nbytes / timed(lambda: d.copy_(h, non_blocking=True)) / 1e9,
+           "d2h_gbs": nbytes / timed(lambda: h2.copy_(d2, non_blocking=True)) / 1e9,
+           "both_each_gbs": nbytes / timed(both) / 1e9}
+    if dist is not None:
+        t = torch.tensor([res["h2d_gbs"], res["d2h_gbs"], res["both_each_gbs"]], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        res = dict(zip(("h2d_gbs", "d2h_gbs", "both_each_gbs"), (float(v) for v in t.tolist())))
+    res["note"] = "per rank, all ranks copying at once, 1 GiB pinned buffers; min over ranks"
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(STACK_WORKLOADS) + sorted(OP_WORKLOADS))
+    ap.add_argument("--target-seconds", type=float, default=1.0, help="repeat the K-step block until this much is timed")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-rows", type=int, default=65536, help="rows per rank and step of the end-to-end leg (a sample of the shard when it is larger)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-other-configs", action="store_true")
+    ap.add_argument("--option", action="append", default=[], metavar="KEY=VALUE", help="agb_set_option before anything runs")
     ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "collective"],
                     help="N > 1: how dgamma crosses the ranks (the library's peer-load kernel, or an NCCL all-reduce)")
     ap.add_argument("--single-process", action="store_true",
@@ -500,11 +746,14 @@ def main():
     import torch
 
     from cgadimpl_b200 import ops
-    from cgadimpl_b200.executor import RowShardedRMSNorm
+    from cgadimpl_b200.executor import RowShardedRMSNorm, shard_rows
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local_rank)
+    for kv in args.option:
+        k, v = kv.split("=")
+        ops.set_option(k, int(v))
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -518,117 +767,75 @@ def main():
 
     rows, hidden, dtype_name, eps = WORKLOADS[args.workload]
     strong = args.workload in STRONG_SCALING
+    total_rows = rows if strong else rows * world
     if strong:
-        from cgadimpl_b200.executor import shard_rows
-
         a, b = shard_rows(rows, world, rank)
-        total_rows_fixed = rows
         rows = b - a
     dtype = getattr(torch, dtype_name)
     elem = 4 if dtype == torch.float32 else 2
-    gen = torch.Generator(device="cuda").manual_seed(1000 * rank)
-    x = torch.randn(rows, hidden, device="cuda", generator=gen, dtype=torch.float32).to(dtype)
-    gy = torch.randn(rows, hidden, device="cuda", generator=gen, dtype=torch.float32).to(dtype)
-    ggen = torch.Generator(device="cuda").manual_seed(7)
-    gamma = (1 + 0.02 * torch.randn(hidden, device="cuda", generator=ggen)).to(dtype)
-    y = torch.empty_like(x)
-    dx = torch.empty_like(x)
-    rstd = torch.empty(rows, dtype=torch.float32, device="cuda")
-    dgamma = torch.empty(hidden, dtype=torch.float32, device="cuda")
+    x, gy, gamma, y, dx, rstd, dgamma = make_operands(args.workload, rows, hidden, dtype, seed=1000 * rank)
     ex = RowShardedRMSNorm(hidden, dtype, eps, exchange=args.exchange)
+    prepared = ex.prepare_step(x, gy, gamma, y, rstd, dx, dgamma)   # operands validated once, bare calls per step
 
-    def step():
-        ex.fwd_bwd(x, gy, gamma, y=y, rstd=rstd, dx=dx, dgamma=dgamma, wait=False)
-
-    def sync_all():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    sync_all()
-    ops.device_status()
-
-    # ---- timed region: K steps, device-timed, plus per-kernel events on the launching stream
+    # ---- timed region
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
         time.sleep(0.3)
-    # per-kernel events on every 5th step only: three event records per step cost a few microseconds of
-    # stream bubbles, which is not negligible against a 0.4 ms step
-    sampled = [k for k in range(args.steps) if k % 5 == 0]
-    ev = {k: [torch.cuda.Event(enable_timing=True) for _ in range(3)] for k in sampled}
-    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    prepared = ex.prepare_step(x, gy, gamma, y, rstd, dx, dgamma)   # operands validated once, bare calls per step
-    launches0 = ops.launch_count()
-    sync_all()
-    t_start.record()
-    for k in range(args.steps):
-        e = ev.get(k)
-        if e:
-            e[0].record()
-        prepared.fwd()
-        if e:
-            e[1].record()
-        # backward on this stream; for N > 1 the exchange of the 8*H-byte fp64 sums and the final rounding
-        # run on the executor's side stream and overlap the next step's kernels (sum buffers alternate)
-        prepared.bwd()
-        if e:
-            e[2].record()
-    if world > 1:
-        ex.wait_dgamma()          # the timed region ends when the last dgamma is final
-    t_end.record()
-    sync_all()
-    launches = ops.launch_count() - launches0
-    elapsed_ms = t_start.elapsed_time(t_end)
-    if dist is not None:
-        t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
+    block_ms, fwd_ms, bwd_ms, launches = time_steps(prepared, ex, args.steps, args.warmup, world, dist, args.target_seconds)
     if sampler:
         time.sleep(0.2)
     clocks = sampler.stop() if sampler else None
-    ops.device_status()
-
-    fwd_ms = statistics.mean(ev[k][0].elapsed_time(ev[k][1]) for k in sampled)
-    bwd_ms = statistics.mean(ev[k][1].elapsed_time(ev[k][2]) for k in sampled)
-    total_rows = total_rows_fixed if strong else rows * world
-    value = total_rows * args.steps / (elapsed_ms / 1e3)
+    block = statistics.median(block_ms)
+    ms_per_step = block / args.steps
+    value = total_rows / (ms_per_step / 1e3)
     bpr = bytes_per_row(hidden, elem)
     peak, peak_kind = measured_peak()
+    if clocks and clocks.get("sm_mhz"):
+        clocks["ms_per_step_x_sm_mhz"] = ms_per_step * clocks["sm_mhz"]
 
-    # dominant launch: the backward call (rmsnorm_bwd_staged followed by the ~µs dgamma reduction)
+    # ---- the exchanged dgamma is the column sum over all ranks' rows (outside the timed region)
+    dgamma_check = check_dgamma(x, gy, gamma, rstd, dgamma, dist, total_rows)
+    if not dgamma_check["ok"]:
+        raise SystemExit(f"rank {rank}: dgamma check failed: {dgamma_check}")
+
+    # dominant launch: the backward call (rmsnorm_bwd followed by the few-microsecond dgamma reduction)
     bwd_bytes = rows * (3 * hidden * elem + 4)
     fwd_bytes = rows * (2 * hidden * elem + 4)
     achieved = bwd_bytes / (bwd_ms / 1e3) / 1e9
+    step_gbs = value / world * bpr / 1e9
     roofline = {
-        "bound": "hbm", "kernel": "rmsnorm_bwd_staged (+dgamma_reduce_kernel)", "achieved": achieved, "peak": peak,
+        "bound": "hbm", "kernel": "rmsnorm_bwd (+dgamma_reduce_kernel)", "achieved": achieved, "peak": peak,
         "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
-        "algorithmic_bytes_per_launch": bwd_bytes, "avg_launch_ms": bwd_ms, "launches_timed": len(sampled),
-        "fwd": {"kernel": "rmsnorm_fwd_staged", "achieved": fwd_bytes / (fwd_ms / 1e3) / 1e9,
+        "algorithmic_bytes_per_launch": bwd_bytes, "avg_launch_ms": bwd_ms,
+        "fwd": {"kernel": "rmsnorm_fwd", "achieved": fwd_bytes / (fwd_ms / 1e3) / 1e9,
                 "frac": fwd_bytes / (fwd_ms / 1e3) / 1e9 / peak, "avg_launch_ms": fwd_ms,
                 "algorithmic_bytes_per_launch": fwd_bytes},
-        "step_gbs": value / world * bpr / 1e9,
-        "step_frac_of_spec_8TBs": value / world * bpr / 1e9 / SPEC_HBM_GBS,
-        "step_frac_of_peak": value / world * bpr / 1e9 / peak,
+        "step_gbs": step_gbs, "step_frac_of_spec_8TBs": step_gbs / SPEC_HBM_GBS, "step_frac_of_peak": step_gbs / peak,
     }
-    tr = NCU_TRAFFIC.get(args.workload)
+    tr = ncu_traffic(rows, hidden, dtype_name)
     if tr:
-        roofline["traffic"] = tr["bwd_dram_bytes_per_launch"]
+        roofline["traffic"] = tr["dram_bytes_per_launch"]
         roofline["traffic_source"] = tr["source"]
 
     # ---- end to end: pinned host buffers in, host buffers out, copies inside the timed region
     e2e = None
     if not args.no_e2e:
-        xh = torch.empty(rows, hidden, dtype=dtype).pin_memory()
-        gyh = torch.empty(rows, hidden, dtype=dtype).pin_memory()
-        xh.copy_(x)
-        gyh.copy_(gy)
+        er = min(rows, args.e2e_rows)
+        xh = torch.empty(er, hidden, dtype=dtype).pin_memory()
+        gyh = torch.empty(er, hidden, dtype=dtype).pin_memory()
+        xh.copy_(x[:er])
+        gyh.copy_(gy[:er])
         gh = gamma.cpu().pin_memory()
-        yh = torch.empty(rows, hidden, dtype=dtype).pin_memory()
-        dxh = torch.empty(rows, hidden, dtype=dtype).pin_memory()
+        yh = torch.empty(er, hidden, dtype=dtype).pin_memory()
+        dxh = torch.empty(er, hidden, dtype=dtype).pin_memory()
         dgh = torch.empty(hidden, dtype=torch.float32).pin_memory()
+
+        def sync_all():
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+
         for _ in range(2):
             ex.fwd_bwd_host(xh, gyh, gh, yh, dxh, dgh)
         sync_all()
@@ -644,18 +851,23 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         # the host results must be the device results
-        assert torch.equal(yh[:64].cuda(), y[:64]) and torch.equal(dxh[-64:].cuda(), dx[-64:]), "e2e mismatch"
-        h2d = rows * hidden * elem * 2 + hidden * elem
-        d2h = rows * hidden * elem * 2 + hidden * 4
-        e2e = {"value": total_rows * args.e2e_steps / (ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+        assert torch.equal(yh[:64].cuda(), y[:64]) and torch.equal(dxh[er - 64:].cuda(), dx[er - 64:er]), "e2e mismatch"
+        e2e_rows_all = er * world if not strong else min(total_rows, er * world)
+        h2d = er * hidden * elem * 2 + hidden * elem
+        d2h = er * hidden * elem * 2 + hidden * 4
+        e2e = {"value": e2e_rows_all * args.e2e_steps / (ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "steps": args.e2e_steps, "ms_per_step": ms / args.e2e_steps,
+               "rows_per_rank_and_step": er,
+               "sample": (f"{er} of this rank's {rows} rows per step" if er < rows else "the rank's whole shard per step")
+                         + "; bytes are per rank",
                "api": "cgadimpl_b200.executor.RowShardedRMSNorm.fwd_bwd_host (pinned host buffers, chunked "
                       "copy/compute overlap on three streams)"}
         del xh, gyh, yh, dxh
+        e2e["copy_probe"] = copy_probe(dist)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        sample_rows = min(rows, 4096)
+        sample_rows = cpu_sample_rows(rows, hidden)
         v, cores, secs, kind, note = cpu_pass(hidden, eps, sample_rows, reps=8)
         cpu_baseline = {"value": v, "unit": UNIT, "cores": cores, "kind": kind,
                         "sample": f"{sample_rows} of {rows} rows, best of 8 passes ({secs*1e3:.1f} ms each); {note}"}
@@ -665,20 +877,38 @@ def main():
         cpu_baseline["fused_single_pass"] = {"value": fv, "unit": UNIT, "cores": fcores,
                                              "note": f"row-fused C restatement (oracle/agb_oracle.c), best of 8 passes ({fsecs*1e3:.1f} ms each)"}
 
+    other = None
+    if rank == 0 and world == 1 and not args.no_other_configs and args.workload == DEFAULT_WORKLOAD:
+        del x, gy, y, dx, prepared          # make room: the other configurations bring their own operands
+        torch.cuda.empty_cache()
+        other = []
+        for name in OTHER_CONFIGS:
+            try:
+                other.append(measure_one(name, args.steps, args.warmup, min(0.5, args.target_seconds)))
+            except Exception as e:  # noqa: BLE001 -- one failing side configuration must not lose the line
+                other.append({"workload": name, "error": repr(e)[:300]})
+        other.append(measure_stack(args.steps, args.warmup))
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "rows_per_gpu": rows, "global_rows": total_rows, "hidden": hidden,
                        "io_dtype": dtype_name, "eps": eps, "parallelism": f"rows{world}",
                        "dgamma_exchange": ex.exchange,
-                       "l2": "inputs+outputs per step (>= 2 GB) exceed the 126 MB L2; no flush needed",
+                       "arithmetic": "fp32 accumulation (16-bit I/O)" if elem == 2 else "reference rounding points, fp64 reductions",
+                       "l2": "inputs+outputs per step (>= 5 GB per GPU) exceed the 126 MB L2; no flush needed",
                        "launch": {"fwd": ops.describe_launch("fwd", rows, hidden, dtype),
                                   "bwd": ops.describe_launch("bwd", rows, hidden, dtype)}},
-            "hbm_gbs": value / world * bpr / 1e9, "bytes_per_row": bpr,
-            "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
-            "e2e": e2e, "cpu_baseline": cpu_baseline,
+            "timing": {"statistic": "median over blocks of exactly `steps` steps; each block barrier + synchronize "
+                                    "bracketed, CUDA events, max over ranks",
+                       "blocks": len(block_ms), "block_ms": [round(b, 4) for b in block_ms],
+                       "block_ms_min": min(block_ms), "block_ms_max": max(block_ms),
+                       "timed_seconds": sum(block_ms) / 1e3},
+            "hbm_gbs": step_gbs, "bytes_per_row": bpr,
+            "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "dgamma_check": dgamma_check,
+            "e2e": e2e, "cpu_baseline": cpu_baseline, "other_configs": other,
         }
         print(json.dumps(line), flush=True)
     ex.close()

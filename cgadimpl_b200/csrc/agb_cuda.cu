@@ -12,6 +12,7 @@
 #include "elementwise.cuh"
 #include "rmsnorm_generic.cuh"
 #include "rmsnorm_staged.cuh"
+#include "rmsnorm_fast.cuh"
 #include "layernorm_staged.cuh"
 #include "softmax_staged.cuh"
 #include "agb_peer_device.cuh"
@@ -78,12 +79,21 @@ int device_info(const DevInfo** out) {
 
 // ------------------------------------------------------------------ options
 std::atomic<int64_t> opt_stages{0}, opt_ctas_per_sm{0}, opt_threads{0}, opt_force_generic{0}, opt_ept{0}, opt_rpw{0};
+// bf16_strict: 16-bit I/O through the strictly rounded fp64-reducing kernels instead of the fp32-accumulating ones.
+// bwd_keep: fast backward variant (0 auto, 1 registers keep x and gy between the passes, 2 re-read the tile).
+// reserve_sms: SMs the persistent grids leave free (for a collective's kernel running beside them).
+// pdl: programmatic dependent launch between the library's own kernels (see launch_pdl).
+std::atomic<int64_t> opt_bf16_strict{0}, opt_bwd_keep{0}, opt_reserve_sms{0}, opt_pdl{1};
+// peer_poll_limit: polls (each sleeping up to 2 us) before a wait on another GPU's counter gives up; process-wide,
+// handed to the waiting kernels as an argument at every launch.
+std::atomic<int64_t> opt_peer_poll_limit{1 << 20};
+inline int peer_poll_limit() { return static_cast<int>(opt_peer_poll_limit.load()); }
 
 // ------------------------------------------------------------------ launch planning
 struct Plan {
     bool generic = true;
     bool full = false;   // every thread's VPT vectors exist: no bounds checks in the kernel
-    int grid = 0, block = 0, smem = 0, vpt = 0;
+    int grid = 0, block = 0, smem = 0, vpt = 0, ctas = 0;
     PipeGeom g{};
 };
 
@@ -102,7 +112,7 @@ constexpr BwdVariant kBwdVariants[3] = {{8, 1024, 64}, {16, 768, 80}, {32, 512, 
 // narr: arrays staged per tile; ngamma: [hidden] fp32 vectors kept in shared memory.
 // extra_static: statically declared shared memory of the kernel, charged against the per-CTA limit.
 void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, int ngamma, const DevInfo& d,
-                 Plan* p, int extra_static = 0, bool heavy = false) {
+                 Plan* p, int extra_static = 0, bool heavy = false, int fast = 0) {
     p->generic = true;
     if (opt_force_generic.load() || rows <= 0) return;
     const int64_t row_bytes64 = hidden * elem;
@@ -115,7 +125,15 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     // row and thread (barrier, two reductions, statistics) is large, so MORE elements per thread
     // win: 32 per thread in the backward (the most whose fp64 column sums fit in registers).
     int vpt = 0, G = 0, max_threads = 1024, regs = 64;
-    if (which == kBwd) {
+    if (which == kBwd && fast) {
+        // fp32-accumulating backward (rmsnorm_bwd_fast): 32 elements per thread; fast == 1 keeps x and gy in
+        // registers between the passes (launch bound 512 threads), fast == 2 re-reads the tile (768 threads)
+        vpt = 32 / epv;
+        G = round_up((nvec + vpt - 1) / vpt, 32);
+        max_threads = fast == 1 ? 512 : 768;
+        regs = fast == 1 ? 128 : 80;
+        if (G > max_threads) return;
+    } else if (which == kBwd) {
         const int want = static_cast<int>(opt_ept.load());
         bool found = false;
         for (int pass = 0; pass < 2 && !found; ++pass)
@@ -212,7 +230,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     // take several rows of a tile back to back, so the block-wide barrier is paid once per tile, as long
     // as the ring stays three tiles deep.
     int rpw = 1;
-    if (which == kBwd && G == 32 && vpt * epv == 32) {
+    if (which == kBwd && !fast && G == 32 && vpt * epv == 32) {
         const int want_rpw = static_cast<int>(opt_rpw.load());
         for (int cand = (want_rpw > 0 ? want_rpw : 4); cand >= 2; --cand) {
             if (static_cast<int64_t>(rpt) * cand > rows) continue;
@@ -256,14 +274,55 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     off += 8 * 16;
     g.off_flag = off;
     off += 16;
+    g.pdl_early = opt_pdl.load() == 2;
     p->smem = off;
     p->block = block;
     p->vpt = vpt;
     p->full = (vpt * G == nvec);
-    int64_t grid = static_cast<int64_t>(d.sms) * ctas;
+    int reserve = static_cast<int>(opt_reserve_sms.load());
+    if (reserve < 0 || reserve >= d.sms) reserve = 0;
+    int64_t grid = static_cast<int64_t>(d.sms - reserve) * ctas;
     if (grid > g.ntiles) grid = g.ntiles;
+    p->ctas = ctas;
     p->grid = static_cast<int>(grid);
     p->generic = false;
+}
+
+// The backward's plan: 16-bit I/O takes the fp32-accumulating kernel (unless "bf16_strict"), which exists with
+// two register budgets: the one that holds more threads on an SM wins; on a tie the register-keeping form,
+// which has fewer instructions per element.
+void plan_bwd(int64_t rows, int64_t hidden, int elem, int narr, int ngamma, const DevInfo& d, Plan* p, bool* keep) {
+    *keep = false;
+    if (elem == 2 && !opt_bf16_strict.load()) {
+        Plan pk, pn;
+        plan_launch(kBwd, rows, hidden, elem, narr, ngamma, d, &pk, 0, false, 1);
+        plan_launch(kBwd, rows, hidden, elem, narr, ngamma, d, &pn, 0, false, 2);
+        const int64_t want_keep = opt_bwd_keep.load();
+        if (want_keep == 1) *keep = !pk.generic;
+        else if (want_keep == 2) *keep = pn.generic && !pk.generic;
+        else *keep = !pk.generic && (pn.generic || pk.block * pk.ctas >= pn.block * pn.ctas);
+        *p = *keep ? pk : pn;
+        return;
+    }
+    plan_launch(kBwd, rows, hidden, elem, narr, ngamma, d, p);
+}
+
+// Launch of a kernel that begins with pdl_wait(): with the "pdl" option (default on) it carries the
+// programmatic-stream-serialization attribute, so its CTAs are placed while the kernel before it in the
+// stream drains and the gap between dependent kernels shrinks to the wait itself.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = opt_pdl.load() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 template <typename K>
@@ -321,10 +380,31 @@ int launch_fwd(const void* x, const void* r, const void* gamma, void* h, void* y
         return after_launch("rmsnorm_fwd_generic");
     }
     agb::FwdArgs a{p.g, x, r, gamma, h, y, rstd, eps};
+    if constexpr (sizeof(T) == 2) if (!opt_bf16_strict.load()) {
+        const float hinv = 1.0f / static_cast<float>(hidden);
+#define AGB_LAUNCH_FWDF(V, HG, FA, FU)                                                       \
+    do {                                                                                     \
+        AGB_TRY(set_smem(agb::rmsnorm_fwd_fast<T, V, HG, FA, FU>, p.smem));                  \
+        AGB_CUDA(launch_pdl(agb::rmsnorm_fwd_fast<T, V, HG, FA, FU>, p.grid, p.block, p.smem, st, a, hinv)); \
+    } while (0)
+#define AGB_FWDF_BY_FLAGS(V, FU)                                 \
+    do {                                                         \
+        if (gamma && fuse) AGB_LAUNCH_FWDF(V, true, true, FU);   \
+        else if (gamma) AGB_LAUNCH_FWDF(V, true, false, FU);     \
+        else if (fuse) AGB_LAUNCH_FWDF(V, false, true, FU);      \
+        else AGB_LAUNCH_FWDF(V, false, false, FU);               \
+    } while (0)
+        if (p.vpt == 4 && p.full) AGB_FWDF_BY_FLAGS(4, true);
+        else if (p.vpt == 4) AGB_FWDF_BY_FLAGS(4, false);
+        else AGB_FWDF_BY_FLAGS(8, false);
+#undef AGB_FWDF_BY_FLAGS
+#undef AGB_LAUNCH_FWDF
+        return after_launch("rmsnorm_fwd_fast");
+    }
 #define AGB_LAUNCH_FWD(V, HG, FA, FU)                                                   \
     do {                                                                                \
         AGB_TRY(set_smem(agb::rmsnorm_fwd_staged<T, V, HG, FA, FU>, p.smem));           \
-        agb::rmsnorm_fwd_staged<T, V, HG, FA, FU><<<p.grid, p.block, p.smem, st>>>(a);  \
+        AGB_CUDA(launch_pdl(agb::rmsnorm_fwd_staged<T, V, HG, FA, FU>, p.grid, p.block, p.smem, st, a)); \
     } while (0)
 #define AGB_FWD_BY_FLAGS(V, FU)                          \
     do {                                                 \
@@ -349,15 +429,15 @@ thread_local bool t_reduce_hook_used = false;
 int launch_dgamma_reduce(const double* partials, int P, int64_t hidden, void* dgamma, int dgamma_dtype,
                          int accumulate, cudaStream_t st) {
     const int mode = dgamma_dtype == AGB_F64 ? (accumulate ? 3 : 2) : (accumulate ? 1 : 0);
-    dim3 block(32, 16);
-    const int grid = static_cast<int>((hidden + 31) / 32);
+    dim3 block(agb::kReduceCols, agb::kReduceLanes);
+    const int grid = static_cast<int>((hidden + agb::kReduceCols - 1) / agb::kReduceCols);
     if (t_reduce_hook && mode == 2) {
         agb::dgamma_reduce_publish_kernel<<<grid, block, 0, st>>>(partials, P, (int)hidden, static_cast<double*>(dgamma),
                                                                   *t_reduce_hook);
         t_reduce_hook_used = true;
         return after_launch("dgamma_reduce_publish");
     }
-    agb::dgamma_reduce_kernel<<<grid, block, 0, st>>>(partials, P, (int)hidden, dgamma, mode);
+    AGB_CUDA(launch_pdl(agb::dgamma_reduce_kernel, grid, block, 0, st, partials, P, (int)hidden, dgamma, mode));
     return after_launch("dgamma_reduce");
 }
 
@@ -384,7 +464,9 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
     Plan p;
     const bool al = aligned16(x) && aligned16(gy) && aligned16(dx) && (!gamma || aligned16(gamma)) &&
                     (add_mode != 1 || aligned16(dx_add));
-    if (al) plan_launch(kBwd, rows, hidden, sizeof(T), add_mode == 1 ? 3 : 2, gamma ? 1 : 0, *d, &p);
+    const bool fast = sizeof(T) == 2 && !opt_bf16_strict.load();
+    bool keep = false;
+    if (al) plan_bwd(rows, hidden, sizeof(T), add_mode == 1 ? 3 : 2, gamma ? 1 : 0, *d, &p, &keep);
     if (want_dg && !p.generic) {
         // every CTA writes the partial row of its block index: never launch more CTAs than the workspace has rows
         const size_t cap = workspace_bytes / (static_cast<size_t>(hidden) * sizeof(double));
@@ -407,6 +489,30 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
         agb::rmsnorm_bwd_generic<T><<<generic_grid(rows, *d), agb::kGenericThreads, 0, st>>>(
             (const T*)x, (const T*)gamma, rstd, (const T*)gy, (const T*)dx_add, (T*)dx, rows, (int)hidden, hf, 1.0f / hf);
         AGB_TRY(after_launch("rmsnorm_bwd_generic"));
+    } else if (fast) {
+      if constexpr (sizeof(T) == 2) {
+        const float hf = static_cast<float>(hidden);
+        agb::BwdArgs a{p.g, x, gy, dx_add, gamma, rstd, dx, want_dg ? partials : nullptr, add_mode, hf, 1.0f / hf};
+        P = p.grid;
+        constexpr int kV = 32 / (16 / static_cast<int>(sizeof(T)));
+#define AGB_LAUNCH_FAST(HG, FU, MT, KP)                                                       \
+    do {                                                                                      \
+        AGB_TRY(set_smem(agb::rmsnorm_bwd_fast<T, kV, HG, FU, MT, KP>, p.smem));              \
+        AGB_CUDA(launch_pdl(agb::rmsnorm_bwd_fast<T, kV, HG, FU, MT, KP>, p.grid, p.block, p.smem, st, a)); \
+    } while (0)
+#define AGB_FAST_BY_FLAGS(MT, KP)                                  \
+    do {                                                           \
+        if (gamma && p.full) AGB_LAUNCH_FAST(true, true, MT, KP);  \
+        else if (gamma) AGB_LAUNCH_FAST(true, false, MT, KP);      \
+        else if (p.full) AGB_LAUNCH_FAST(false, true, MT, KP);     \
+        else AGB_LAUNCH_FAST(false, false, MT, KP);                \
+    } while (0)
+        if (keep) AGB_FAST_BY_FLAGS(512, true);
+        else AGB_FAST_BY_FLAGS(768, false);
+#undef AGB_FAST_BY_FLAGS
+#undef AGB_LAUNCH_FAST
+        AGB_TRY(after_launch("rmsnorm_bwd_fast"));
+      }
     } else {
         const float hf = static_cast<float>(hidden);
         agb::BwdArgs a{p.g, x, gy, dx_add, gamma, rstd, dx, want_dg ? partials : nullptr, add_mode, hf, 1.0f / hf};
@@ -414,7 +520,7 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
 #define AGB_LAUNCH_BWD2(V, HG, FU, MT, P2)                                                   \
     do {                                                                                     \
         AGB_TRY(set_smem(agb::rmsnorm_bwd_staged<T, V, HG, FU, MT, P2>, p.smem));            \
-        agb::rmsnorm_bwd_staged<T, V, HG, FU, MT, P2><<<p.grid, p.block, p.smem, st>>>(a);   \
+        AGB_CUDA(launch_pdl(agb::rmsnorm_bwd_staged<T, V, HG, FU, MT, P2>, p.grid, p.block, p.smem, st, a)); \
     } while (0)
 #define AGB_LAUNCH_BWD(V, HG, FU, MT)                     \
     do {                                                  \
@@ -437,7 +543,7 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
 #define AGB_LAUNCH_MULTI(HG, FU, P2)                                                                              \
     do {                                                                                                          \
         AGB_TRY(set_smem(agb::rmsnorm_bwd_staged<T, 32 / kEpv, HG, FU, 512, P2, true>, p.smem));                  \
-        agb::rmsnorm_bwd_staged<T, 32 / kEpv, HG, FU, 512, P2, true><<<p.grid, p.block, p.smem, st>>>(a);         \
+        AGB_CUDA(launch_pdl(agb::rmsnorm_bwd_staged<T, 32 / kEpv, HG, FU, 512, P2, true>, p.grid, p.block, p.smem, st, a)); \
     } while (0)
 #define AGB_MULTI_P2(HG, FU)                        \
     do {                                            \
@@ -715,11 +821,13 @@ int agb_set_option(const char* key, int64_t value) {
     else if (!strcmp(key, "threads")) opt_threads = value;
     else if (!strcmp(key, "force_generic")) opt_force_generic = value;
     else if (!strcmp(key, "ept")) opt_ept = value;
+    else if (!strcmp(key, "pdl")) opt_pdl = value;
+    else if (!strcmp(key, "bf16_strict")) opt_bf16_strict = value;
+    else if (!strcmp(key, "bwd_keep")) opt_bwd_keep = value;
+    else if (!strcmp(key, "reserve_sms")) opt_reserve_sms = value;
     else if (!strcmp(key, "rows_per_warp")) opt_rpw = value;   // backward, one-warp rows: 0 auto, 1 off, 2..4 forced
-    else if (!strcmp(key, "peer_poll_limit")) {   // polls before a cross-GPU wait gives up (0 = default, ~2 s)
-        const int v = value > 0 ? static_cast<int>(value < (1 << 22) ? value : (1 << 22)) : (1 << 20);
-        AGB_CUDA(cudaMemcpyToSymbol(agb::g_peer_poll_limit, &v, sizeof(int)));
-    }
+    else if (!strcmp(key, "peer_poll_limit"))     // polls before a cross-GPU wait gives up (0 = default, ~2 s)
+        opt_peer_poll_limit = value > 0 ? (value < (1 << 22) ? value : (1 << 22)) : (1 << 20);
     else return fail(AGB_ERR_INVALID_ARG, "unknown option '%s'", key);
     return AGB_OK;
 }
@@ -733,7 +841,9 @@ int agb_describe_launch(int which, int64_t rows, int64_t hidden, int dtype, int 
     const int elem = dtype == AGB_F32 ? 4 : 2;
     if (which <= 2) {
         const int narr = which == kFwd ? (fused_add ? 2 : 1) : (which == kBwd ? (fused_add == 1 ? 3 : 2) : 2);
-        plan_launch(static_cast<Which>(which), rows, hidden, elem, narr, 1, *d, &p);
+        bool keep = false;
+        if (which == kBwd) plan_bwd(rows, hidden, elem, narr, 1, *d, &p, &keep);
+        else plan_launch(static_cast<Which>(which), rows, hidden, elem, narr, 1, *d, &p);
     } else if (which == 3) {   // the same calls as launch_ln_fwd / launch_ln_bwd / launch_ln_jvp
         plan_launch(kFwd, rows, hidden, elem, 1, 0, *d, &p, 0, true);
     } else if (which == 4) {

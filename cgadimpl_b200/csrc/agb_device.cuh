@@ -14,10 +14,6 @@ namespace agb {
 // (defined here: the library is a single translation unit)
 __device__ int g_device_status = 0;
 
-// Polls of a counter in another GPU's memory before a cross-GPU wait gives up (a poll sleeps up to
-// 2 us: about two seconds); agb_set_option("peer_poll_limit") changes it.
-__device__ int g_peer_poll_limit = 1 << 20;
-
 // A wait gives up after kWaitPollLimit polls of mbarrier.try_wait, each of which may suspend the
 // thread in hardware for up to kWaitSuspendNs: at most ~2.6 s in total.
 constexpr int kWaitPollLimit = 1 << 18;
@@ -64,6 +60,15 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
         "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
 }
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may have its CTAs placed on
+// the SMs while the kernel before it in the stream is still draining; it must not touch global memory
+// before pdl_wait(), which returns once that kernel has completed and its writes are visible (at once
+// when the launch carried no such attribute).  pdl_trigger() tells the scheduler that the kernel
+// AFTER this one may be placed as soon as room frees up.  Both are no-ops for plain launches.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---------------------------------------------------------------- strict fp32 arithmetic
 // The reference materialises an fp32 tensor after every elementwise call, so products must not

@@ -119,7 +119,7 @@ int agb_peer_acquire(agb_peer_t* p, agb_stream_t stream, double** sums) {
     const unsigned long long t = p->step + 1;
     const int b = static_cast<int>(t & 1);
     if (p->world > 1 && t > 2) {   // everybody must have read what this rank wrote into buffer b at step t-2
-        agb::peer_wait_ack_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p->blk, p->world, b, t - 2);
+        agb::peer_wait_ack_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p->blk, p->world, b, t - 2, peer_poll_limit());
         AGB_TRY(after_launch("peer_wait_ack"));
     }
     *sums = reinterpret_cast<double*>(p->blk.base[p->rank] + agb::kPeerHeaderBytes +
@@ -146,7 +146,7 @@ int agb_peer_rmsnorm_bwd(agb_peer_t* p, const void* x, const void* gamma, const 
     }
     const unsigned long long t = p->step + 1;
     const int b = static_cast<int>(t & 1);
-    agb::PeerHook hook{p->blk, p->world, p->rank, b, (p->world > 1 && t > 2) ? t - 2 : 0ull, t};
+    agb::PeerHook hook{p->blk, p->world, p->rank, b, (p->world > 1 && t > 2) ? t - 2 : 0ull, t, peer_poll_limit()};
     double* sums = reinterpret_cast<double*>(p->blk.base[p->rank] + agb::kPeerHeaderBytes +
                                              static_cast<size_t>(b) * static_cast<size_t>(p->max_hidden) * sizeof(double));
     t_reduce_hook = &hook;
@@ -180,7 +180,7 @@ int agb_peer_sum(agb_peer_t* p, float* dgamma, int64_t hidden, int accumulate, a
     const unsigned long long t = p->step + 1;
     agb::peer_sum_kernel<<<1, agb::kPeerSumThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         p->blk, p->world, p->rank, static_cast<int>(t & 1), t, static_cast<long long>(p->max_hidden),
-        static_cast<int>(hidden), dgamma, accumulate);
+        static_cast<int>(hidden), dgamma, accumulate, peer_poll_limit());
     AGB_TRY(after_launch("peer_sum"));
     p->step = t;
     p->acquired = p->published = false;

@@ -3,12 +3,15 @@
 #pragma once
 #include "agb/agb_shard.h"
 #include "agb_device.cuh"
+#include "rmsnorm_staged.cuh"   // kReduceCols / kReduceLanes: the column reduction's block shape
 
 namespace agb {
 
 constexpr int kPeerHeaderBytes = 128;
 constexpr int kPeerCounterOffset = 32;   // an unsigned int used by the fused reduce kernel to find its last CTA
-// (g_peer_poll_limit, the bound of every wait below, lives in agb_device.cuh beside the status word)
+constexpr int kPeerTimeoutsOffset = 36;  // an unsigned int: CTAs of the current fused reduce whose ack wait ran out
+// The bound of every wait below (polls; each sleeps up to 2 us) is a kernel argument taken from the
+// process-wide "peer_poll_limit" option at launch, so that it holds on every device a process drives.
 
 struct PeerBlocks {
     unsigned char* base[AGB_SHARD_MAX];
@@ -32,8 +35,7 @@ __device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long
 // the CTAs of the next forward and backward: an acquire load every half microsecond (each one invalidates
 // the SM's L1) slowed the co-resident forward CTA, and with it the whole statically partitioned kernel,
 // by tens of microseconds.
-__device__ __forceinline__ bool poll_until_at_least(const unsigned long long* p, unsigned long long want) {
-    const int limit = g_peer_poll_limit;
+__device__ __forceinline__ bool poll_until_at_least(const unsigned long long* p, unsigned long long want, int limit) {
     unsigned int ns = 200;
     for (int i = 0; i < limit; ++i) {
         if (ld_relaxed_sys(p) >= want) {
@@ -53,9 +55,9 @@ __device__ __forceinline__ unsigned long long* peer_ack(unsigned char* base, int
 }
 
 // One warp: lane j waits until rank j has acknowledged step `need` on buffer b.
-__global__ void peer_wait_ack_kernel(PeerBlocks blk, int n, int b, unsigned long long need) {
+__global__ void peer_wait_ack_kernel(PeerBlocks blk, int n, int b, unsigned long long need, int poll_limit) {
     const int j = threadIdx.x;
-    if (j < n && !poll_until_at_least(peer_ack(blk.base[j], b), need)) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
+    if (j < n && !poll_until_at_least(peer_ack(blk.base[j], b), need, poll_limit)) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
 }
 
 // The sums of step t are complete in this rank's buffer b (written by earlier kernels of the same
@@ -72,11 +74,12 @@ __global__ void peer_publish_kernel(unsigned char* own, int b, unsigned long lon
 constexpr int kPeerSumThreads = 256;
 __global__ void __launch_bounds__(kPeerSumThreads) peer_sum_kernel(PeerBlocks blk, int n, int self, int b,
                                                                    unsigned long long t, long long max_hidden, int hidden,
-                                                                   float* __restrict__ dgamma, int accumulate) {
+                                                                   float* __restrict__ dgamma, int accumulate,
+                                                                   int poll_limit) {
     __shared__ int timed_out;
     if (threadIdx.x == 0) timed_out = 0;
     __syncthreads();
-    if (threadIdx.x < n && !poll_until_at_least(peer_ready(blk.base[threadIdx.x], b), t)) timed_out = 1;
+    if (threadIdx.x < n && !poll_until_at_least(peer_ready(blk.base[threadIdx.x], b), t, poll_limit)) timed_out = 1;
     __syncthreads();
     if (timed_out) {
         if (threadIdx.x == 0) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
@@ -116,51 +119,65 @@ struct PeerHook {
     PeerBlocks blk;
     int n, self, b;
     unsigned long long need_ack, t;
+    int poll_limit;
 };
 
 // dgamma_reduce_kernel (fp64 store form) with the wait in front and the publication behind, so that the
 // exchange adds no kernel to the backward's stream.  Same summation order, same bits.
 __global__ void __launch_bounds__(512) dgamma_reduce_publish_kernel(const double* __restrict__ partials, int P, int hidden,
                                                                     double* __restrict__ out, PeerHook h) {
-    __shared__ double s[16][33];
+    __shared__ double s[kReduceLanes][kReduceCols + 1];
     __shared__ int timed_out;
     const int cx = threadIdx.x, py = threadIdx.y;
-    const int c = blockIdx.x * 32 + cx;
+    const int c = blockIdx.x * kReduceCols + cx;
     if (cx == 0 && py == 0) timed_out = 0;
     __syncthreads();
-    if (h.need_ack > 0 && py == 0 && cx < h.n && !poll_until_at_least(peer_ack(h.blk.base[cx], h.b), h.need_ack))
+    static_assert(AGB_SHARD_MAX <= kReduceCols * kReduceLanes, "one thread per rank polls");
+    const int tid = py * kReduceCols + cx;
+    if (h.need_ack > 0 && tid < h.n && !poll_until_at_least(peer_ack(h.blk.base[tid], h.b), h.need_ack, h.poll_limit))
         timed_out = 1;
     double v0 = 0.0, v1 = 0.0, v2 = 0.0, v3 = 0.0;
     if (c < hidden) {
         int p = py;
-        for (; p + 48 < P; p += 64) {
+        for (; p + 3 * kReduceLanes < P; p += 4 * kReduceLanes) {
             v0 += partials[static_cast<size_t>(p) * hidden + c];
-            v1 += partials[static_cast<size_t>(p + 16) * hidden + c];
-            v2 += partials[static_cast<size_t>(p + 32) * hidden + c];
-            v3 += partials[static_cast<size_t>(p + 48) * hidden + c];
+            v1 += partials[static_cast<size_t>(p + kReduceLanes) * hidden + c];
+            v2 += partials[static_cast<size_t>(p + 2 * kReduceLanes) * hidden + c];
+            v3 += partials[static_cast<size_t>(p + 3 * kReduceLanes) * hidden + c];
         }
-        for (; p < P; p += 16) v0 += partials[static_cast<size_t>(p) * hidden + c];
+        for (; p < P; p += kReduceLanes) v0 += partials[static_cast<size_t>(p) * hidden + c];
     }
     s[py][cx] = (v0 + v1) + (v2 + v3);
     __syncthreads();
-    if (timed_out) {   // somebody may still be reading the old sums: write nothing, publish nothing
-        if (cx == 0 && py == 0) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
-        return;
-    }
-    if (py == 0 && c < hidden) {
+    // Every CTA polls on its own, so an acknowledgement that lands near the limit can leave some CTAs timed
+    // out and others not.  A CTA whose wait ran out writes nothing (somebody may still be reading the old
+    // sums) but still counts itself, so the "last CTA" counter always returns to zero; the step is published
+    // only if NO CTA of this launch timed out.
+    const bool expired = timed_out != 0;
+    if (!expired && py == 0 && c < hidden) {
         double t = s[0][cx];
 #pragma unroll
-        for (int j = 1; j < 16; ++j) t += s[j][cx];
+        for (int j = 1; j < kReduceLanes; ++j) t += s[j][cx];
         out[c] = t;
         __threadfence();
     }
     __syncthreads();
     if (cx == 0 && py == 0) {
         unsigned int* counter = reinterpret_cast<unsigned int*>(h.blk.base[h.self] + kPeerCounterOffset);
-        if (atomicAdd(counter, 1u) == gridDim.x - 1) {   // the last CTA: every column is written
+        unsigned int* expired_ctas = reinterpret_cast<unsigned int*>(h.blk.base[h.self] + kPeerTimeoutsOffset);
+        if (expired) {
+            atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
+            atomicAdd(expired_ctas, 1u);
+            __threadfence();
+        }
+        if (atomicAdd(counter, 1u) == gridDim.x - 1) {   // the last CTA of this launch
+            __threadfence();
+            const unsigned int bad = atomicExch(expired_ctas, 0u);
             atomicExch(counter, 0u);
-            __threadfence_system();
-            st_release_sys(peer_ready(h.blk.base[h.self], h.b), h.t);
+            if (bad == 0) {                              // every column is written: publish the step
+                __threadfence_system();
+                st_release_sys(peer_ready(h.blk.base[h.self], h.b), h.t);
+            }
         }
     }
 }

@@ -39,6 +39,7 @@ struct PipeGeom {
     int off_red;
     int off_bar;
     int off_flag;
+    int pdl_early;      // 1: let the next kernel's CTAs be placed as soon as this one has started (else: when it drains)
 };
 
 // ---------------------------------------------------------------- packed fp32 helpers
@@ -204,8 +205,11 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_staged(const __grid_const
         for (int s = 0; s < S; ++s) mbar_init(&s_full[s], 1);
         *s_abort = 0;
         mbar_fence_init();
-        for (; issued < my_tiles && issued < S; ++issued) issue(first + issued * stride, static_cast<int>(issued));
     }
+    pdl_wait();      // the inputs may be the output of the kernel before this one in the stream
+    if (g.pdl_early) pdl_trigger();
+    if (tid == 0)
+        for (; issued < my_tiles && issued < S; ++issued) issue(first + issued * stride, static_cast<int>(issued));
     if (HAS_GAMMA) stage_gamma<T>(s_gamma, a.gamma, g.nvec);
     __syncthreads();
 
@@ -292,6 +296,7 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_staged(const __grid_const
             }
         }
     }
+    pdl_trigger();   // this CTA has no tiles left: the next kernel's CTAs may take the room it frees
     if (aborted && tid == 0) drain_after_abort(g, s_full, k, issued);
 }
 
@@ -352,8 +357,11 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
         for (int s = 0; s < S; ++s) mbar_init(&s_full[s], 1);
         *s_abort = 0;
         mbar_fence_init();
-        for (; issued < my_tiles && issued < S; ++issued) issue(first + issued * stride, static_cast<int>(issued));
     }
+    pdl_wait();      // the inputs may be the output of the kernel before this one in the stream
+    if (g.pdl_early) pdl_trigger();
+    if (tid == 0)
+        for (; issued < my_tiles && issued < S; ++issued) issue(first + issued * stride, static_cast<int>(issued));
     if (HAS_GAMMA) stage_gamma<T>(s_gamma, a.gamma, g.nvec);
     __syncthreads();
 
@@ -540,6 +548,7 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_staged(const __grid_const
             }
         }
     }
+    pdl_trigger();   // this CTA has no tiles left: the next kernel's CTAs may take the room it frees
     if (aborted) {
         if (tid == 0) drain_after_abort(g, s_full, k, issued);
         return;
@@ -604,31 +613,36 @@ __global__ void __launch_bounds__(32) bounded_wait_selftest_kernel(int poll_limi
 }
 
 // Stage 2: dgamma[c] = sum over partial rows p = 0..P-1, fixed order, fp64.
-// Block (32, 16): thread (cx, py) sums rows py, py+16, ... of column c with four independent
-// chains, then the 16 sub-sums are added in py order.
+// Block (kReduceCols, kReduceLanes): thread (cx, py) sums rows py, py+32, ... of column c with four
+// independent chains, then the 32 sub-sums are added in py order.  16 columns (128 bytes of every partial
+// row) per CTA make hidden/16 CTAs: more than one per SM from hidden = 4096 on, and the partial rows come
+// out of L2 in a few microseconds.
+constexpr int kReduceCols = 16, kReduceLanes = 32;
 // out_mode 0: fp32 store, 1: fp32 accumulate, 2: fp64 store, 3: fp64 accumulate.
 __global__ void __launch_bounds__(512) dgamma_reduce_kernel(const double* __restrict__ partials, int P, int hidden,
                                                             void* out, int out_mode) {
-    __shared__ double s[16][33];
+    __shared__ double s[kReduceLanes][kReduceCols + 1];
     const int cx = threadIdx.x, py = threadIdx.y;
-    const int c = blockIdx.x * 32 + cx;
+    const int c = blockIdx.x * kReduceCols + cx;
+    pdl_wait();   // the partial rows are written by the backward kernel launched just before
+    pdl_trigger();
     double v0 = 0.0, v1 = 0.0, v2 = 0.0, v3 = 0.0;
     if (c < hidden) {
         int p = py;
-        for (; p + 48 < P; p += 64) {
+        for (; p + 3 * kReduceLanes < P; p += 4 * kReduceLanes) {
             v0 += partials[static_cast<size_t>(p) * hidden + c];
-            v1 += partials[static_cast<size_t>(p + 16) * hidden + c];
-            v2 += partials[static_cast<size_t>(p + 32) * hidden + c];
-            v3 += partials[static_cast<size_t>(p + 48) * hidden + c];
+            v1 += partials[static_cast<size_t>(p + kReduceLanes) * hidden + c];
+            v2 += partials[static_cast<size_t>(p + 2 * kReduceLanes) * hidden + c];
+            v3 += partials[static_cast<size_t>(p + 3 * kReduceLanes) * hidden + c];
         }
-        for (; p < P; p += 16) v0 += partials[static_cast<size_t>(p) * hidden + c];
+        for (; p < P; p += kReduceLanes) v0 += partials[static_cast<size_t>(p) * hidden + c];
     }
     s[py][cx] = (v0 + v1) + (v2 + v3);
     __syncthreads();
     if (py == 0 && c < hidden) {
         double t = s[0][cx];
 #pragma unroll
-        for (int j = 1; j < 16; ++j) t += s[j][cx];
+        for (int j = 1; j < kReduceLanes; ++j) t += s[j][cx];
         if (out_mode == 2)
             static_cast<double*>(out)[c] = t;
         else if (out_mode == 3)

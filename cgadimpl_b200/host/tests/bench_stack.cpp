@@ -1,10 +1,12 @@
 // bench_stack.cpp -- times the fused residual-add + RMSNorm layer stack (forward + VJP through all
 // layers) as ONE CUDA graph replayed on ag::CudaGraphRunner's stream.
-//   bench_stack [layers=32] [rows=16384] [hidden=4096] [iters=10] [warmup=3] [bf16=0]
+//   bench_stack [layers=32] [rows=16384] [hidden=4096] [iters=10] [warmup=3] [bf16=0] [option=value ...]
+// (trailing option=value pairs go to agb_set_option before anything runs)
 // Prints one JSON object: ms per replay (CUDA events around `iters` replays), graph node count,
 // row-layers per second and algorithmic GB/s at (7*H*s + 8) bytes per row and layer.
 #include <cstdio>
 #include <cstdlib>
+#include <string>
 #include <vector>
 
 #include "ad/ag_all.hpp"
@@ -20,6 +22,14 @@ int main(int argc, char** argv) {
     const int iters = argc > 4 ? std::atoi(argv[4]) : 10;
     const int warmup = argc > 5 ? std::atoi(argv[5]) : 3;
     const bool bf16 = argc > 6 && std::atoi(argv[6]) != 0;
+    for (int i = 7; i < argc; ++i) {
+        std::string kv(argv[i]);
+        const size_t eq = kv.find('=');
+        if (eq == std::string::npos || agb_set_option(kv.substr(0, eq).c_str(), std::atoll(kv.c_str() + eq + 1)) != 0) {
+            std::fprintf(stderr, "bench_stack: bad option '%s'\n", argv[i]);
+            return 1;
+        }
+    }
     try {
         const auto dev = DeviceIndex(Device::CUDA);
         const Dtype dt = bf16 ? Dtype::Bfloat16 : Dtype::Float32;

@@ -4,6 +4,7 @@
 // fused residual-add + RMSNorm layers go into one graph; the replay is checked against the eager
 // run and the CPU oracle, and re-run with new input contents at the same addresses.
 #include "ad/ag_all.hpp"
+#include "agb/agb.h"
 #include "agb_oracle.h"
 #include "check.hpp"
 #include "nn/rmsnorm_stack.hpp"
@@ -77,6 +78,51 @@ int main() {
         CHECK(all_close(stack.y_last().to_vector(), wy, 1e-5, 1e-6, "replayed y_last"));
         CHECK(all_close(stack.dh0().to_vector(), wdh, 1e-5, 1e-6, "replayed dh0"));
         CHECK(all_close(stack.dgammas().to_vector(), wdg, 1e-5, 1e-6, "replayed dgammas"));
+    });
+
+    run_test("stack at the benchmark's full size (32 layers x 16384 rows x 4096): graph replay == eager, row slice == oracle", [&] {
+        // The launch plans depend on the row count, so the plans the benchmark times are checked here.  Rows are
+        // independent in y_last and dh0: the oracle runs the whole 32-layer stack on a strided slice of rows.
+        const int LF = 32;
+        const int64_t RF = 16384, HF = 4096;
+        auto x0 = randv(RF * HF, 31), r0 = randv(RF * HF, 32), g0 = randv(RF * HF, 33), gam = randv(LF * HF, 34, 0.02f, 1.f);
+        nn::ResidualRMSNormStack stack(LF, RF, HF, Dtype::Float32, eps, kDev);
+        stack.gammas().copy_(Tensor::from_host(gam.data(), Shape{{LF, HF}}, opt));
+        Tensor x = Tensor::from_host(x0.data(), Shape{{RF, HF}}, opt), r = Tensor::from_host(r0.data(), Shape{{RF, HF}}, opt),
+               g = Tensor::from_host(g0.data(), Shape{{RF, HF}}, opt);
+        stack.forward(x, r);
+        stack.backward(g);
+        cudaDeviceSynchronize();
+        const auto eager_y = stack.y_last().to_vector(), eager_dh = stack.dh0().to_vector(), eager_dg = stack.dgammas().to_vector();
+
+        const int64_t NS = 48, stride = 337;
+        std::vector<float> sx(NS * HF), sr(NS * HF), sg(NS * HF), wy(NS * HF), wdh(NS * HF), wdg(LF * HF), gy_(NS * HF), gdh(NS * HF);
+        for (int64_t i = 0; i < NS; ++i) {
+            const int64_t row = i * stride;
+            std::copy(x0.begin() + row * HF, x0.begin() + (row + 1) * HF, sx.begin() + i * HF);
+            std::copy(r0.begin() + row * HF, r0.begin() + (row + 1) * HF, sr.begin() + i * HF);
+            std::copy(g0.begin() + row * HF, g0.begin() + (row + 1) * HF, sg.begin() + i * HF);
+            std::copy(eager_y.begin() + row * HF, eager_y.begin() + (row + 1) * HF, gy_.begin() + i * HF);
+            std::copy(eager_dh.begin() + row * HF, eager_dh.begin() + (row + 1) * HF, gdh.begin() + i * HF);
+        }
+        agb_oracle_residual_stack(sx.data(), sr.data(), gam.data(), sg.data(), wy.data(), wdh.data(), wdg.data(), NS, HF, LF, eps, AGB_RED_F64);
+        CHECK(all_close(gy_, wy, 1e-5, 1e-6, "full-size y_last, row slice"));
+        CHECK(all_close(gdh, wdh, 1e-5, 1e-6, "full-size dh0, row slice"));
+        CHECK(frac_equal(gy_, wy) >= 0.999);
+        CHECK(frac_equal(gdh, wdh) >= 0.999);
+
+        CudaGraphRunner runner;
+        stack.capture(runner, x, r, g);
+        CHECK(runner.num_nodes() == static_cast<size_t>(3 * LF));
+        const_cast<Tensor&>(stack.y_last()).zero_();
+        const_cast<Tensor&>(stack.dgammas()).zero_();
+        cudaDeviceSynchronize();
+        for (int i = 0; i < 2; ++i) CHECK(runner.replay());
+        runner.synchronize();
+        CHECK(stack.y_last().to_vector() == eager_y);
+        CHECK(stack.dh0().to_vector() == eager_dh);
+        CHECK(stack.dgammas().to_vector() == eager_dg);
+        CHECK(agb_device_status() == 0);
     });
 
     run_test("graph API under capture after warm-up (the reference's pattern)", [&] {

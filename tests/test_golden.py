@@ -122,10 +122,20 @@ def test_cuda_reproduces_bf16_jvp_and_stack_golden():
     c = load("bf16_16x256_outliers")
     bf = torch.bfloat16
     x, gamma, gy = _dev(c["x"].view(np.int16), bf), _dev(c["gamma"].view(np.int16), bf), _dev(c["gy"].view(np.int16), bf)
+    # default for 16-bit I/O: fp32 accumulation, held to the bf16 tolerance
     y, rstd = ops.rmsnorm_fwd(x, gamma, float(c["eps"]))
     dx, dg = ops.rmsnorm_bwd(x, gamma, rstd, gy)
     assert_close(y.float().cpu().numpy(), O.bf16_bits_to_f32(c["y"]), 2e-2, 1e-6, "y")
     assert_close(dx.float().cpu().numpy(), O.bf16_bits_to_f32(c["dx"]), 2e-2, 1e-6, "dx")
+    assert_close(rstd.cpu().numpy(), c["rstd"], 1e-5, 0, "rstd")
+    assert_close(dg.cpu().numpy(), c["dgamma"], 1e-5, 4e-6 * 4, "dgamma (fp32-accumulated over 16 rows)")
+    # the strictly rounded kernels reproduce the stored bits
+    ops.set_option("bf16_strict", 1)
+    try:
+        y, rstd = ops.rmsnorm_fwd(x, gamma, float(c["eps"]))
+        dx, dg = ops.rmsnorm_bwd(x, gamma, rstd, gy)
+    finally:
+        ops.set_option("bf16_strict", 0)
     assert np.array_equal(y.view(torch.int16).cpu().numpy().view(np.uint16), c["y"])
     assert np.array_equal(rstd.cpu().numpy(), c["rstd"]) and np.array_equal(dg.cpu().numpy(), c["dgamma"])
     c = load("jvp_8x64")

@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import oracle_ffi as O
-from inputs import assert_close, make_inputs
+from inputs import assert_close, fp32_accum_dgamma_tol, make_inputs
 
 pytestmark = pytest.mark.gpu
 
@@ -98,8 +98,12 @@ def test_fp32_matches_fp32_reduced_reference_within_its_noise(ops):
     assert np.linalg.norm(host(dg) - ref["dgamma"]) / np.linalg.norm(ref["dgamma"]) < 2e-5
 
 
+@pytest.mark.parametrize("strict", [False, True])
 @pytest.mark.parametrize("hidden", [1000, 5120, 8192, 12288])   # configuration 3 widths
-def test_bf16_parity_with_outlier_rows(ops, hidden):
+def test_bf16_parity_with_outlier_rows(ops, hidden, strict):
+    """bf16 I/O.  Default: the fp32-accumulating kernels (what the task specifies for 16-bit I/O), held to
+    rel 2e-2 on the bf16 outputs and to fp32-accumulation bounds on rstd / dgamma.  strict: the
+    fp64-reducing kernels with the reference's rounding points, which reproduce the oracle's bf16 bits."""
     rows = 384
     x, gamma, gy = make_inputs(rows, hidden, seed=hidden, x_std=3.0, gamma_std=0.1, outlier_frac=0.01)
     xb, gb, gyb = O.f32_to_bf16_bits(x), O.f32_to_bf16_bits(gamma), O.f32_to_bf16_bits(gy)
@@ -107,17 +111,28 @@ def test_bf16_parity_with_outlier_rows(ops, hidden):
     xd = dev(xb.view(np.int16)).view(torch.bfloat16)
     gd = dev(gb.view(np.int16)).view(torch.bfloat16)
     gyd = dev(gyb.view(np.int16)).view(torch.bfloat16)
-    y, rstd = ops.rmsnorm_fwd(xd, gd, 1e-6)
-    dx, dg = ops.rmsnorm_bwd(xd, gd, rstd, gyd)
-    torch.cuda.synchronize()
+    ops.set_option("bf16_strict", int(strict))
+    try:
+        y, rstd = ops.rmsnorm_fwd(xd, gd, 1e-6)
+        dx, dg = ops.rmsnorm_bwd(xd, gd, rstd, gyd)
+        torch.cuda.synchronize()
+    finally:
+        ops.set_option("bf16_strict", 0)
     # stated tolerance: rel 2e-2 (plus the fp32 abs floor for exact zeros)
     assert_close(host(y), O.bf16_bits_to_f32(ref["y"]), BF16_RTOL, F32_ATOL, "y")
     assert_close(host(dx), O.bf16_bits_to_f32(ref["dx"]), BF16_RTOL, F32_ATOL, "dx")
-    assert_close(host(rstd), ref["rstd"], F32_RTOL, 0, "rstd")
-    assert_close(host(dg), ref["dgamma"], F32_RTOL, F32_ATOL, "dgamma")
-    # and in fact the bf16 bit patterns agree
-    assert frac_bit_equal(bits16(y), ref["y"]) >= 0.999
-    assert frac_bit_equal(bits16(dx), ref["dx"]) >= 0.999
+    if strict:
+        assert_close(host(rstd), ref["rstd"], F32_RTOL, 0, "rstd")
+        assert_close(host(dg), ref["dgamma"], F32_RTOL, F32_ATOL, "dgamma")
+        # and in fact the bf16 bit patterns agree
+        assert frac_bit_equal(bits16(y), ref["y"]) >= 0.999
+        assert frac_bit_equal(bits16(dx), ref["dx"]) >= 0.999
+    else:
+        assert_close(host(rstd), ref["rstd"], F32_RTOL, 0, "rstd")          # an fp32 sum of squares: ~1e-6 relative
+        assert_close(host(dg), ref["dgamma"], *fp32_accum_dgamma_tol(rows), "dgamma")
+        # outputs are rounded to bf16 once: almost all of them are the oracle's bits, the rest one bf16 step away
+        assert frac_bit_equal(bits16(y), ref["y"]) >= 0.99
+        assert frac_bit_equal(bits16(dx), ref["dx"]) >= 0.98
 
 
 def test_plain_rms_is_the_reference_op(ops):
@@ -157,7 +172,10 @@ def test_backward_stays_inside_its_workspace(ops, rows, hidden, dtype):
         assert bool((buf[nbytes:] == 0x5A).all()), f"wrote past a {nbytes}-byte workspace"
         results.append((host(dx), host(dg)))
     assert np.array_equal(results[0][0], results[1][0])
-    assert frac_bit_equal(results[0][1], results[1][1]) >= 0.99
+    if dtype == torch.float32:
+        assert frac_bit_equal(results[0][1], results[1][1]) >= 0.99
+    else:   # fp32 column sums: a different grid is a different summation order
+        assert_close(results[0][1], results[1][1], *fp32_accum_dgamma_tol(rows), "dgamma across workspace sizes")
     with pytest.raises(Exception):
         ops.rmsnorm_bwd(xd, gd, rstd, gyd, workspace=torch.empty(smallest - 8, dtype=torch.uint8, device="cuda"))
     ops.device_status()
@@ -264,6 +282,73 @@ def test_full_size_properties_configuration_2(ops):
     assert_close(host(y[idx]), ref["y"], F32_RTOL, F32_ATOL, "y slice")
     assert_close(host(dx[idx]), ref["dx"], F32_RTOL, F32_ATOL, "dx slice")
     assert_close(host(rstd[idx]), ref["rstd"], F32_RTOL, F32_ATOL, "rstd slice")
+
+
+def _device_rows(rows, hidden, seed, std, outlier_rows=None, chunk=16384):
+    """bf16 [rows, hidden] ~ N(0, std) made on the device chunk by chunk; outlier_rows are scaled by 100."""
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    out = torch.empty(rows, hidden, dtype=torch.bfloat16, device="cuda")
+    scale = torch.full((rows, 1), float(std), device="cuda")
+    if outlier_rows is not None:
+        scale[outlier_rows] = 100.0 * std
+    for r0 in range(0, rows, chunk):
+        n = min(chunk, rows - r0)
+        out[r0:r0 + n] = (torch.randn(n, hidden, device="cuda", generator=gen) * scale[r0:r0 + n]).to(torch.bfloat16)
+    return out
+
+
+@pytest.mark.parametrize("hidden,x_std,gamma_std,outliers", [
+    (1000, 3.0, 0.1, True), (5120, 3.0, 0.1, True), (8192, 3.0, 0.1, True), (12288, 3.0, 0.1, True),   # odd-width configuration
+    (8192, 1.0, 0.02, False),                                   # one rank's shard of the 524288-row configuration at 8 GPUs
+])
+def test_full_size_bf16_configurations(ops, hidden, x_std, gamma_std, outliers):
+    """The bf16 benchmark shapes at their FULL row count (65536 rows), i.e. with the launch plans the bench times:
+    the oracle on a slice of rows that contains outlier rows, size-independent identities on every row, and dgamma
+    against an fp64 column sum computed on the device."""
+    rows, eps = 65536, 1e-6
+    pick = torch.Generator().manual_seed(hidden)
+    out_rows = torch.randperm(rows, generator=pick)[: rows // 100].cuda() if outliers else None
+    x = _device_rows(rows, hidden, 1, x_std, out_rows)
+    gy = _device_rows(rows, hidden, 2, 1.0)
+    gamma = (1 + gamma_std * torch.randn(hidden, generator=pick)).to(torch.bfloat16).cuda()
+    y, rstd = ops.rmsnorm_fwd(x, gamma, eps)
+    dx, dg = ops.rmsnorm_bwd(x, gamma, rstd, gy)
+    torch.cuda.synchronize()
+    ops.device_status()
+    assert ops.describe_launch("bwd", rows, hidden, torch.bfloat16)["generic"] == 0
+    # (1) every row: rstd * sqrt(mean(x^2) + eps) == 1 and mean((y/gamma)^2) == 1 - eps*rstd^2
+    want_dg = torch.zeros(hidden, dtype=torch.float64, device="cuda")
+    for r0 in range(0, rows, 8192):
+        sl = slice(r0, r0 + 8192)
+        xd, gd = x[sl].double(), gy[sl].double()
+        ms = (xd * xd).mean(-1)
+        assert torch.allclose(rstd[sl].double() * torch.sqrt(ms + eps), torch.ones_like(ms), rtol=0, atol=2e-6)
+        want_dg += (gd * xd * rstd[sl].double()[:, None]).sum(0)
+        # y / gamma has unit mean square up to eps * rstd^2 and the bf16 rounding of y (2^-9 per element, averaging out)
+        yh = y[sl].double() / gamma.double()
+        assert torch.allclose((yh * yh).mean(-1), 1 - eps * rstd[sl].double() ** 2, rtol=0, atol=2e-3)
+    # (2) dgamma against the fp64 column sum
+    rt, at = fp32_accum_dgamma_tol(rows)
+    err = (dg.double() - want_dg).abs()
+    assert bool((err <= at + rt * want_dg.abs()).all()), f"dgamma: max err {float(err.max()):.3e}"
+    # (3) the oracle on a slice: outlier rows first, then a stride through the rest
+    idx = torch.arange(0, rows, 1021, device="cuda")[:64]
+    if outliers:
+        idx = torch.cat([out_rows[:32], idx])
+    xs, gys = x[idx].contiguous(), gy[idx].contiguous()
+    ref = O.rmsnorm_fwd_bwd_bf16(bits16(xs), bits16(gamma), bits16(gys), eps, O.RED_F64)
+    assert_close(host(y[idx]), O.bf16_bits_to_f32(ref["y"]), BF16_RTOL, F32_ATOL, "y slice")
+    assert_close(host(dx[idx]), O.bf16_bits_to_f32(ref["dx"]), BF16_RTOL, F32_ATOL, "dx slice")
+    assert_close(host(rstd[idx]), ref["rstd"], F32_RTOL, 0, "rstd slice")
+    assert frac_bit_equal(bits16(y[idx].contiguous()), ref["y"]) >= 0.99
+    # (4) the strictly rounded kernels on the same slice give the oracle's bits
+    ops.set_option("bf16_strict", 1)
+    try:
+        ys, rs = ops.rmsnorm_fwd(xs, gamma, eps)
+        dxs, _ = ops.rmsnorm_bwd(xs, gamma, rs, gys)
+    finally:
+        ops.set_option("bf16_strict", 0)
+    assert frac_bit_equal(bits16(ys), ref["y"]) >= 0.999 and frac_bit_equal(bits16(dxs), ref["dx"]) >= 0.999
 
 
 def test_fused_add_forward_backward_and_stack(ops):

@@ -147,6 +147,70 @@ def test_wait_that_runs_out_reports_timeout_and_leaves_dgamma_untouched(ops):
         _destroy(lib, peers)
 
 
+def test_fused_reduce_whose_ack_wait_runs_out_publishes_nothing_and_leaves_its_counter_at_zero(ops):
+    """agb_peer_rmsnorm_bwd waits, inside the backward's column reduction, for every rank's acknowledgement of the
+    step before last.  Here that acknowledgement is wiped (a rank that fell behind), the wait runs out after a small
+    poll limit, and the kernel must report AGB_ERR_TIMEOUT, publish nothing, write no sums, and leave the
+    "last CTA" counter of its block at zero -- a counter left part-way would make a later launch publish early."""
+    cudart = pytest.importorskip("cuda.bindings.runtime")
+    from cgadimpl_b200 import ops as O2
+    from cgadimpl_b200._lib import AgbError, check
+
+    hidden, eps, world = 1024, 1e-6, 2
+    x, gamma, gy = make_inputs(512, hidden, seed=5)
+    xs = [torch.from_numpy(x[:256]).cuda(), torch.from_numpy(x[256:]).cuda()]
+    gys = [torch.from_numpy(gy[:256]).cuda(), torch.from_numpy(gy[256:]).cuda()]
+    gd = torch.from_numpy(gamma).cuda()
+    lib, peers = _make_ranks(world, hidden)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = O2._p
+
+    def words(base, offset, n, dtype):
+        host = np.zeros(n, dtype)
+        (err,) = cudart.cudaMemcpy(host.ctypes.data, base + offset, host.nbytes, cudart.cudaMemcpyKind.cudaMemcpyDeviceToHost)
+        assert int(err) == 0
+        return host
+
+    try:
+        rstds = [ops.rmsnorm_fwd(xs[r], gd, eps)[1] for r in range(world)]
+        ws = ops.bwd_workspace(xs[0])
+        outs = [torch.zeros(hidden, device="cuda") for _ in range(world)]
+        dxs = [torch.empty_like(t) for t in xs]
+
+        def fused_bwd(r):
+            return lib.agb_peer_rmsnorm_bwd(peers[r], p(xs[r]), p(gd), p(rstds[r]), p(gys[r]), None, p(dxs[r]), p(ws),
+                                            ws.numel(), xs[r].shape[0], hidden, 0, stream)
+
+        for _ in range(2):                                  # steps 1 and 2: everybody publishes, sums, acknowledges
+            for r in range(world):
+                check(fused_bwd(r))
+            for r in range(world):
+                check(lib.agb_peer_sum(peers[r], C.c_void_p(outs[r].data_ptr()), hidden, 0, stream))
+        torch.cuda.synchronize()
+        ops.device_status()
+        base0, base1 = C.c_void_p(), C.c_void_p()
+        check(lib.agb_peer_block(peers[0], C.byref(base0)))
+        check(lib.agb_peer_block(peers[1], C.byref(base1)))
+        assert list(words(base0.value, 0, 4, np.uint64)) == [2, 1, 2, 1]        # ready[2], ack[2] after two steps
+        (err,) = cudart.cudaMemset(base1.value + 16, 0, 16)                     # rank 1 "has not acknowledged" anything
+        assert int(err) == 0
+        sums_before = words(base0.value, 128 + hidden * 8, hidden, np.float64)  # buffer 1: step 3 would overwrite it
+        ops.set_option("peer_poll_limit", 2000)
+        check(fused_bwd(0))                                                     # step 3 of rank 0: needs ack >= 1 of rank 1
+        torch.cuda.synchronize()
+        with pytest.raises(AgbError) as e:
+            ops.device_status()
+        assert e.value.status == 6
+        assert list(words(base0.value, 0, 2, np.uint64)) == [2, 1]              # step 3 was not published
+        assert list(words(base0.value, 32, 2, np.uint32)) == [0, 0]             # counter and expired-CTA count back at zero
+        assert np.array_equal(words(base0.value, 128 + hidden * 8, hidden, np.float64), sums_before)   # no sums written
+        y, _ = ops.rmsnorm_fwd(torch.ones(4, 64, device="cuda"), None, 1e-5)    # the context still works
+        assert torch.isfinite(y).all()
+    finally:
+        ops.set_option("peer_poll_limit", 0)
+        _destroy(lib, peers)
+
+
 def test_call_order_is_checked(ops):
     lib, peers = _make_ranks(1, 256)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)

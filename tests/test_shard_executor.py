@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import oracle_ffi as O
-from inputs import assert_close, make_inputs
+from inputs import assert_close, fp32_accum_dgamma_tol, make_inputs
 
 pytestmark = pytest.mark.gpu
 
@@ -125,7 +125,8 @@ def test_bf16_shards(ops):
     y1, rstd1 = ops.rmsnorm_fwd(xd, gd, eps)
     dx1, dg1 = ops.rmsnorm_bwd(xd, gd, rstd1, gyd)
     assert torch.equal(y, y1) and torch.equal(rstd, rstd1) and torch.equal(dx, dx1)
-    assert_close(dgs[0].cpu().numpy(), dg1.cpu().numpy(), 1e-6, 1e-7, "bf16 dgamma sharded vs single call")
+    # fp32-accumulated column sums: three shards add up in another order than one call over all rows
+    assert_close(dgs[0].cpu().numpy(), dg1.cpu().numpy(), *fp32_accum_dgamma_tol(256), "bf16 dgamma sharded vs single call")
 
 
 def test_without_gamma_and_argument_errors(ops):
@@ -172,4 +173,5 @@ def test_two_devices_exchange_over_peer_mappings(ops, dtype, deferred):
     assert torch.equal(y, y1) and torch.equal(rstd, rstd1) and torch.equal(dx, dx1)
     for d in dgs[1:]:
         assert torch.equal(d, dgs[0])
-    assert_close(dgs[0].cpu().numpy(), dg1.cpu().numpy(), 1e-6, 1e-7, "dgamma over peers vs single device")
+    tol = (1e-6, 1e-7) if dtype == torch.float32 else fp32_accum_dgamma_tol(sum(rows_per_shard))
+    assert_close(dgs[0].cpu().numpy(), dg1.cpu().numpy(), *tol, "dgamma over peers vs single device")
