@@ -128,10 +128,11 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     if (which == kBwd && fast) {
         // fp32-accumulating backward (rmsnorm_bwd_fast): 32 elements per thread; fast == 1 keeps x and gy in
         // registers between the passes (launch bound 512 threads), fast == 2 re-reads the tile (768 threads)
-        vpt = 32 / epv;
+        // fast == 3: 64 elements per thread, tile re-read (half the per-row fixed cost per element; 384 threads)
+        vpt = (fast == 3 ? 64 : 32) / epv;
         G = round_up((nvec + vpt - 1) / vpt, 32);
-        max_threads = fast == 1 ? 512 : 768;
-        regs = fast == 1 ? 128 : 80;
+        max_threads = fast == 2 ? 768 : (fast == 3 ? 384 : 512);
+        regs = fast == 2 ? 80 : (fast == 3 ? 168 : 128);
         if (G > max_threads) return;
     } else if (which == kBwd) {
         const int want = static_cast<int>(opt_ept.load());
@@ -185,7 +186,11 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     // heavy: the caller's kernel has several times the instructions per byte of the RMSNorm forward (LayerNorm:
     // measured 4.5 -> 5.4-6.4 TB/s in fp32 when it gets the full thread count)
     const bool light = !heavy && which == kFwd && elem == 4;
-    const int max_resident = light && !want_ctas && !opt_threads.load() ? 512 : 2048;
+    // The fp32-accumulating 16-bit forward is as light per byte as the fp32 one, and measured the same way:
+    // ONE CTA per SM with about 768 threads streams 6-15 % faster than two or four CTAs on every width tried
+    // (8192: 6.25 against 5.70 TB/s, 5120: 6.59 / 5.52, 12288: 6.3-6.7 / 5.88, 1000: 6.07 / 5.36, 4096: 6.25 / 5.49).
+    const bool light16 = !heavy && which == kFwd && elem == 2 && narr == 1 && !opt_bf16_strict.load();
+    const int max_resident = (light || light16) && !want_ctas && !opt_threads.load() ? (light16 ? 768 : 512) : 2048;
     // The forward with the fused residual add (two arrays in, two out) is an exception, measured on the
     // 32-layer stack shape: ONE CTA per SM streams best -- bf16 with the usual tile (6.4 against 6.2 TB/s),
     // fp32 with a single row group and a two-slot ring (6.45-6.55 against 5.9 TB/s; a third slot brings it
@@ -196,7 +201,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     // 256-thread ones on every fp32 shape measured (6.1-6.2 against 5.25 TB/s at 32768 x 4096, 5.7 against
     // 5.1 at hidden 1024); in bf16, where the kernel is bound by instruction issue, four stay ahead.
     const bool ln_fwd32 = heavy && which == kFwd && narr == 1 && elem == 4;
-    const int c_hi = want_ctas ? want_ctas : (fused_fwd ? 1 : (ln_fwd32 ? 2 : 4));
+    const int c_hi = want_ctas ? want_ctas : (fused_fwd || light16 ? 1 : (ln_fwd32 ? 2 : 4));
     int rpt = 0, ctas = 0, S = 0, best = 0;
     for (int c = (want_ctas ? want_ctas : 1); c <= c_hi; ++c)
         for (int r = target / G > 0 ? target / G : 1; r >= 1; --r) {
@@ -211,7 +216,9 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
             break;  // the largest tile that fits for this CTA count
         }
     // (fused-add forward, fp32, wide rows: a single row group and a two-slot ring, see above)
-    if (fused_fwd && elem == 4 && G >= 256 && !opt_threads.load() && stages_for(1, 1) >= 2) {
+    // (measured again with the fp32-accumulating 16-bit kernel: 8192 6.82 against 5.92 TB/s, 4096 6.64 / 5.87,
+    //  12288 6.18 / 5.88; so the rule holds for both element sizes when the strict 16-bit kernel is not asked for)
+    if (fused_fwd && (elem == 4 || !opt_bf16_strict.load()) && G >= 256 && !opt_threads.load() && stages_for(1, 1) >= 2) {
         rpt = 1; ctas = 1; S = 2;
     }
     if (rpt == 0) return;
@@ -219,7 +226,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     // short rows 2 against 3: +4 %): deeper prefetch only scatters the DRAM accesses of an SM over more rows.
     if (which == kFwd && !heavy && narr == 1) {
         const int cap = elem == 4 ? 3 : 2;
-        if (S > cap) S = cap;
+        if (S > cap && !(opt_stages.load() > cap)) S = cap;
     }
     if (ln_fwd32 && ctas > 1 && S > 2) S = 2;
     const int want_stages = static_cast<int>(opt_stages.load());
@@ -289,8 +296,9 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
 }
 
 // The backward's plan: 16-bit I/O takes the fp32-accumulating kernel (unless "bf16_strict"), which exists with
-// two register budgets: the one that holds more threads on an SM wins; on a tie the register-keeping form,
-// which has fewer instructions per element.
+// three register budgets ("bwd_keep" 1, 2, 3 force one): 64 elements per thread where that fits (see below);
+// else, of the two 32-element forms, the one that holds more threads on an SM, and on a tie the
+// register-keeping one, which has fewer instructions per element.
 void plan_bwd(int64_t rows, int64_t hidden, int elem, int narr, int ngamma, const DevInfo& d, Plan* p, bool* keep) {
     *keep = false;
     if (elem == 2 && !opt_bf16_strict.load()) {
@@ -298,6 +306,15 @@ void plan_bwd(int64_t rows, int64_t hidden, int elem, int narr, int ngamma, cons
         plan_launch(kBwd, rows, hidden, elem, narr, ngamma, d, &pk, 0, false, 1);
         plan_launch(kBwd, rows, hidden, elem, narr, ngamma, d, &pn, 0, false, 2);
         const int64_t want_keep = opt_bwd_keep.load();
+        // 64 elements per thread halve the fixed cost per row and thread (barrier, two reductions): measured
+        // +10 % at 4096 columns, +2 % at 8192, but -8 % at 12288, where a row group of 192 threads is all an SM
+        // can hold.  Taken when every thread's vectors exist, a row is at most 16 KB and 256 threads stay resident.
+        if (want_keep == 3 || want_keep == 0) {
+            Plan pw;
+            plan_launch(kBwd, rows, hidden, elem, narr, ngamma, d, &pw, 0, false, 3);
+            const bool fits = !pw.generic && pw.full;
+            if (fits && (want_keep == 3 || (hidden * elem <= 16384 && pw.block * pw.ctas >= 256))) { *p = pw; return; }
+        }
         if (want_keep == 1) *keep = !pk.generic;
         else if (want_keep == 2) *keep = pn.generic && !pk.generic;
         else *keep = !pk.generic && (pn.generic || pk.block * pk.ctas >= pn.block * pn.ctas);
@@ -495,11 +512,12 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
         agb::BwdArgs a{p.g, x, gy, dx_add, gamma, rstd, dx, want_dg ? partials : nullptr, add_mode, hf, 1.0f / hf};
         P = p.grid;
         constexpr int kV = 32 / (16 / static_cast<int>(sizeof(T)));
-#define AGB_LAUNCH_FAST(HG, FU, MT, KP)                                                       \
+#define AGB_LAUNCH_FAST_V(V, HG, FU, MT, KP)                                                  \
     do {                                                                                      \
-        AGB_TRY(set_smem(agb::rmsnorm_bwd_fast<T, kV, HG, FU, MT, KP>, p.smem));              \
-        AGB_CUDA(launch_pdl(agb::rmsnorm_bwd_fast<T, kV, HG, FU, MT, KP>, p.grid, p.block, p.smem, st, a)); \
+        AGB_TRY(set_smem(agb::rmsnorm_bwd_fast<T, V, HG, FU, MT, KP>, p.smem));               \
+        AGB_CUDA(launch_pdl(agb::rmsnorm_bwd_fast<T, V, HG, FU, MT, KP>, p.grid, p.block, p.smem, st, a)); \
     } while (0)
+#define AGB_LAUNCH_FAST(HG, FU, MT, KP) AGB_LAUNCH_FAST_V(kV, HG, FU, MT, KP)
 #define AGB_FAST_BY_FLAGS(MT, KP)                                  \
     do {                                                           \
         if (gamma && p.full) AGB_LAUNCH_FAST(true, true, MT, KP);  \
@@ -507,8 +525,12 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
         else if (p.full) AGB_LAUNCH_FAST(false, true, MT, KP);     \
         else AGB_LAUNCH_FAST(false, false, MT, KP);                \
     } while (0)
-        if (keep) AGB_FAST_BY_FLAGS(512, true);
+        if (p.vpt == 2 * kV) {   // 64 elements per thread (planned only when full)
+            if (gamma) AGB_LAUNCH_FAST_V(2 * kV, true, true, 384, false);
+            else AGB_LAUNCH_FAST_V(2 * kV, false, true, 384, false);
+        } else if (keep) AGB_FAST_BY_FLAGS(512, true);
         else AGB_FAST_BY_FLAGS(768, false);
+#undef AGB_LAUNCH_FAST_V
 #undef AGB_FAST_BY_FLAGS
 #undef AGB_LAUNCH_FAST
         AGB_TRY(after_launch("rmsnorm_bwd_fast"));

@@ -68,9 +68,11 @@ def build(force: bool = False) -> str:
         exe = os.path.join(BIN, f[:-4])
         src = os.path.join(tdir, f)
         if force or not _newer(exe, [src, LIB, oracle] + _all_headers()):
-            _run([_cxx()] + CXXFLAGS + INCLUDES + ["-o", exe, src, "-L", HERE, "-lagb_host",
-                                                  "-L", os.path.dirname(oracle), "-l:liboracle.so"] + link +
-                 ["-Wl,-rpath,$ORIGIN/..", "-Wl,-rpath,$ORIGIN/../..", "-Wl,-rpath," + os.path.dirname(oracle)])
+            # the timing programs (bench_*.cpp) are product-side: they neither include nor link the CPU checker
+            checker = [] if f.startswith("bench_") else ["-L", os.path.dirname(oracle), "-l:liboracle.so",
+                                                         "-Wl,-rpath," + os.path.dirname(oracle)]
+            _run([_cxx()] + CXXFLAGS + INCLUDES + ["-o", exe, src, "-L", HERE, "-lagb_host"] + checker + link +
+                 ["-Wl,-rpath,$ORIGIN/..", "-Wl,-rpath,$ORIGIN/../.."])
     return LIB
 
 

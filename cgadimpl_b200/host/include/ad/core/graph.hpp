@@ -76,6 +76,21 @@ struct Node : std::enable_shared_from_this<Node> {
     // or [1] against [rows, hidden]), as `grad += gy` is in the reference's row-reduction rules.
     void accumulate_grad(const Tensor& grad_contribution);
 
+    // Lazy gradients.  The reference allocates and zero-fills a full-size gradient for every node that
+    // needs one when the node is built (graph.cpp:36) and every rule then reads it back to add to it:
+    // one write and one read of [rows, hidden] per node that the arithmetic does not need.  Here `grad`
+    // stays unallocated until the first contribution of a backward pass, which WRITES it (no zero fill,
+    // no read-back); later contributions add.  zero_grad() only clears `grad_live`.  A reader that goes
+    // through Value::grad() / materialized_grad() sees what the reference shows: zeros until something
+    // has been accumulated.  Code that touches the `grad` member directly sees an empty tensor (or the
+    // previous pass's values after zero_grad) until then.
+    bool grad_live{false};          // guarded by grad_mutex: `grad` holds the sum of this pass's contributions
+    // With grad_mutex held: makes sure `grad` has the value's shape and returns it; *first says whether the
+    // caller must overwrite it (no contribution yet) or add to it.  Marks the gradient live.
+    Tensor& open_grad(bool* first);
+    // What a reader sees: the accumulated gradient, zeros (allocated on demand) when there is none yet.
+    Tensor& materialized_grad();
+
     Node(const Tensor& v, Op op_, bool req_grad, const char* nm = "");
     Node() = default;
 };

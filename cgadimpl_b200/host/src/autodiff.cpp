@@ -19,11 +19,10 @@ namespace ag {
 void zero_grad(const Value& root) {
     for (Node* n : topo_from(root.node.get()))
         if (n->requires_grad()) {
-            detail::StreamGuard g(n->creation_context.stream);
-            const bool gone = n->value_released && n->value.numel() == 0;  // activation dropped: use what it looked like
-            const Shape& shape = gone ? n->released_shape : n->value.shape();
-            if (n->grad.defined() && n->grad.numel() == shape.numel()) n->grad.zero_();
-            else n->grad = Tensor::zeros(shape, gone ? n->released_options : ag::options(n->value));
+            // Lazy: the buffer (if any) is kept, marked empty, and overwritten by the next pass's first
+            // contribution; a reader sees zeros through Value::grad().  No memset here.
+            std::lock_guard<std::mutex> lock(n->grad_mutex);
+            n->grad_live = false;
         }
 }
 
@@ -84,7 +83,7 @@ void run_rule(Node* n) {
         for (auto& p : n->inputs)
             if (!checkpoint_impl::ensure_value_present(p))
                 throw std::runtime_error("autodiff: an input activation is gone and cannot be recomputed");
-    fn(n, n->grad);
+    fn(n, n->materialized_grad());
     // `value_released` means careful deletion dropped this activation once: whoever brought it back
     // (this rule or a child's) no longer needs it
     if (n->is_checkpoint && n->value_released) memory::try_delete_node(n, memory::DeletePolicy::ForwardPass);
@@ -102,6 +101,7 @@ void backward(const Value& root, const Tensor* grad_seed, bool enable_parallel) 
             if (p && p->requires_grad()) p->child_grad_count++;
 
     if (root.node->requires_grad()) {
+        std::lock_guard<std::mutex> lock(root.node->grad_mutex);
         if (grad_seed) {
             root.node->grad = *grad_seed;
         } else {
@@ -110,13 +110,14 @@ void backward(const Value& root, const Tensor* grad_seed, bool enable_parallel) 
             root.node->grad = root.node->value.numel() == 1 ? Tensor::ones(Shape{{1}}, opts)
                                                             : Tensor::ones(root.node->value.shape(), opts);
         }
+        root.node->grad_live = true;
     }
 
     if (!enable_parallel) {
         for (auto it = order.rbegin(); it != order.rend(); ++it) {
             Node* n = *it;
             if (!n->requires_grad()) continue;
-            debug::on_backprop_step(n, n->grad);
+            debug::on_backprop_step(n, n->materialized_grad());
             run_rule(n);
             run_hooks(n);
         }

@@ -173,7 +173,10 @@ bool try_delete_node(Node* node, DeletePolicy policy, const std::unordered_set<N
     node->released_options = ag::options(node->value);
     node->value = Tensor();
     node->tape.clear();
-    if (policy != DeletePolicy::ForwardPass) node->grad = Tensor();
+    if (policy != DeletePolicy::ForwardPass) {
+        node->grad = Tensor();
+        node->grad_live = false;
+    }
     g_del.nodes_deleted++;
     return true;
 }

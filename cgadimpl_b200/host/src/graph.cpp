@@ -11,33 +11,57 @@ Node::Node(const Tensor& v, Op op_, bool req_grad, const char* nm)
     : value(v), debug_name(nm), op(op_), is_leaf(op_ == Op::Leaf), requires_grad_flag_(req_grad) {
     creation_context.stream = current_stream();
     creation_context.device = v.device();
-    // The reference allocates a zero gradient of the value's shape for every node that needs one
-    // (graph.cpp:36); kept, so Value::grad() is defined right after construction.
-    if (requires_grad_flag_) {
-        detail::StreamGuard g(creation_context.stream);
-        grad = Tensor::zeros(v.shape(), ag::options(v));
+    // No gradient buffer yet: see "Lazy gradients" in graph.hpp (the reference zero-fills one here, graph.cpp:36).
+}
+
+Tensor& Node::open_grad(bool* first) {
+    const bool gone = value_released && value.numel() == 0;  // activation dropped by careful deletion
+    const Shape& want = gone ? released_shape : value.shape();
+    if (!grad.defined() || grad.numel() != want.numel()) {
+        grad = Tensor(want, (gone ? released_options : ag::options(value)).with_req_grad(false));
+        grad_live = false;
     }
+    *first = !grad_live;
+    grad_live = true;
+    return grad;
+}
+
+Tensor& Node::materialized_grad() {
+    std::lock_guard<std::mutex> lock(grad_mutex);
+    if (!requires_grad_flag_) return grad;
+    detail::StreamGuard g(creation_context.stream);
+    bool first = false;
+    Tensor& out = open_grad(&first);
+    if (first) out.zero_();
+    return out;
 }
 
 void Node::accumulate_grad(const Tensor& c) {
     std::lock_guard<std::mutex> lock(grad_mutex);
-    const bool gone = value_released && value.numel() == 0;  // activation dropped by careful deletion
-    const Shape& want = gone ? released_shape : value.shape();
-    if (!grad.defined() || grad.numel() != want.numel()) grad = Tensor::zeros(want, gone ? released_options : ag::options(value));
-    if (c.numel() == 0) return;
+    bool first = false;
+    open_grad(&first);
+    if (c.numel() == 0) {
+        if (first) grad.zero_();
+        return;
+    }
     if (!grad.is_cuda()) {
         // CPU nodes are scalar literals and tiny test inputs: plain loop, fp32 only
         if (grad.dtype() != Dtype::Float32 || c.is_cuda() || (c.numel() != grad.numel() && c.numel() != 1))
             throw std::runtime_error("accumulate_grad: unsupported CPU gradient");
         float* g = grad.data<float>();
         const float* s = c.data<float>();
-        for (int64_t i = 0; i < grad.numel(); ++i) g[i] += s[c.numel() == 1 ? 0 : i];
+        for (int64_t i = 0; i < grad.numel(); ++i) g[i] = (first ? 0.0f : g[i]) + s[c.numel() == 1 ? 0 : i];
         return;
     }
     const Tensor src = detail::on_device_of(c, grad);
     const auto rh = detail::rows_hidden(grad);
     const int mode = detail::classify_broadcast(grad, src);
     ag_cuda_stream_t st = reinterpret_cast<ag_cuda_stream_t>(OwnTensor::cuda::getCurrentStream());
+    if (first && mode == AGB_BCAST_FULL && src.dtype() == grad.dtype()) {
+        grad.copy_(src);        // the first contribution is the gradient
+        return;
+    }
+    if (first) grad.zero_();    // a broadcast first contribution: clear, then add as below
     if (mode == AGB_BCAST_FULL)
         detail::check_status(agb_vjp_add(grad.raw(), nullptr, src.raw(), grad.numel(), detail::agb_dtype(grad), st),
                              "accumulate_grad");
@@ -49,8 +73,8 @@ void Node::accumulate_grad(const Tensor& c) {
 
 Tensor& Value::val() { return node->value; }
 const Tensor& Value::val() const { return node->value; }
-Tensor& Value::grad() { return node->grad; }
-const Tensor& Value::grad() const { return node->grad; }
+Tensor& Value::grad() { return node->materialized_grad(); }
+const Tensor& Value::grad() const { return node->materialized_grad(); }
 Value::Value() = default;
 Value::Value(std::shared_ptr<Node> n) : node(std::move(n)) {}
 Value::Value(float v) {

@@ -9,7 +9,8 @@ void Module::to(DeviceIndex dev) {
     for (Value& p : params_)
         if (p.node) {
             p.node->value = p.node->value.to(dev);
-            p.node->grad = Tensor::zeros(p.node->value.shape(), ag::options(p.node->value));
+            p.node->grad = Tensor();          // allocated on the new device by the first contribution
+            p.node->grad_live = false;
             p.node->creation_context.device = dev;
         }
 }
@@ -17,8 +18,8 @@ void Module::to(DeviceIndex dev) {
 void Module::zero_grad() {
     for (Value& p : params_)
         if (p.node && p.node->requires_grad()) {
-            if (p.node->grad.defined() && p.node->grad.numel() == p.node->value.numel()) p.node->grad.zero_();
-            else p.node->grad = Tensor::zeros(p.node->value.shape(), ag::options(p.node->value));
+            std::lock_guard<std::mutex> lock(p.node->grad_mutex);
+            p.node->grad_live = false;        // reads as zeros; the next backward overwrites the buffer
         }
 }
 

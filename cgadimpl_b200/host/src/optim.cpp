@@ -11,7 +11,7 @@ void SGD(const Value& root, const Tensor*, float learning_rate) {
     for (Node* n : topo_from(root.node.get())) {
         if (n->op != Op::Leaf || !n->requires_grad()) continue;
         detail::require_cuda(n->value, "SGD");
-        detail::check_status(agb_sgd_step(n->value.raw(), n->grad.raw(), n->value.numel(), learning_rate,
+        detail::check_status(agb_sgd_step(n->value.raw(), n->materialized_grad().raw(), n->value.numel(), learning_rate,
                                           detail::agb_dtype(n->value), n->creation_context.stream),
                              "SGD");
     }
@@ -40,7 +40,7 @@ void Adam::step() {
         Node* n = p.node.get();
         if (!n->requires_grad()) continue;
         detail::require_cuda(n->value, "Adam");
-        detail::check_status(agb_adam_step(n->value.data<float>(), n->grad.data<float>(), m_[n].data<float>(),
+        detail::check_status(agb_adam_step(n->value.data<float>(), n->materialized_grad().data<float>(), m_[n].data<float>(),
                                            v_[n].data<float>(), n->value.numel(), beta1_, beta2_, alpha_eff, eps_eff,
                                            n->creation_context.stream),
                              "Adam::step");
@@ -50,7 +50,10 @@ void Adam::step() {
 void Adam::zero_grad() {
     for (const auto& p : params_) {
         Node* n = p.node.get();
-        if (n->requires_grad() && n->grad.defined()) n->grad.zero_();
+        if (n->requires_grad()) {
+            std::lock_guard<std::mutex> lock(n->grad_mutex);
+            n->grad_live = false;
+        }
     }
 }
 

@@ -15,24 +15,34 @@ ag_cuda_stream_t rule_stream(Node* n) { return n->creation_context.stream; }
 // P.grad += reduce_for_broadcast(g * a, P.value)   (a may be null: plain g)
 // autodiff_vjp_ops.cpp:15-35 picks the axes to sum from the shapes; here the shape class does.
 void accumulate_reduced(Node* P, const Tensor& g, const Tensor* a, ag_cuda_stream_t st) {
-    // classified against P's grad, which has P's shape: P's value may have been dropped
-    const int mode = classify_broadcast(g, P->grad);
+    std::unique_lock<std::mutex> lock(P->grad_mutex);
+    bool first = false;
+    Tensor& G = P->open_grad(&first);   // has P's shape even when P's value has been dropped
+    int mode;
+    try {
+        mode = classify_broadcast(g, G);
+    } catch (...) {
+        if (first) P->grad_live = false;
+        throw;
+    }
     if (mode == AGB_BCAST_FULL) {
+        if (first) P->grad_live = false;  // accumulate_grad opens the slot itself
+        lock.unlock();
         P->accumulate_grad(a ? binary_op(1, g, *a, st) : g);
         return;
     }
-    require_cuda(P->grad, "broadcast gradient");
+    require_cuda(G, "broadcast gradient");
     const auto rh = rows_hidden(g);
     const size_t wsb = agb_mul_reduce_workspace_bytes(rh.rows, rh.hidden);
     void* ws = workspace(wsb, g, st);
-    std::lock_guard<std::mutex> lock(P->grad_mutex);
-    check_status(agb_mul_reduce(g.raw(), a ? a->raw() : nullptr, P->grad.raw(), rh.rows, rh.hidden, mode, /*accumulate=*/1,
+    check_status(agb_mul_reduce(g.raw(), a ? a->raw() : nullptr, G.raw(), rh.rows, rh.hidden, mode, /*accumulate=*/first ? 0 : 1,
                                 ws, wsb, agb_dtype(g), st),
                  "reduce_for_broadcast");
 }
 
-// X.grad += rms_vjp(x, gamma, rstd, gy): dx_add == dx == X.grad fuses accumulate_grad's `+=`.
-// dgamma (fp32) accumulates into G->grad when G is given.
+// X.grad += rms_vjp(x, gamma, rstd, gy): dx_add == dx == X.grad fuses accumulate_grad's `+=`; the FIRST
+// contribution to X.grad is written instead (dx_add = NULL), so the buffer is neither zero-filled nor read.
+// dgamma (fp32) is written to / accumulates into G->grad when G is given.
 void norm_backward(Node* X, Node* G, const Tensor& rstd, const Tensor& gy, ag_cuda_stream_t st) {
     const Tensor& x = X->value;
     const auto rh = rows_hidden(x);
@@ -53,10 +63,13 @@ void norm_backward(Node* X, Node* G, const Tensor& rstd, const Tensor& gy, ag_cu
     std::unique_lock<std::mutex> lx(X->grad_mutex, std::defer_lock), lg;
     if (want_dx) lx.lock();
     if (want_dg) lg = std::unique_lock<std::mutex>(G->grad_mutex);
+    bool first_dx = false, first_dg = false;
+    Tensor* gx = want_dx ? &X->open_grad(&first_dx) : nullptr;
+    Tensor* gg = want_dg ? &G->open_grad(&first_dg) : nullptr;
     check_status(agb_rmsnorm_bwd(x.raw(), G ? G->value.raw() : nullptr, rstd.data<float>(), gy.raw(),
-                                 want_dx ? X->grad.raw() : nullptr, want_dx ? X->grad.raw() : scratch_dx.raw(),
-                                 want_dg ? G->grad.raw() : nullptr, AGB_F32, /*accumulate_dgamma=*/1, ws, wsb, rh.rows,
-                                 rh.hidden, agb_dtype(x), st),
+                                 want_dx && !first_dx ? gx->raw() : nullptr, want_dx ? gx->raw() : scratch_dx.raw(),
+                                 want_dg ? gg->raw() : nullptr, AGB_F32, /*accumulate_dgamma=*/first_dg ? 0 : 1, ws, wsb,
+                                 rh.rows, rh.hidden, agb_dtype(x), st),
                  "rmsnorm backward");
 }
 
@@ -101,8 +114,10 @@ void vjp_LayerNorm(Node* n, const Tensor& gy) {
     if (!X->requires_grad()) return;
     const auto rh = rows_hidden(X->value);
     std::lock_guard<std::mutex> lock(X->grad_mutex);
+    bool first = false;
+    Tensor& G = X->open_grad(&first);
     check_status(agb_layernorm_bwd(X->value.raw(), n->tape[1]->data<float>(), n->tape[0]->data<float>(), gy.raw(),
-                                   X->grad.raw(), X->grad.raw(), rh.rows, rh.hidden, n->eps, agb_dtype(X->value),
+                                   first ? nullptr : G.raw(), G.raw(), rh.rows, rh.hidden, n->eps, agb_dtype(X->value),
                                    rule_stream(n)),
                  "laynor backward");
 }
@@ -142,12 +157,15 @@ void vjp_MeanAll(Node* n, const Tensor& gy) {
     StreamGuard g(rule_stream(n));
     Node* X = n->inputs[0].get();
     if (!X->requires_grad()) return;
-    const float scale = 1.0f / static_cast<float>(X->grad.numel());
-    const auto rh = rows_hidden(X->grad);
-    const Tensor src = on_device_of(gy, X->grad);
     std::lock_guard<std::mutex> lock(X->grad_mutex);
-    check_status(agb_accumulate_broadcast(X->grad.raw(), src.raw(), rh.rows, rh.hidden, AGB_BCAST_SCALAR, scale,
-                                          agb_dtype(X->grad), rule_stream(n)),
+    bool first = false;
+    Tensor& G = X->open_grad(&first);
+    if (first) G.zero_();
+    const float scale = 1.0f / static_cast<float>(G.numel());
+    const auto rh = rows_hidden(G);
+    const Tensor src = on_device_of(gy, G);
+    check_status(agb_accumulate_broadcast(G.raw(), src.raw(), rh.rows, rh.hidden, AGB_BCAST_SCALAR, scale,
+                                          agb_dtype(G), rule_stream(n)),
                  "vjp_MeanAll");
 }
 // autodiff_vjp_ops.cpp:411-414: X.grad += gy ([B,1] broadcast)
@@ -166,7 +184,9 @@ void vjp_SoftmaxRow(Node* n, const Tensor& gy) {
     if (!Z->requires_grad()) return;
     const auto rh = rows_hidden(n->value);
     std::lock_guard<std::mutex> lock(Z->grad_mutex);
-    check_status(agb_softmax_row_bwd(n->value.raw(), gy.raw(), Z->grad.raw(), Z->grad.raw(), rh.rows, rh.hidden,
+    bool first = false;
+    Tensor& G = Z->open_grad(&first);
+    check_status(agb_softmax_row_bwd(n->value.raw(), gy.raw(), first ? nullptr : G.raw(), G.raw(), rh.rows, rh.hidden,
                                      agb_dtype(n->value), rule_stream(n)),
                  "vjp_SoftmaxRow");
 }
@@ -178,7 +198,9 @@ void vjp_LogSumExpRow(Node* n, const Tensor& gy) {
     const auto rh = rows_hidden(Z->value);
     if (gy.numel() != rh.rows) throw std::runtime_error("vjp_LogSumExpRow: gy must have one entry per row");
     std::lock_guard<std::mutex> lock(Z->grad_mutex);
-    check_status(agb_logsumexp_row_bwd(Z->value.raw(), gy.raw(), Z->grad.raw(), Z->grad.raw(), rh.rows, rh.hidden,
+    bool first = false;
+    Tensor& G = Z->open_grad(&first);
+    check_status(agb_logsumexp_row_bwd(Z->value.raw(), gy.raw(), first ? nullptr : G.raw(), G.raw(), rh.rows, rh.hidden,
                                        agb_dtype(Z->value), rule_stream(n)),
                  "vjp_LogSumExpRow");
 }

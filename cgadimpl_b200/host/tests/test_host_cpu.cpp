@@ -160,10 +160,10 @@ int main() {
         CHECK(memory::sweep_safe_nodes(Value(root), memory::DeletePolicy::ForwardPass, keep) == 2);  // n1 and n3
         CHECK(n1->value.numel() == 0 && n3->value.numel() == 0 && n2->value.numel() == 6 && root->value.numel() == 6);
         CHECK(n1->shape() == std::vector<int64_t>({2, 3}) && n1->value_released);
-        CHECK(n1->grad.numel() == 6);                      // ForwardPass keeps gradients
+        CHECK(n1->materialized_grad().numel() == 6);       // ForwardPass keeps gradients
         CHECK(memory::deletion_stats().nodes_deleted == 2 && memory::deletion_stats().memory_freed == 2 * 24);
         zero_grad(Value(root));                            // works on dropped nodes: the shape is remembered
-        CHECK(n3->grad.numel() == 6);
+        CHECK(n3->materialized_grad().numel() == 6);
         // recompute needs kernels, so on CPU it fails cleanly and is counted
         CHECK(!checkpoint_impl::recompute_subgraph(n3));
         CHECK(checkpoint_stats().failed_recomputes >= 1 && checkpoint_stats().successful_recomputes == 0);

@@ -135,6 +135,30 @@ def test_bf16_parity_with_outlier_rows(ops, hidden, strict):
         assert frac_bit_equal(bits16(dx), ref["dx"]) >= 0.98
 
 
+@pytest.mark.parametrize("rows,hidden", [(700, 8192), (513, 4096), (300, 12288), (1000, 1000)])
+def test_bf16_backward_variants_agree(ops, rows, hidden):
+    """The fp32-accumulating backward exists with three register budgets (x and gy kept in registers between the
+    passes; tile re-read; 64 elements per thread).  They share the arithmetic per element and differ only in how
+    a row's dot product and a column's sum are split over threads, so they agree to fp32 rounding."""
+    x, gamma, gy = make_inputs(rows, hidden, seed=rows, x_std=3.0, gamma_std=0.1, outlier_frac=0.01)
+    xd, gd, gyd = dev(x, torch.bfloat16), dev(gamma, torch.bfloat16), dev(gy, torch.bfloat16)
+    _, rstd = ops.rmsnorm_fwd(xd, gd, 1e-6)
+    outs = []
+    try:
+        for keep in (1, 2, 3):
+            ops.set_option("bwd_keep", keep)
+            dx, dg = ops.rmsnorm_bwd(xd, gd, rstd, gyd)
+            dxa, _ = ops.rmsnorm_bwd(xd, gd, rstd, gyd, dx_add=gyd)          # the residual-stream form
+            outs.append((host(dx), host(dg), host(dxa)))
+    finally:
+        ops.set_option("bwd_keep", 0)
+    ops.device_status()
+    for dx, dg, dxa in outs[1:]:
+        assert frac_bit_equal(dx, outs[0][0]) >= 0.995 and frac_bit_equal(dxa, outs[0][2]) >= 0.995
+        assert_close(dx, outs[0][0], BF16_RTOL, F32_ATOL, "dx across variants")
+        assert_close(dg, outs[0][1], *fp32_accum_dgamma_tol(rows), "dgamma across variants")
+
+
 def test_plain_rms_is_the_reference_op(ops):
     """ag::rms(x): no gamma, eps fixed at 1e-5 (normalization.cpp:23-35); backward of sum(rms(a)) on
     the reference's own [4,10] test shape (test_core_ops_gpu.cpp:262-267) against the oracle."""
