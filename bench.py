@@ -659,6 +659,25 @@ def measure_stack(steps, warmup):
             "api": "ag::nn::ResidualRMSNormStack captured by ag::CudaGraphRunner (C++ host layer)"}
 
 
+def measure_api(steps, warmup):
+    """The path a cgadimpl user calls -- ag::rmsnorm + ag::backward through the C++ graph API -- on the fp32
+    Llama-7B-width configuration, eager and as one CUDA graph (cgadimpl_b200/host/build/bench_api)."""
+    from cgadimpl_b200.host import build as host_build
+
+    host_build.build()
+    rows, hidden, _, _ = WORKLOADS["rmsnorm_fwd_vjp_fp32_16x2048x4096"]
+    exe = os.path.join(os.path.dirname(host_build.__file__), "build", "bench_api")
+    r = subprocess.run([exe, str(rows), str(hidden), str(max(steps, 50)), str(max(3, warmup)), "0"], capture_output=True, text=True)
+    if r.returncode != 0:
+        return {"error": (r.stdout + r.stderr)[-400:]}
+    d = json.loads(r.stdout.strip().splitlines()[-1])
+    peak, _ = measured_peak()
+    return {"workload": "rmsnorm_fwd_vjp_fp32_16x2048x4096", "api": "ag::rmsnorm + ag::zero_grad + ag::backward (C++ host layer)",
+            "eager_ms_per_step": d["eager_ms_per_step"], "eager_frac": d["eager_gbs"] / peak,
+            "graph_ms_per_step": d["graph_ms_per_step"], "graph_frac": d["graph_gbs"] / peak,
+            "cuda_graph_nodes": d["graph_nodes"], "launches_per_step": d["launches_per_step"]}
+
+
 def copy_probe(dist, nbytes=1 << 30):
     """Host <-> device copy rate of this rank's GPU with every rank copying at the same time (pinned memory,
     one direction at a time, then both): what bounds the end-to-end figure.  GB/s, min over ranks."""
@@ -877,7 +896,7 @@ def main():
         cpu_baseline["fused_single_pass"] = {"value": fv, "unit": UNIT, "cores": fcores,
                                              "note": f"row-fused C restatement (oracle/agb_oracle.c), best of 8 passes ({fsecs*1e3:.1f} ms each)"}
 
-    other = None
+    other = api_path = None
     if rank == 0 and world == 1 and not args.no_other_configs and args.workload == DEFAULT_WORKLOAD:
         del x, gy, y, dx, prepared          # make room: the other configurations bring their own operands
         torch.cuda.empty_cache()
@@ -888,6 +907,7 @@ def main():
             except Exception as e:  # noqa: BLE001 -- one failing side configuration must not lose the line
                 other.append({"workload": name, "error": repr(e)[:300]})
         other.append(measure_stack(args.steps, args.warmup))
+        api_path = measure_api(args.steps, args.warmup)
 
     if rank == 0:
         line = {
@@ -908,7 +928,7 @@ def main():
                        "timed_seconds": sum(block_ms) / 1e3},
             "hbm_gbs": step_gbs, "bytes_per_row": bpr,
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "dgamma_check": dgamma_check,
-            "e2e": e2e, "cpu_baseline": cpu_baseline, "other_configs": other,
+            "e2e": e2e, "cpu_baseline": cpu_baseline, "other_configs": other, "api_path": api_path,
         }
         print(json.dumps(line), flush=True)
     ex.close()

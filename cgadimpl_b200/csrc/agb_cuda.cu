@@ -2,6 +2,8 @@
 // heuristics behind it.  Single translation unit: all kernels are included here.
 #include "agb/agb.h"
 
+#include <nvtx3/nvToolsExt.h>
+
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -42,6 +44,16 @@ int cuda_fail(cudaError_t e, const char* what) {
     } while (0)
 
 std::atomic<uint64_t> g_launches{0};
+
+// An NVTX range around every compute entry point, so that a timeline tool shows which C-ABI call enqueued
+// which kernels (header-only NVTX 3: a no-op costing a few nanoseconds when no tool is attached).
+struct NvtxRange {
+    explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+    NvtxRange(const NvtxRange&) = delete;
+    NvtxRange& operator=(const NvtxRange&) = delete;
+};
+#define AGB_RANGE() NvtxRange nvtx_range__(__func__)
 
 int after_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
@@ -449,8 +461,7 @@ int launch_dgamma_reduce(const double* partials, int P, int64_t hidden, void* dg
     dim3 block(agb::kReduceCols, agb::kReduceLanes);
     const int grid = static_cast<int>((hidden + agb::kReduceCols - 1) / agb::kReduceCols);
     if (t_reduce_hook && mode == 2) {
-        agb::dgamma_reduce_publish_kernel<<<grid, block, 0, st>>>(partials, P, (int)hidden, static_cast<double*>(dgamma),
-                                                                  *t_reduce_hook);
+        agb::dgamma_reduce_publish_kernel<<<grid, block, 0, st>>>(partials, P, (int)hidden, *t_reduce_hook);
         t_reduce_hook_used = true;
         return after_launch("dgamma_reduce_publish");
     }
@@ -883,6 +894,7 @@ int agb_describe_launch(int which, int64_t rows, int64_t hidden, int dtype, int 
 
 int agb_rmsnorm_fwd(const void* x, const void* gamma, void* y, float* rstd, int64_t rows, int64_t hidden, float eps,
                     int dtype, agb_stream_t stream) {
+    AGB_RANGE();
     AGB_TRY(check_common(rows, hidden, dtype));
     if (rows == 0) return AGB_OK;
     const int elem = dtype == AGB_F32 ? 4 : 2;
@@ -897,6 +909,7 @@ int agb_rmsnorm_fwd(const void* x, const void* gamma, void* y, float* rstd, int6
 
 int agb_add_rmsnorm_fwd(const void* x, const void* r, const void* gamma, void* h, void* y, float* rstd, int64_t rows,
                         int64_t hidden, float eps, int dtype, agb_stream_t stream) {
+    AGB_RANGE();
     AGB_TRY(check_common(rows, hidden, dtype));
     if (rows == 0) return AGB_OK;
     const int elem = dtype == AGB_F32 ? 4 : 2;
@@ -922,6 +935,7 @@ size_t agb_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t hidden, int dtype) 
 int agb_rmsnorm_bwd(const void* x, const void* gamma, const float* rstd, const void* gy, const void* dx_add, void* dx,
                     void* dgamma, int dgamma_dtype, int accumulate_dgamma, void* workspace, size_t workspace_bytes,
                     int64_t rows, int64_t hidden, int dtype, agb_stream_t stream) {
+    AGB_RANGE();
     AGB_TRY(check_common(rows, hidden, dtype));
     const int elem = dtype == AGB_F32 ? 4 : 2;
     if (dgamma && dgamma_dtype != AGB_F32 && dgamma_dtype != AGB_F64)
@@ -947,6 +961,7 @@ int agb_rmsnorm_bwd(const void* x, const void* gamma, const float* rstd, const v
 int agb_rmsnorm_bwd_static(const void* x, const void* gamma, const float* rstd, const void* gy, const void* dx_add,
                            void* dx, float* dgamma, int accumulate_dgamma, int64_t rows, int64_t hidden, int dtype,
                            agb_stream_t stream) {
+    AGB_RANGE();
     AGB_TRY(check_common(rows, hidden, dtype));
     const int elem = dtype == AGB_F32 ? 4 : 2;
     if (dgamma && !gamma) return fail(AGB_ERR_INVALID_ARG, "dgamma requested without gamma");
@@ -981,6 +996,7 @@ int agb_rmsnorm_bwd_static(const void* x, const void* gamma, const float* rstd, 
 }
 
 int agb_dgamma_finalize(const double* sum, float* dgamma, int64_t hidden, int accumulate, agb_stream_t stream) {
+    AGB_RANGE();
     if (hidden <= 0) return fail(AGB_ERR_INVALID_ARG, "hidden=%lld", (long long)hidden);
     AGB_TRY(check_ptr(sum, "sum", 8));
     AGB_TRY(check_ptr(dgamma, "dgamma", 4));
@@ -991,6 +1007,7 @@ int agb_dgamma_finalize(const double* sum, float* dgamma, int64_t hidden, int ac
 
 int agb_rmsnorm_jvp(const void* x, const void* gamma, const float* rstd, const void* tx, const void* tgamma, void* ty,
                     int64_t rows, int64_t hidden, int dtype, agb_stream_t stream) {
+    AGB_RANGE();
     AGB_TRY(check_common(rows, hidden, dtype));
     if (rows == 0) return AGB_OK;
     const int elem = dtype == AGB_F32 ? 4 : 2;
@@ -1009,6 +1026,7 @@ int agb_rmsnorm_jvp(const void* x, const void* gamma, const float* rstd, const v
 namespace {
 int softmax_family(int mode, const void* z, const void* t, const void* rowscale, const void* add, void* out, void* out_row,
                    int64_t rows, int64_t hidden, int dtype, agb_stream_t stream) {
+    AGB_RANGE();
     AGB_TRY(check_common(rows, hidden, dtype));
     if (rows == 0) return AGB_OK;
     const int elem = dtype == AGB_F32 ? 4 : 2;
@@ -1026,6 +1044,7 @@ int softmax_family(int mode, const void* z, const void* t, const void* rowscale,
 
 int agb_layernorm_jvp(const void* y, const void* t, const float* var, void* ty, int64_t rows, int64_t hidden, float eps,
                       int dtype, agb_stream_t stream) {
+    AGB_RANGE();
     AGB_TRY(check_common(rows, hidden, dtype));
     if (rows == 0) return AGB_OK;
     const int elem = dtype == AGB_F32 ? 4 : 2;
@@ -1054,6 +1073,7 @@ int agb_logsumexp_row_jvp(const void* z, const void* tz, void* out, int64_t rows
 }
 int agb_softmax_row_bwd(const void* y, const void* g, const void* dz_add, void* dz, int64_t rows, int64_t hidden,
                         int dtype, agb_stream_t stream) {
+    AGB_RANGE();
     AGB_TRY(check_common(rows, hidden, dtype));
     if (rows == 0) return AGB_OK;
     const int elem = dtype == AGB_F32 ? 4 : 2;
@@ -1067,6 +1087,7 @@ int agb_softmax_row_bwd(const void* y, const void* g, const void* dz_add, void* 
 }
 
 int agb_residual_add(const void* a, const void* b, void* out, int64_t n, int dtype, agb_stream_t stream) {
+    AGB_RANGE();
     if (n < 0) return fail(AGB_ERR_INVALID_ARG, "n=%lld", (long long)n);
     if (dtype != AGB_F32 && dtype != AGB_BF16) return fail(AGB_ERR_UNSUPPORTED, "dtype %d", dtype);
     if (n == 0) return AGB_OK;
@@ -1085,6 +1106,7 @@ int agb_residual_add(const void* a, const void* b, void* out, int64_t n, int dty
 }
 
 int agb_vjp_add(void* ga, void* gb, const void* gy, int64_t n, int dtype, agb_stream_t stream) {
+    AGB_RANGE();
     if (n < 0) return fail(AGB_ERR_INVALID_ARG, "n=%lld", (long long)n);
     if (dtype != AGB_F32 && dtype != AGB_BF16) return fail(AGB_ERR_UNSUPPORTED, "dtype %d", dtype);
     if (n == 0 || (!ga && !gb)) return AGB_OK;
@@ -1203,6 +1225,7 @@ extern "C" {
 
 int agb_mul_reduce(const void* g, const void* a, void* out, int64_t rows, int64_t hidden, int out_mode, int accumulate,
                    void* workspace, size_t workspace_bytes, int dtype, agb_stream_t stream) {
+    AGB_RANGE();
     AGB_TRY(check_common(rows, hidden, dtype));
     if (out_mode < AGB_BCAST_LASTVEC || out_mode > AGB_BCAST_SCALAR) return fail(AGB_ERR_INVALID_ARG, "out_mode %d", out_mode);
     if (rows == 0) return fail(AGB_ERR_INVALID_ARG, "rows == 0");
@@ -1222,6 +1245,7 @@ int agb_mul_reduce(const void* g, const void* a, void* out, int64_t rows, int64_
 
 int agb_layernorm_fwd(const void* x, void* y, float* mean, float* var, int64_t rows, int64_t hidden, float eps,
                       int dtype, agb_stream_t stream) {
+    AGB_RANGE();
     AGB_TRY(check_common(rows, hidden, dtype));
     if (rows == 0) return AGB_OK;
     const int elem = dtype == AGB_F32 ? 4 : 2;
@@ -1236,6 +1260,7 @@ int agb_layernorm_fwd(const void* x, void* y, float* mean, float* var, int64_t r
 
 int agb_layernorm_bwd(const void* x, const float* mean, const float* var, const void* gy, const void* dx_add, void* dx,
                       int64_t rows, int64_t hidden, float eps, int dtype, agb_stream_t stream) {
+    AGB_RANGE();
     AGB_TRY(check_common(rows, hidden, dtype));
     if (rows == 0) return AGB_OK;
     const int elem = dtype == AGB_F32 ? 4 : 2;
@@ -1251,6 +1276,7 @@ int agb_layernorm_bwd(const void* x, const float* mean, const float* var, const 
 }
 
 int agb_sgd_step(void* param, const void* grad, int64_t n, float learning_rate, int dtype, agb_stream_t stream) {
+    AGB_RANGE();
     if (n < 0) return fail(AGB_ERR_INVALID_ARG, "n=%lld", (long long)n);
     if (dtype != AGB_F32 && dtype != AGB_BF16) return fail(AGB_ERR_UNSUPPORTED, "dtype %d", dtype);
     if (n == 0) return AGB_OK;
@@ -1267,6 +1293,7 @@ int agb_sgd_step(void* param, const void* grad, int64_t n, float learning_rate, 
 
 int agb_adam_step(float* param, const float* grad, float* m, float* v, int64_t n, float beta1, float beta2,
                   float alpha_eff, float eps_eff, agb_stream_t stream) {
+    AGB_RANGE();
     if (n < 0) return fail(AGB_ERR_INVALID_ARG, "n=%lld", (long long)n);
     if (n == 0) return AGB_OK;
     AGB_TRY(check_ptr(param, "param", 4));
@@ -1281,6 +1308,7 @@ int agb_adam_step(float* param, const float* grad, float* m, float* v, int64_t n
 }
 
 int agb_row_reduce(int op, const void* x, void* out, int64_t rows, int64_t hidden, int dtype, agb_stream_t stream) {
+    AGB_RANGE();
     AGB_TRY(check_common(rows, hidden, dtype));
     if (op < AGB_REDUCE_SUM || op > AGB_REDUCE_MAX) return fail(AGB_ERR_INVALID_ARG, "op %d", op);
     if (rows == 0) return AGB_OK;
@@ -1322,6 +1350,7 @@ size_t agb_reduce_all_workspace_bytes(int64_t n) {
 
 int agb_reduce_all(int op, const void* x, void* out, int64_t n, int dtype, void* workspace, size_t workspace_bytes,
                    agb_stream_t stream) {
+    AGB_RANGE();
     if (n <= 0) return fail(AGB_ERR_INVALID_ARG, "n=%lld", (long long)n);
     if (dtype != AGB_F32 && dtype != AGB_BF16) return fail(AGB_ERR_UNSUPPORTED, "dtype %d", dtype);
     if (op != AGB_REDUCE_SUM && op != AGB_REDUCE_MEAN) return fail(AGB_ERR_INVALID_ARG, "op %d (sum or mean)", op);

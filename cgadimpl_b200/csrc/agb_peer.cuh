@@ -1,14 +1,14 @@
 // agb_peer.cuh -- the dgamma exchange between ranks that are separate PROCESSES (one per GPU, one
 // node), declared in include/agb/agb_shard.h.  Included at the end of agb_cuda.cu.
 //
-// Each rank owns one device block:
-//   [0,16)   ready[2]  step number whose sums are complete in buffer b   (written by the owner)
-//   [16,32)  ack[2]    step number up to which the OWNER has read everybody's buffer b
-//   [128..)  sums[2][max_hidden] fp64
-// and maps every other rank's block through CUDA IPC (plain peer loads over NVLink, no multicast).
-// Step t uses buffer b = t & 1.  Rank r may overwrite its buffer b at step t once every rank has
-// acknowledged step t-2; it publishes with a release store of t; a reader acquires every rank's
-// ready[b] >= t before it loads the sums.  All waits are bounded polls.
+// Each rank owns one device block (layout in agb_peer_device.cuh): for every source rank s and buffer b a
+// ready counter and an fp64 [max_hidden] slot that s STORES into, and for every reader r an ack counter that
+// r stores into.  Every rank maps every other rank's block through CUDA IPC; only plain peer STORES cross
+// NVLink (no multicast, no remote load).  Step t uses buffer b = t & 1.  Rank p may overwrite its slot b in
+// the blocks at step t once every reader has acknowledged step t-2 (polled in p's own block); it publishes
+// by storing t into ready[p][b] of every block with release semantics; a reader polls ready[s][b] >= t for all
+// s in ITS OWN block, sums the local slots in rank order, and stores its ack into every producer's block.
+// All waits are bounded polls of local memory.
 #pragma once
 #include "agb/agb_shard.h"
 #include "agb_peer_device.cuh"
@@ -26,8 +26,8 @@ struct agb_peer {
 
 namespace {
 
-size_t peer_block_bytes(int64_t max_hidden) {
-    return agb::kPeerHeaderBytes + 2 * static_cast<size_t>(max_hidden) * sizeof(double);
+size_t peer_block_bytes(int world, int64_t max_hidden) {
+    return agb::peer_sums_offset(world, 0, max_hidden);
 }
 
 int peer_check(const agb_peer_t* p, bool need_connected) {
@@ -56,8 +56,8 @@ int agb_peer_create(int rank, int world, int64_t max_hidden, agb_peer_t** out, u
     p->max_hidden = max_hidden;
     cudaError_t e = cudaGetDevice(&p->dev);
     void* mem = nullptr;
-    if (e == cudaSuccess) e = cudaMalloc(&mem, peer_block_bytes(max_hidden));
-    if (e == cudaSuccess) e = cudaMemset(mem, 0, peer_block_bytes(max_hidden));
+    if (e == cudaSuccess) e = cudaMalloc(&mem, peer_block_bytes(world, max_hidden));
+    if (e == cudaSuccess) e = cudaMemset(mem, 0, peer_block_bytes(world, max_hidden));
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->ev_pub, cudaEventDisableTiming);
     if (e == cudaSuccess && handle) {
         cudaIpcMemHandle_t h;
@@ -119,11 +119,11 @@ int agb_peer_acquire(agb_peer_t* p, agb_stream_t stream, double** sums) {
     const unsigned long long t = p->step + 1;
     const int b = static_cast<int>(t & 1);
     if (p->world > 1 && t > 2) {   // everybody must have read what this rank wrote into buffer b at step t-2
-        agb::peer_wait_ack_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p->blk, p->world, b, t - 2, peer_poll_limit());
+        agb::peer_wait_ack_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p->blk.base[p->rank], p->world, b, t - 2,
+                                                                                  peer_poll_limit());
         AGB_TRY(after_launch("peer_wait_ack"));
     }
-    *sums = reinterpret_cast<double*>(p->blk.base[p->rank] + agb::kPeerHeaderBytes +
-                                      static_cast<size_t>(b) * static_cast<size_t>(p->max_hidden) * sizeof(double));
+    *sums = reinterpret_cast<double*>(p->blk.base[p->rank] + agb::peer_sums_offset(p->rank, b, p->max_hidden));
     p->acquired = true;
     p->published = false;
     return AGB_OK;
@@ -146,9 +146,9 @@ int agb_peer_rmsnorm_bwd(agb_peer_t* p, const void* x, const void* gamma, const 
     }
     const unsigned long long t = p->step + 1;
     const int b = static_cast<int>(t & 1);
-    agb::PeerHook hook{p->blk, p->world, p->rank, b, (p->world > 1 && t > 2) ? t - 2 : 0ull, t, peer_poll_limit()};
-    double* sums = reinterpret_cast<double*>(p->blk.base[p->rank] + agb::kPeerHeaderBytes +
-                                             static_cast<size_t>(b) * static_cast<size_t>(p->max_hidden) * sizeof(double));
+    agb::PeerHook hook{p->blk, p->world, p->rank, b, (p->world > 1 && t > 2) ? t - 2 : 0ull, t,
+                       static_cast<long long>(p->max_hidden), peer_poll_limit()};
+    double* sums = reinterpret_cast<double*>(p->blk.base[p->rank] + agb::peer_sums_offset(p->rank, b, p->max_hidden));
     t_reduce_hook = &hook;
     t_reduce_hook_used = false;
     const int st = agb_rmsnorm_bwd(x, gamma, rstd, gy, dx_add, dx, sums, AGB_F64, 0, workspace, workspace_bytes, rows, hidden,
@@ -165,7 +165,10 @@ int agb_peer_publish(agb_peer_t* p, agb_stream_t stream) {
     AGB_TRY(peer_check(p, true));
     if (!p->acquired || p->published) return fail(AGB_ERR_INVALID_ARG, "agb_peer_publish needs one agb_peer_acquire before it");
     const unsigned long long t = p->step + 1;
-    agb::peer_publish_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(p->blk.base[p->rank], static_cast<int>(t & 1), t);
+    // the whole slot is pushed: the width of the step's sums is not known here, and max_hidden doubles are 8 * max_hidden bytes
+    agb::peer_publish_kernel<<<1, agb::kPeerPublishThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        p->blk, p->world, p->rank, static_cast<int>(t & 1), t, static_cast<long long>(p->max_hidden),
+        static_cast<int>(p->max_hidden));
     AGB_TRY(after_launch("peer_publish"));
     p->published = true;
     return AGB_OK;

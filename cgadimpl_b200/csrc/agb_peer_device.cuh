@@ -1,5 +1,4 @@
-// agb_peer_device.cuh -- device side of the cross-process dgamma exchange (host side: agb_peer.cuh;
-// block layout and protocol are described there).
+// agb_peer_device.cuh -- device side of the cross-process dgamma exchange (host side: agb_peer.cuh).
 #pragma once
 #include "agb/agb_shard.h"
 #include "agb_device.cuh"
@@ -7,9 +6,21 @@
 
 namespace agb {
 
-constexpr int kPeerHeaderBytes = 128;
-constexpr int kPeerCounterOffset = 32;   // an unsigned int used by the fused reduce kernel to find its last CTA
-constexpr int kPeerTimeoutsOffset = 36;  // an unsigned int: CTAs of the current fused reduce whose ack wait ran out
+// Block layout (one block per rank, in that rank's memory; N = world size, MH = max_hidden):
+//   [0, 256)     ready[s][b]  u64, s < 16, b < 2: step whose sums rank s has STORED INTO THIS BLOCK (written by s)
+//   [256, 512)   ack[r][b]    u64: step up to which reader r has consumed THIS rank's sums (written by r)
+//   [512, 516)   counter      u32: the fused reduce kernel's "last CTA" ticket
+//   [516, 520)   expired      u32: CTAs of the current fused reduce whose ack wait ran out
+//   [1024, ...)  sums[s][b][MH] fp64, s < N: rank s's column sums of the step that uses buffer b
+// Push protocol: a producer STORES its sums and its ready counter into every rank's block (plain peer stores
+// over NVLink, no multicast) and a reader stores its ack into every producer's block, so every WAIT polls the
+// waiting GPU's own memory and every read of sums is local; nothing but fire-and-forget stores crosses NVLink.
+constexpr int kPeerReadyOffset = 0;
+constexpr int kPeerAckOffset = 256;
+constexpr int kPeerCounterOffset = 512;
+constexpr int kPeerTimeoutsOffset = 516;
+constexpr int kPeerHeaderBytes = 1024;
+static_assert(AGB_SHARD_MAX * 2 * 8 <= 256, "counter tables");
 // The bound of every wait below (polls; each sleeps up to 2 us) is a kernel argument taken from the
 // process-wide "peer_poll_limit" option at launch, so that it holds on every device a process drives.
 
@@ -17,11 +28,6 @@ struct PeerBlocks {
     unsigned char* base[AGB_SHARD_MAX];
 };
 
-__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
-    unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
 __device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
@@ -31,10 +37,7 @@ __device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long
     return v;
 }
 // Polls with RELAXED loads and a growing sleep (0.2 -> 2 us), and pays for the acquire once, with a fence,
-// when the value has arrived.  A rank that runs ahead of the others waits here for most of a step, beside
-// the CTAs of the next forward and backward: an acquire load every half microsecond (each one invalidates
-// the SM's L1) slowed the co-resident forward CTA, and with it the whole statically partitioned kernel,
-// by tens of microseconds.
+// when the value has arrived.  The polled word always lives in the polling GPU's own memory.
 __device__ __forceinline__ bool poll_until_at_least(const unsigned long long* p, unsigned long long want, int limit) {
     unsigned int ns = 200;
     for (int i = 0; i < limit; ++i) {
@@ -47,30 +50,48 @@ __device__ __forceinline__ bool poll_until_at_least(const unsigned long long* p,
     }
     return false;
 }
-__device__ __forceinline__ unsigned long long* peer_ready(unsigned char* base, int b) {
-    return reinterpret_cast<unsigned long long*>(base) + b;
+// ready counter of source rank s / ack counter of reader r, buffer b, in the block at `base`
+__device__ __forceinline__ unsigned long long* peer_ready(unsigned char* base, int s, int b) {
+    return reinterpret_cast<unsigned long long*>(base + kPeerReadyOffset) + 2 * s + b;
 }
-__device__ __forceinline__ unsigned long long* peer_ack(unsigned char* base, int b) {
-    return reinterpret_cast<unsigned long long*>(base) + 2 + b;
+__device__ __forceinline__ unsigned long long* peer_ack(unsigned char* base, int r, int b) {
+    return reinterpret_cast<unsigned long long*>(base + kPeerAckOffset) + 2 * r + b;
+}
+// where rank s's sums of buffer b live inside a block
+__device__ __host__ __forceinline__ size_t peer_sums_offset(int s, int b, long long max_hidden) {
+    return kPeerHeaderBytes +
+           (static_cast<size_t>(s) * 2 + static_cast<size_t>(b)) * static_cast<size_t>(max_hidden) * sizeof(double);
 }
 
-// One warp: lane j waits until rank j has acknowledged step `need` on buffer b.
-__global__ void peer_wait_ack_kernel(PeerBlocks blk, int n, int b, unsigned long long need, int poll_limit) {
-    const int j = threadIdx.x;
-    if (j < n && !poll_until_at_least(peer_ack(blk.base[j], b), need, poll_limit)) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
+// One warp: lane r waits (in this rank's own block) until reader r has acknowledged step `need` on buffer b.
+__global__ void peer_wait_ack_kernel(unsigned char* own, int n, int b, unsigned long long need, int poll_limit) {
+    const int r = threadIdx.x;
+    if (r < n && !poll_until_at_least(peer_ack(own, r, b), need, poll_limit)) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
 }
 
-// The sums of step t are complete in this rank's buffer b (written by earlier kernels of the same
-// stream): make them visible system-wide, then publish the step number.
-__global__ void peer_publish_kernel(unsigned char* own, int b, unsigned long long t) {
+// The sums of step t are complete in this rank's own slot of its own block (written by earlier kernels of the
+// same stream): copy them into this rank's slot of every other rank's block, then store the step number
+// into every block.  One CTA.
+constexpr int kPeerPublishThreads = 1024;
+__global__ void __launch_bounds__(kPeerPublishThreads) peer_publish_kernel(PeerBlocks blk, int n, int self, int b,
+                                                                           unsigned long long t, long long max_hidden,
+                                                                           int hidden) {
+    const size_t off = peer_sums_offset(self, b, max_hidden);
+    const double* src = reinterpret_cast<const double*>(blk.base[self] + off);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const double v = src[c];
+        for (int r = 0; r < n; ++r)
+            if (r != self) reinterpret_cast<double*>(blk.base[r] + off)[c] = v;
+    }
     __threadfence_system();
-    st_release_sys(peer_ready(own, b), t);
+    __syncthreads();
+    if (threadIdx.x < n) st_release_sys(peer_ready(blk.base[threadIdx.x], self, b), t);
 }
 
 // One small CTA (256 threads, few registers: it must fit beside a resident CTA of the persistent forward
-// or backward kernel instead of taking an SM from it -- a 1024-thread version delayed the next forward by
-// ~10 us per step): wait for every rank's publication of step t, add the sums in rank order, round
-// once, acknowledge.  On a timeout nothing is written and nothing is acknowledged.
+// or backward kernel instead of taking an SM from it): wait, in this rank's own block, for every rank's
+// publication of step t, add the sums in rank order (all local reads), round once, and store the
+// acknowledgement into every producer's block.  On a timeout nothing is written and nothing is acknowledged.
 constexpr int kPeerSumThreads = 256;
 __global__ void __launch_bounds__(kPeerSumThreads) peer_sum_kernel(PeerBlocks blk, int n, int self, int b,
                                                                    unsigned long long t, long long max_hidden, int hidden,
@@ -79,19 +100,21 @@ __global__ void __launch_bounds__(kPeerSumThreads) peer_sum_kernel(PeerBlocks bl
     __shared__ int timed_out;
     if (threadIdx.x == 0) timed_out = 0;
     __syncthreads();
-    if (threadIdx.x < n && !poll_until_at_least(peer_ready(blk.base[threadIdx.x], b), t, poll_limit)) timed_out = 1;
+    unsigned char* own = blk.base[self];
+    if (threadIdx.x < n && !poll_until_at_least(peer_ready(own, threadIdx.x, b), t, poll_limit)) timed_out = 1;
     __syncthreads();
     if (timed_out) {
         if (threadIdx.x == 0) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
         return;
     }
-    const size_t off = kPeerHeaderBytes + static_cast<size_t>(b) * static_cast<size_t>(max_hidden) * sizeof(double);
-    // two columns per thread and pass (16-byte loads) when the buffers are 16-byte aligned: max_hidden even
+    const size_t stride = 2 * static_cast<size_t>(max_hidden);   // doubles between consecutive ranks' slots
+    const double* base = reinterpret_cast<const double*>(own + peer_sums_offset(0, b, max_hidden));
+    // two columns per thread and pass (16-byte loads) when the slots are 16-byte aligned: max_hidden even
     const int pairs = (max_hidden % 2 == 0) ? hidden / 2 : 0;
     for (int q = threadIdx.x; q < pairs; q += blockDim.x) {
-        double2 s = __ldcg(reinterpret_cast<const double2*>(blk.base[0] + off) + q);
+        double2 s = __ldcg(reinterpret_cast<const double2*>(base) + q);
         for (int r = 1; r < n; ++r) {
-            const double2 v = __ldcg(reinterpret_cast<const double2*>(blk.base[r] + off) + q);
+            const double2 v = __ldcg(reinterpret_cast<const double2*>(base + r * stride) + q);
             s.x += v.x;
             s.y += v.y;
         }
@@ -100,41 +123,45 @@ __global__ void __launch_bounds__(kPeerSumThreads) peer_sum_kernel(PeerBlocks bl
         dgamma[2 * q + 1] = accumulate ? add_rn(dgamma[2 * q + 1], v1) : v1;
     }
     for (int c = 2 * pairs + threadIdx.x; c < hidden; c += blockDim.x) {
-        double s = __ldcg(reinterpret_cast<const double*>(blk.base[0] + off) + c);
-        for (int r = 1; r < n; ++r) s += __ldcg(reinterpret_cast<const double*>(blk.base[r] + off) + c);
+        double s = __ldcg(base + c);
+        for (int r = 1; r < n; ++r) s += __ldcg(base + r * stride + c);
         const float v = static_cast<float>(s);
         dgamma[c] = accumulate ? add_rn(dgamma[c], v) : v;
     }
     __syncthreads();   // every load of this CTA has returned (its value was used above)
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < n) {
         __threadfence_system();
-        st_release_sys(peer_ack(blk.base[self], b), t);
+        st_release_sys(peer_ack(blk.base[threadIdx.x], self, b), t);   // producer threadIdx.x: your slot b here is free
     }
 }
 
 // What the backward's final column reduction needs to do the exchange's bookkeeping itself: wait until
-// every rank has acknowledged step need_ack (0: nothing to wait for) before it overwrites the sums, and
-// publish step t once the last CTA has written its columns.
+// every reader has acknowledged step need_ack (0: nothing to wait for) before it overwrites the sums, and
+// publish step t once the last CTA has stored its columns.
 struct PeerHook {
     PeerBlocks blk;
     int n, self, b;
     unsigned long long need_ack, t;
+    long long max_hidden;
     int poll_limit;
 };
 
 // dgamma_reduce_kernel (fp64 store form) with the wait in front and the publication behind, so that the
-// exchange adds no kernel to the backward's stream.  Same summation order, same bits.
+// exchange adds no kernel to the backward's stream.  Same summation order, same bits; every column sum is
+// stored into this rank's slot of EVERY rank's block (row lane py stores to rank py).
 __global__ void __launch_bounds__(512) dgamma_reduce_publish_kernel(const double* __restrict__ partials, int P, int hidden,
-                                                                    double* __restrict__ out, PeerHook h) {
+                                                                    PeerHook h) {
     __shared__ double s[kReduceLanes][kReduceCols + 1];
+    __shared__ double total[kReduceCols];
     __shared__ int timed_out;
     const int cx = threadIdx.x, py = threadIdx.y;
     const int c = blockIdx.x * kReduceCols + cx;
     if (cx == 0 && py == 0) timed_out = 0;
     __syncthreads();
-    static_assert(AGB_SHARD_MAX <= kReduceCols * kReduceLanes, "one thread per rank polls");
+    static_assert(AGB_SHARD_MAX <= kReduceLanes, "row lane py stores to rank py");
     const int tid = py * kReduceCols + cx;
-    if (h.need_ack > 0 && tid < h.n && !poll_until_at_least(peer_ack(h.blk.base[tid], h.b), h.need_ack, h.poll_limit))
+    unsigned char* own = h.blk.base[h.self];
+    if (h.need_ack > 0 && tid < h.n && !poll_until_at_least(peer_ack(own, tid, h.b), h.need_ack, h.poll_limit))
         timed_out = 1;
     double v0 = 0.0, v1 = 0.0, v2 = 0.0, v3 = 0.0;
     if (c < hidden) {
@@ -150,7 +177,7 @@ __global__ void __launch_bounds__(512) dgamma_reduce_publish_kernel(const double
     s[py][cx] = (v0 + v1) + (v2 + v3);
     __syncthreads();
     // Every CTA polls on its own, so an acknowledgement that lands near the limit can leave some CTAs timed
-    // out and others not.  A CTA whose wait ran out writes nothing (somebody may still be reading the old
+    // out and others not.  A CTA whose wait ran out stores nothing (somebody may still be reading the old
     // sums) but still counts itself, so the "last CTA" counter always returns to zero; the step is published
     // only if NO CTA of this launch timed out.
     const bool expired = timed_out != 0;
@@ -158,13 +185,17 @@ __global__ void __launch_bounds__(512) dgamma_reduce_publish_kernel(const double
         double t = s[0][cx];
 #pragma unroll
         for (int j = 1; j < kReduceLanes; ++j) t += s[j][cx];
-        out[c] = t;
-        __threadfence();
+        total[cx] = t;
+    }
+    __syncthreads();
+    if (!expired && py < h.n && c < hidden) {
+        reinterpret_cast<double*>(h.blk.base[py] + peer_sums_offset(h.self, h.b, h.max_hidden))[c] = total[cx];
+        __threadfence_system();
     }
     __syncthreads();
     if (cx == 0 && py == 0) {
-        unsigned int* counter = reinterpret_cast<unsigned int*>(h.blk.base[h.self] + kPeerCounterOffset);
-        unsigned int* expired_ctas = reinterpret_cast<unsigned int*>(h.blk.base[h.self] + kPeerTimeoutsOffset);
+        unsigned int* counter = reinterpret_cast<unsigned int*>(own + kPeerCounterOffset);
+        unsigned int* expired_ctas = reinterpret_cast<unsigned int*>(own + kPeerTimeoutsOffset);
         if (expired) {
             atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
             atomicAdd(expired_ctas, 1u);
@@ -174,9 +205,9 @@ __global__ void __launch_bounds__(512) dgamma_reduce_publish_kernel(const double
             __threadfence();
             const unsigned int bad = atomicExch(expired_ctas, 0u);
             atomicExch(counter, 0u);
-            if (bad == 0) {                              // every column is written: publish the step
+            if (bad == 0) {                              // every column is stored everywhere: publish the step
                 __threadfence_system();
-                st_release_sys(peer_ready(h.blk.base[h.self], h.b), h.t);
+                for (int r = 0; r < h.n; ++r) st_release_sys(peer_ready(h.blk.base[r], h.self, h.b), h.t);
             }
         }
     }

@@ -29,20 +29,59 @@ def shard_rows(total_rows, world_size, rank):
     return start, start + base + (1 if rank < extra else 0)
 
 
-def allreduce_dgamma_f64(dg64, group=None):
+class ExchangeTimeout(RuntimeError):
+    """The dgamma exchange did not complete within the caller's deadline: a rank is late, has left, or never
+    entered the collective.  The collective may still be pending; the caller decides whether to wait on or
+    tear the process group down (its buffers must not be reused before then)."""
+
+
+def allreduce_dgamma_f64(dg64, group=None, timeout_s=None):
     """The path's only exchange: sum the [hidden] fp64 dgamma partials of all ranks in place.
-    Works on CUDA tensors (NCCL) and CPU tensors (gloo); a no-op without a process group."""
+    Works on CUDA tensors (NCCL) and CPU tensors (gloo); a no-op without a process group.
+
+    timeout_s: a host-side deadline.  The collective is started asynchronously and waited for at most that
+    long; on expiry ExchangeTimeout is raised instead of blocking forever on a rank that never arrives
+    (the reference's only failure handling is print-and-exit, cgadimpl/src/runtime/cuda_graphs.cpp:12-19).
+    On CPU tensors the wait is the work handle's own; on CUDA tensors, where a collective is stream-ordered
+    and its handle's wait returns at once, the deadline applies to an event recorded behind the collective."""
     if dg64.dtype != torch.float64:
         raise TypeError("dgamma partials are exchanged in fp64 so that the N-rank result rounds like the 1-rank one")
-    if torch.distributed.is_available() and torch.distributed.is_initialized() and \
-            torch.distributed.get_world_size(group) > 1:
-        torch.distributed.all_reduce(dg64, op=torch.distributed.ReduceOp.SUM, group=group)
+    dist = torch.distributed
+    if not (dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1):
+        return dg64
+    if timeout_s is None:
+        dist.all_reduce(dg64, op=dist.ReduceOp.SUM, group=group)
+        return dg64
+    import datetime
+    import time
+
+    work = dist.all_reduce(dg64, op=dist.ReduceOp.SUM, group=group, async_op=True)
+    if dg64.is_cuda:
+        work.wait()                                   # stream-ordered: returns once the collective is enqueued
+        done = torch.cuda.Event()
+        done.record(torch.cuda.current_stream(dg64.device))
+        deadline = time.monotonic() + float(timeout_s)
+        while not done.query():
+            if time.monotonic() > deadline:
+                raise ExchangeTimeout(f"dgamma all-reduce not complete after {timeout_s} s")
+            time.sleep(0.0005)
+        return dg64
+    try:
+        ok = work.wait(timeout=datetime.timedelta(seconds=float(timeout_s)))
+    except RuntimeError as e:                         # gloo reports an expired wait as a RuntimeError
+        raise ExchangeTimeout(f"dgamma all-reduce not complete after {timeout_s} s: {e}") from None
+    if ok is False:
+        raise ExchangeTimeout(f"dgamma all-reduce not complete after {timeout_s} s")
     return dg64
 
 
 class RowShardedRMSNorm:
     def __init__(self, hidden, dtype=torch.float32, eps=1e-5, device=None, group=None, chunk_rows=None, overlap=True,
-                 exchange="auto"):
+                 exchange="auto", exchange_timeout_s=None):
+        """exchange_timeout_s: host-side deadline of every BLOCKING dgamma exchange of this executor
+        (fwd_bwd with overlap off, fwd_bwd_host, and wait_dgamma(timeout_s=...) for the overlapped one);
+        ExchangeTimeout is raised when it runs out.  None waits as long as the process group does."""
+        self.exchange_timeout_s = exchange_timeout_s
         self.hidden = int(hidden)
         self.dtype = dtype
         self.eps = float(eps)
@@ -111,7 +150,7 @@ class RowShardedRMSNorm:
             return y, rstd, dx, dgamma
         if not self.overlap:
             dx, _ = ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=self._dg64, workspace=self._workspace(x))
-            allreduce_dgamma_f64(self._dg64, self.group)
+            allreduce_dgamma_f64(self._dg64, self.group, self.exchange_timeout_s)
             ops.dgamma_finalize(self._dg64, dgamma)
             return y, rstd, dx, dgamma
         dx = self.bwd_and_exchange(x, gamma, rstd, gy, dx, dgamma)
@@ -146,12 +185,29 @@ class RowShardedRMSNorm:
         self._newest = ev
         return dx
 
-    def wait_dgamma(self):
-        """Orders the current stream after the newest dgamma exchange (no-op without overlap)."""
-        if self.overlap and self._peer is not None:
+    def wait_dgamma(self, timeout_s=None):
+        """Orders the current stream after the newest dgamma exchange (no-op without overlap).  With timeout_s
+        the HOST also waits, at most that long, for the exchange to have completed, and raises ExchangeTimeout
+        otherwise (a rank that never arrived)."""
+        if not self.overlap:
+            return
+        if self._peer is not None:
             torch.cuda.current_stream(self.device).wait_stream(self._side)
-        elif self.overlap and self._newest is not None:
+            ev = torch.cuda.Event()
+            ev.record(self._side)
+        else:
+            if self._newest is None:
+                return
             torch.cuda.current_stream(self.device).wait_event(self._newest)
+            ev = self._newest
+        if timeout_s is not None:
+            import time
+
+            deadline = time.monotonic() + float(timeout_s)
+            while not ev.query():
+                if time.monotonic() > deadline:
+                    raise ExchangeTimeout(f"dgamma exchange not complete after {timeout_s} s")
+                time.sleep(0.0005)
 
     def prepare_step(self, x, gy, gamma, y, rstd, dx, dgamma):
         """For loops that repeat a step over the same buffers: validates the operands once and returns an
@@ -247,6 +303,10 @@ class RowShardedRMSNorm:
             gamma_ready = torch.cuda.Event()
             gamma_ready.record()
         nchunks = (rows + chunk - 1) // chunk
+        if nchunks == 0:
+            # an empty shard (more ranks than rows) contributes zeros, not the sums of an earlier call
+            with torch.cuda.stream(st["compute"]):
+                self._dg64.zero_()
         first = True
         for c in range(nchunks):
             r0, r1 = c * chunk, min(rows, (c + 1) * chunk)
@@ -278,7 +338,7 @@ class RowShardedRMSNorm:
                     rstd_host[r0:r1].copy_(s["rstd"][:n], non_blocking=True)
                 s["out_done"].record()
         with torch.cuda.stream(st["compute"]):
-            allreduce_dgamma_f64(self._dg64, self.group)
+            allreduce_dgamma_f64(self._dg64, self.group, self.exchange_timeout_s)
             ops.dgamma_finalize(self._dg64, self._dg32)
             dgamma_host.copy_(self._dg32, non_blocking=True)
         for s in st.values():

@@ -91,9 +91,26 @@ void run_rule(Node* n) {
 
 }  // namespace
 
+// One stream per graph.  Every rule launches on its node's creation stream, writes its parents' gradients
+// there, and the parents' own rules read them on THEIR creation streams; the per-node mutex orders only the
+// host-side enqueue, and the caching allocator hands a freed block back to the pool of the stream it was
+// allocated on.  So an interior node whose stream differs from its consumer's would race on the GPU.  The
+// reference runs everything on one thread-local stream; here that is a checked rule: interior nodes of a
+// graph must share one creation stream (the current stream while the graph was built).  Leaves are exempt --
+// they are long-lived tensors that the caller orders (e.g. parameters made before a capture stream exists).
+void check_single_stream(const std::vector<Node*>& order) {
+    for (Node* n : order)
+        for (auto& p : n->inputs)
+            if (p && !p->is_leaf && p->creation_context.stream != n->creation_context.stream)
+                throw std::runtime_error(std::string("autodiff: node '") + op_name(n->op) + "' was built on another stream than its input '" +
+                                         op_name(p->op) + "'; build a graph under ONE current stream (ag::set_current_stream) -- "
+                                         "gradients and activations are not ordered across streams");
+}
+
 void backward(const Value& root, const Tensor* grad_seed, bool enable_parallel) {
     if (!root.node) return;
     auto order = topo_from(root.node.get());
+    check_single_stream(order);
 
     for (Node* n : order) n->child_grad_count = 0;
     for (Node* n : order)

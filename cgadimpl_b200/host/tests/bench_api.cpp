@@ -45,7 +45,8 @@ int main(int argc, char** argv) {
         // The step a user writes.  Gradients of the leaves are cleared (lazily) every step, so each backward
         // writes them instead of adding to them, like the C-ABI calls the headline numbers time.
         Value x = make_tensor(tiled(1, true), "x");
-        Value gamma = make_tensor(Tensor::from_host(gv.data(), Shape{{H}}, TensorOptions().with_device(dev).with_req_grad(true)), "gamma");
+        // (dgamma is produced in fp32: a 16-bit gamma node takes no gradient through the graph API)
+        Value gamma = make_tensor(Tensor::from_host(gv.data(), Shape{{H}}, TensorOptions().with_device(dev).with_dtype(dt).with_req_grad(!bf16)), "gamma");
         auto step = [&] {
             Value y = rmsnorm(x, gamma, eps);
             zero_grad(y);

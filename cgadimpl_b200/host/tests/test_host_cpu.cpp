@@ -90,6 +90,41 @@ int main() {
         CHECK(fired == 1);
     });
 
+    run_test("one stream per graph is a checked rule; lazy gradients read as zeros", [] {
+        // interior nodes built under different current streams: backward refuses before it launches anything
+        Value a = make_tensor(Tensor::zeros(Shape{{2, 3}}, TensorOptions().with_req_grad(true)), "a");
+        auto mk = [](std::initializer_list<std::shared_ptr<Node>> in) {
+            auto n = std::make_shared<Node>(Tensor::zeros(Shape{{2, 3}}), Op::Add, true, "n");
+            n->inputs.assign(in.begin(), in.end());
+            return n;
+        };
+        set_current_stream(reinterpret_cast<ag_cuda_stream_t>(0x10));
+        auto b = mk({a.node, a.node});
+        set_current_stream(reinterpret_cast<ag_cuda_stream_t>(0x20));
+        auto c = mk({b, b});
+        set_current_stream(nullptr);
+        bool threw = false;
+        try {
+            backward(Value(c));
+        } catch (const std::runtime_error& e) {
+            threw = std::string(e.what()).find("ONE current stream") != std::string::npos;
+        }
+        CHECK(threw);
+        // a leaf made under another stream (a parameter that exists before a capture stream does) is allowed:
+        // the check passes and the walk reaches the rule (which, on CPU tensors, is where it stops)
+        CHECK(b->creation_context.stream != a.node->creation_context.stream);
+        // a gradient nobody has contributed to is not allocated, and reads as zeros through Value::grad()
+        CHECK(!a.node->grad.defined() && !a.node->grad_live);
+        CHECK(a.grad().numel() == 6 && a.grad().to_vector() == std::vector<float>(6, 0.0f));
+        a.node->accumulate_grad(Tensor::full(Shape{{2, 3}}, TensorOptions(), 2.0f));   // first contribution: written
+        a.node->accumulate_grad(Tensor::full(Shape{{1}}, TensorOptions(), 0.5f));      // second: added (broadcast)
+        CHECK(a.grad().to_vector() == std::vector<float>(6, 2.5f));
+        zero_grad(a);                                                                  // lazily: marks the buffer empty
+        CHECK(!a.node->grad_live && a.grad().to_vector() == std::vector<float>(6, 0.0f));
+        a.node->accumulate_grad(Tensor::full(Shape{{1}}, TensorOptions(), 1.5f));      // a broadcast FIRST contribution
+        CHECK(a.grad().to_vector() == std::vector<float>(6, 1.5f));
+    });
+
     run_test("broadcast classification", [] {
         Tensor full = Tensor::zeros(Shape{{4, 5}});
         CHECK(detail::classify_broadcast(full, Tensor::zeros(Shape{{4, 5}})) == AGB_BCAST_FULL);

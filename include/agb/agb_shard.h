@@ -88,17 +88,19 @@ int agb_shard_synchronize(agb_shard_t* s);
 int agb_shard_destroy(agb_shard_t* s);
 
 /* ---- the same exchange between PROCESSES (one process per GPU, all on one node) ----
- * Each rank owns one device block (two fp64 [max_hidden] sum buffers used in turn, a "ready" and an
- * "ack" counter per buffer) and maps the blocks of all other ranks through CUDA IPC.  Per step:
- *   agb_peer_acquire   enqueues, on `stream`, a wait until every rank has read what this rank put into
- *                      the buffer two steps ago, and returns where this step's backward must leave its
+ * Each rank owns one device block with, for every rank, two fp64 [max_hidden] slots used in turn plus a
+ * "ready" and an "ack" counter per slot, and maps the blocks of all other ranks through CUDA IPC.  The
+ * exchange PUSHES: a rank stores its sums and its counters into every rank's block (plain peer stores over
+ * NVLink), so every wait polls the waiting GPU's own memory and every read of sums is local.  Per step:
+ *   agb_peer_acquire   enqueues, on `stream`, a wait until every rank has read what this rank pushed
+ *                      two steps ago, and returns where this step's backward must leave its
  *                      sums (pass it to agb_rmsnorm_bwd as dgamma with dgamma_dtype = AGB_F64);
- *   agb_peer_exchange  enqueues, on `stream`, the publication of those sums (a release store of the step
- *                      number, visible to the peers over NVLink) and, on `sum_stream` (may be the same
- *                      stream; a second one keeps the caller's stream from waiting for the slowest rank),
- *                      one kernel that waits for every rank's publication of this step, adds all ranks'
- *                      sums in rank order in fp64, rounds once to fp32 into `dgamma` (+= with accumulate)
- *                      and acknowledges the read.  Every rank gets the same bits.
+ *   agb_peer_exchange  enqueues, on `stream`, the publication of those sums (they are stored into every
+ *                      rank's block, then the step number with release semantics) and, on `sum_stream`
+ *                      (may be the same stream; a second one keeps the caller's stream from waiting for the
+ *                      slowest rank), one kernel that waits for every rank's publication of this step, adds
+ *                      all ranks' sums in rank order in fp64, rounds once to fp32 into `dgamma` (+= with
+ *                      accumulate) and acknowledges the read.  Every rank gets the same bits.
  * Processes cannot order each other's streams with events, so these kernels wait on counters in
  * device memory that kernels on OTHER GPUs write.  Every such wait is bounded (about two seconds);
  * when it runs out the kernel raises the device status word (agb_device_status -> AGB_ERR_TIMEOUT),

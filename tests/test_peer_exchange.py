@@ -191,19 +191,25 @@ def test_fused_reduce_whose_ack_wait_runs_out_publishes_nothing_and_leaves_its_c
         base0, base1 = C.c_void_p(), C.c_void_p()
         check(lib.agb_peer_block(peers[0], C.byref(base0)))
         check(lib.agb_peer_block(peers[1], C.byref(base1)))
-        assert list(words(base0.value, 0, 4, np.uint64)) == [2, 1, 2, 1]        # ready[2], ack[2] after two steps
-        (err,) = cudart.cudaMemset(base1.value + 16, 0, 16)                     # rank 1 "has not acknowledged" anything
+        # rank 0's block after two steps: ready[s][b] of both sources and ack[r][b] of both readers
+        assert list(words(base0.value, 0, 4, np.uint64)) == [2, 1, 2, 1]
+        assert list(words(base0.value, 256, 4, np.uint64)) == [2, 1, 2, 1]
+        (err,) = cudart.cudaMemset(base0.value + 256 + 16, 0, 16)               # reader 1 "has not acknowledged" anything
         assert int(err) == 0
-        sums_before = words(base0.value, 128 + hidden * 8, hidden, np.float64)  # buffer 1: step 3 would overwrite it
+        slot = 1024 + (0 * 2 + 1) * hidden * 8                                  # rank 0's slot of buffer 1 (step 3's buffer)
+        sums_before = words(base0.value, slot, hidden, np.float64)
+        remote_before = words(base1.value, slot, hidden, np.float64)            # and its copy in rank 1's block
         ops.set_option("peer_poll_limit", 2000)
         check(fused_bwd(0))                                                     # step 3 of rank 0: needs ack >= 1 of rank 1
         torch.cuda.synchronize()
         with pytest.raises(AgbError) as e:
             ops.device_status()
         assert e.value.status == 6
-        assert list(words(base0.value, 0, 2, np.uint64)) == [2, 1]              # step 3 was not published
-        assert list(words(base0.value, 32, 2, np.uint32)) == [0, 0]             # counter and expired-CTA count back at zero
-        assert np.array_equal(words(base0.value, 128 + hidden * 8, hidden, np.float64), sums_before)   # no sums written
+        assert list(words(base0.value, 0, 2, np.uint64)) == [2, 1]              # step 3 was published nowhere
+        assert list(words(base1.value, 0, 2, np.uint64)) == [2, 1]
+        assert list(words(base0.value, 512, 2, np.uint32)) == [0, 0]            # counter and expired-CTA count back at zero
+        assert np.array_equal(words(base0.value, slot, hidden, np.float64), sums_before)      # no sums stored, here or there
+        assert np.array_equal(words(base1.value, slot, hidden, np.float64), remote_before)
         y, _ = ops.rmsnorm_fwd(torch.ones(4, 64, device="cuda"), None, 1e-5)    # the context still works
         assert torch.isfinite(y).all()
     finally:

@@ -56,6 +56,47 @@ def _rank_main(rank, world, port, rows, hidden, q):
         dist.destroy_process_group()
 
 
+def _late_rank_main(rank, world, port, q):
+    """Rank 1 never enters the all-reduce; rank 0's exchange must give up after its host deadline."""
+    import time
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from cgadimpl_b200.executor import ExchangeTimeout, allreduce_dgamma_f64
+
+    part = torch.ones(64, dtype=torch.float64)
+    if rank == 0:
+        t0 = time.monotonic()
+        try:
+            allreduce_dgamma_f64(part, timeout_s=1.0)
+            q.put(("no error", time.monotonic() - t0))
+        except ExchangeTimeout as e:
+            q.put(("timeout", time.monotonic() - t0, str(e)))
+    else:
+        time.sleep(4.0)          # the failure is made on the host: this rank simply does not show up
+    # no destroy_process_group: a collective is still pending on rank 0; the processes just exit
+    os._exit(0)
+
+
+def test_a_rank_that_never_arrives_ends_the_exchange_with_an_error_after_the_deadline():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_late_rank_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        if p.is_alive():
+            p.terminate()
+    assert not q.empty(), "rank 0 reported nothing"
+    got = q.get()
+    assert got[0] == "timeout", got
+    assert 0.9 <= got[1] < 3.5, f"gave up after {got[1]:.2f} s, deadline was 1 s"
+
+
 def test_two_rank_dgamma_exchange_matches_single_rank():
     rows, hidden, world = 1000, 256, 2
     ctx = mp.get_context("spawn")
