@@ -95,7 +95,7 @@ std::atomic<int64_t> opt_stages{0}, opt_ctas_per_sm{0}, opt_threads{0}, opt_forc
 // bwd_keep: fast backward variant (0 auto, 1 registers keep x and gy between the passes, 2 re-read the tile).
 // reserve_sms: SMs the persistent grids leave free (for a collective's kernel running beside them).
 // pdl: programmatic dependent launch between the library's own kernels (see launch_pdl).
-std::atomic<int64_t> opt_bf16_strict{0}, opt_bwd_keep{0}, opt_reserve_sms{0}, opt_pdl{1};
+std::atomic<int64_t> opt_bf16_strict{0}, opt_bwd_keep{0}, opt_reserve_sms{0}, opt_pdl{1}, opt_lone_ring{0};
 // peer_poll_limit: polls (each sleeping up to 2 us) before a wait on another GPU's counter gives up; process-wide,
 // handed to the waiting kernels as an argument at every launch.
 std::atomic<int64_t> opt_peer_poll_limit{1 << 20};
@@ -215,6 +215,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     const bool ln_fwd32 = heavy && which == kFwd && narr == 1 && elem == 4;
     const int c_hi = want_ctas ? want_ctas : (fused_fwd || light16 ? 1 : (ln_fwd32 ? 2 : 4));
     int rpt = 0, ctas = 0, S = 0, best = 0;
+    const int lone_ring = opt_lone_ring.load() == 2 ? 2 : 3;
     for (int c = (want_ctas ? want_ctas : 1); c <= c_hi; ++c)
         for (int r = target / G > 0 ? target / G : 1; r >= 1; --r) {
             if (r > rows && r > 1) continue;
@@ -222,7 +223,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
             if (blk * c > max_resident && !(c == 1 && r == 1)) continue;
             if (static_cast<int64_t>(regs) * blk * c > 65536) continue;
             const int st = stages_for(r, c);
-            if (st < 2 || (c == 1 && st < 3 && r > 1)) continue;  // a lone CTA wants a 3-deep ring
+            if (st < 2 || (c == 1 && st < lone_ring && r > 1)) continue;  // a lone CTA wants a 3-deep ring
             const bool better = blk * c > best || (blk * c == best && !light);
             if (better) { best = blk * c; rpt = r; ctas = c; S = st; }
             break;  // the largest tile that fits for this CTA count
@@ -329,7 +330,8 @@ void plan_bwd(int64_t rows, int64_t hidden, int elem, int narr, int ngamma, cons
         }
         if (want_keep == 1) *keep = !pk.generic;
         else if (want_keep == 2) *keep = pn.generic && !pk.generic;
-        else *keep = !pk.generic && (pn.generic || pk.block * pk.ctas >= pn.block * pn.ctas);
+        // (rows that one warp owns, hidden <= 1024: the register-keeping form measured 4-5 % ahead at 1000 columns)
+        else *keep = !pk.generic && (pn.generic || pk.block * pk.ctas >= pn.block * pn.ctas || pk.g.group_threads == 32);
         *p = *keep ? pk : pn;
         return;
     }
@@ -855,6 +857,7 @@ int agb_set_option(const char* key, int64_t value) {
     else if (!strcmp(key, "force_generic")) opt_force_generic = value;
     else if (!strcmp(key, "ept")) opt_ept = value;
     else if (!strcmp(key, "pdl")) opt_pdl = value;
+    else if (!strcmp(key, "lone_ring")) opt_lone_ring = value;   // 2: a single CTA per SM may run a two-slot ring
     else if (!strcmp(key, "bf16_strict")) opt_bf16_strict = value;
     else if (!strcmp(key, "bwd_keep")) opt_bwd_keep = value;
     else if (!strcmp(key, "reserve_sms")) opt_reserve_sms = value;

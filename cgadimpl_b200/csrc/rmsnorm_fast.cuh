@@ -1,7 +1,8 @@
 // rmsnorm_fast.cuh -- RMSNorm forward / VJP for 16-bit I/O with fp32 accumulation.
 //
 // Same pipeline as rmsnorm_staged.cuh (persistent CTAs, bulk-copy ring signalled on mbarriers, a
-// group of threads per row, 16-byte conflict-free shared-memory reads, streaming 16-byte stores),
+// group of threads per row, 16-byte conflict-free shared-memory reads, streaming 16-byte stores;
+// only the assignment of a row's vectors to the group's threads differs, see v0 below),
 // different arithmetic: every sum is carried in fp32 (packed two-lane FMA chains, fp32 warp
 // shuffles), multiply-adds are fused, and no value passes through fp64 until the per-CTA dgamma
 // partial row is written.  That is what "bf16 I/O with fp32 accumulation" asks for, and it is what
@@ -54,6 +55,10 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_fast(const __grid_constan
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int G = g.group_threads, wpr = G >> 5;
     const int grp = tid / G, tig = tid - grp * G;
+    // Vector i of this thread: each warp of a row group owns VPT*32 consecutive vectors, lane-interleaved, so the
+    // stride between a thread's vectors is a compile-time 512 bytes (immediate offsets, no address arithmetic
+    // per access) and a warp's 16-byte accesses stay consecutive (conflict-free, coalesced).
+    const int v0 = (tig >> 5) * (VPT * 32) + lane;
     const int S = g.stages;
 
     const unsigned char* const src2[2] = {reinterpret_cast<const unsigned char*>(a.x),
@@ -98,7 +103,7 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_fast(const __grid_constan
         if (valid) {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                const int v = tig + i * G;
+                const int v = v0 + i * 32;
                 if (FULL || v < g.nvec) {
                     uint4 raw = sx[v];
                     float2 xv[NP];
@@ -138,7 +143,7 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_fast(const __grid_constan
             uint4* gy = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.y) + row * g.row_bytes);
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                const int v = tig + i * G;
+                const int v = v0 + i * 32;
                 if (FULL || v < g.nvec) {
                     float2 xv[NP];
                     Pairs<T>::unpack(keep[i], xv);
@@ -183,6 +188,10 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int G = g.group_threads, wpr = G >> 5;
     const int grp = tid / G, tig = tid - grp * G;
+    // Vector i of this thread: each warp of a row group owns VPT*32 consecutive vectors, lane-interleaved, so the
+    // stride between a thread's vectors is a compile-time 512 bytes (immediate offsets, no address arithmetic
+    // per access) and a warp's 16-byte accesses stay consecutive (conflict-free, coalesced).
+    const int v0 = (tig >> 5) * (VPT * 32) + lane;
     const int S = g.stages;
     const bool staged_add = a.add_mode == 1;
 
@@ -236,7 +245,7 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
         if (valid) {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                const int v = tig + i * G;
+                const int v = v0 + i * 32;
                 if (FULL || v < g.nvec) {
                     float2 xv[NP], gv[NP];
                     const uint4 graw = sg[v];
@@ -279,7 +288,7 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
             uint4* gdx = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.dx) + row * g.row_bytes);
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                const int v = tig + i * G;
+                const int v = v0 + i * 32;
                 if (FULL || v < g.nvec) {
                     float2 xv[NP], gv[NP], ov[NP], wv[NP];
                     if (KEEP) {
@@ -328,7 +337,7 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
         if (ngroups == 1) {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                const int v = tig + i * G;
+                const int v = v0 + i * 32;
                 if (FULL || v < g.nvec) {
 #pragma unroll
                     for (int e = 0; e < NP; ++e)
@@ -344,7 +353,7 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
                 if (grp == gi) {
 #pragma unroll
                     for (int i = 0; i < VPT; ++i) {
-                        const int v = tig + i * G;
+                        const int v = v0 + i * 32;
                         if (FULL || v < g.nvec) {
 #pragma unroll
                             for (int e = 0; e < NP; ++e) {
