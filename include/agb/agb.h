@@ -12,16 +12,21 @@
  *   - All tensors are row-major and contiguous: [rows, hidden]; `rows` is the product of all
  *     leading dimensions, `hidden` the last one.  rows == 0 is a no-op.
  *   - `dtype` is the storage type of x / y / gy / dx / gamma (AGB_F32 or AGB_BF16).  Statistics
- *     (rstd) and dgamma are always fp32; all arithmetic is fp32 with fp64 reductions, rounded
- *     exactly where the reference materialises a tensor.
+ *     (rstd) and dgamma are always fp32.  AGB_F32: all arithmetic is fp32 with fp64 reductions, rounded
+ *     exactly where the reference materialises a tensor.  AGB_BF16 (RMSNorm forward and VJP): values are
+ *     widened once, sums are carried in fp32 with fused multiply-adds, outputs are rounded once; the
+ *     "bf16_strict" option selects the fp32 arithmetic above for 16-bit I/O as well.
  *   - `stream` is a cudaStream_t (NULL = the legacy default stream).  Calls only enqueue work;
  *     they never synchronise, allocate or free.
  *   - Return value: AGB_OK or an agb_status_t; agb_last_error() gives a message for the
  *     calling thread.  Nothing here calls exit() (the reference's CUDA_CHECK does,
  *     cgadimpl/src/runtime/cuda_graphs.cpp:12-19).
- *   - Re-entrant: no mutable global state except the launch counter and the per-device
- *     properties cache (both atomic / locked).  cgadimpl's parallel backward calls VJP rules
- *     from many threads (cgadimpl/src/core/autodiff.cpp:155-159).
+ *   - Re-entrant: every entry point may be called from many threads at once (cgadimpl's parallel
+ *     backward calls VJP rules from many threads, cgadimpl/src/core/autodiff.cpp:155-159).  The
+ *     process-wide state is: the launch counter and the tuning options of agb_set_option (atomics), the
+ *     per-device properties cache and the per-device address of the built-in scratch array (each under
+ *     a mutex), the device status word that bounded waits raise (one per device, in device memory), and
+ *     the built-in scratch array itself, which calls of agb_rmsnorm_bwd_static share.
  *   - There is no CPU fallback: without a CUDA device every compute entry point returns
  *     AGB_ERR_CUDA.
  */
@@ -70,8 +75,19 @@ int agb_device_status(void);
  * pointer, nullable) receives the number of polls made. */
 int agb_selftest_bounded_wait(int poll_limit, int* polls_done, agb_stream_t stream);
 
-/* Tuning knobs for sweeps ("stages", "ctas_per_sm", "threads", "force_generic"); value 0
- * restores the built-in heuristic.  Returns AGB_ERR_INVALID_ARG for an unknown key. */
+/* Process-wide options; value 0 restores the built-in behaviour unless stated.  Unknown key:
+ * AGB_ERR_INVALID_ARG.
+ *   launch-plan knobs for sweeps: "stages", "ctas_per_sm", "threads", "ept" (elements per thread of the
+ *     strict backward), "rows_per_warp" (strict backward, one-warp rows), "bwd_keep" (16-bit backward:
+ *     1 keep x/gy in registers, 2 re-read the tile, 3 64 elements per thread), "lone_ring" (2: a single
+ *     CTA per SM may run a two-slot ring), "reserve_sms" (SMs the persistent grids leave free),
+ *     "force_generic" (1: the unstaged kernels);
+ *   "bf16_strict"  1: 16-bit I/O through the strictly rounded, fp64-reducing kernels (the fp32 path's
+ *                  arithmetic) instead of the fp32-accumulating ones;
+ *   "pdl"          programmatic dependent launch between the library's kernels: 1 (default) a kernel's CTAs
+ *                  are placed while the previous one drains, 2 as soon as it has started, 0 off;
+ *   "peer_poll_limit"  polls (up to 2 us each) before a wait on another rank's counter gives up
+ *                  (0 = default, about two seconds); process-wide, applies on every device. */
 int agb_set_option(const char* key, int64_t value);
 
 /* Describes the launch the heuristic would make: out[0]=grid, out[1]=block, out[2]=dynamic

@@ -19,7 +19,9 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("CGADIMPL_REFERENCE", "/root/reference/cgadimpl")
+# The reference checkout's cgadimpl/ directory: $CGADIMPL_REFERENCE, else a checkout named "reference" beside
+# this repository; neither = not available (the prebuilt library, if any, is used as it is).
+REF = os.environ.get("CGADIMPL_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference", "cgadimpl")
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT = os.path.join(OUT_DIR, "libcgadimpl_ref.so")
 SHIM = os.path.join(HERE, "ref_shim")
@@ -38,7 +40,7 @@ INCLUDES = ["-I", SHIM, "-I", os.path.join(REF, "include"), "-I", CUDA_INC]
 
 
 def available() -> bool:
-    return os.path.isdir(os.path.join(REF, "src"))
+    return bool(REF) and os.path.isdir(os.path.join(REF, "src"))
 
 
 def build(force: bool = False) -> str:
