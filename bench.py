@@ -879,8 +879,9 @@ def main():
                "rows_per_rank_and_step": er,
                "sample": (f"{er} of this rank's {rows} rows per step" if er < rows else "the rank's whole shard per step")
                          + "; bytes are per rank",
-               "api": "cgadimpl_b200.executor.RowShardedRMSNorm.fwd_bwd_host (pinned host buffers, chunked "
-                      "copy/compute overlap on three streams)"}
+               "api": ("agb_host_pipe_fwd_bwd (C ABI, include/agb/agb_host.h) through RowShardedRMSNorm.fwd_bwd_host"
+                       if world == 1 else "cgadimpl_b200.executor.RowShardedRMSNorm.fwd_bwd_host") +
+                      ": pinned host buffers, chunked copy/compute overlap on three streams"}
         del xh, gyh, yh, dxh
         e2e["copy_probe"] = copy_probe(dist)
 

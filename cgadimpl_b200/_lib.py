@@ -28,6 +28,8 @@ SIGNATURES = {
     "agb_add_rmsnorm_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _vp]),
     "agb_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64, _i]),
     "agb_rmsnorm_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _sz, _i64, _i64, _i, _vp]),
+    "agb_rmsnorm_bwd_partials": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i64, _i64, _i, _vp, C.POINTER(_i)]),
+    "agb_dgamma_reduce": (_i, [_vp, _i, _i64, _vp, _i, _i, _vp]),
     "agb_rmsnorm_bwd_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i, _vp]),
     "agb_dgamma_finalize": (_i, [_vp, _vp, _i64, _i, _vp]),
     "agb_rmsnorm_jvp": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i, _vp]),
@@ -86,6 +88,15 @@ SHARD_SIGNATURES = {
 }
 
 
+# every symbol include/agb/agb_host.h declares (same library)
+HOST_SIGNATURES = {
+    "agb_host_pipe_create": (_i, [_i64, _i, _i64, C.POINTER(_vp)]),
+    "agb_host_pipe_chunk_rows": (_i64, [_vp]),
+    "agb_host_pipe_fwd_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _f, _vp]),
+    "agb_host_pipe_destroy": (_i, [_vp]),
+}
+
+
 class AgbError(RuntimeError):
     def __init__(self, status, message):
         super().__init__(f"agb status {status}: {message}")
@@ -104,7 +115,7 @@ def lib():
                 f"{LIB_PATH} is missing: build it with `python -m cgadimpl_b200.build` "
                 "(there is no CPU or PyTorch fallback)")
         h = C.CDLL(LIB_PATH)
-        for name, (res, args) in list(SIGNATURES.items()) + list(SHARD_SIGNATURES.items()):
+        for name, (res, args) in list(SIGNATURES.items()) + list(SHARD_SIGNATURES.items()) + list(HOST_SIGNATURES.items()):
             fn = getattr(h, name)
             fn.restype = res
             fn.argtypes = args

@@ -47,13 +47,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and os.path.exists(LIB) and os.path.exists(PTXAS_LOG) and \
             all(os.path.getmtime(LIB) >= os.path.getmtime(s) for s in srcs):
         return LIB
-    cmd = [_nvcc()] + NVCC_FLAGS + ["-Xptxas", "-v", "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-o", LIB,
+    tmp = LIB + ".new"     # written beside the target and renamed: a reader never sees a half-written library
+    cmd = [_nvcc()] + NVCC_FLAGS + ["-Xptxas", "-v", "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-o", tmp,
                                     os.path.join(CSRC, "agb_cuda.cu")]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if verbose:
         sys.stderr.write(r.stderr)
     if r.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
         raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+    os.replace(tmp, LIB)
     with open(PTXAS_LOG, "w") as f:
         f.write(r.stderr)
     return LIB

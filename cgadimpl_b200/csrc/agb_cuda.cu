@@ -98,6 +98,9 @@ std::atomic<int64_t> opt_stages{0}, opt_ctas_per_sm{0}, opt_threads{0}, opt_forc
 std::atomic<int64_t> opt_bf16_strict{0}, opt_bwd_keep{0}, opt_reserve_sms{0}, opt_pdl{1}, opt_lone_ring{0};
 // peer_poll_limit: polls (each sleeping up to 2 us) before a wait on another GPU's counter gives up; process-wide,
 // handed to the waiting kernels as an argument at every launch.
+// softmax_strict: the softmax / logsumexp forward family with the reference composition's rounding points
+// (table-driven exp to 2^-33, fp64 sums, exact division) instead of the approximate exp and fp32 sums.
+std::atomic<int64_t> opt_softmax_strict{0};
 std::atomic<int64_t> opt_peer_poll_limit{1 << 20};
 inline int peer_poll_limit() { return static_cast<int>(opt_peer_poll_limit.load()); }
 
@@ -458,7 +461,7 @@ thread_local const agb::PeerHook* t_reduce_hook = nullptr;
 thread_local bool t_reduce_hook_used = false;
 
 int launch_dgamma_reduce(const double* partials, int P, int64_t hidden, void* dgamma, int dgamma_dtype,
-                         int accumulate, cudaStream_t st) {
+                         int accumulate, cudaStream_t st, bool behind_backward = true) {
     const int mode = dgamma_dtype == AGB_F64 ? (accumulate ? 3 : 2) : (accumulate ? 1 : 0);
     dim3 block(agb::kReduceCols, agb::kReduceLanes);
     const int grid = static_cast<int>((hidden + agb::kReduceCols - 1) / agb::kReduceCols);
@@ -467,17 +470,21 @@ int launch_dgamma_reduce(const double* partials, int P, int64_t hidden, void* dg
         t_reduce_hook_used = true;
         return after_launch("dgamma_reduce_publish");
     }
-    AGB_CUDA(launch_pdl(agb::dgamma_reduce_kernel, grid, block, 0, st, partials, P, (int)hidden, dgamma, mode));
+    // placed early only when the kernel before it in this stream is the backward that wrote the partials
+    if (behind_backward) AGB_CUDA(launch_pdl(agb::dgamma_reduce_kernel, grid, block, 0, st, partials, P, (int)hidden, dgamma, mode));
+    else agb::dgamma_reduce_kernel<<<grid, block, 0, st>>>(partials, P, (int)hidden, dgamma, mode);
     return after_launch("dgamma_reduce");
 }
 
 template <typename T>
 int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* gy, const void* dx_add, void* dx,
                void* dgamma, int dgamma_dtype, int accumulate_dgamma, void* workspace, size_t workspace_bytes,
-               int64_t rows, int64_t hidden, cudaStream_t st) {
+               int64_t rows, int64_t hidden, cudaStream_t st, int* partials_only = nullptr) {
+    // partials_only: leave the partial rows in the workspace, report their number, run no reduction
     const DevInfo* d;
     AGB_TRY(device_info(&d));
-    const bool want_dg = gamma != nullptr && dgamma != nullptr;
+    const bool want_dg = gamma != nullptr && (dgamma != nullptr || partials_only != nullptr);
+    if (partials_only) *partials_only = 0;
     if (want_dg) {
         const size_t need = static_cast<size_t>(max_partials(*d)) * hidden * sizeof(double);
         if (!workspace || workspace_bytes < need)
@@ -485,7 +492,7 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
         if (reinterpret_cast<uintptr_t>(workspace) % 16) return fail(AGB_ERR_MISALIGNED, "workspace not 16-byte aligned");
     }
     if (rows == 0) {
-        if (want_dg && !accumulate_dgamma)
+        if (want_dg && !accumulate_dgamma && !partials_only)
             AGB_CUDA(cudaMemsetAsync(dgamma, 0, hidden * (dgamma_dtype == AGB_F64 ? 8 : 4), st));
         return AGB_OK;
     }
@@ -599,6 +606,10 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
 #undef AGB_LAUNCH_BWD2
         AGB_TRY(after_launch("rmsnorm_bwd_staged"));
     }
+    if (partials_only) {
+        *partials_only = P;
+        return AGB_OK;
+    }
     if (want_dg) AGB_TRY(launch_dgamma_reduce(partials, P, hidden, dgamma, dgamma_dtype, accumulate_dgamma, st));
     return AGB_OK;
 }
@@ -682,10 +693,15 @@ int launch_softmax_fwd(int mode, const void* z, const void* t, const void* rowsc
         return after_launch("softmax_fwd_generic");
     }
     agb::SoftmaxArgs a{p.g, z, t, rowscale, add, out, out_row, scratch ? (mode == 3 ? 2 : 1) * p.g.tile_stride : 0};
-#define AGB_SM_STAGED(M)                                                       \
-    do {                                                                       \
-        AGB_TRY(set_smem(agb::softmax_fwd_staged<T, M>, p.smem));              \
-        agb::softmax_fwd_staged<T, M><<<p.grid, p.block, p.smem, st>>>(a);     \
+#define AGB_SM_STAGED(M)                                                              \
+    do {                                                                              \
+        if (opt_softmax_strict.load()) {                                              \
+            AGB_TRY(set_smem(agb::softmax_fwd_staged<T, M, false>, p.smem));          \
+            agb::softmax_fwd_staged<T, M, false><<<p.grid, p.block, p.smem, st>>>(a); \
+        } else {                                                                      \
+            AGB_TRY(set_smem(agb::softmax_fwd_staged<T, M, true>, p.smem));           \
+            agb::softmax_fwd_staged<T, M, true><<<p.grid, p.block, p.smem, st>>>(a);  \
+        }                                                                             \
     } while (0)
     if (mode == 0) AGB_SM_STAGED(0);
     else if (mode == 1) AGB_SM_STAGED(1);
@@ -857,6 +873,7 @@ int agb_set_option(const char* key, int64_t value) {
     else if (!strcmp(key, "force_generic")) opt_force_generic = value;
     else if (!strcmp(key, "ept")) opt_ept = value;
     else if (!strcmp(key, "pdl")) opt_pdl = value;
+    else if (!strcmp(key, "softmax_strict")) opt_softmax_strict = value;
     else if (!strcmp(key, "lone_ring")) opt_lone_ring = value;   // 2: a single CTA per SM may run a two-slot ring
     else if (!strcmp(key, "bf16_strict")) opt_bf16_strict = value;
     else if (!strcmp(key, "bwd_keep")) opt_bwd_keep = value;
@@ -959,6 +976,44 @@ int agb_rmsnorm_bwd(const void* x, const void* gamma, const float* rstd, const v
                                    workspace_bytes, rows, hidden, st)
                : launch_bwd<bf16>(x, gamma, rstd, gy, dx_add, dx, dgamma, dgamma_dtype, accumulate_dgamma, workspace,
                                   workspace_bytes, rows, hidden, st);
+}
+
+int agb_rmsnorm_bwd_partials(const void* x, const void* gamma, const float* rstd, const void* gy, const void* dx_add,
+                             void* dx, void* workspace, size_t workspace_bytes, int64_t rows, int64_t hidden, int dtype,
+                             agb_stream_t stream, int* n_partials) {
+    AGB_RANGE();
+    AGB_TRY(check_common(rows, hidden, dtype));
+    const int elem = dtype == AGB_F32 ? 4 : 2;
+    if (!gamma || !n_partials) return fail(AGB_ERR_INVALID_ARG, "gamma and n_partials are required");
+    if (rows > 0) {
+        AGB_TRY(check_ptr(x, "x", elem));
+        AGB_TRY(check_ptr(gy, "gy", elem));
+        AGB_TRY(check_ptr(dx, "dx", elem));
+        AGB_TRY(check_ptr(rstd, "rstd", 4));
+        AGB_TRY(check_ptr(dx_add, "dx_add", elem, false));
+    }
+    AGB_TRY(check_ptr(gamma, "gamma", elem));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == AGB_F32 ? launch_bwd<float>(x, gamma, rstd, gy, dx_add, dx, nullptr, AGB_F32, 0, workspace, workspace_bytes,
+                                                rows, hidden, st, n_partials)
+                            : launch_bwd<bf16>(x, gamma, rstd, gy, dx_add, dx, nullptr, AGB_F32, 0, workspace, workspace_bytes,
+                                               rows, hidden, st, n_partials);
+}
+
+int agb_dgamma_reduce(const void* partials, int n_partials, int64_t hidden, void* dgamma, int dgamma_dtype, int accumulate,
+                      agb_stream_t stream) {
+    AGB_RANGE();
+    if (hidden <= 0 || n_partials < 0) return fail(AGB_ERR_INVALID_ARG, "hidden=%lld n_partials=%d", (long long)hidden, n_partials);
+    if (dgamma_dtype != AGB_F32 && dgamma_dtype != AGB_F64) return fail(AGB_ERR_INVALID_ARG, "dgamma_dtype must be AGB_F32 or AGB_F64");
+    AGB_TRY(check_ptr(dgamma, "dgamma", dgamma_dtype == AGB_F64 ? 8 : 4));
+    if (n_partials > 0) AGB_TRY(check_ptr(partials, "partials", 8));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (n_partials == 0) {   // an empty sum
+        if (!accumulate) AGB_CUDA(cudaMemsetAsync(dgamma, 0, hidden * (dgamma_dtype == AGB_F64 ? 8 : 4), st));
+        return AGB_OK;
+    }
+    return launch_dgamma_reduce(static_cast<const double*>(partials), n_partials, hidden, dgamma, dgamma_dtype, accumulate, st,
+                                /*behind_backward=*/false);
 }
 
 int agb_rmsnorm_bwd_static(const void* x, const void* gamma, const float* rstd, const void* gy, const void* dx_add,
@@ -1383,3 +1438,4 @@ int agb_reduce_all(int op, const void* x, void* out, int64_t n, int dtype, void*
 }  // extern "C"
 #include "agb_shard.cuh"
 #include "agb_peer.cuh"
+#include "agb_host.cuh"

@@ -13,7 +13,7 @@
 #pragma once
 #include <math.h>
 
-#include "rmsnorm_staged.cuh"
+#include "rmsnorm_fast.cuh"
 
 namespace agb {
 
@@ -88,6 +88,22 @@ __device__ __forceinline__ void exp_nonpositive32_vec(float (&f)[N], float vmin,
     }
 }
 
+// The approximate form (softmax "fast" arithmetic): Cody-Waite split x = n ln2 + r, |r| <= ln2/2, then the
+// hardware 2^u approximation on u = r log2(e) in [-1/2, 1/2] (2 ulp) and an exponent add; about 2e-7
+// relative for -86 <= x <= 0, 0 below (results within a factor 4 of the smallest normal float, or under it, are flushed).  Eight instructions.
+__device__ __forceinline__ float exp_approx_nonpositive(float x) {
+    const float kMagic = 12582912.0f;                     // 1.5 * 2^23: the low mantissa bits of t hold n
+    const float xc = fmaxf(x, -86.0f);
+    const float t = __fmaf_rn(xc, 0x1.715476p+0f /* log2(e) */, kMagic);
+    const float n = __fsub_rn(t, kMagic);
+    float r = __fmaf_rn(n, -0x1.62e400p-1f /* ln2, high 15 bits: n * this is exact */, xc);
+    r = __fmaf_rn(n, -0x1.7f7d1cp-20f /* ln2, rest */, r);
+    float p;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(__fmul_rn(r, 0x1.715476p+0f)));
+    const float y = __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+    return x < -86.0f ? 0.0f : y;
+}
+
 __device__ __forceinline__ float log_rounded(float s) { return static_cast<float>(log(static_cast<double>(s))); }
 
 // a / d for one divisor per row (1 <= d <= 2^24, 0 <= a <= 1).  `fast` is the three-instruction exact
@@ -137,7 +153,10 @@ struct SoftmaxArgs {
     int scratch_offset;    // bytes from the start of a stage to the fp32 scratch (0: in place over z)
 };
 
-template <typename T, int MODE>
+// FAST: exp by exp_approx_nonpositive, sums in fp32, y = e * (1/s) -- about 2e-7 relative per element, far
+// inside the path's rel 1e-5, at under half the instructions of the strictly rounded form (which reproduces
+// the reference composition's bits and stays available through the "softmax_strict" option).
+template <typename T, int MODE, bool FAST>
 __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_constant__ SoftmaxArgs a) {
     constexpr int EPV = Vec<T>::EPV;
     constexpr int NARR = MODE == 3 ? 2 : 1;
@@ -219,11 +238,20 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
         // pass 2: e = exp(z - max), its sum in fp64; `tiny`: some z - max is so low that the fast
         // division of pass 3 would not be exact
         double d0 = 0.0, d1 = 0.0;
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;   // FAST: four fp32 chains
         bool tiny = false;
         if (valid)
             for (int v = tig; v < g.nvec; v += G) {
                 float f[EPV];
                 Vec<T>::unpack(sz[v], f);
+                if constexpr (FAST) {
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) f[e] = exp_approx_nonpositive(f[e] - mx);
+#pragma unroll
+                    for (int e = 0; e < EPV; e += 4) {
+                        a0 += f[e]; a1 += f[e + 1]; a2 += f[e + 2]; a3 += f[e + 3];
+                    }
+                } else {
                 float vmin = 0.0f;
 #pragma unroll
                 for (int e = 0; e < EPV; ++e) {
@@ -237,13 +265,14 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
                     d0 += static_cast<double>(f[e]);
                     d1 += static_cast<double>(f[e + 1]);
                 }
+                }
                 if (kThreePasses) {
 #pragma unroll
                     for (int q = 0; q < EPV / 4; ++q)
                         se[v * (EPV / 4) + q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
                 }
             }
-        const double dsum = warp_sum(d0 + d1);
+        const double dsum = FAST ? static_cast<double>(warp_sum_f32((a0 + a1) + (a2 + a3))) : warp_sum(d0 + d1);
         const bool warp_tiny = __any_sync(0xffffffffu, tiny);
         if (lane == 0) {
             red[nwarps + warp] = dsum;
@@ -266,7 +295,9 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
         // pass 3: y = e / s and what the mode makes of it
         const RowDiv div_s = make_row_div(s);
         const float scale = (MODE == 2 && valid) ? Vec<T>::load1(static_cast<const T*>(a.rowscale) + row) : 0.0f;
+        const float fast_mul = FAST ? (MODE == 2 ? scale * div_s.dinv : div_s.dinv) : 0.0f;   // y (or scale*y) = e * this
         double j0 = 0.0, j1 = 0.0;
+        float jf0 = 0.0f, jf1 = 0.0f;
         if (valid) {
             uint4* gout = MODE == 3 ? nullptr : reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.out) + row * g.row_bytes);
             const uint4* gadd = (MODE == 2 && a.add)
@@ -281,11 +312,18 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
                         const float4 e4 = se[v * (EPV / 4) + q];
                         f[4 * q] = e4.x; f[4 * q + 1] = e4.y; f[4 * q + 2] = e4.z; f[4 * q + 3] = e4.w;
                     }
+                    if constexpr (FAST) {
+#pragma unroll
+                        for (int e = 0; e < EPV; ++e) f[e] = f[e] * fast_mul;
+                    } else {
 #pragma unroll
                     for (int e = 0; e < EPV; ++e) f[e] = kGuarded ? div_s.guarded(f[e]) : div_s.fast(f[e]);
+                    }
                     if (MODE == 2) {
+                        if constexpr (!FAST) {
 #pragma unroll
                         for (int e = 0; e < EPV; ++e) f[e] = mul_rn(scale, f[e]);
+                        }
                         if (gadd) {
                             float ad[EPV];
                             Vec<T>::unpack(gadd[v], ad);
@@ -296,10 +334,18 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
                     if (MODE == 3) {
                         float tv[EPV];
                         Vec<T>::unpack(st[v], tv);
+                        if constexpr (FAST) {
+#pragma unroll
+                            for (int e = 0; e < EPV; e += 2) {
+                                jf0 = fmaf(f[e], tv[e], jf0);
+                                jf1 = fmaf(f[e + 1], tv[e + 1], jf1);
+                            }
+                        } else {
 #pragma unroll
                         for (int e = 0; e < EPV; e += 2) {
                             j0 += static_cast<double>(mul_rn(f[e], tv[e]));
                             j1 += static_cast<double>(mul_rn(f[e + 1], tv[e + 1]));
+                        }
                         }
                     } else {
                         store_vec_streaming(gout + v, Vec<T>::pack(f));
@@ -310,7 +356,7 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
             else pass3(FalseTag{});
         }
         if (MODE == 3) {
-            const double jsum = warp_sum(j0 + j1);
+            const double jsum = FAST ? static_cast<double>(warp_sum_f32(jf0 + jf1)) : warp_sum(j0 + j1);
             if (lane == 0) red[2 * nwarps + warp] = jsum;
             __syncthreads();
             const float tot = static_cast<float>(group_total(red + 2 * nwarps + grp * wpr, wpr, lane));

@@ -120,6 +120,11 @@ class RowShardedRMSNorm:
 
     def close(self):
         """Collective when the peer exchange is in use: every rank must call it (before the process group goes)."""
+        if getattr(self, "_pipe", None) is not None:
+            from . import _lib
+
+            _lib.lib().agb_host_pipe_destroy(self._pipe)
+            self._pipe = None
         if self._peer is not None:
             self._peer.close()
             self._peer = None
@@ -287,11 +292,39 @@ class RowShardedRMSNorm:
         per_row = self.hidden * torch.empty((), dtype=self.dtype).element_size()
         return max(1, min(rows, (64 << 20) // per_row))
 
+    def _host_pipe(self):
+        """The library's own host-buffer pipe (include/agb/agb_host.h), created on first use."""
+        import ctypes as C
+
+        from . import _lib
+
+        if getattr(self, "_pipe", None) is None:
+            h = C.c_void_p()
+            with torch.cuda.device(self.device):
+                _lib.check(_lib.lib().agb_host_pipe_create(self.hidden, ops._DT[self.dtype], int(self._chunk_rows or 0), C.byref(h)))
+            self._pipe = h
+        return self._pipe
+
     def fwd_bwd_host(self, x_host, gy_host, gamma_host, y_host, dx_host, dgamma_host, rstd_host=None):
         """x_host, gy_host [rows, hidden] and gamma_host [hidden] are pinned host tensors; y_host,
         dx_host, dgamma_host (fp32 [hidden]) and optionally rstd_host receive the results.
-        Returns when everything has landed in host memory."""
+        Returns when everything has landed in host memory.  A single rank goes through the library's own
+        host-buffer entry point (agb_host_pipe_fwd_bwd: the call a C or C++ user makes); with several ranks the
+        same pipeline runs here, around the all-reduce of the dgamma sums."""
         rows = x_host.shape[0]
+        if self.world == 1:
+            import ctypes as C
+
+            from . import _lib
+
+            for t in (x_host, gy_host, y_host, dx_host):
+                if t.is_cuda or not t.is_contiguous() or t.dtype != self.dtype or t.shape != x_host.shape:
+                    raise ValueError("fwd_bwd_host: contiguous host tensors of the executor's dtype and one shape, please")
+            hp = lambda t: None if t is None else C.c_void_p(t.data_ptr())  # noqa: E731
+            with torch.cuda.device(self.device):
+                _lib.check(_lib.lib().agb_host_pipe_fwd_bwd(self._host_pipe(), hp(x_host), hp(gy_host), hp(gamma_host), hp(y_host),
+                                                            hp(dx_host), hp(dgamma_host), hp(rstd_host), rows, self.eps, None))
+            return y_host, dx_host, dgamma_host
         chunk = self.default_chunk_rows(rows)
         self._ensure_slots(chunk)
         st = self._streams

@@ -55,7 +55,8 @@ def build(force: bool = False) -> str:
     link = ["-L", PKG, "-lagb_cuda", "-L", os.path.join(CUDA, "lib64"), "-lcudart",
             "-Wl,-rpath,$ORIGIN/..", "-Wl,-rpath," + os.path.join(CUDA, "lib64")]
     if force or not _newer(LIB, deps):
-        _run([_cxx()] + CXXFLAGS + INCLUDES + ["-shared", "-o", LIB] + srcs + link)
+        _run([_cxx()] + CXXFLAGS + INCLUDES + ["-shared", "-o", LIB + ".new"] + srcs + link)
+        os.replace(LIB + ".new", LIB)   # renamed into place: a reader never sees a half-written library
     os.makedirs(BIN, exist_ok=True)
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import build_oracle
@@ -71,8 +72,9 @@ def build(force: bool = False) -> str:
             # the timing programs (bench_*.cpp) are product-side: they neither include nor link the CPU checker
             checker = [] if f.startswith("bench_") else ["-L", os.path.dirname(oracle), "-l:liboracle.so",
                                                          "-Wl,-rpath," + os.path.dirname(oracle)]
-            _run([_cxx()] + CXXFLAGS + INCLUDES + ["-o", exe, src, "-L", HERE, "-lagb_host"] + checker + link +
+            _run([_cxx()] + CXXFLAGS + INCLUDES + ["-o", exe + ".new", src, "-L", HERE, "-lagb_host"] + checker + link +
                  ["-Wl,-rpath,$ORIGIN/..", "-Wl,-rpath,$ORIGIN/../.."])
+            os.replace(exe + ".new", exe)
     return LIB
 
 

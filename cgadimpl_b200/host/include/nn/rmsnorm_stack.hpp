@@ -5,6 +5,10 @@
 // gradient IS dh_{l+1}, so it is read once).  Every buffer is allocated in the constructor, so
 // forward + backward can be captured into one CUDA graph with ag::CudaGraphRunner: 2L kernel
 // launches plus L dgamma reductions, no allocation, no host work between layers.
+// The column reduction of layer l's dgamma does not sit between the backward kernels of layers l and l-1:
+// it runs on a second stream behind an event (a forked branch of the captured graph), over two partial-row
+// workspaces used in turn, so that it overlaps the next layer's backward instead of adding its few
+// microseconds to every layer; the branch is joined before backward() returns.
 // The reference has no such class; it would run this as 3L graph nodes and ~25 tensor calls per
 // layer (add_nodeops, rms_nodeops, mul_nodeops and their VJPs).
 #pragma once
@@ -18,6 +22,9 @@ namespace ag::nn {
 class ResidualRMSNormStack {
 public:
     ResidualRMSNormStack(int layers, int64_t rows, int64_t hidden, Dtype dtype, float eps, DeviceIndex device);
+    ~ResidualRMSNormStack();
+    ResidualRMSNormStack(const ResidualRMSNormStack&) = delete;
+    ResidualRMSNormStack& operator=(const ResidualRMSNormStack&) = delete;
 
     int layers() const { return layers_; }
     Tensor& gammas() { return gammas_; }            // [L, hidden], dtype of the stack; fill before use
@@ -41,7 +48,10 @@ private:
     Dtype dtype_;
     float eps_;
     DeviceIndex device_;
-    Tensor gammas_, dgammas_, workspace_;
+    Tensor gammas_, dgammas_, workspace_[2];
+    void* side_stream_ = nullptr;         // cudaStream_t of the dgamma reductions
+    void* ev_bwd_[2] = {nullptr, nullptr};     // cudaEvent_t: layer's backward kernel done (per workspace)
+    void* ev_reduce_[2] = {nullptr, nullptr};  // cudaEvent_t: the reduction that read the workspace done
     std::vector<Tensor> h_, rstd_;
     Tensor y_[2], dh_[2];
     int dh_final_ = 0;

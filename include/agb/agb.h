@@ -84,6 +84,9 @@ int agb_selftest_bounded_wait(int poll_limit, int* polls_done, agb_stream_t stre
  *     "force_generic" (1: the unstaged kernels);
  *   "bf16_strict"  1: 16-bit I/O through the strictly rounded, fp64-reducing kernels (the fp32 path's
  *                  arithmetic) instead of the fp32-accumulating ones;
+ *   "softmax_strict"  1: softmax / logsumexp forward with the reference composition's rounding points
+ *                  (exp to 2^-33, fp64 sums, exact division; reproduces the CPU composition's bits) instead
+ *                  of the default approximate exp (2e-7 relative) with fp32 sums;
  *   "pdl"          programmatic dependent launch between the library's kernels: 1 (default) a kernel's CTAs
  *                  are placed while the previous one drains, 2 as soon as it has started, 0 off;
  *   "peer_poll_limit"  polls (up to 2 us each) before a wait on another rank's counter gives up
@@ -135,6 +138,18 @@ int agb_rmsnorm_bwd(const void* x, const void* gamma, const float* rstd, const v
                     const void* dx_add, void* dx, void* dgamma, int dgamma_dtype, int accumulate_dgamma,
                     void* workspace, size_t workspace_bytes,
                     int64_t rows, int64_t hidden, int dtype, agb_stream_t stream);
+
+/* The two stages of agb_rmsnorm_bwd as separate calls, for callers that overlap the column reduction of one
+ * layer with the backward of the next (two workspaces used in turn, the reduction on a second stream
+ * behind an event): the VJP kernel alone, which leaves one fp64 [hidden] partial row per CTA in `workspace`
+ * and reports how many in *n_partials (gamma is required), and the fixed-order reduction of those rows
+ * (the second half of reduce_for_broadcast, cgadimpl/src/autodiff/autodiff_vjp_ops.cpp:15-35).  Calling
+ * them back to back on one stream gives the bits of agb_rmsnorm_bwd. */
+int agb_rmsnorm_bwd_partials(const void* x, const void* gamma, const float* rstd, const void* gy,
+                             const void* dx_add, void* dx, void* workspace, size_t workspace_bytes,
+                             int64_t rows, int64_t hidden, int dtype, agb_stream_t stream, int* n_partials);
+int agb_dgamma_reduce(const void* partials, int n_partials, int64_t hidden, void* dgamma, int dgamma_dtype,
+                      int accumulate, agb_stream_t stream);
 
 /* ---- RMSNorm VJP without a caller workspace ----
  * No counterpart in the reference.  Same computation and same results as agb_rmsnorm_bwd with an

@@ -38,6 +38,19 @@ def test_shard_header_and_binding_agree(lib):
         assert hasattr(lib, name), f"{name} declared in agb_shard.h but not exported"
 
 
+def test_host_header_and_binding_agree(lib):
+    declared = _declared_symbols("agb_host.h")
+    assert sorted(_lib.HOST_SIGNATURES) == declared
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in agb_host.h but not exported"
+    out = C.c_void_p()
+    assert lib.agb_host_pipe_create(0, 0, 0, C.byref(out)) == 1          # hidden must be positive
+    assert lib.agb_host_pipe_create(4096, 7, 0, C.byref(out)) == 2       # unknown dtype
+    assert lib.agb_host_pipe_create(4096, 0, 0, None) == 1
+    assert lib.agb_host_pipe_fwd_bwd(None, None, None, None, None, None, None, None, 0, 1e-5, None) == 1
+    assert lib.agb_host_pipe_destroy(None) == 0 and lib.agb_host_pipe_chunk_rows(None) == 0
+
+
 def test_shard_argument_validation_needs_no_device(lib):
     out = C.c_void_p()
     devs = (C.c_int * 2)(0, 0)

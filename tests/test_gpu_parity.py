@@ -643,11 +643,22 @@ def _logits(rows, hidden, seed):
                                                (9, 70000, torch.float32), (1024, 32000, torch.float32),
                                                (300, 8192, torch.bfloat16), (129, 1000, torch.bfloat16),
                                                (64, 50257, torch.bfloat16), (32, 50304, torch.bfloat16)])
-def test_softmax_and_logsumexp_rows(ops, rows, hidden, dtype):
+@pytest.mark.parametrize("strict", [False, True])
+def test_softmax_and_logsumexp_rows(ops, rows, hidden, dtype, strict):
     """cgadimpl's softmax_row / logsumexp_row with their VJP and JVP rules against the oracle, which
-    tests/test_reference_build.py pins bit for bit to the reference's own builders and rules.  The only
-    place the CUDA path may differ from the oracle beyond rare double-rounding ties is exp / log: fp64
-    evaluation rounded once here, the C library's expf / logf (< 1 ulp, not always correctly rounded) there."""
+    tests/test_reference_build.py pins bit for bit to the reference's own builders and rules.
+    strict ("softmax_strict" option): the reference composition's rounding points; the only place the CUDA
+    path may then differ from the oracle beyond rare double-rounding ties is exp / log (evaluated to 2^-33 and
+    rounded once here, the C library's expf / logf there).  Default: approximate exp (2e-7 relative), fp32
+    sums, one multiplication instead of the division -- held to the path's stated rel 1e-5."""
+    ops.set_option("softmax_strict", int(strict))
+    try:
+        _softmax_and_logsumexp_rows(ops, rows, hidden, dtype, strict)
+    finally:
+        ops.set_option("softmax_strict", 0)
+
+
+def _softmax_and_logsumexp_rows(ops, rows, hidden, dtype, strict):
     z = _logits(rows, hidden, seed=rows + hidden)
     rng = np.random.default_rng(11)
     gy = rng.standard_normal((rows, hidden)).astype(np.float32)
@@ -666,10 +677,12 @@ def test_softmax_and_logsumexp_rows(ops, rows, hidden, dtype):
     assert np.all(np.isfinite(yh)) and np.all(yh >= 0)
     np.testing.assert_allclose(yh.astype(np.float64).sum(-1), 1.0, atol=2e-2 if bf else 1e-5)   # rows sum to one
     if not bf:
-        assert_close(yh, y_ref, F32_RTOL, 1e-30, "softmax")          # relative even for the tiny masked entries
-        assert frac_bit_equal(yh, y_ref) >= 0.99
+        # relative even for the tiny masked entries; the approximate form flushes results below 4.5e-38 to zero
+        assert_close(yh, y_ref, F32_RTOL, 1e-30 if strict else 5e-38, "softmax")
         assert_close(host(lse), lse_ref, F32_RTOL, F32_ATOL, "logsumexp")
-        assert frac_bit_equal(host(lse), lse_ref) >= 0.99
+        if strict:
+            assert frac_bit_equal(yh, y_ref) >= 0.99
+            assert frac_bit_equal(host(lse), lse_ref) >= 0.99
         # the rules, fed with the oracle's y so that only the rule itself is compared
         yd = dev(y_ref)
         dz = ops.softmax_row_bwd(yd, gyd)
@@ -685,8 +698,9 @@ def test_softmax_and_logsumexp_rows(ops, rows, hidden, dtype):
         assert np.array_equal(host(inplace), host(acc) + host(dz))
         dl = ops.logsumexp_row_bwd(zd, gyrd)
         want = O.logsumexp_row_vjp(z, gy_row)
-        assert_close(host(dl), want, F32_RTOL, 1e-30, "logsumexp vjp")
-        assert frac_bit_equal(host(dl), want) >= 0.99
+        assert_close(host(dl), want, F32_RTOL, 1e-30 if strict else 5e-37, "logsumexp vjp")
+        if strict:
+            assert frac_bit_equal(host(dl), want) >= 0.99
         assert np.array_equal(host(ops.logsumexp_row_bwd(zd, gyrd, dz_add=acc)), host(acc) + host(dl))
         jl = ops.logsumexp_row_jvp(zd, td)
         assert_close(host(jl), O.logsumexp_row_jvp(z, t), F32_RTOL, F32_ATOL, "logsumexp jvp")
@@ -704,6 +718,14 @@ def test_softmax_and_logsumexp_rows(ops, rows, hidden, dtype):
 
 
 def test_softmax_generic_kernels_agree_bitwise_with_staged(ops):
+    ops.set_option("softmax_strict", 1)     # the unstaged kernels carry the strict arithmetic only
+    try:
+        _softmax_generic_vs_staged(ops)
+    finally:
+        ops.set_option("softmax_strict", 0)
+
+
+def _softmax_generic_vs_staged(ops):
     z = _logits(257, 2048, seed=3)
     rng = np.random.default_rng(4)
     g = rng.standard_normal(z.shape).astype(np.float32)
