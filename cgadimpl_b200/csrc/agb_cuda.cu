@@ -661,10 +661,22 @@ int launch_softmax_fwd(int mode, const void* z, const void* t, const void* rowsc
     AGB_TRY(device_info(&d));
     Plan p;
     const bool al = aligned16(z) && (!t || aligned16(t)) && (!out || aligned16(out)) && (!add || aligned16(add));
-    // arrays per stage: z [, t] [, fp32 scratch = two bf16 row-widths]; fp32 parks e in place over z
-    const bool scratch = mode != 1 && sizeof(T) == 2;
+    // arrays per stage: z [, t] [, fp32 scratch = two bf16 row-widths]; fp32 parks e in place over z.
+    // The approximate form keeps e in registers (32 values per thread) when the plan gives every thread at most
+    // that many, and then needs no scratch at all.
+    constexpr int kKeepVecs = 32 / (16 / static_cast<int>(sizeof(T)));   // 8 fp32 vectors, 4 bf16 vectors
+    const bool fastmode = !opt_softmax_strict.load();
+    bool keep_regs = false;
+    if (al && fastmode && mode != 1) {
+        plan_launch(kSoftmax, rows, hidden, sizeof(T), mode == 3 ? 2 : 1, 0, *d, &p, agb::kExpTableSize * 8 + agb::kExp32Size * 8);
+        keep_regs = !p.generic && static_cast<int64_t>(kKeepVecs) * p.g.group_threads >= p.g.nvec;
+    }
+    const bool scratch = mode != 1 && sizeof(T) == 2 && !keep_regs;
     const int narr = (mode == 3 ? 2 : 1) + (scratch ? 2 : 0);
-    if (al) plan_launch(kSoftmax, rows, hidden, sizeof(T), narr, 0, *d, &p, agb::kExpTableSize * 8 + agb::kExp32Size * 8);
+    if (al && !keep_regs) {
+        p = Plan();
+        plan_launch(kSoftmax, rows, hidden, sizeof(T), narr, 0, *d, &p, agb::kExpTableSize * 8 + agb::kExp32Size * 8);
+    }
     if (p.generic && al && (hidden * static_cast<int64_t>(sizeof(T))) % 16 == 0 && !opt_force_generic.load()) {
         // too wide for the ring, but vectorisable: one 1024-thread CTA per row
         agb::SoftmaxArgs a{};
@@ -698,6 +710,9 @@ int launch_softmax_fwd(int mode, const void* z, const void* t, const void* rowsc
         if (opt_softmax_strict.load()) {                                              \
             AGB_TRY(set_smem(agb::softmax_fwd_staged<T, M, false>, p.smem));          \
             agb::softmax_fwd_staged<T, M, false><<<p.grid, p.block, p.smem, st>>>(a); \
+        } else if (keep_regs) {                                                       \
+            AGB_TRY(set_smem(agb::softmax_fwd_staged<T, M, true, kKeepVecs>, p.smem));          \
+            agb::softmax_fwd_staged<T, M, true, kKeepVecs><<<p.grid, p.block, p.smem, st>>>(a); \
         } else {                                                                      \
             AGB_TRY(set_smem(agb::softmax_fwd_staged<T, M, true>, p.smem));           \
             agb::softmax_fwd_staged<T, M, true><<<p.grid, p.block, p.smem, st>>>(a);  \

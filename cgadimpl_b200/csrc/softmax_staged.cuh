@@ -104,6 +104,31 @@ __device__ __forceinline__ float exp_approx_nonpositive(float x) {
     return x < -86.0f ? 0.0f : y;
 }
 
+// e = exp(x - mx) for 16-bit I/O: one multiply-add and the hardware 2^u approximation, with nmx2 = -mx*log2(e)
+// computed once per row.  The argument's rounding (2^-24 of |x - mx| <= 126) bounds the relative error by
+// ~3e-6, three orders below the 16-bit output's own rounding; results under the normal range flush to zero.
+__device__ __forceinline__ float exp_rel16(float x, float nmx2) {
+    float p;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(__fmaf_rn(x, 0x1.715476p+0f, nmx2)));
+    return p;
+}
+
+// e = exp(z - mx) for one vector, in place, and its contribution to four fp32 sum chains
+template <typename T>
+__device__ __forceinline__ void exp_fast_vec(float (&f)[Vec<T>::EPV], float mx, float nmx2, float& a0, float& a1, float& a2,
+                                             float& a3) {
+    constexpr int EPV = Vec<T>::EPV;
+#pragma unroll
+    for (int e = 0; e < EPV; ++e) {
+        if constexpr (sizeof(T) == 2) f[e] = exp_rel16(f[e], nmx2);
+        else f[e] = exp_approx_nonpositive(f[e] - mx);
+    }
+#pragma unroll
+    for (int e = 0; e < EPV; e += 4) {
+        a0 += f[e]; a1 += f[e + 1]; a2 += f[e + 2]; a3 += f[e + 3];
+    }
+}
+
 __device__ __forceinline__ float log_rounded(float s) { return static_cast<float>(log(static_cast<double>(s))); }
 
 // a / d for one divisor per row (1 <= d <= 2^24, 0 <= a <= 1).  `fast` is the three-instruction exact
@@ -156,8 +181,11 @@ struct SoftmaxArgs {
 // FAST: exp by exp_approx_nonpositive, sums in fp32, y = e * (1/s) -- about 2e-7 relative per element, far
 // inside the path's rel 1e-5, at under half the instructions of the strictly rounded form (which reproduces
 // the reference composition's bits and stays available through the "softmax_strict" option).
-template <typename T, int MODE, bool FAST>
+// KV > 0 (FAST only): every thread owns at most KV vectors of its row and keeps their e in registers between
+// the passes instead of parking them in shared memory (no scratch region, one shared-memory round trip less).
+template <typename T, int MODE, bool FAST, int KV = 0>
 __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_constant__ SoftmaxArgs a) {
+    static_assert(KV == 0 || FAST, "registers keep e only in the approximate form");
     constexpr int EPV = Vec<T>::EPV;
     constexpr int NARR = MODE == 3 ? 2 : 1;
     constexpr bool kThreePasses = MODE != 1;
@@ -239,18 +267,29 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
         // division of pass 3 would not be exact
         double d0 = 0.0, d1 = 0.0;
         float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;   // FAST: four fp32 chains
+        float keep[KV > 0 ? KV * EPV : 1];
+        const float nmx2 = -mx * 0x1.715476p+0f;
         bool tiny = false;
-        if (valid)
+        if constexpr (KV > 0) {
+            if (valid) {
+#pragma unroll
+                for (int i = 0; i < KV; ++i) {
+                    const int v = tig + i * G;
+                    if (v < g.nvec) {
+                        float f[EPV];
+                        Vec<T>::unpack(sz[v], f);
+                        exp_fast_vec<T>(f, mx, nmx2, a0, a1, a2, a3);
+#pragma unroll
+                        for (int e = 0; e < EPV; ++e) keep[i * EPV + e] = f[e];
+                    }
+                }
+            }
+        } else if (valid)
             for (int v = tig; v < g.nvec; v += G) {
                 float f[EPV];
                 Vec<T>::unpack(sz[v], f);
                 if constexpr (FAST) {
-#pragma unroll
-                    for (int e = 0; e < EPV; ++e) f[e] = exp_approx_nonpositive(f[e] - mx);
-#pragma unroll
-                    for (int e = 0; e < EPV; e += 4) {
-                        a0 += f[e]; a1 += f[e + 1]; a2 += f[e + 2]; a3 += f[e + 3];
-                    }
+                    exp_fast_vec<T>(f, mx, nmx2, a0, a1, a2, a3);
                 } else {
                 float vmin = 0.0f;
 #pragma unroll
@@ -272,13 +311,14 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
                         se[v * (EPV / 4) + q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
                 }
             }
+        (void)keep;
         const double dsum = FAST ? static_cast<double>(warp_sum_f32((a0 + a1) + (a2 + a3))) : warp_sum(d0 + d1);
         const bool warp_tiny = __any_sync(0xffffffffu, tiny);
         if (lane == 0) {
             red[nwarps + warp] = dsum;
             redf[nwarps + warp] = warp_tiny ? 1.0f : 0.0f;  // second half of the max region
         }
-        if (kThreePasses) fence_generic_to_async_smem();  // the slot this thread wrote is refilled by the copy engine later
+        if (kThreePasses && KV == 0) fence_generic_to_async_smem();  // the slot this thread wrote is refilled by the copy engine later
         __syncthreads();
         if (!kThreePasses && tid == 0 && issued < my_tiles) {  // nobody reads the slot again
             issue(first + issued * stride, slot);
@@ -303,21 +343,20 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
             const uint4* gadd = (MODE == 2 && a.add)
                                     ? reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(a.add) + row * g.row_bytes)
                                     : nullptr;
-            auto pass3 = [&](auto guarded_tag) {
-                constexpr bool kGuarded = decltype(guarded_tag)::value;
-                for (int v = tig; v < g.nvec; v += G) {
-                    float f[EPV];
-#pragma unroll
-                    for (int q = 0; q < EPV / 4; ++q) {
-                        const float4 e4 = se[v * (EPV / 4) + q];
-                        f[4 * q] = e4.x; f[4 * q + 1] = e4.y; f[4 * q + 2] = e4.z; f[4 * q + 3] = e4.w;
-                    }
+            // what becomes of one vector of e (in f): y = e / s and the mode's use of it
+            auto finish_vec = [&](int v, float (&f)[EPV], bool guarded) {
+                {
                     if constexpr (FAST) {
 #pragma unroll
                         for (int e = 0; e < EPV; ++e) f[e] = f[e] * fast_mul;
                     } else {
+                    if (guarded) {
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) f[e] = kGuarded ? div_s.guarded(f[e]) : div_s.fast(f[e]);
+                        for (int e = 0; e < EPV; ++e) f[e] = div_s.guarded(f[e]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < EPV; ++e) f[e] = div_s.fast(f[e]);
+                    }
                     }
                     if (MODE == 2) {
                         if constexpr (!FAST) {
@@ -352,8 +391,29 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
                     }
                 }
             };
-            if (row_tiny) pass3(TrueTag{});
-            else pass3(FalseTag{});
+            auto pass3 = [&](bool guarded) {
+                for (int v = tig; v < g.nvec; v += G) {
+                    float f[EPV];
+#pragma unroll
+                    for (int q = 0; q < EPV / 4; ++q) {
+                        const float4 e4 = se[v * (EPV / 4) + q];
+                        f[4 * q] = e4.x; f[4 * q + 1] = e4.y; f[4 * q + 2] = e4.z; f[4 * q + 3] = e4.w;
+                    }
+                    finish_vec(v, f, guarded);
+                }
+            };
+            if constexpr (KV > 0) {
+#pragma unroll
+                for (int i = 0; i < KV; ++i) {
+                    const int v = tig + i * G;
+                    if (v < g.nvec) {
+                        float f[EPV];
+#pragma unroll
+                        for (int e = 0; e < EPV; ++e) f[e] = keep[i * EPV + e];
+                        finish_vec(v, f, false);
+                    }
+                }
+            } else pass3(row_tiny);
         }
         if (MODE == 3) {
             const double jsum = FAST ? static_cast<double>(warp_sum_f32(jf0 + jf1)) : warp_sum(j0 + j1);
