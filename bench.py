@@ -66,16 +66,30 @@ OP_WORKLOADS = {
     "layernorm_fwd_vjp_fp32_8192x4096": ("layernorm", 8192, 4096, "float32"),     # small cases for ncu captures
     "softmax_fwd_vjp_fp32_8192x4096": ("softmax", 8192, 4096, "float32"),
 }
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of ONE backward launch at the benchmarked shape,
-# read from profiles/ncu_traffic.json (written from ncu captures of exactly these shapes; see that file's
-# "command" entries).  Absent entry -> roofline.traffic is null.
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of ONE backward launch at the benchmarked shape:
+# the table cgadimpl_b200/ncu_traffic.json holds the figures of the ncu captures summarised under profiles/
+# (its "command" entry is the capture command).  No entry for a width and type -> roofline.traffic is null.
 def ncu_traffic(rows, hidden, dtype_name):
+    """The capture of exactly this shape, else the largest captured shape of the same width and type with
+    fewer rows, scaled by the row count (the kernel streams rows: its traffic is proportional to them)."""
     try:
-        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
-            table = json.load(f)
+        with open(os.path.join(ROOT, "cgadimpl_b200", "ncu_traffic.json")) as f:
+            table = json.load(f)["captures"]
     except Exception:
         return None
-    return table.get(f"rmsnorm_bwd_{dtype_name}_{rows}x{hidden}")
+    exact = table.get(f"rmsnorm_bwd_{dtype_name}_{rows}x{hidden}")
+    if exact:
+        return exact
+    best = None
+    for key, entry in table.items():
+        if entry.get("hidden") == hidden and entry.get("dtype") == dtype_name and entry.get("rows", 0) < rows:
+            if best is None or entry["rows"] > best["rows"]:
+                best = entry
+    if best is None:
+        return None
+    scale = rows / best["rows"]
+    return {"dram_bytes_per_launch": int(best["dram_bytes_per_launch"] * scale),
+            "source": f"{best['source']}; scaled x{scale:g} by rows ({rows} rows here: too large to capture under ncu)"}
 
 
 DEFAULT_WORKLOAD = "rmsnorm_fwd_vjp_bf16_sharded_64x8192x8192"
@@ -813,6 +827,36 @@ def main():
     if clocks and clocks.get("sm_mhz"):
         clocks["ms_per_step_x_sm_mhz"] = ms_per_step * clocks["sm_mhz"]
 
+    # ---- N > 1: what each GPU does on its shard with NO exchange, all ranks busy at the same time (outside the
+    # timed region): the spread over ranks is the part of the scaling loss that no exchange can remove
+    no_exchange = None
+    if world > 1:
+        ws = ops.bwd_workspace(x)
+        scratch_dg = torch.empty(hidden, dtype=torch.float32, device="cuda")
+
+        def local_step():
+            ops.rmsnorm_fwd(x, gamma, eps, out=y, rstd=rstd)
+            ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=scratch_dg, workspace=ws)
+
+        for _ in range(3):
+            local_step()
+        dist.barrier()
+        torch.cuda.synchronize()
+        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        q0.record()
+        for _ in range(args.steps * 5):
+            local_step()
+        q1.record()
+        torch.cuda.synchronize()
+        every = torch.zeros(world, device="cuda", dtype=torch.float64)   # a SUM all-reduce of a one-hot table: it
+        every[rank] = q0.elapsed_time(q1) / (args.steps * 5)             # exists for every algorithm NCCL may be pinned to
+        dist.all_reduce(every, op=dist.ReduceOp.SUM)
+        per_rank = [float(v) for v in every.tolist()]
+        no_exchange = {"per_rank_ms_per_step": [round(v, 4) for v in per_rank], "slowest_ms": max(per_rank),
+                       "fastest_ms": min(per_rank),
+                       "note": "forward + VJP on each rank's shard without any exchange, all ranks running at once"}
+        ex.fwd_bwd(x, gy, gamma, y=y, rstd=rstd, dx=dx, dgamma=dgamma, wait=True)   # dgamma of the real path again
+
     # ---- the exchanged dgamma is the column sum over all ranks' rows (outside the timed region)
     dgamma_check = check_dgamma(x, gy, gamma, rstd, dgamma, dist, total_rows)
     if not dgamma_check["ok"]:
@@ -929,6 +973,7 @@ def main():
                        "timed_seconds": sum(block_ms) / 1e3},
             "hbm_gbs": step_gbs, "bytes_per_row": bpr,
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "dgamma_check": dgamma_check,
+            "no_exchange": no_exchange,
             "e2e": e2e, "cpu_baseline": cpu_baseline, "other_configs": other, "api_path": api_path,
         }
         print(json.dumps(line), flush=True)

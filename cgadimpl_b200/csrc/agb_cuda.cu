@@ -768,10 +768,15 @@ int launch_ln_fwd(const void* x, void* y, float* mean, float* var, int64_t rows,
         return after_launch("layernorm_fwd_generic");
     }
     agb::LnFwdArgs a{p.g, x, y, mean, var, eps};
-#define AGB_LN_FWD(V, FU)                                                              \
-    do {                                                                               \
-        AGB_TRY(set_smem(agb::layernorm_fwd_staged<T, V, FU>, p.smem));                \
-        agb::layernorm_fwd_staged<T, V, FU><<<p.grid, p.block, p.smem, st>>>(a);       \
+#define AGB_LN_FWD(V, FU)                                                                    \
+    do {                                                                                     \
+        if (sizeof(T) == 2 && !opt_bf16_strict.load()) {                                     \
+            AGB_TRY(set_smem(agb::layernorm_fwd_staged<T, V, FU, true>, p.smem));            \
+            agb::layernorm_fwd_staged<T, V, FU, true><<<p.grid, p.block, p.smem, st>>>(a);   \
+        } else {                                                                             \
+            AGB_TRY(set_smem(agb::layernorm_fwd_staged<T, V, FU, false>, p.smem));           \
+            agb::layernorm_fwd_staged<T, V, FU, false><<<p.grid, p.block, p.smem, st>>>(a);  \
+        }                                                                                    \
     } while (0)
     if (p.vpt == 4 && p.full) AGB_LN_FWD(4, true);
     else if (p.vpt == 4) AGB_LN_FWD(4, false);
@@ -797,10 +802,15 @@ int launch_ln_bwd(const void* x, const float* mean, const float* var, const void
         return after_launch("layernorm_bwd_generic");
     }
     agb::LnBwdArgs a{p.g, x, gy, dx_add, mean, var, dx, add_mode, eps, hf, 2.0f / hf};
-#define AGB_LN_BWD(V, FU)                                                              \
-    do {                                                                               \
-        AGB_TRY(set_smem(agb::layernorm_bwd_staged<T, V, FU>, p.smem));                \
-        agb::layernorm_bwd_staged<T, V, FU><<<p.grid, p.block, p.smem, st>>>(a);       \
+#define AGB_LN_BWD(V, FU)                                                                    \
+    do {                                                                                     \
+        if (sizeof(T) == 2 && !opt_bf16_strict.load()) {                                     \
+            AGB_TRY(set_smem(agb::layernorm_bwd_staged<T, V, FU, true>, p.smem));            \
+            agb::layernorm_bwd_staged<T, V, FU, true><<<p.grid, p.block, p.smem, st>>>(a);   \
+        } else {                                                                             \
+            AGB_TRY(set_smem(agb::layernorm_bwd_staged<T, V, FU, false>, p.smem));           \
+            agb::layernorm_bwd_staged<T, V, FU, false><<<p.grid, p.block, p.smem, st>>>(a);  \
+        }                                                                                    \
     } while (0)
     if (p.vpt == 4 && p.full) AGB_LN_BWD(4, true);
     else if (p.vpt == 4) AGB_LN_BWD(4, false);

@@ -10,8 +10,11 @@
 // `y = xm / s` is a true division in the reference; here it is the exact three-instruction
 // division by the per-row constant s (quotient estimate, FMA residual, one correction; checked
 // against IEEE division on 1.5e9 random operand pairs).
+// FAST (16-bit I/O unless "bf16_strict"): sums carried in fp32 with fused multiply-adds, y = xm * (1/s), and the
+// backward's three row sums reduced to A = sum(gy*xm), B = sum(gy), C = sum(xm) -- the same algebra, a third
+// of the instructions, outputs rounded to the 16-bit type once (rel 2e-2).
 #pragma once
-#include "rmsnorm_staged.cuh"
+#include "rmsnorm_fast.cuh"
 
 namespace agb {
 
@@ -24,7 +27,7 @@ struct LnFwdArgs {
     float eps;
 };
 
-template <typename T, int VPT, bool FULL>
+template <typename T, int VPT, bool FULL, bool FAST = false>
 __global__ void __launch_bounds__(1024, 1) layernorm_fwd_staged(const __grid_constant__ LnFwdArgs a) {
     constexpr int NP = Pairs<T>::NP;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -70,6 +73,7 @@ __global__ void __launch_bounds__(1024, 1) layernorm_fwd_staged(const __grid_con
         // pass 1: sum of x; the vectors stay in registers
         uint4 keep[VPT];
         double s0 = 0.0, s1 = 0.0;
+        float2 fs0 = make_float2(0.f, 0.f), fs1 = make_float2(0.f, 0.f);
         if (valid) {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
@@ -80,13 +84,18 @@ __global__ void __launch_bounds__(1024, 1) layernorm_fwd_staged(const __grid_con
                     Pairs<T>::unpack(keep[i], xv);
 #pragma unroll
                     for (int e = 0; e < NP; ++e) {
-                        s0 += static_cast<double>(xv[e].x);
-                        s1 += static_cast<double>(xv[e].y);
+                        if constexpr (FAST) {
+                            if (e & 1) fs1 = add2(fs1, xv[e]);
+                            else fs0 = add2(fs0, xv[e]);
+                        } else {
+                            s0 += static_cast<double>(xv[e].x);
+                            s1 += static_cast<double>(xv[e].y);
+                        }
                     }
                 }
             }
         }
-        const double wsum = warp_sum(s0 + s1);
+        const double wsum = FAST ? static_cast<double>(warp_sum_f32((fs0.x + fs0.y) + (fs1.x + fs1.y))) : warp_sum(s0 + s1);
         if (lane == 0) red_sum[warp] = wsum;
         __syncthreads();
         if (*s_abort) { aborted = true; break; }
@@ -99,6 +108,7 @@ __global__ void __launch_bounds__(1024, 1) layernorm_fwd_staged(const __grid_con
 
         // pass 2: variance of the centred values
         double q0 = 0.0, q1 = 0.0;
+        float2 fq0 = make_float2(0.f, 0.f), fq1 = make_float2(0.f, 0.f);
         if (valid) {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
@@ -109,14 +119,19 @@ __global__ void __launch_bounds__(1024, 1) layernorm_fwd_staged(const __grid_con
 #pragma unroll
                     for (int e = 0; e < NP; ++e) {
                         const float2 xm = sub2(xv[e], mean2);
-                        const float2 q = mul2(xm, xm);
-                        q0 += static_cast<double>(q.x);
-                        q1 += static_cast<double>(q.y);
+                        if constexpr (FAST) {
+                            if (e & 1) fq1 = fma2(xm, xm, fq1);
+                            else fq0 = fma2(xm, xm, fq0);
+                        } else {
+                            const float2 q = mul2(xm, xm);
+                            q0 += static_cast<double>(q.x);
+                            q1 += static_cast<double>(q.y);
+                        }
                     }
                 }
             }
         }
-        const double wsq = warp_sum(q0 + q1);
+        const double wsq = FAST ? static_cast<double>(warp_sum_f32((fq0.x + fq0.y) + (fq1.x + fq1.y))) : warp_sum(q0 + q1);
         if (lane == 0) red_sq[warp] = wsq;
         __syncthreads();
         const float var = static_cast<float>(group_total(red_sq + grp * wpr, wpr, lane) / static_cast<double>(g.hidden));
@@ -137,7 +152,7 @@ __global__ void __launch_bounds__(1024, 1) layernorm_fwd_staged(const __grid_con
                     float2 xv[NP];
                     Pairs<T>::unpack(keep[i], xv);
 #pragma unroll
-                    for (int e = 0; e < NP; ++e) xv[e] = div_s(sub2(xv[e], mean2));
+                    for (int e = 0; e < NP; ++e) xv[e] = FAST ? mul2(sub2(xv[e], mean2), div_s.dinv) : div_s(sub2(xv[e], mean2));
                     store_vec_streaming(gy + v, Pairs<T>::pack(xv));
                 }
             }
@@ -158,7 +173,7 @@ struct LnBwdArgs {
     float eps, hidden_f, two_over_h;
 };
 
-template <typename T, int VPT, bool FULL>
+template <typename T, int VPT, bool FULL, bool FAST = false>
 __global__ void __launch_bounds__(1024, 1) layernorm_bwd_staged(const __grid_constant__ LnBwdArgs a) {
     constexpr int NP = Pairs<T>::NP;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -219,6 +234,7 @@ __global__ void __launch_bounds__(1024, 1) layernorm_bwd_staged(const __grid_con
 
         // pass 1: the three row sums
         double a0 = 0.0, a1 = 0.0, b0 = 0.0, b1 = 0.0, c0 = 0.0, c1 = 0.0;
+        float2 fa = make_float2(0.f, 0.f), fb = make_float2(0.f, 0.f), fc = make_float2(0.f, 0.f);
         if (valid) {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
@@ -227,6 +243,16 @@ __global__ void __launch_bounds__(1024, 1) layernorm_bwd_staged(const __grid_con
                     float2 xv[NP], gv[NP];
                     Pairs<T>::unpack(sx[v], xv);
                     Pairs<T>::unpack(sg[v], gv);
+                    if constexpr (FAST) {
+#pragma unroll
+                        for (int e = 0; e < NP; ++e) {
+                            const float2 xm = sub2(xv[e], mean2);
+                            fa = fma2(gv[e], xm, fa);   // A = sum gy*xm
+                            fb = add2(fb, gv[e]);       // B = sum gy
+                            fc = add2(fc, xm);          // C = sum xm
+                        }
+                        continue;
+                    }
 #pragma unroll
                     for (int e = 0; e < NP; ++e) {
                         const float2 xm = sub2(xv[e], mean2);
@@ -245,7 +271,11 @@ __global__ void __launch_bounds__(1024, 1) layernorm_bwd_staged(const __grid_con
                 }
             }
         }
-        const double ra = warp_sum(a0 + a1), rb = warp_sum(b0 + b1), rc = warp_sum(c0 + c1);
+        // FAST: d_var = -0.5 std_inv^3 A, sum1 = -std_inv B, sum2 = -2 C: the same three quantities the strict
+        // form accumulates term by term
+        const double ra = FAST ? static_cast<double>(-0.5f * c3 * warp_sum_f32(fa.x + fa.y)) : warp_sum(a0 + a1);
+        const double rb = FAST ? static_cast<double>(-std_inv * warp_sum_f32(fb.x + fb.y)) : warp_sum(b0 + b1);
+        const double rc = FAST ? static_cast<double>(-2.0f * warp_sum_f32(fc.x + fc.y)) : warp_sum(c0 + c1);
         if (lane == 0) {
             red[warp] = ra;
             red[nwarps + warp] = rb;
@@ -277,10 +307,14 @@ __global__ void __launch_bounds__(1024, 1) layernorm_bwd_staged(const __grid_con
 #pragma unroll
                     for (int e = 0; e < NP; ++e) {
                         const float2 xm = sub2(xv[e], mean2);
-                        const float2 dxh = mul2(gv[e], si2);
-                        float2 u = mul2(dvar2, xm);
-                        u = mul2(u, k22);
-                        ov[e] = add2_after_mul(add2_after_mul(dxh, u), md2);
+                        if constexpr (FAST) {
+                            ov[e] = fma2(gv[e], si2, fma2(xm, splat(d_var * a.two_over_h), md2));
+                        } else {
+                            const float2 dxh = mul2(gv[e], si2);
+                            float2 u = mul2(dvar2, xm);
+                            u = mul2(u, k22);
+                            ov[e] = add2_after_mul(add2_after_mul(dxh, u), md2);
+                        }
                     }
                     if (a.add_mode == 2) {
 #pragma unroll

@@ -104,18 +104,27 @@ class RowShardedRMSNorm:
         self._streams = None
         # How the fp64 dgamma sums cross the ranks: "collective" = torch.distributed all-reduce (NCCL, or gloo
         # on CPU); "peer" = the library's own kernels over CUDA-IPC peer mappings (PeerExchange; CUDA ranks of
-        # one node).  "auto" is the collective: with one Python process per GPU the two measured within 2 % of
-        # each other (8 GPUs: 0.454 ms per step with NCCL, 0.460 with the peer kernels; 2 GPUs: 0.426 / 0.434).
-        # The peer-load exchange pays off when ONE process drives all GPUs (ShardExecutor: 0.427 ms at 8 GPUs).
+        # one node): the backward's last kernel stores this rank's sums into every rank's block, one small
+        # kernel per rank adds the local copies.  "auto" takes the peer exchange on CUDA ranks with the
+        # overlapped mode -- measured on the row-sharded bf16 configuration (65536 x 8192 rows per rank):
+        # 8 GPUs 0.946-0.948 ms per step against 0.952-0.956 with the NCCL all-reduce, 2 GPUs 0.923 against
+        # 0.925-0.929, and with a smaller spread between blocks -- and falls back to the collective if the
+        # blocks cannot be mapped (ranks on different nodes, no peer access).
         if exchange not in ("auto", "peer", "collective"):
             raise ValueError("exchange must be 'auto', 'peer' or 'collective'")
         self._peer = None
-        if self.world > 1 and exchange == "peer":
+        want_peer = exchange == "peer" or (exchange == "auto" and self.device.type == "cuda" and self.overlap)
+        if self.world > 1 and want_peer:
             if self.device.type != "cuda":
                 raise ValueError("exchange='peer' needs CUDA ranks")
             from .peer_exchange import PeerExchange
 
-            self._peer = PeerExchange(self.hidden, group=group, device=self.device)
+            try:
+                self._peer = PeerExchange(self.hidden, group=group, device=self.device)
+            except RuntimeError:
+                if exchange == "peer":
+                    raise
+                self._peer = None      # every rank fails together (the constructor agrees on it): use the collective
         self.exchange = "peer" if self._peer is not None else ("collective" if self.world > 1 else "none")
 
     def close(self):
