@@ -692,6 +692,38 @@ def measure_api(steps, warmup):
             "cuda_graph_nodes": d["graph_nodes"], "launches_per_step": d["launches_per_step"]}
 
 
+def no_exchange_pace(x, gy, gamma, y, dx, rstd, eps, steps, dist, rank, world):
+    """N > 1: what each GPU does on its shard with NO exchange while all ranks are busy at the same time
+    (ms per step, per rank).  The spread over the ranks is the part of the scaling loss that no exchange can
+    remove; it is taken before and after the timed region because a GPU under its power cap drifts by a few
+    per cent within seconds."""
+    import torch
+
+    from cgadimpl_b200 import ops
+
+    ws = ops.bwd_workspace(x)
+    scratch_dg = torch.empty(x.shape[-1], dtype=torch.float32, device="cuda")
+
+    def local_step():
+        ops.rmsnorm_fwd(x, gamma, eps, out=y, rstd=rstd)
+        ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=scratch_dg, workspace=ws)
+
+    for _ in range(3):
+        local_step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    q0.record()
+    for _ in range(steps):
+        local_step()
+    q1.record()
+    torch.cuda.synchronize()
+    every = torch.zeros(world, device="cuda", dtype=torch.float64)   # a SUM all-reduce of a one-hot table: it
+    every[rank] = q0.elapsed_time(q1) / steps                        # exists for every algorithm NCCL may be pinned to
+    dist.all_reduce(every, op=dist.ReduceOp.SUM)
+    return [round(float(v), 4) for v in every.tolist()]
+
+
 def copy_probe(dist, nbytes=1 << 30):
     """Host <-> device copy rate of this rank's GPU with every rank copying at the same time (pinned memory,
     one direction at a time, then both): what bounds the end-to-end figure.  GB/s, min over ranks."""
@@ -810,6 +842,8 @@ def main():
     ex = RowShardedRMSNorm(hidden, dtype, eps, exchange=args.exchange)
     prepared = ex.prepare_step(x, gy, gamma, y, rstd, dx, dgamma)   # operands validated once, bare calls per step
 
+    pace_before = no_exchange_pace(x, gy, gamma, y, dx, rstd, eps, args.steps * 3, dist, rank, world) if world > 1 else None
+
     # ---- timed region
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
@@ -827,34 +861,14 @@ def main():
     if clocks and clocks.get("sm_mhz"):
         clocks["ms_per_step_x_sm_mhz"] = ms_per_step * clocks["sm_mhz"]
 
-    # ---- N > 1: what each GPU does on its shard with NO exchange, all ranks busy at the same time (outside the
-    # timed region): the spread over ranks is the part of the scaling loss that no exchange can remove
+    # ---- N > 1: the ranks' own pace without any exchange, again after the timed region
     no_exchange = None
     if world > 1:
-        ws = ops.bwd_workspace(x)
-        scratch_dg = torch.empty(hidden, dtype=torch.float32, device="cuda")
-
-        def local_step():
-            ops.rmsnorm_fwd(x, gamma, eps, out=y, rstd=rstd)
-            ops.rmsnorm_bwd(x, gamma, rstd, gy, dx=dx, dgamma=scratch_dg, workspace=ws)
-
-        for _ in range(3):
-            local_step()
-        dist.barrier()
-        torch.cuda.synchronize()
-        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        q0.record()
-        for _ in range(args.steps * 5):
-            local_step()
-        q1.record()
-        torch.cuda.synchronize()
-        every = torch.zeros(world, device="cuda", dtype=torch.float64)   # a SUM all-reduce of a one-hot table: it
-        every[rank] = q0.elapsed_time(q1) / (args.steps * 5)             # exists for every algorithm NCCL may be pinned to
-        dist.all_reduce(every, op=dist.ReduceOp.SUM)
-        per_rank = [float(v) for v in every.tolist()]
-        no_exchange = {"per_rank_ms_per_step": [round(v, 4) for v in per_rank], "slowest_ms": max(per_rank),
-                       "fastest_ms": min(per_rank),
-                       "note": "forward + VJP on each rank's shard without any exchange, all ranks running at once"}
+        after = no_exchange_pace(x, gy, gamma, y, dx, rstd, eps, args.steps * 3, dist, rank, world)
+        no_exchange = {"per_rank_ms_per_step_before": pace_before, "per_rank_ms_per_step_after": after,
+                       "slowest_ms": min(max(pace_before), max(after)),
+                       "note": "forward + VJP on each rank's shard without any exchange, all ranks running at once; "
+                               "taken right before and right after the timed region"}
         ex.fwd_bwd(x, gy, gamma, y=y, rstd=rstd, dx=dx, dgamma=dgamma, wait=True)   # dgamma of the real path again
 
     # ---- the exchanged dgamma is the column sum over all ranks' rows (outside the timed region)

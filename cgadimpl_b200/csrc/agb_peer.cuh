@@ -4,8 +4,8 @@
 // Each rank owns one device block (layout in agb_peer_device.cuh): for every source rank s and buffer b a
 // ready counter and an fp64 [max_hidden] slot that s STORES into, and for every reader r an ack counter that
 // r stores into.  Every rank maps every other rank's block through CUDA IPC; only plain peer STORES cross
-// NVLink (no multicast, no remote load).  Step t uses buffer b = t & 1.  Rank p may overwrite its slot b in
-// the blocks at step t once every reader has acknowledged step t-2 (polled in p's own block); it publishes
+// NVLink (no multicast, no remote load).  Step t uses buffer b = t mod 8.  Rank p may overwrite its slot b in
+// the blocks at step t once every reader has acknowledged step t-8 (polled in p's own block); it publishes
 // by storing t into ready[p][b] of every block with release semantics; a reader polls ready[s][b] >= t for all
 // s in ITS OWN block, sums the local slots in rank order, and stores its ack into every producer's block.
 // All waits are bounded polls of local memory.
@@ -117,9 +117,9 @@ int agb_peer_acquire(agb_peer_t* p, agb_stream_t stream, double** sums) {
     if (!sums) return fail(AGB_ERR_INVALID_ARG, "sums is NULL");
     if (p->acquired) return fail(AGB_ERR_INVALID_ARG, "agb_peer_acquire called twice without agb_peer_sum in between");
     const unsigned long long t = p->step + 1;
-    const int b = static_cast<int>(t & 1);
-    if (p->world > 1 && t > 2) {   // everybody must have read what this rank wrote into buffer b at step t-2
-        agb::peer_wait_ack_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p->blk.base[p->rank], p->world, b, t - 2,
+    const int b = static_cast<int>(t % agb::kPeerBuffers);
+    if (p->world > 1 && t > agb::kPeerBuffers) {   // everybody must have read what this rank wrote into buffer b kPeerBuffers steps ago
+        agb::peer_wait_ack_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p->blk.base[p->rank], p->world, b, t - agb::kPeerBuffers,
                                                                                   peer_poll_limit());
         AGB_TRY(after_launch("peer_wait_ack"));
     }
@@ -145,8 +145,8 @@ int agb_peer_rmsnorm_bwd(agb_peer_t* p, const void* x, const void* gamma, const 
         return agb_peer_publish(p, stream);
     }
     const unsigned long long t = p->step + 1;
-    const int b = static_cast<int>(t & 1);
-    agb::PeerHook hook{p->blk, p->world, p->rank, b, (p->world > 1 && t > 2) ? t - 2 : 0ull, t,
+    const int b = static_cast<int>(t % agb::kPeerBuffers);
+    agb::PeerHook hook{p->blk, p->world, p->rank, b, (p->world > 1 && t > agb::kPeerBuffers) ? t - agb::kPeerBuffers : 0ull, t,
                        static_cast<long long>(p->max_hidden), peer_poll_limit()};
     double* sums = reinterpret_cast<double*>(p->blk.base[p->rank] + agb::peer_sums_offset(p->rank, b, p->max_hidden));
     t_reduce_hook = &hook;
@@ -167,7 +167,7 @@ int agb_peer_publish(agb_peer_t* p, agb_stream_t stream) {
     const unsigned long long t = p->step + 1;
     // the whole slot is pushed: the width of the step's sums is not known here, and max_hidden doubles are 8 * max_hidden bytes
     agb::peer_publish_kernel<<<1, agb::kPeerPublishThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        p->blk, p->world, p->rank, static_cast<int>(t & 1), t, static_cast<long long>(p->max_hidden),
+        p->blk, p->world, p->rank, static_cast<int>(t % agb::kPeerBuffers), t, static_cast<long long>(p->max_hidden),
         static_cast<int>(p->max_hidden));
     AGB_TRY(after_launch("peer_publish"));
     p->published = true;
@@ -182,7 +182,7 @@ int agb_peer_sum(agb_peer_t* p, float* dgamma, int64_t hidden, int accumulate, a
     AGB_TRY(check_ptr(dgamma, "dgamma", 4));
     const unsigned long long t = p->step + 1;
     agb::peer_sum_kernel<<<1, agb::kPeerSumThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        p->blk, p->world, p->rank, static_cast<int>(t & 1), t, static_cast<long long>(p->max_hidden),
+        p->blk, p->world, p->rank, static_cast<int>(t % agb::kPeerBuffers), t, static_cast<long long>(p->max_hidden),
         static_cast<int>(hidden), dgamma, accumulate, peer_poll_limit());
     AGB_TRY(after_launch("peer_sum"));
     p->step = t;

@@ -6,21 +6,25 @@
 
 namespace agb {
 
-// Block layout (one block per rank, in that rank's memory; N = world size, MH = max_hidden):
-//   [0, 256)     ready[s][b]  u64, s < 16, b < 2: step whose sums rank s has STORED INTO THIS BLOCK (written by s)
-//   [256, 512)   ack[r][b]    u64: step up to which reader r has consumed THIS rank's sums (written by r)
-//   [512, 516)   counter      u32: the fused reduce kernel's "last CTA" ticket
-//   [516, 520)   expired      u32: CTAs of the current fused reduce whose ack wait ran out
-//   [1024, ...)  sums[s][b][MH] fp64, s < N: rank s's column sums of the step that uses buffer b
+// Block layout (one block per rank, in that rank's memory; N = world size, MH = max_hidden, NB = kPeerBuffers):
+//   [0, 1024)     ready[s][b]  u64, s < 16, b < NB: step whose sums rank s has STORED INTO THIS BLOCK (written by s)
+//   [1024, 2048)  ack[r][b]    u64: step up to which reader r has consumed THIS rank's sums (written by r)
+//   [2048, 2052)  counter      u32: the fused reduce kernel's "last CTA" ticket
+//   [2052, 2056)  expired      u32: CTAs of the current fused reduce whose ack wait ran out
+//   [4096, ...)   sums[s][b][MH] fp64, s < N: rank s's column sums of the step that uses buffer b = t mod NB
+// NB buffers in turn: a rank may run up to NB steps ahead of the slowest reader before it has to wait, so the
+// ranks are coupled over windows of NB steps instead of step by step (a GPU under its power cap does not run
+// every step at the same speed, and a step-by-step lock step runs at the slowest GPU OF EACH STEP).
 // Push protocol: a producer STORES its sums and its ready counter into every rank's block (plain peer stores
 // over NVLink, no multicast) and a reader stores its ack into every producer's block, so every WAIT polls the
 // waiting GPU's own memory and every read of sums is local; nothing but fire-and-forget stores crosses NVLink.
+constexpr int kPeerBuffers = 8;
 constexpr int kPeerReadyOffset = 0;
-constexpr int kPeerAckOffset = 256;
-constexpr int kPeerCounterOffset = 512;
-constexpr int kPeerTimeoutsOffset = 516;
-constexpr int kPeerHeaderBytes = 1024;
-static_assert(AGB_SHARD_MAX * 2 * 8 <= 256, "counter tables");
+constexpr int kPeerAckOffset = 1024;
+constexpr int kPeerCounterOffset = 2048;
+constexpr int kPeerTimeoutsOffset = 2052;
+constexpr int kPeerHeaderBytes = 4096;
+static_assert(AGB_SHARD_MAX * kPeerBuffers * 8 <= 1024, "counter tables");
 // The bound of every wait below (polls; each sleeps up to 2 us) is a kernel argument taken from the
 // process-wide "peer_poll_limit" option at launch, so that it holds on every device a process drives.
 
@@ -52,15 +56,15 @@ __device__ __forceinline__ bool poll_until_at_least(const unsigned long long* p,
 }
 // ready counter of source rank s / ack counter of reader r, buffer b, in the block at `base`
 __device__ __forceinline__ unsigned long long* peer_ready(unsigned char* base, int s, int b) {
-    return reinterpret_cast<unsigned long long*>(base + kPeerReadyOffset) + 2 * s + b;
+    return reinterpret_cast<unsigned long long*>(base + kPeerReadyOffset) + kPeerBuffers * s + b;
 }
 __device__ __forceinline__ unsigned long long* peer_ack(unsigned char* base, int r, int b) {
-    return reinterpret_cast<unsigned long long*>(base + kPeerAckOffset) + 2 * r + b;
+    return reinterpret_cast<unsigned long long*>(base + kPeerAckOffset) + kPeerBuffers * r + b;
 }
 // where rank s's sums of buffer b live inside a block
 __device__ __host__ __forceinline__ size_t peer_sums_offset(int s, int b, long long max_hidden) {
     return kPeerHeaderBytes +
-           (static_cast<size_t>(s) * 2 + static_cast<size_t>(b)) * static_cast<size_t>(max_hidden) * sizeof(double);
+           (static_cast<size_t>(s) * kPeerBuffers + static_cast<size_t>(b)) * static_cast<size_t>(max_hidden) * sizeof(double);
 }
 
 // One warp: lane r waits (in this rank's own block) until reader r has acknowledged step `need` on buffer b.
@@ -107,7 +111,7 @@ __global__ void __launch_bounds__(kPeerSumThreads) peer_sum_kernel(PeerBlocks bl
         if (threadIdx.x == 0) atomicExch(&g_device_status, AGB_ERR_TIMEOUT);
         return;
     }
-    const size_t stride = 2 * static_cast<size_t>(max_hidden);   // doubles between consecutive ranks' slots
+    const size_t stride = kPeerBuffers * static_cast<size_t>(max_hidden);   // doubles between consecutive ranks' slots
     const double* base = reinterpret_cast<const double*>(own + peer_sums_offset(0, b, max_hidden));
     // two columns per thread and pass (16-byte loads) when the slots are 16-byte aligned: max_hidden even
     const int pairs = (max_hidden % 2 == 0) ? hidden / 2 : 0;

@@ -62,12 +62,12 @@ def _rank_main(rank, world, port, rows, hidden, dtype_name, exchange, q):
         # overlapped exchange: several steps back to back with alternating upstream gradients, the
         # all-reduce of step k running beside the kernels of step k+1; every dgamma must be its own step's
         xs, gs, gam = x[a:b].cuda().contiguous(), gy[a:b].cuda().contiguous(), gamma.cuda()
-        outs = [torch.empty(hidden, device="cuda") for _ in range(5)]
-        for k in range(5):
+        outs = [torch.empty(hidden, device="cuda") for _ in range(12)]
+        for k in range(12):
             ex.fwd_bwd(xs, gs * float(k + 1), gam, dgamma=outs[k], wait=False)
         ex.wait_dgamma()
         torch.cuda.synchronize()
-        for k in range(5):
+        for k in range(12):
             _, want = ops.rmsnorm_bwd(x.cuda(), gam, rs, gy.cuda() * float(k + 1))
             ok = ok and close(outs[k], want, float(k + 1))
         # the prepared step (operands validated once, bare C-ABI calls per step)

@@ -50,7 +50,7 @@ def _destroy(lib, peers):
 def test_two_ranks_in_one_process_sum_in_rank_order(ops):
     from cgadimpl_b200._lib import check
 
-    hidden, eps, world, steps = 2048, 1e-5, 2, 5      # 5 steps: both buffers reused, acks consulted from step 3
+    hidden, eps, world, steps = 2048, 1e-5, 2, 19     # 19 steps: all eight buffers reused twice, acks consulted from step 9
     x, gamma, gy = make_inputs(1000, hidden, seed=4)
     cut = 600
     xs = [torch.from_numpy(x[:cut]).cuda(), torch.from_numpy(x[cut:]).cuda()]
@@ -85,7 +85,7 @@ def test_fused_backward_publishes_and_matches_the_unfused_sequence(ops):
     from cgadimpl_b200 import ops as O2
     from cgadimpl_b200._lib import check
 
-    hidden, eps, world, steps = 1024, 1e-6, 2, 6
+    hidden, eps, world, steps = 1024, 1e-6, 2, 19
     x, gamma, gy = make_inputs(777, hidden, seed=12)
     cut = 300
     xs = [torch.from_numpy(x[:cut]).cuda(), torch.from_numpy(x[cut:]).cuda()]
@@ -149,7 +149,7 @@ def test_wait_that_runs_out_reports_timeout_and_leaves_dgamma_untouched(ops):
 
 def test_fused_reduce_whose_ack_wait_runs_out_publishes_nothing_and_leaves_its_counter_at_zero(ops):
     """agb_peer_rmsnorm_bwd waits, inside the backward's column reduction, for every rank's acknowledgement of the
-    step before last.  Here that acknowledgement is wiped (a rank that fell behind), the wait runs out after a small
+    step eight steps back (eight buffers are used in turn).  Here that acknowledgement is wiped (a rank that fell behind), the wait runs out after a small
     poll limit, and the kernel must report AGB_ERR_TIMEOUT, publish nothing, write no sums, and leave the
     "last CTA" counter of its block at zero -- a counter left part-way would make a later launch publish early."""
     cudart = pytest.importorskip("cuda.bindings.runtime")
@@ -181,7 +181,7 @@ def test_fused_reduce_whose_ack_wait_runs_out_publishes_nothing_and_leaves_its_c
             return lib.agb_peer_rmsnorm_bwd(peers[r], p(xs[r]), p(gd), p(rstds[r]), p(gys[r]), None, p(dxs[r]), p(ws),
                                             ws.numel(), xs[r].shape[0], hidden, 0, stream)
 
-        for _ in range(2):                                  # steps 1 and 2: everybody publishes, sums, acknowledges
+        for _ in range(8):                                  # steps 1..8: everybody publishes, sums, acknowledges; every buffer used once
             for r in range(world):
                 check(fused_bwd(r))
             for r in range(world):
@@ -191,23 +191,24 @@ def test_fused_reduce_whose_ack_wait_runs_out_publishes_nothing_and_leaves_its_c
         base0, base1 = C.c_void_p(), C.c_void_p()
         check(lib.agb_peer_block(peers[0], C.byref(base0)))
         check(lib.agb_peer_block(peers[1], C.byref(base1)))
-        # rank 0's block after two steps: ready[s][b] of both sources and ack[r][b] of both readers
-        assert list(words(base0.value, 0, 4, np.uint64)) == [2, 1, 2, 1]
-        assert list(words(base0.value, 256, 4, np.uint64)) == [2, 1, 2, 1]
-        (err,) = cudart.cudaMemset(base0.value + 256 + 16, 0, 16)               # reader 1 "has not acknowledged" anything
+        # rank 0's block after eight steps (buffer b = step mod 8): ready[s][b] of both sources, ack[r][b] of both readers
+        after8 = [8, 1, 2, 3, 4, 5, 6, 7]
+        assert list(words(base0.value, 0, 16, np.uint64)) == after8 + after8
+        assert list(words(base0.value, 1024, 16, np.uint64)) == after8 + after8
+        (err,) = cudart.cudaMemset(base0.value + 1024 + 64, 0, 64)              # reader 1 "has not acknowledged" anything
         assert int(err) == 0
-        slot = 1024 + (0 * 2 + 1) * hidden * 8                                  # rank 0's slot of buffer 1 (step 3's buffer)
+        slot = 4096 + (0 * 8 + 1) * hidden * 8                                  # rank 0's slot of buffer 1 (step 9's buffer)
         sums_before = words(base0.value, slot, hidden, np.float64)
         remote_before = words(base1.value, slot, hidden, np.float64)            # and its copy in rank 1's block
         ops.set_option("peer_poll_limit", 2000)
-        check(fused_bwd(0))                                                     # step 3 of rank 0: needs ack >= 1 of rank 1
+        check(fused_bwd(0))                                                     # step 9 of rank 0: needs ack >= 1 of reader 1
         torch.cuda.synchronize()
         with pytest.raises(AgbError) as e:
             ops.device_status()
         assert e.value.status == 6
-        assert list(words(base0.value, 0, 2, np.uint64)) == [2, 1]              # step 3 was published nowhere
-        assert list(words(base1.value, 0, 2, np.uint64)) == [2, 1]
-        assert list(words(base0.value, 512, 2, np.uint32)) == [0, 0]            # counter and expired-CTA count back at zero
+        assert list(words(base0.value, 0, 8, np.uint64)) == after8              # step 9 was published nowhere
+        assert list(words(base1.value, 0, 8, np.uint64)) == after8
+        assert list(words(base0.value, 2048, 2, np.uint32)) == [0, 0]           # counter and expired-CTA count back at zero
         assert np.array_equal(words(base0.value, slot, hidden, np.float64), sums_before)      # no sums stored, here or there
         assert np.array_equal(words(base1.value, slot, hidden, np.float64), remote_before)
         y, _ = ops.rmsnorm_fwd(torch.ones(4, 64, device="cuda"), None, 1e-5)    # the context still works
