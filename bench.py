@@ -646,7 +646,9 @@ def measure_one(name, steps, warmup, target_s):
            "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
            "fwd_frac": rows * (2 * hidden * elem + 4) / (fwd_ms / 1e3) / 1e9 / peak,
            "bwd_frac": rows * (3 * hidden * elem + 4) / (bwd_ms / 1e3) / 1e9 / peak,
-           "blocks": len(block_ms), "dgamma_check_ok": chk["ok"],
+           "blocks": len(block_ms), "fastest_block_ms_per_step": min(block_ms) / steps,
+           "slowest_block_ms_per_step": max(block_ms) / steps,
+           "dgamma_check_ok": chk["ok"],
            "launch": {"fwd": ops.describe_launch("fwd", rows, hidden, dtype), "bwd": ops.describe_launch("bwd", rows, hidden, dtype)}}
     ex.close()
     del x, gy, gamma, y, dx, rstd, dgamma, prepared
@@ -661,14 +663,16 @@ def measure_stack(steps, warmup):
     host_build.build()
     layers, rows, hidden, bf16 = STACK_WORKLOADS[OTHER_STACK]
     exe = os.path.join(os.path.dirname(host_build.__file__), "build", "bench_stack")
-    r = subprocess.run([exe, str(layers), str(rows), str(hidden), str(max(steps, 10)), str(max(3, warmup)), str(bf16)],
+    # 60 replays of ~10 ms: long enough to settle under the power cap; the first five are reported beside them
+    r = subprocess.run([exe, str(layers), str(rows), str(hidden), str(max(steps, 60)), str(max(3, warmup)), str(bf16)],
                        capture_output=True, text=True)
     if r.returncode != 0:
         return {"workload": OTHER_STACK, "error": (r.stdout + r.stderr)[-400:]}
     d = json.loads(r.stdout.strip().splitlines()[-1])
     peak, _ = measured_peak()
     return {"workload": OTHER_STACK, "layers": layers, "rows": rows, "hidden": hidden, "io_dtype": "float32",
-            "ms_per_step": d["ms_per_replay"], "row_layers_per_s": d["row_layers_per_s"], "step_gbs": d["gbs"],
+            "ms_per_step": d["ms_per_replay"], "first_replays_ms_per_step": d.get("first_replays_ms"),
+            "replays": d["iters"], "row_layers_per_s": d["row_layers_per_s"], "step_gbs": d["gbs"],
             "frac": d["gbs"] / peak, "frac_of_spec_8TBs": d["gbs"] / SPEC_HBM_GBS, "cuda_graph_nodes": d["graph_nodes"],
             "api": "ag::nn::ResidualRMSNormStack captured by ag::CudaGraphRunner (C++ host layer)"}
 
@@ -681,13 +685,15 @@ def measure_api(steps, warmup):
     host_build.build()
     rows, hidden, _, _ = WORKLOADS["rmsnorm_fwd_vjp_fp32_16x2048x4096"]
     exe = os.path.join(os.path.dirname(host_build.__file__), "build", "bench_api")
-    r = subprocess.run([exe, str(rows), str(hidden), str(max(steps, 50)), str(max(3, warmup)), "0"], capture_output=True, text=True)
+    # 1500 steps of ~0.4 ms per mode: long enough to settle under the power cap; the first twenty are reported too
+    r = subprocess.run([exe, str(rows), str(hidden), str(max(steps, 1500)), str(max(3, warmup)), "0"], capture_output=True, text=True)
     if r.returncode != 0:
         return {"error": (r.stdout + r.stderr)[-400:]}
     d = json.loads(r.stdout.strip().splitlines()[-1])
     peak, _ = measured_peak()
     return {"workload": "rmsnorm_fwd_vjp_fp32_16x2048x4096", "api": "ag::rmsnorm + ag::zero_grad + ag::backward (C++ host layer)",
-            "eager_ms_per_step": d["eager_ms_per_step"], "eager_frac": d["eager_gbs"] / peak,
+            "steps": d["iters"], "eager_ms_per_step": d["eager_ms_per_step"],
+            "eager_first_steps_ms_per_step": d.get("eager_first_steps_ms"), "eager_frac": d["eager_gbs"] / peak,
             "graph_ms_per_step": d["graph_ms_per_step"], "graph_frac": d["graph_gbs"] / peak,
             "cuda_graph_nodes": d["graph_nodes"], "launches_per_step": d["launches_per_step"]}
 
@@ -960,12 +966,21 @@ def main():
         del x, gy, y, dx, prepared          # make room: the other configurations bring their own operands
         torch.cuda.empty_cache()
         other = []
+        # Each side configuration gets a short pause first: the main workload has just held the GPU at its
+        # 1 kW cap for tens of seconds, and a configuration's own half second of timed work should show ITS
+        # sustained pace, not the heat of the one before it (the pause is reported; clocks are not touched).
+        pause_s = 3.0
         for name in OTHER_CONFIGS:
+            time.sleep(pause_s)
             try:
-                other.append(measure_one(name, args.steps, args.warmup, min(0.5, args.target_seconds)))
+                o = measure_one(name, args.steps, args.warmup, min(0.5, args.target_seconds))
+                o["pause_before_s"] = pause_s
+                other.append(o)
             except Exception as e:  # noqa: BLE001 -- one failing side configuration must not lose the line
                 other.append({"workload": name, "error": repr(e)[:300]})
+        time.sleep(pause_s)
         other.append(measure_stack(args.steps, args.warmup))
+        time.sleep(pause_s)
         api_path = measure_api(args.steps, args.warmup)
 
     if rank == 0:

@@ -95,7 +95,7 @@ std::atomic<int64_t> opt_stages{0}, opt_ctas_per_sm{0}, opt_threads{0}, opt_forc
 // bwd_keep: fast backward variant (0 auto, 1 registers keep x and gy between the passes, 2 re-read the tile).
 // reserve_sms: SMs the persistent grids leave free (for a collective's kernel running beside them).
 // pdl: programmatic dependent launch between the library's own kernels (see launch_pdl).
-std::atomic<int64_t> opt_bf16_strict{0}, opt_bwd_keep{0}, opt_reserve_sms{0}, opt_pdl{1}, opt_lone_ring{0};
+std::atomic<int64_t> opt_bf16_strict{0}, opt_bwd_keep{0}, opt_reserve_sms{0}, opt_pdl{1}, opt_lone_ring{0}, opt_bwd_refill{0};
 // peer_poll_limit: polls (each sleeping up to 2 us) before a wait on another GPU's counter gives up; process-wide,
 // handed to the waiting kernels as an argument at every launch.
 // softmax_strict: the softmax / logsumexp forward family with the reference composition's rounding points
@@ -182,7 +182,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     auto tile_stride_of = [&](int rpt) { return round_up(rpt * row_bytes, 128); };
     auto stages_for = [&](int rpt, int c) {
         const int nw = rpt * G / 32;
-        const int fixed = ngamma * gamma_bytes + 8 * nw * 8 /*reduction scratch*/ + 8 * 16 /*barriers*/ + 16 /*flag*/ + 128 /*slack*/ +
+        const int fixed = ngamma * gamma_bytes + 8 * nw * 8 /*reduction scratch*/ + 8 * 16 /*barriers*/ + 32 /*flag, slot counters*/ + 112 /*slack*/ +
                           extra_static;
         int avail = d.smem_per_sm / c - 1024;  // the runtime reserves 1 KB per resident CTA
         if (avail > d.smem_optin) avail = d.smem_optin;
@@ -259,7 +259,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
             if (static_cast<int64_t>(rpt) * cand > rows) continue;
             int avail = d.smem_per_sm / ctas - 1024;
             if (avail > d.smem_optin) avail = d.smem_optin;
-            const int fixed = ngamma * gamma_bytes + 8 * nwarps * 8 + 8 * 16 + 16 + 128 + extra_static;
+            const int fixed = ngamma * gamma_bytes + 8 * nwarps * 8 + 8 * 16 + 32 + 112 + extra_static;
             const int st = (avail - fixed) / (narr * tile_stride_of(rpt * cand));
             if (st >= 3 || (want_rpw > 0 && st >= 2)) {
                 rpw = cand;
@@ -296,8 +296,10 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     g.off_bar = off;
     off += 8 * 16;
     g.off_flag = off;
-    off += 16;
+    off += 32;   // the abort flag, then one release counter per ring slot (at most four)
     g.pdl_early = opt_pdl.load() == 2;
+    // (the 64-element backward only; "bwd_refill" 1 / 2 force late / early)
+    g.early_refill = fast == 3 && (opt_bwd_refill.load() == 2 || (opt_bwd_refill.load() == 0 && rpt == 1));
     p->smem = off;
     p->block = block;
     p->vpt = vpt;
@@ -532,12 +534,12 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
         agb::BwdArgs a{p.g, x, gy, dx_add, gamma, rstd, dx, want_dg ? partials : nullptr, add_mode, hf, 1.0f / hf};
         P = p.grid;
         constexpr int kV = 32 / (16 / static_cast<int>(sizeof(T)));
-#define AGB_LAUNCH_FAST_V(V, HG, FU, MT, KP)                                                  \
+#define AGB_LAUNCH_FAST_V(V, HG, FU, MT, KP, EA)                                              \
     do {                                                                                      \
-        AGB_TRY(set_smem(agb::rmsnorm_bwd_fast<T, V, HG, FU, MT, KP>, p.smem));               \
-        AGB_CUDA(launch_pdl(agb::rmsnorm_bwd_fast<T, V, HG, FU, MT, KP>, p.grid, p.block, p.smem, st, a)); \
+        AGB_TRY(set_smem(agb::rmsnorm_bwd_fast<T, V, HG, FU, MT, KP, EA>, p.smem));           \
+        AGB_CUDA(launch_pdl(agb::rmsnorm_bwd_fast<T, V, HG, FU, MT, KP, EA>, p.grid, p.block, p.smem, st, a)); \
     } while (0)
-#define AGB_LAUNCH_FAST(HG, FU, MT, KP) AGB_LAUNCH_FAST_V(kV, HG, FU, MT, KP)
+#define AGB_LAUNCH_FAST(HG, FU, MT, KP) AGB_LAUNCH_FAST_V(kV, HG, FU, MT, KP, false)
 #define AGB_FAST_BY_FLAGS(MT, KP)                                  \
     do {                                                           \
         if (gamma && p.full) AGB_LAUNCH_FAST(true, true, MT, KP);  \
@@ -546,8 +548,9 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
         else AGB_LAUNCH_FAST(false, false, MT, KP);                \
     } while (0)
         if (p.vpt == 2 * kV) {   // 64 elements per thread (planned only when full)
-            if (gamma) AGB_LAUNCH_FAST_V(2 * kV, true, true, 384, false);
-            else AGB_LAUNCH_FAST_V(2 * kV, false, true, 384, false);
+            if (gamma && p.g.early_refill) AGB_LAUNCH_FAST_V(2 * kV, true, true, 384, false, true);
+            else if (gamma) AGB_LAUNCH_FAST_V(2 * kV, true, true, 384, false, false);
+            else AGB_LAUNCH_FAST_V(2 * kV, false, true, 384, false, false);
         } else if (keep) AGB_FAST_BY_FLAGS(512, true);
         else AGB_FAST_BY_FLAGS(768, false);
 #undef AGB_LAUNCH_FAST_V
@@ -899,6 +902,7 @@ int agb_set_option(const char* key, int64_t value) {
     else if (!strcmp(key, "ept")) opt_ept = value;
     else if (!strcmp(key, "pdl")) opt_pdl = value;
     else if (!strcmp(key, "softmax_strict")) opt_softmax_strict = value;
+    else if (!strcmp(key, "bwd_refill")) opt_bwd_refill = value;  // 1: thread 0 refills after the mid-tile barrier, 2: the last warp out of a slot does
     else if (!strcmp(key, "lone_ring")) opt_lone_ring = value;   // 2: a single CTA per SM may run a two-slot ring
     else if (!strcmp(key, "bf16_strict")) opt_bf16_strict = value;
     else if (!strcmp(key, "bwd_keep")) opt_bwd_keep = value;

@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_fast(const __grid_constan
 // end the row groups of the CTA are added in group order in fp64 and the CTA writes one fp64
 // partial row, exactly the layout dgamma_reduce_kernel expects.
 // ------------------------------------------------------------------------------------------
-template <typename T, int VPT, bool HAS_GAMMA, bool FULL, int MAXT, bool KEEP>
+template <typename T, int VPT, bool HAS_GAMMA, bool FULL, int MAXT, bool KEEP, bool EARLY = false>
 __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constant__ BwdArgs a) {
     constexpr int NP = Pairs<T>::NP;
     constexpr int EPV = 2 * NP;
@@ -194,6 +194,13 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
     const int v0 = (tig >> 5) * (VPT * 32) + lane;
     const int S = g.stages;
     const bool staged_add = a.add_mode == 1;
+    // Slot release.  EARLY: every warp counts itself out of a slot when its pass 2 is done and the LAST one refills
+    // the slot at once, so a copy has a whole tile's time to arrive, and rstd is fetched one tile ahead; otherwise
+    // thread 0 refills the slot of tile k-1 after the block-wide barrier in the middle of tile k (half a tile
+    // later).  Measured at 65536 x 8192 bf16 (one row per tile, two CTAs per SM): 6053 against 5735 GB/s; with
+    // three rows per tile (4096 columns) the early form is 4 % behind, and its extra state spills in the
+    // 32-element variants, so it is a template parameter used where the plan asks for it.
+    int* s_cnt = reinterpret_cast<int*>(smem + g.off_flag + 16);
 
     const unsigned char* const src3[3] = {reinterpret_cast<const unsigned char*>(a.x),
                                           reinterpret_cast<const unsigned char*>(a.gy),
@@ -208,7 +215,7 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
     const long long my_tiles = g.ntiles > first ? (g.ntiles - first + stride - 1) / stride : 0;
     long long issued = 0;
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) mbar_init(&s_full[s], 1);
+        for (int s = 0; s < S; ++s) { mbar_init(&s_full[s], 1); s_cnt[s] = 0; }
         *s_abort = 0;
         mbar_fence_init();
     }
@@ -225,12 +232,24 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
 
     long long k = 0;
     bool aborted = false;
+    float rs_ahead = 0.0f;
+    if constexpr (EARLY) {
+        const long long row0 = first * g.rows_per_tile + grp;
+        if (my_tiles > 0 && row0 < g.rows) rs_ahead = a.rstd[row0];
+    }
     for (; k < my_tiles; ++k) {
         const int slot = static_cast<int>(k % S);
         const uint32_t parity = static_cast<uint32_t>((k / S) & 1);
         const long long row = (first + k * stride) * g.rows_per_tile + grp;
         const bool valid = row < g.rows;
-        const float rs = valid ? a.rstd[row] : 0.0f;
+        float rs;
+        if constexpr (EARLY) {
+            rs = rs_ahead;
+            const long long nrow = row + stride * g.rows_per_tile;
+            rs_ahead = (k + 1 < my_tiles && nrow < g.rows) ? a.rstd[nrow] : 0.0f;
+        } else {
+            rs = valid ? a.rstd[row] : 0.0f;
+        }
         if (!mbar_wait_bounded(&s_full[slot], parity)) *s_abort = 1;
 
         const unsigned char* base = ring + static_cast<size_t>(slot) * g.stage_stride + static_cast<size_t>(grp) * g.row_bytes;
@@ -275,7 +294,7 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
         __syncthreads();
         if (*s_abort) { aborted = true; break; }
         // all threads are past pass 2 of the previous tile: its slot can be refilled
-        if (tid == 0 && k >= 1 && issued < my_tiles) {
+        if (!EARLY && tid == 0 && k >= 1 && issued < my_tiles) {
             issue(first + issued * stride, static_cast<int>((k - 1) % S));
             ++issued;
         }
@@ -324,9 +343,23 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
                 }
             }
         }
+        if constexpr (EARLY) {
+            // this warp's shared-memory reads of the slot are complete (their values were consumed above)
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence_block();
+                if (atomicAdd(&s_cnt[slot], 1) == nwarps - 1) {
+                    __threadfence_block();
+                    s_cnt[slot] = 0;   // nobody counts on this slot again before the refill below has been consumed
+                    if (k + S < my_tiles) issue(first + (k + S) * stride, slot);
+                }
+            }
+        }
     }
     pdl_trigger();   // this CTA has no tiles left: the next kernel's CTAs may take the room it frees
     if (aborted) {
+        // early: every warp passed the barrier of tile k, so the refill after tile k-1 (tile k-1+S) was issued
+        if (EARLY) issued = k + S < my_tiles ? k + S : my_tiles;
         if (tid == 0) drain_after_abort(g, s_full, k, issued);
         return;
     }

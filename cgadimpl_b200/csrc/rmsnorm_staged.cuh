@@ -40,6 +40,7 @@ struct PipeGeom {
     int off_bar;
     int off_flag;
     int pdl_early;      // 1: let the next kernel's CTAs be placed as soon as this one has started (else: when it drains)
+    int early_refill;   // backward (fp32-accumulating): the last warp to leave a ring slot refills it at once
 };
 
 // ---------------------------------------------------------------- packed fp32 helpers
