@@ -698,11 +698,12 @@ def measure_api(steps, warmup):
             "cuda_graph_nodes": d["graph_nodes"], "launches_per_step": d["launches_per_step"]}
 
 
-def no_exchange_pace(x, gy, gamma, y, dx, rstd, eps, steps, dist, rank, world):
+def no_exchange_pace(x, gy, gamma, y, dx, rstd, eps, steps, dist, rank, world, blocks=1):
     """N > 1: what each GPU does on its shard with NO exchange while all ranks are busy at the same time
-    (ms per step, per rank).  The spread over the ranks is the part of the scaling loss that no exchange can
-    remove; it is taken before and after the timed region because a GPU under its power cap drifts by a few
-    per cent within seconds."""
+    (ms per step, per rank; the median of `blocks` blocks of `steps` steps).  Taken briefly before the timed
+    region (a GPU that has not yet met its power cap) and after it for as many blocks as the timed region had
+    (the settled pace: under the 1 kW cap the SM clock sinks within a second and these kernels slow down by
+    several per cent), so that the cost of coupling the ranks can be told from what each GPU does alone."""
     import torch
 
     from cgadimpl_b200 import ops
@@ -718,14 +719,17 @@ def no_exchange_pace(x, gy, gamma, y, dx, rstd, eps, steps, dist, rank, world):
         local_step()
     dist.barrier()
     torch.cuda.synchronize()
-    q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    q0.record()
-    for _ in range(steps):
-        local_step()
-    q1.record()
-    torch.cuda.synchronize()
+    per_block = []
+    for _ in range(blocks):
+        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        q0.record()
+        for _ in range(steps):
+            local_step()
+        q1.record()
+        torch.cuda.synchronize()
+        per_block.append(q0.elapsed_time(q1) / steps)
     every = torch.zeros(world, device="cuda", dtype=torch.float64)   # a SUM all-reduce of a one-hot table: it
-    every[rank] = q0.elapsed_time(q1) / steps                        # exists for every algorithm NCCL may be pinned to
+    every[rank] = statistics.median(per_block)                       # exists for every algorithm NCCL may be pinned to
     dist.all_reduce(every, op=dist.ReduceOp.SUM)
     return [round(float(v), 4) for v in every.tolist()]
 
@@ -870,11 +874,13 @@ def main():
     # ---- N > 1: the ranks' own pace without any exchange, again after the timed region
     no_exchange = None
     if world > 1:
-        after = no_exchange_pace(x, gy, gamma, y, dx, rstd, eps, args.steps * 3, dist, rank, world)
+        after = no_exchange_pace(x, gy, gamma, y, dx, rstd, eps, args.steps, dist, rank, world, blocks=len(block_ms))
         no_exchange = {"per_rank_ms_per_step_before": pace_before, "per_rank_ms_per_step_after": after,
-                       "slowest_ms": min(max(pace_before), max(after)),
+                       "slowest_ms": max(after), "slowest_before_ms": max(pace_before),
+                       "blocks_after": len(block_ms),
                        "note": "forward + VJP on each rank's shard without any exchange, all ranks running at once; "
-                               "taken right before and right after the timed region"}
+                               "before: one short block ahead of the timed region (GPU not yet at its power cap); "
+                               "after: as many blocks as the timed region, right after it (the settled pace)"}
         ex.fwd_bwd(x, gy, gamma, y=y, rstd=rstd, dx=dx, dgamma=dgamma, wait=True)   # dgamma of the real path again
 
     # ---- the exchanged dgamma is the column sum over all ranks' rows (outside the timed region)

@@ -95,7 +95,7 @@ std::atomic<int64_t> opt_stages{0}, opt_ctas_per_sm{0}, opt_threads{0}, opt_forc
 // bwd_keep: fast backward variant (0 auto, 1 registers keep x and gy between the passes, 2 re-read the tile).
 // reserve_sms: SMs the persistent grids leave free (for a collective's kernel running beside them).
 // pdl: programmatic dependent launch between the library's own kernels (see launch_pdl).
-std::atomic<int64_t> opt_bf16_strict{0}, opt_bwd_keep{0}, opt_reserve_sms{0}, opt_pdl{1}, opt_lone_ring{0}, opt_bwd_refill{0};
+std::atomic<int64_t> opt_bf16_strict{0}, opt_bwd_keep{0}, opt_reserve_sms{0}, opt_pdl{1}, opt_lone_ring{0}, opt_bwd_refill{0}, opt_softmax_two_pass{0};
 // peer_poll_limit: polls (each sleeping up to 2 us) before a wait on another GPU's counter gives up; process-wide,
 // handed to the waiting kernels as an argument at every launch.
 // softmax_strict: the softmax / logsumexp forward family with the reference composition's rounding points
@@ -670,10 +670,18 @@ int launch_softmax_fwd(int mode, const void* z, const void* t, const void* rowsc
     constexpr int kKeepVecs = 32 / (16 / static_cast<int>(sizeof(T)));   // 8 fp32 vectors, 4 bf16 vectors
     const bool fastmode = !opt_softmax_strict.load();
     bool keep_regs = false;
-    if (al && fastmode && mode != 1) {
+    if (al && fastmode) {
         plan_launch(kSoftmax, rows, hidden, sizeof(T), mode == 3 ? 2 : 1, 0, *d, &p, agb::kExpTableSize * 8 + agb::kExp32Size * 8);
         keep_regs = !p.generic && static_cast<int64_t>(kKeepVecs) * p.g.group_threads >= p.g.nvec;
     }
+    // One pass (softmax_fwd_online) or two: logsumexp and the 16-bit softmax gain everywhere measured (logsumexp
+    // +3 to +44 %, bf16 softmax +1 to +16 %); the fp32 softmax gains with wide row groups (16384 columns: 6.17
+    // against 5.50 TB/s) and loses with narrow ones (4096 columns, 128 threads per row: 5.37 against 5.94).
+    // "softmax_two_pass" 1 / 2 force two / one.
+    const int64_t two_pass = opt_softmax_two_pass.load();
+    const bool online = keep_regs && mode <= 1 && two_pass != 1 &&
+                        (two_pass == 2 || mode == 1 || sizeof(T) == 2 || p.g.group_threads >= 256);
+    if (mode == 1 && !online) keep_regs = false;   // (the two-pass logsumexp keeps nothing between its passes)
     const bool scratch = mode != 1 && sizeof(T) == 2 && !keep_regs;
     const int narr = (mode == 3 ? 2 : 1) + (scratch ? 2 : 0);
     if (al && !keep_regs) {
@@ -708,6 +716,17 @@ int launch_softmax_fwd(int mode, const void* z, const void* t, const void* rowsc
         return after_launch("softmax_fwd_generic");
     }
     agb::SoftmaxArgs a{p.g, z, t, rowscale, add, out, out_row, scratch ? (mode == 3 ? 2 : 1) * p.g.tile_stride : 0};
+    // softmax and logsumexp forward, approximate arithmetic, row in registers: the one-pass kernel
+    if (online) {
+        if (mode == 0) {
+            AGB_TRY(set_smem(agb::softmax_fwd_online<T, 0, kKeepVecs>, p.smem));
+            agb::softmax_fwd_online<T, 0, kKeepVecs><<<p.grid, p.block, p.smem, st>>>(a);
+        } else {
+            AGB_TRY(set_smem(agb::softmax_fwd_online<T, 1, kKeepVecs>, p.smem));
+            agb::softmax_fwd_online<T, 1, kKeepVecs><<<p.grid, p.block, p.smem, st>>>(a);
+        }
+        return after_launch("softmax_fwd_online");
+    }
 #define AGB_SM_STAGED(M)                                                              \
     do {                                                                              \
         if (opt_softmax_strict.load()) {                                              \
@@ -903,6 +922,7 @@ int agb_set_option(const char* key, int64_t value) {
     else if (!strcmp(key, "pdl")) opt_pdl = value;
     else if (!strcmp(key, "softmax_strict")) opt_softmax_strict = value;
     else if (!strcmp(key, "bwd_refill")) opt_bwd_refill = value;  // 1: thread 0 refills after the mid-tile barrier, 2: the last warp out of a slot does
+    else if (!strcmp(key, "softmax_two_pass")) opt_softmax_two_pass = value;  // 1: maximum first, then exp; 2: always the one-pass kernel
     else if (!strcmp(key, "lone_ring")) opt_lone_ring = value;   // 2: a single CTA per SM may run a two-slot ring
     else if (!strcmp(key, "bf16_strict")) opt_bf16_strict = value;
     else if (!strcmp(key, "bwd_keep")) opt_bwd_keep = value;

@@ -113,6 +113,21 @@ __device__ __forceinline__ float exp_rel16(float x, float nmx2) {
     return p;
 }
 
+// exp(t), t <= 0, for a term of a SUM (logsumexp): the hardware 2^u on t*log2(e).  Relative error about
+// 2.4e-7 + 1.2e-7*|t|: the terms that matter to the sum (t near 0) are as good as the careful form's, the
+// others are wrong by a little more in proportion to how little they matter; under the normal range it flushes.
+__device__ __forceinline__ float exp_for_sum(float t) {
+    float p;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(__fmul_rn(t, 0x1.715476p+0f)));
+    return p;
+}
+
+// max of two packed bf16 pairs, lane by lane (a NaN lane yields the other operand, like fmaxf)
+__device__ __forceinline__ uint32_t packed_max(uint32_t a, uint32_t b) {
+    const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
 // e = exp(z - mx) for one vector, in place, and its contribution to four fp32 sum chains
 template <typename T>
 __device__ __forceinline__ void exp_fast_vec(float (&f)[Vec<T>::EPV], float mx, float nmx2, float& a0, float& a1, float& a2,
@@ -324,7 +339,9 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
             issue(first + issued * stride, slot);
             ++issued;
         }
-        const float s = static_cast<float>(group_total(red + nwarps + grp * wpr, wpr, lane));
+        float s = static_cast<float>(group_total(red + nwarps + grp * wpr, wpr, lane));
+        // an infinite row maximum makes z - max NaN in the composition; the clamped approximate exp would hide it
+        if (FAST && fabsf(mx) == INFINITY) s = __int_as_float(0x7fc00000);
         const bool row_tiny = __any_sync(0xffffffffu, lane < wpr && redf[nwarps + grp * wpr + lane] != 0.0f);
 
         if (MODE == 1) {
@@ -421,6 +438,142 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_staged(const __grid_const
             __syncthreads();
             const float tot = static_cast<float>(group_total(red + 2 * nwarps + grp * wpr, wpr, lane));
             if (valid && tig == 0) Vec<T>::store1(static_cast<T*>(a.out_row) + row, tot);
+        }
+    }
+    if (aborted && tid == 0) drain_after_abort(g, s_full, k, issued);
+}
+
+// ------------------------------------------------------------------------------------------
+// Forward in ONE pass over the staged row (approximate arithmetic only; MODE 0 softmax, 1 logsumexp).
+// Every thread owns at most KV vectors of its row.  It reads them once, takes ITS OWN maximum m_t, forms
+// e = exp(z - m_t) and their sum s_t in registers, and only then meets the rest of the row: the pairs (m, s)
+// are merged by  M = max m,  S = sum s * exp(m - M)  inside the warp and, through shared memory, across the
+// row's warps.  The result is y = e * (exp(m_t - M) / S), or log(S) + M.  One shared-memory pass and one
+// block-wide barrier per tile instead of two each, and the slot is free for its refill at that barrier.
+// A thread whose values are all -inf contributes nothing; a row whose maximum is infinite yields NaN, as the
+// composition does (z - max is NaN there).
+// ------------------------------------------------------------------------------------------
+template <typename T, int MODE, int KV>
+__global__ void __launch_bounds__(1024, 1) softmax_fwd_online(const __grid_constant__ SoftmaxArgs a) {
+    static_assert(MODE == 0 || MODE == 1, "softmax or logsumexp");
+    constexpr int EPV = Vec<T>::EPV;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const PipeGeom& g = a.g;
+    unsigned char* ring = smem;
+    float2* s_red = reinterpret_cast<float2*>(smem + g.off_red);   // [2 tiles in turn][nwarps] of (max, sum)
+    uint64_t* s_full = reinterpret_cast<uint64_t*>(smem + g.off_bar);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + g.off_flag);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const int G = g.group_threads, wpr = G >> 5;
+    const int grp = tid / G, tig = tid - grp * G;
+    const int S = g.stages;
+    constexpr float kLog2e = 0x1.715476p+0f;
+    // the factor exp(m - M) of a merge: it scales a SUM in the logsumexp, an output element in the softmax
+    auto merge_exp = [](float t) { return MODE == 1 ? exp_for_sum(t) : exp_approx_nonpositive(t); };
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) mbar_init(&s_full[s], 1);
+        *s_abort = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const unsigned char* const src1[1] = {reinterpret_cast<const unsigned char*>(a.z)};
+    const long long first = blockIdx.x, stride = gridDim.x;
+    const long long my_tiles = g.ntiles > first ? (g.ntiles - first + stride - 1) / stride : 0;
+    long long issued = 0;
+    if (tid == 0)
+        for (; issued < my_tiles && issued < S; ++issued) issue_tile<1>(g, ring, s_full, src1, first + issued * stride, static_cast<int>(issued));
+
+    long long k = 0;
+    bool aborted = false;
+    for (; k < my_tiles; ++k) {
+        const int slot = static_cast<int>(k % S);
+        const uint32_t parity = static_cast<uint32_t>((k / S) & 1);
+        const long long row = (first + k * stride) * g.rows_per_tile + grp;
+        const bool valid = row < g.rows;
+        if (!mbar_wait_bounded(&s_full[slot], parity)) *s_abort = 1;
+        const uint4* sz = reinterpret_cast<const uint4*>(ring + static_cast<size_t>(slot) * g.stage_stride + static_cast<size_t>(grp) * g.row_bytes);
+
+        float f[KV * EPV];
+        float m = -INFINITY;
+        uint32_t mp = 0xFF80FF80u;   // 16-bit I/O: the maximum is taken on the packed pairs, two values per instruction
+#pragma unroll
+        for (int i = 0; i < KV; ++i) {
+            const int v = tig + i * G;
+            if (valid && v < g.nvec) {
+                const uint4 raw = sz[v];
+                float t[EPV];
+                Vec<T>::unpack(raw, t);
+                if constexpr (sizeof(T) == 2) {
+                    mp = packed_max(packed_max(mp, raw.x), packed_max(raw.y, packed_max(raw.z, raw.w)));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) m = fmaxf(m, t[e]);
+                }
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) f[i * EPV + e] = t[e];
+            } else {
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) f[i * EPV + e] = -INFINITY;
+            }
+        }
+        if constexpr (sizeof(T) == 2) m = fmaxf(__uint_as_float(mp << 16), __uint_as_float(mp & 0xffff0000u));
+        const float ms = m == -INFINITY ? 0.0f : m;    // the shift this thread uses (a thread of -inf shifts by 0: e = 0)
+        const float nms2 = -ms * kLog2e;
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < KV * EPV; i += 4) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if constexpr (sizeof(T) == 2) f[i + e] = exp_rel16(f[i + e], nms2);
+                else if constexpr (MODE == 1) f[i + e] = exp_for_sum(f[i + e] - ms);
+                else f[i + e] = exp_approx_nonpositive(f[i + e] - ms);
+            }
+            a0 += f[i]; a1 += f[i + 1]; a2 += f[i + 2]; a3 += f[i + 3];
+        }
+        const float st = (a0 + a1) + (a2 + a3);
+        // merge inside the warp
+        const float mw = warp_max(m);
+        const float mws = mw == -INFINITY ? 0.0f : mw;
+        const float sw = warp_sum_f32(m == -INFINITY ? 0.0f : st * merge_exp(ms - mws));
+        float2* red = s_red + (k & 1) * nwarps;
+        if (lane == 0) red[warp] = make_float2(mw, sw);
+        __syncthreads();
+        if (*s_abort) { aborted = true; break; }
+        // every thread holds its part of the tile in registers: the slot can be refilled now
+        if (tid == 0 && issued < my_tiles) {
+            issue_tile<1>(g, ring, s_full, src1, first + issued * stride, slot);
+            ++issued;
+        }
+        // merge the row's warps (every thread of the row computes the same M and S)
+        float M = mw, Ssum = sw;
+        if (wpr > 1) {
+            const float2 p = lane < wpr ? red[grp * wpr + lane] : make_float2(-INFINITY, 0.0f);
+            M = warp_max(p.x);
+            const float Msafe = M == -INFINITY ? 0.0f : M;
+            Ssum = warp_sum_f32(p.x == -INFINITY ? 0.0f : p.y * merge_exp(p.x - Msafe));
+        }
+        const float Ms = M == -INFINITY ? 0.0f : M;
+        const float nan = __int_as_float(0x7fc00000);
+        if (MODE == 1) {
+            if (valid && tig == 0)
+                Vec<T>::store1(static_cast<T*>(a.out_row) + row, fabsf(M) == INFINITY ? nan : logf(Ssum) + M);
+            continue;
+        }
+        const float c = fabsf(M) == INFINITY ? nan : (m == -INFINITY ? 0.0f : exp_approx_nonpositive(ms - Ms) * __frcp_rn(Ssum));
+        if (valid) {
+            uint4* gout = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.out) + row * g.row_bytes);
+#pragma unroll
+            for (int i = 0; i < KV; ++i) {
+                const int v = tig + i * G;
+                if (v < g.nvec) {
+                    float t[EPV];
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) t[e] = f[i * EPV + e] * c;
+                    store_vec_streaming(gout + v, Vec<T>::pack(t));
+                }
+            }
         }
     }
     if (aborted && tid == 0) drain_after_abort(g, s_full, k, issued);

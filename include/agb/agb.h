@@ -81,12 +81,15 @@ int agb_selftest_bounded_wait(int poll_limit, int* polls_done, agb_stream_t stre
  *     strict backward), "rows_per_warp" (strict backward, one-warp rows), "bwd_keep" (16-bit backward:
  *     1 keep x/gy in registers, 2 re-read the tile, 3 64 elements per thread), "lone_ring" (2: a single
  *     CTA per SM may run a two-slot ring), "reserve_sms" (SMs the persistent grids leave free),
- *     "force_generic" (1: the unstaged kernels);
+ *     "bwd_refill" (64-element 16-bit backward: 1 thread 0 refills a ring slot after the mid-tile barrier,
+ *     2 the last warp out of the slot does), "softmax_two_pass" (approximate softmax / logsumexp forward:
+ *     1 maximum first, then exp; 2 always the one-pass kernel), "force_generic" (1: the unstaged kernels);
  *   "bf16_strict"  1: 16-bit I/O through the strictly rounded, fp64-reducing kernels (the fp32 path's
  *                  arithmetic) instead of the fp32-accumulating ones;
  *   "softmax_strict"  1: softmax / logsumexp forward with the reference composition's rounding points
  *                  (exp to 2^-33, fp64 sums, exact division; reproduces the CPU composition's bits) instead
- *                  of the default approximate exp (2e-7 relative) with fp32 sums;
+ *                  of the default approximate exp (2e-7 relative; the terms of a logsumexp sum 2.4e-7 +
+ *                  1.2e-7 per unit below the row maximum) with fp32 sums;
  *   "pdl"          programmatic dependent launch between the library's kernels: 1 (default) a kernel's CTAs
  *                  are placed while the previous one drains, 2 as soon as it has started, 0 off;
  *   "peer_poll_limit"  polls (up to 2 us each) before a wait on another rank's counter gives up
