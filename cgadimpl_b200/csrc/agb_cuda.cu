@@ -95,7 +95,7 @@ std::atomic<int64_t> opt_stages{0}, opt_ctas_per_sm{0}, opt_threads{0}, opt_forc
 // bwd_keep: fast backward variant (0 auto, 1 registers keep x and gy between the passes, 2 re-read the tile).
 // reserve_sms: SMs the persistent grids leave free (for a collective's kernel running beside them).
 // pdl: programmatic dependent launch between the library's own kernels (see launch_pdl).
-std::atomic<int64_t> opt_bf16_strict{0}, opt_bwd_keep{0}, opt_reserve_sms{0}, opt_pdl{1}, opt_lone_ring{0}, opt_bwd_refill{0}, opt_softmax_two_pass{0};
+std::atomic<int64_t> opt_bf16_strict{0}, opt_bwd_keep{0}, opt_reserve_sms{0}, opt_pdl{1}, opt_lone_ring{0}, opt_bwd_refill{0}, opt_softmax_two_pass{0}, opt_free_rows{0};
 // peer_poll_limit: polls (each sleeping up to 2 us) before a wait on another GPU's counter gives up; process-wide,
 // handed to the waiting kernels as an argument at every launch.
 // softmax_strict: the softmax / logsumexp forward family with the reference composition's rounding points
@@ -418,11 +418,12 @@ int launch_fwd(const void* x, const void* r, const void* gamma, void* h, void* y
     agb::FwdArgs a{p.g, x, r, gamma, h, y, rstd, eps};
     if constexpr (sizeof(T) == 2) if (!opt_bf16_strict.load()) {
         const float hinv = 1.0f / static_cast<float>(hidden);
-#define AGB_LAUNCH_FWDF(V, HG, FA, FU)                                                       \
+#define AGB_LAUNCH_FWDF_R(V, HG, FA, FU, FR)                                                 \
     do {                                                                                     \
-        AGB_TRY(set_smem(agb::rmsnorm_fwd_fast<T, V, HG, FA, FU>, p.smem));                  \
-        AGB_CUDA(launch_pdl(agb::rmsnorm_fwd_fast<T, V, HG, FA, FU>, p.grid, p.block, p.smem, st, a, hinv)); \
+        AGB_TRY(set_smem(agb::rmsnorm_fwd_fast<T, V, HG, FA, FU, FR>, p.smem));              \
+        AGB_CUDA(launch_pdl(agb::rmsnorm_fwd_fast<T, V, HG, FA, FU, FR>, p.grid, p.block, p.smem, st, a, hinv)); \
     } while (0)
+#define AGB_LAUNCH_FWDF(V, HG, FA, FU) AGB_LAUNCH_FWDF_R(V, HG, FA, FU, false)
 #define AGB_FWDF_BY_FLAGS(V, FU)                                 \
     do {                                                         \
         if (gamma && fuse) AGB_LAUNCH_FWDF(V, true, true, FU);   \
@@ -430,11 +431,18 @@ int launch_fwd(const void* x, const void* r, const void* gamma, void* h, void* y
         else if (fuse) AGB_LAUNCH_FWDF(V, false, true, FU);      \
         else AGB_LAUNCH_FWDF(V, false, false, FU);               \
     } while (0)
-        if (p.vpt == 4 && p.full) AGB_FWDF_BY_FLAGS(4, true);
+        // rows that one warp owns, several per tile, gamma, no fused add: the form without a block-wide barrier
+        // (measured 65536 x 1000 bf16: 6143 against 5923 GB/s; 262144 x 512: 5574 against 5237; level at 768 / 1024)
+        const bool free_rows = p.g.group_threads == 32 && p.block > 32 && gamma && !fuse && p.vpt == 4 &&
+                               opt_free_rows.load() != 1;
+        if (free_rows && p.full) AGB_LAUNCH_FWDF_R(4, true, false, true, true);
+        else if (free_rows) AGB_LAUNCH_FWDF_R(4, true, false, false, true);
+        else if (p.vpt == 4 && p.full) AGB_FWDF_BY_FLAGS(4, true);
         else if (p.vpt == 4) AGB_FWDF_BY_FLAGS(4, false);
         else AGB_FWDF_BY_FLAGS(8, false);
 #undef AGB_FWDF_BY_FLAGS
 #undef AGB_LAUNCH_FWDF
+#undef AGB_LAUNCH_FWDF_R
         return after_launch("rmsnorm_fwd_fast");
     }
 #define AGB_LAUNCH_FWD(V, HG, FA, FU)                                                   \
@@ -539,7 +547,7 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
         AGB_TRY(set_smem(agb::rmsnorm_bwd_fast<T, V, HG, FU, MT, KP, EA>, p.smem));           \
         AGB_CUDA(launch_pdl(agb::rmsnorm_bwd_fast<T, V, HG, FU, MT, KP, EA>, p.grid, p.block, p.smem, st, a)); \
     } while (0)
-#define AGB_LAUNCH_FAST(HG, FU, MT, KP) AGB_LAUNCH_FAST_V(kV, HG, FU, MT, KP, false)
+#define AGB_LAUNCH_FAST(HG, FU, MT, KP) AGB_LAUNCH_FAST_V(kV, HG, FU, MT, KP, 0)
 #define AGB_FAST_BY_FLAGS(MT, KP)                                  \
     do {                                                           \
         if (gamma && p.full) AGB_LAUNCH_FAST(true, true, MT, KP);  \
@@ -548,9 +556,9 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
         else AGB_LAUNCH_FAST(false, false, MT, KP);                \
     } while (0)
         if (p.vpt == 2 * kV) {   // 64 elements per thread (planned only when full)
-            if (gamma && p.g.early_refill) AGB_LAUNCH_FAST_V(2 * kV, true, true, 384, false, true);
-            else if (gamma) AGB_LAUNCH_FAST_V(2 * kV, true, true, 384, false, false);
-            else AGB_LAUNCH_FAST_V(2 * kV, false, true, 384, false, false);
+            if (gamma && p.g.early_refill) AGB_LAUNCH_FAST_V(2 * kV, true, true, 384, false, 1);
+            else if (gamma) AGB_LAUNCH_FAST_V(2 * kV, true, true, 384, false, 0);
+            else AGB_LAUNCH_FAST_V(2 * kV, false, true, 384, false, 0);
         } else if (keep) AGB_FAST_BY_FLAGS(512, true);
         else AGB_FAST_BY_FLAGS(768, false);
 #undef AGB_LAUNCH_FAST_V
@@ -923,6 +931,7 @@ int agb_set_option(const char* key, int64_t value) {
     else if (!strcmp(key, "softmax_strict")) opt_softmax_strict = value;
     else if (!strcmp(key, "bwd_refill")) opt_bwd_refill = value;  // 1: thread 0 refills after the mid-tile barrier, 2: the last warp out of a slot does
     else if (!strcmp(key, "softmax_two_pass")) opt_softmax_two_pass = value;  // 1: maximum first, then exp; 2: always the one-pass kernel
+    else if (!strcmp(key, "free_rows")) opt_free_rows = value;   // 1: the 16-bit forward keeps its block-wide barrier per tile for one-warp rows too
     else if (!strcmp(key, "lone_ring")) opt_lone_ring = value;   // 2: a single CTA per SM may run a two-slot ring
     else if (!strcmp(key, "bf16_strict")) opt_bf16_strict = value;
     else if (!strcmp(key, "bwd_keep")) opt_bwd_keep = value;

@@ -38,10 +38,40 @@ __device__ __forceinline__ float rstd_from_sumsq_f32(float sumsq, float hidden_i
     return __fdiv_rn(1.0f, __fsqrt_rn(fmaf(sumsq, hidden_inv, eps)));
 }
 
+// Slot release by count: every warp calls this when it has read all it needs from ring slot `slot` (tile k of
+// the CTA); the LAST warp to arrive refills the slot with tile k + stages.  Words behind the abort flag:
+// flag[1] = tiles issued so far (for the drain after an abort), flag[4 + slot] = arrivals.
+template <typename Issue>
+__device__ __forceinline__ void release_slot(volatile int* flag, int slot, int nwarps, long long k, int stages,
+                                             long long my_tiles, int lane, Issue&& issue) {
+    __syncwarp();   // this warp's shared-memory reads of the slot are complete (their values were consumed)
+    if (lane == 0) {
+        int* cnt = const_cast<int*>(flag) + 4 + slot;
+        __threadfence_block();
+        if (atomicAdd(cnt, 1) == nwarps - 1) {
+            __threadfence_block();
+            *cnt = 0;   // nobody counts on this slot again before the refill below has been consumed
+            if (k + stages < my_tiles) {
+                issue(k + stages, slot);
+                atomicMax(const_cast<int*>(flag) + 1, static_cast<int>(k + stages + 1));
+            }
+        }
+    }
+}
+// After an abort in a kernel that releases by count: wait (bounded) for the last `stages` tiles issued.
+__device__ __forceinline__ void drain_counted(const PipeGeom& g, uint64_t* full, volatile int* flag) {
+    const long long issued = flag[1];
+    drain_after_abort(g, full, issued > g.stages ? issued - g.stages : 0, issued);
+}
+
 // ------------------------------------------------------------------------------------------
 // Forward.  Arguments as rmsnorm_fwd_staged (FwdArgs); hidden_inv = 1/H.
+// FREE (rows that one warp owns): no block-wide barrier in the tile loop at all -- a warp needs nothing from
+// the others, takes its row into registers, counts itself out of the slot and goes on; warps drift apart by
+// up to the ring's depth, which hides the fixed latencies of a row (wait, reduction, statistics) that a
+// barrier per tile would line up in every warp at once.
 // ------------------------------------------------------------------------------------------
-template <typename T, int VPT, bool HAS_GAMMA, bool FUSE_ADD, bool FULL>
+template <typename T, int VPT, bool HAS_GAMMA, bool FUSE_ADD, bool FULL, bool FREE = false>
 __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_fast(const __grid_constant__ FwdArgs a, const float hidden_inv) {
     constexpr int NP = Pairs<T>::NP;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -73,14 +103,16 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_fast(const __grid_constan
     const long long my_tiles = g.ntiles > first ? (g.ntiles - first + stride - 1) / stride : 0;
     long long issued = 0;
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) mbar_init(&s_full[s], 1);
+        for (int s = 0; s < S; ++s) { mbar_init(&s_full[s], 1); s_abort[4 + s] = 0; }
         *s_abort = 0;
         mbar_fence_init();
     }
     pdl_wait();      // the inputs may be the output of the kernel before this one in the stream
     if (g.pdl_early) pdl_trigger();
-    if (tid == 0)
+    if (tid == 0) {
         for (; issued < my_tiles && issued < S; ++issued) issue(first + issued * stride, static_cast<int>(issued));
+        s_abort[1] = static_cast<int>(issued);
+    }
     if (HAS_GAMMA) stage_gamma<T>(s_gamma, a.gamma, g.nvec);
     __syncthreads();
 
@@ -92,6 +124,7 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_fast(const __grid_constan
         const long long row = (first + k * stride) * g.rows_per_tile + grp;
         const bool valid = row < g.rows;
         if (!mbar_wait_bounded(&s_full[slot], parity)) *s_abort = 1;
+        if (FREE && *s_abort) break;
 
         const uint4* sx = reinterpret_cast<const uint4*>(ring + static_cast<size_t>(slot) * g.stage_stride +
                                                          static_cast<size_t>(grp) * g.row_bytes);
@@ -127,14 +160,22 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_fast(const __grid_constan
             }
         }
         const float ssum = warp_sum_f32((s0.x + s0.y) + (s1.x + s1.y));
-        if (wpr > 1 && lane == 0) s_red[(k & 1) * nwarps + warp] = ssum;
-        __syncthreads();
-        if (*s_abort) { aborted = true; break; }
-        if (tid == 0 && issued < my_tiles) {   // every thread holds its vectors in registers: refill now
-            issue(first + issued * stride, slot);
-            ++issued;
+        float tot;
+        if constexpr (FREE) {
+            // this warp holds its row in registers: it is done with the slot
+            release_slot(s_abort, slot, nwarps, k, S, my_tiles, lane,
+                         [&](long long kk, int sl) { issue(first + kk * stride, sl); });
+            tot = ssum;
+        } else {
+            if (wpr > 1 && lane == 0) s_red[(k & 1) * nwarps + warp] = ssum;
+            __syncthreads();
+            if (*s_abort) { aborted = true; break; }
+            if (tid == 0 && issued < my_tiles) {   // every thread holds its vectors in registers: refill now
+                issue(first + issued * stride, slot);
+                ++issued;
+            }
+            tot = wpr == 1 ? ssum : group_total_f32(s_red + (k & 1) * nwarps + grp * wpr, wpr, lane);
         }
-        const float tot = wpr == 1 ? ssum : group_total_f32(s_red + (k & 1) * nwarps + grp * wpr, wpr, lane);
         const float rs = rstd_from_sumsq_f32(tot, hidden_inv, a.eps);
         const float2 rs2 = splat(rs);
 
@@ -162,7 +203,12 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_fast(const __grid_constan
         }
     }
     pdl_trigger();   // this CTA has no tiles left: the next kernel's CTAs may take the room it frees
-    if (aborted && tid == 0) drain_after_abort(g, s_full, k, issued);
+    if constexpr (FREE) {
+        __syncthreads();
+        if (*s_abort && tid == 0) drain_counted(g, s_full, s_abort);
+    } else {
+        if (aborted && tid == 0) drain_after_abort(g, s_full, k, issued);
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -173,7 +219,7 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_fwd_fast(const __grid_constan
 // end the row groups of the CTA are added in group order in fp64 and the CTA writes one fp64
 // partial row, exactly the layout dgamma_reduce_kernel expects.
 // ------------------------------------------------------------------------------------------
-template <typename T, int VPT, bool HAS_GAMMA, bool FULL, int MAXT, bool KEEP, bool EARLY = false>
+template <typename T, int VPT, bool HAS_GAMMA, bool FULL, int MAXT, bool KEEP, int REL = 0>
 __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constant__ BwdArgs a) {
     constexpr int NP = Pairs<T>::NP;
     constexpr int EPV = 2 * NP;
@@ -194,13 +240,15 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
     const int v0 = (tig >> 5) * (VPT * 32) + lane;
     const int S = g.stages;
     const bool staged_add = a.add_mode == 1;
-    // Slot release.  EARLY: every warp counts itself out of a slot when its pass 2 is done and the LAST one refills
-    // the slot at once, so a copy has a whole tile's time to arrive, and rstd is fetched one tile ahead; otherwise
-    // thread 0 refills the slot of tile k-1 after the block-wide barrier in the middle of tile k (half a tile
-    // later).  Measured at 65536 x 8192 bf16 (one row per tile, two CTAs per SM): 6053 against 5735 GB/s; with
-    // three rows per tile (4096 columns) the early form is 4 % behind, and its extra state spills in the
-    // 32-element variants, so it is a template parameter used where the plan asks for it.
-    int* s_cnt = reinterpret_cast<int*>(smem + g.off_flag + 16);
+    // Slot release.  REL 0: thread 0 refills the slot of tile k-1 after the block-wide barrier in the middle of
+    // tile k.  REL 1 (EARLY): every warp counts itself out of a slot when its pass 2 is done and the LAST one
+    // refills the slot at once, so a copy has a whole tile's time to arrive instead of half, and rstd is fetched
+    // one tile ahead.  Measured at 65536 x 8192 bf16 (one row per tile, two CTAs per SM): 6053 against 5735 GB/s;
+    // with three rows per tile (4096 columns) it is 4 % behind, and its extra state spills in the 32-element
+    // variants, so it is a template parameter used where the plan asks for it.  (A third form for rows that one
+    // warp owns, release by count and no block-wide barrier at all as in the forward, measured 5-8 % BEHIND the
+    // barrier form here -- 4941 against 5192 GB/s at 1000 columns, 4606 against 4969 at 1024 -- and was dropped.)
+    static_assert(REL == 0 || REL == 1, "late or early refill");
 
     const unsigned char* const src3[3] = {reinterpret_cast<const unsigned char*>(a.x),
                                           reinterpret_cast<const unsigned char*>(a.gy),
@@ -215,14 +263,16 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
     const long long my_tiles = g.ntiles > first ? (g.ntiles - first + stride - 1) / stride : 0;
     long long issued = 0;
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(&s_full[s], 1); s_cnt[s] = 0; }
+        for (int s = 0; s < S; ++s) { mbar_init(&s_full[s], 1); s_abort[4 + s] = 0; }
         *s_abort = 0;
         mbar_fence_init();
     }
     pdl_wait();      // the inputs may be the output of the kernel before this one in the stream
     if (g.pdl_early) pdl_trigger();
-    if (tid == 0)
+    if (tid == 0) {
         for (; issued < my_tiles && issued < S; ++issued) issue(first + issued * stride, static_cast<int>(issued));
+        s_abort[1] = static_cast<int>(issued);
+    }
     if (HAS_GAMMA) stage_gamma<T>(s_gamma, a.gamma, g.nvec);
     __syncthreads();
 
@@ -233,7 +283,7 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
     long long k = 0;
     bool aborted = false;
     float rs_ahead = 0.0f;
-    if constexpr (EARLY) {
+    if constexpr (REL != 0) {
         const long long row0 = first * g.rows_per_tile + grp;
         if (my_tiles > 0 && row0 < g.rows) rs_ahead = a.rstd[row0];
     }
@@ -243,7 +293,7 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
         const long long row = (first + k * stride) * g.rows_per_tile + grp;
         const bool valid = row < g.rows;
         float rs;
-        if constexpr (EARLY) {
+        if constexpr (REL != 0) {
             rs = rs_ahead;
             const long long nrow = row + stride * g.rows_per_tile;
             rs_ahead = (k + 1 < my_tiles && nrow < g.rows) ? a.rstd[nrow] : 0.0f;
@@ -294,7 +344,7 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
         __syncthreads();
         if (*s_abort) { aborted = true; break; }
         // all threads are past pass 2 of the previous tile: its slot can be refilled
-        if (!EARLY && tid == 0 && k >= 1 && issued < my_tiles) {
+        if (REL == 0 && tid == 0 && k >= 1 && issued < my_tiles) {
             issue(first + issued * stride, static_cast<int>((k - 1) % S));
             ++issued;
         }
@@ -343,24 +393,15 @@ __global__ void __launch_bounds__(MAXT, 1) rmsnorm_bwd_fast(const __grid_constan
                 }
             }
         }
-        if constexpr (EARLY) {
-            // this warp's shared-memory reads of the slot are complete (their values were consumed above)
-            __syncwarp();
-            if (lane == 0) {
-                __threadfence_block();
-                if (atomicAdd(&s_cnt[slot], 1) == nwarps - 1) {
-                    __threadfence_block();
-                    s_cnt[slot] = 0;   // nobody counts on this slot again before the refill below has been consumed
-                    if (k + S < my_tiles) issue(first + (k + S) * stride, slot);
-                }
-            }
-        }
+        if constexpr (REL != 0)
+            release_slot(s_abort, slot, nwarps, k, S, my_tiles, lane, [&](long long kk, int sl) { issue(first + kk * stride, sl); });
     }
     pdl_trigger();   // this CTA has no tiles left: the next kernel's CTAs may take the room it frees
     if (aborted) {
-        // early: every warp passed the barrier of tile k, so the refill after tile k-1 (tile k-1+S) was issued
-        if (EARLY) issued = k + S < my_tiles ? k + S : my_tiles;
-        if (tid == 0) drain_after_abort(g, s_full, k, issued);
+        if (tid == 0) {
+            if (REL != 0) drain_counted(g, s_full, s_abort);
+            else drain_after_abort(g, s_full, k, issued);
+        }
         return;
     }
 
