@@ -299,6 +299,7 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     off += 32;   // the abort flag, then one release counter per ring slot (at most four)
     g.pdl_early = opt_pdl.load() == 2;
     // (the 64-element backward only; "bwd_refill" 1 / 2 force late / early)
+    // (the 64-element backward; plan_bwd decides for the 32-element re-reading one; "bwd_refill" 1 / 2 force late / early)
     g.early_refill = fast == 3 && (opt_bwd_refill.load() == 2 || (opt_bwd_refill.load() == 0 && rpt == 1));
     p->smem = off;
     p->block = block;
@@ -337,7 +338,17 @@ void plan_bwd(int64_t rows, int64_t hidden, int elem, int narr, int ngamma, cons
         else if (want_keep == 2) *keep = pn.generic && !pk.generic;
         // (rows that one warp owns, hidden <= 1024: the register-keeping form measured 4-5 % ahead at 1000 columns)
         else *keep = !pk.generic && (pn.generic || pk.block * pk.ctas >= pn.block * pn.ctas || pk.g.group_threads == 32);
+        // The re-reading form with the early slot refill (instantiated for up to 640 resident threads, full tilings,
+        // gamma): measured settled, 65536 rows -- 5120 columns (two rows per tile) 557 against 575 us per step;
+        // 12288 and 10240 columns (one CTA per SM, one row per tile) 1367 / 1197 against 1382 / 1226 us with the
+        // register-keeping form, which it therefore replaces there; at 7168 columns (two CTAs) the register-keeping
+        // form stays ahead (803 against 824 us), and with three or more rows per tile the early refill loses.
+        const int64_t refill = opt_bwd_refill.load();
+        const bool early_ok = refill != 1 && ngamma == 1 && !pn.generic && pn.full && pn.g.rows_per_tile <= 2 &&
+                              pn.block * pn.ctas <= 640;
+        if (*keep && want_keep == 0 && early_ok && pn.ctas == 1 && pn.g.rows_per_tile == 1) *keep = false;
         *p = *keep ? pk : pn;
+        if (!*keep) p->g.early_refill = early_ok;
         return;
     }
     plan_launch(kBwd, rows, hidden, elem, narr, ngamma, d, p);
@@ -559,6 +570,10 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
             if (gamma && p.g.early_refill) AGB_LAUNCH_FAST_V(2 * kV, true, true, 384, false, 1);
             else if (gamma) AGB_LAUNCH_FAST_V(2 * kV, true, true, 384, false, 0);
             else AGB_LAUNCH_FAST_V(2 * kV, false, true, 384, false, 0);
+        } else if (!keep && gamma && p.full && p.g.early_refill && p.block * p.ctas <= 384) {
+            AGB_LAUNCH_FAST_V(kV, true, true, 384, false, 1);
+        } else if (!keep && gamma && p.full && p.g.early_refill && p.block * p.ctas <= 640) {
+            AGB_LAUNCH_FAST_V(kV, true, true, 640, false, 1);
         } else if (keep) AGB_FAST_BY_FLAGS(512, true);
         else AGB_FAST_BY_FLAGS(768, false);
 #undef AGB_LAUNCH_FAST_V

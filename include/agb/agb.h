@@ -81,8 +81,8 @@ int agb_selftest_bounded_wait(int poll_limit, int* polls_done, agb_stream_t stre
  *     strict backward), "rows_per_warp" (strict backward, one-warp rows), "bwd_keep" (16-bit backward:
  *     1 keep x/gy in registers, 2 re-read the tile, 3 64 elements per thread), "lone_ring" (2: a single
  *     CTA per SM may run a two-slot ring), "reserve_sms" (SMs the persistent grids leave free),
- *     "bwd_refill" (64-element 16-bit backward: 1 thread 0 refills a ring slot after the mid-tile barrier,
- *     2 the last warp out of the slot does), "softmax_two_pass" (approximate softmax / logsumexp forward:
+ *     "bwd_refill" (16-bit backward: 1 thread 0 refills a ring slot after the mid-tile barrier, 2 the
+ *     last warp out of the slot does wherever that form is built), "softmax_two_pass" (approximate softmax / logsumexp forward:
  *     1 maximum first, then exp; 2 always the one-pass kernel), "free_rows" (1: the 16-bit forward keeps a
  *     block-wide barrier per tile also for rows that one warp owns), "force_generic" (1: the unstaged kernels);
  *   "bf16_strict"  1: 16-bit I/O through the strictly rounded, fp64-reducing kernels (the fp32 path's
