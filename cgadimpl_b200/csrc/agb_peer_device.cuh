@@ -192,12 +192,14 @@ __global__ void __launch_bounds__(512) dgamma_reduce_publish_kernel(const double
         total[cx] = t;
     }
     __syncthreads();
-    if (!expired && py < h.n && c < hidden) {
+    if (!expired && py < h.n && c < hidden)
         reinterpret_cast<double*>(h.blk.base[py] + peer_sums_offset(h.self, h.b, h.max_hidden))[c] = total[cx];
-        __threadfence_system();
-    }
     __syncthreads();
     if (cx == 0 && py == 0) {
+        // ONE system-scope fence per CTA, after the barrier: it is cumulative over the stores the barrier has
+        // ordered before it (the CTA's 16 columns in every rank's block), so the count below, and the flags the
+        // last CTA writes after its own fence, cannot overtake them.
+        __threadfence_system();
         unsigned int* counter = reinterpret_cast<unsigned int*>(own + kPeerCounterOffset);
         unsigned int* expired_ctas = reinterpret_cast<unsigned int*>(own + kPeerTimeoutsOffset);
         if (expired) {
