@@ -337,6 +337,9 @@ def run_op(args, rank):
 
     from cgadimpl_b200 import ops
 
+    for kv in args.option:
+        k, v = kv.split("=")
+        ops.set_option(k, int(v))
     op, rows, hidden, dtype_name = OP_WORKLOADS[args.workload]
     dtype = getattr(torch, dtype_name)
     elem = 4 if dtype == torch.float32 else 2

@@ -216,7 +216,11 @@ void plan_launch(Which which, int64_t rows, int64_t hidden, int elem, int narr, 
     // 256-thread ones on every fp32 shape measured (6.1-6.2 against 5.25 TB/s at 32768 x 4096, 5.7 against
     // 5.1 at hidden 1024); in bf16, where the kernel is bound by instruction issue, four stay ahead.
     const bool ln_fwd32 = heavy && which == kFwd && narr == 1 && elem == 4;
-    const int c_hi = want_ctas ? want_ctas : (fused_fwd || light16 ? 1 : (ln_fwd32 ? 2 : 4));
+    // The fp32-accumulating 16-bit LayerNorm forward takes two CTAs per SM as well (65536 rows of bf16, two / four
+    // / one CTA: 8192 columns 6.17 / 5.60 / 6.27 TB/s, 4096: 5.94 / 5.76 / 5.61, 5120: 5.93 / 5.68 / 5.58, 12288:
+    // 6.31 / no ring / 5.64, 2048: 5.84 / 5.22 / 5.55; only at 1000 columns four stay ahead, 4.70 against 4.55).
+    const bool ln_fwd16 = heavy && which == kFwd && narr == 1 && elem == 2 && !opt_bf16_strict.load();
+    const int c_hi = want_ctas ? want_ctas : (fused_fwd || light16 ? 1 : (ln_fwd32 || ln_fwd16 ? 2 : 4));
     int rpt = 0, ctas = 0, S = 0, best = 0;
     const int lone_ring = opt_lone_ring.load() == 2 ? 2 : 3;
     for (int c = (want_ctas ? want_ctas : 1); c <= c_hi; ++c)
