@@ -660,6 +660,11 @@ int launch_jvp(const void* x, const void* gamma, const float* rstd, const void* 
         return after_launch("rmsnorm_jvp_generic");
     }
     agb::JvpArgs a{p.g, x, tx, gamma, tgamma, rstd, ty, hf};
+    if constexpr (sizeof(T) == 2) if (!opt_bf16_strict.load()) {   // 16-bit I/O: fp32 accumulation
+        AGB_TRY(set_smem(agb::rmsnorm_jvp_staged<T, true>, p.smem));
+        agb::rmsnorm_jvp_staged<T, true><<<p.grid, p.block, p.smem, st>>>(a);
+        return after_launch("rmsnorm_jvp_staged");
+    }
     AGB_TRY(set_smem(agb::rmsnorm_jvp_staged<T>, p.smem));
     agb::rmsnorm_jvp_staged<T><<<p.grid, p.block, p.smem, st>>>(a);
     return after_launch("rmsnorm_jvp_staged");

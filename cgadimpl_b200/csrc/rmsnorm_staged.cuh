@@ -678,7 +678,9 @@ struct JvpArgs {
     float hidden_f;
 };
 
-template <typename T>
+// FAST (16-bit I/O): fp32 sums and fused multiply-adds, ty = (rstd*t + x*k)*gamma [+ x*rstd*tgamma] with
+// k = -rstd^3 * sum(t*x) / H per row -- the same algebra as the fp32-accumulating backward (rmsnorm_fast.cuh).
+template <typename T, bool FAST = false>
 __global__ void __launch_bounds__(1024, 1) rmsnorm_jvp_staged(const __grid_constant__ JvpArgs a) {
     constexpr int NP = Pairs<T>::NP;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -729,6 +731,7 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_jvp_staged(const __grid_const
         const uint4* st = reinterpret_cast<const uint4*>(base + g.tile_stride);
 
         double d0 = 0.0, d1 = 0.0;
+        float2 f0 = make_float2(0.f, 0.f), f1 = make_float2(0.f, 0.f);
         if (valid) {
 #pragma unroll 2
             for (int v = tig; v < g.nvec; v += G) {
@@ -737,13 +740,19 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_jvp_staged(const __grid_const
                 Pairs<T>::unpack(st[v], tv);
 #pragma unroll
                 for (int e = 0; e < NP; ++e) {
-                    const float2 p = mul2(tv[e], mul2(xv[e], rs2));
-                    d0 += static_cast<double>(p.x);
-                    d1 += static_cast<double>(p.y);
+                    if constexpr (FAST) {
+                        if (e & 1) f1 = __ffma2_rn(tv[e], xv[e], f1);
+                        else f0 = __ffma2_rn(tv[e], xv[e], f0);
+                    } else {
+                        const float2 p = mul2(tv[e], mul2(xv[e], rs2));
+                        d0 += static_cast<double>(p.x);
+                        d1 += static_cast<double>(p.y);
+                    }
                 }
             }
         }
-        const double dsum = warp_sum(d0 + d1);
+        // (FAST: the per-lane fp32 sums, widened only for the shared reduction path; rstd is applied after the sum)
+        const double dsum = FAST ? warp_sum(static_cast<double>((f0.x + f0.y) + (f1.x + f1.y))) : warp_sum(d0 + d1);
         if (lane == 0) s_red[(k & 1) * nwarps + warp] = dsum;
         __syncthreads();
         if (*s_abort) { aborted = true; break; }
@@ -753,6 +762,7 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_jvp_staged(const __grid_const
         }
         const float dot = static_cast<float>(wpr == 1 ? dsum : group_total(s_red + (k & 1) * nwarps + grp * wpr, wpr, lane));
         const float2 dot2 = splat(dot), c2 = splat(__fdiv_rn(rs, a.hidden_f));
+        const float2 k2 = splat(-(rs * rs) * (rs * dot) / a.hidden_f);   // FAST (dot = sum(t*x) there)
 
         if (valid) {
             uint4* gout = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.ty) + row * g.row_bytes);
@@ -765,14 +775,23 @@ __global__ void __launch_bounds__(1024, 1) rmsnorm_jvp_staged(const __grid_const
                 if (has_tgamma) load_gamma<T>(s_tgamma, g.nvec, v, twv);
 #pragma unroll
                 for (int e = 0; e < NP; ++e) {
-                    const float2 yh = mul2(xv[e], rs2);
-                    const float2 q = mul2(tv[e], rs2);
-                    float2 p = mul2(yh, dot2);
-                    p = mul2(p, c2);
-                    float2 o = sub2_after_mul(q, p);
-                    if (has_gamma) {
-                        o = mul2(o, wv[e]);
-                        if (has_tgamma) o = add2_after_mul(o, mul2(yh, twv[e]));
+                    float2 o;
+                    if constexpr (FAST) {
+                        o = __ffma2_rn(tv[e], rs2, mul2(xv[e], k2));
+                        if (has_gamma) {
+                            o = mul2(o, wv[e]);
+                            if (has_tgamma) o = __ffma2_rn(mul2(xv[e], rs2), twv[e], o);
+                        }
+                    } else {
+                        const float2 yh = mul2(xv[e], rs2);
+                        const float2 q = mul2(tv[e], rs2);
+                        float2 p = mul2(yh, dot2);
+                        p = mul2(p, c2);
+                        o = sub2_after_mul(q, p);
+                        if (has_gamma) {
+                            o = mul2(o, wv[e]);
+                            if (has_tgamma) o = add2_after_mul(o, mul2(yh, twv[e]));
+                        }
                     }
                     xv[e] = o;
                 }

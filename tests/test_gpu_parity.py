@@ -409,8 +409,21 @@ def test_fused_add_forward_backward_and_stack(ops):
 
 
 @pytest.mark.parametrize("rows,hidden,dtype", [(64, 1024, torch.float32), (33, 1000, torch.float32),
-                                               (5, 10, torch.float32), (48, 8192, torch.bfloat16)])
-def test_jvp_corrected_form(ops, rows, hidden, dtype):
+                                               (5, 10, torch.float32), (48, 8192, torch.bfloat16),
+                                               (129, 1000, torch.bfloat16), (300, 5120, torch.bfloat16)])
+@pytest.mark.parametrize("strict", [False, True])
+def test_jvp_corrected_form(ops, rows, hidden, dtype, strict):
+    """strict ("bf16_strict"): 16-bit I/O through the strictly rounded kernel; default: fp32 accumulation."""
+    if strict and dtype == torch.float32:
+        pytest.skip("fp32 I/O has one arithmetic")
+    ops.set_option("bf16_strict", int(strict))
+    try:
+        _jvp_corrected_form(ops, rows, hidden, dtype)
+    finally:
+        ops.set_option("bf16_strict", 0)
+
+
+def _jvp_corrected_form(ops, rows, hidden, dtype):
     eps = 1e-5
     x, gamma, gy = make_inputs(rows, hidden, seed=4)
     rng = np.random.default_rng(8)
@@ -436,6 +449,13 @@ def test_jvp_corrected_form(ops, rows, hidden, dtype):
         assert_close(host(ty_plain), O.rmsnorm_jvp(x, None, tx, None, eps), F32_RTOL, F32_ATOL, "jvp plain")
     else:
         assert_close(host(ty), O.bf16_bits_to_f32(O.f32_to_bf16_bits(ref)), BF16_RTOL, F32_ATOL, "jvp bf16")
+        # adjoint identity with the bf16 VJP, to what 16-bit outputs allow
+        ty0 = ops.rmsnorm_jvp(xd, gd, rstd, txd, None)
+        dx, _ = ops.rmsnorm_bwd(xd, gd, rstd, dev(gy, dtype))
+        lhs = float((dev(gy, dtype).double() * ty0.double()).sum())
+        rhs = float((dx.double() * txd.double()).sum())
+        scale = float((dev(gy, dtype).double().abs() * ty0.double().abs()).sum())
+        assert abs(lhs - rhs) <= 2e-3 * scale
 
 
 def test_elementwise_and_reductions(ops):
