@@ -683,6 +683,11 @@ int launch_ln_jvp(const void* y, const void* t, const float* var, void* ty, int6
         return after_launch("layernorm_jvp_generic");
     }
     agb::LnJvpArgs a{p.g, y, t, var, ty, eps};
+    if constexpr (sizeof(T) == 2) if (!opt_bf16_strict.load()) {   // 16-bit I/O: fp32 accumulation
+        AGB_TRY(set_smem(agb::layernorm_jvp_staged<T, true>, p.smem));
+        agb::layernorm_jvp_staged<T, true><<<p.grid, p.block, p.smem, st>>>(a);
+        return after_launch("layernorm_jvp_staged");
+    }
     AGB_TRY(set_smem(agb::layernorm_jvp_staged<T>, p.smem));
     agb::layernorm_jvp_staged<T><<<p.grid, p.block, p.smem, st>>>(a);
     return after_launch("layernorm_jvp_staged");

@@ -426,7 +426,9 @@ __device__ __forceinline__ void ln_jvp_stats(double st, double sy, double syt, i
     *d = static_cast<float>((syt - tm * sy) / static_cast<double>(hidden));
 }
 
-template <typename T>
+// FAST (16-bit I/O): the three row sums in fp32, ty = std_inv*t - std_inv*mean(t) - y*(std_inv*d) as two fused
+// multiply-adds per pair.
+template <typename T, bool FAST = false>
 __global__ void __launch_bounds__(1024, 1) layernorm_jvp_staged(const __grid_constant__ LnJvpArgs a) {
     constexpr int NP = Pairs<T>::NP;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -471,6 +473,7 @@ __global__ void __launch_bounds__(1024, 1) layernorm_jvp_staged(const __grid_con
         const uint4* st = reinterpret_cast<const uint4*>(base + g.tile_stride);
 
         double at = 0.0, ay = 0.0, ayt0 = 0.0, ayt1 = 0.0;
+        float2 ft = make_float2(0.f, 0.f), fy = make_float2(0.f, 0.f), fyt = make_float2(0.f, 0.f);
         if (valid) {
 #pragma unroll 2
             for (int v = tig; v < g.nvec; v += G) {
@@ -479,13 +482,24 @@ __global__ void __launch_bounds__(1024, 1) layernorm_jvp_staged(const __grid_con
                 Pairs<T>::unpack(st[v], tv);
 #pragma unroll
                 for (int e = 0; e < NP; ++e) {
-                    const float2 p = mul2(yv[e], tv[e]);
-                    at += static_cast<double>(tv[e].x) + static_cast<double>(tv[e].y);
-                    ay += static_cast<double>(yv[e].x) + static_cast<double>(yv[e].y);
-                    ayt0 += static_cast<double>(p.x);
-                    ayt1 += static_cast<double>(p.y);
+                    if constexpr (FAST) {
+                        ft = add2(ft, tv[e]);
+                        fy = add2(fy, yv[e]);
+                        fyt = __ffma2_rn(yv[e], tv[e], fyt);
+                    } else {
+                        const float2 p = mul2(yv[e], tv[e]);
+                        at += static_cast<double>(tv[e].x) + static_cast<double>(tv[e].y);
+                        ay += static_cast<double>(yv[e].x) + static_cast<double>(yv[e].y);
+                        ayt0 += static_cast<double>(p.x);
+                        ayt1 += static_cast<double>(p.y);
+                    }
                 }
             }
+        }
+        if constexpr (FAST) {   // the per-lane fp32 sums join the shared fp64 reduction path
+            at = static_cast<double>(ft.x + ft.y);
+            ay = static_cast<double>(fy.x + fy.y);
+            ayt0 = static_cast<double>(fyt.x + fyt.y);
         }
         double* red = s_red + (k & 1) * 3 * nwarps;
         const double wt = warp_sum(at), wy = warp_sum(ay), wyt = warp_sum(ayt0 + ayt1);
@@ -505,6 +519,7 @@ __global__ void __launch_bounds__(1024, 1) layernorm_jvp_staged(const __grid_con
                      group_total(red + 2 * nwarps + grp * wpr, wpr, lane), g.hidden, &tmean, &d);
         const float std_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, a.eps)));
         const float2 tm2 = splat(tmean), d2 = splat(d), si2 = splat(std_inv);
+        const float2 c02 = splat(-std_inv * tmean), nsd2 = splat(-std_inv * d);   // FAST
 
         if (valid) {
             uint4* gout = reinterpret_cast<uint4*>(static_cast<unsigned char*>(a.ty) + row * g.row_bytes);
@@ -515,8 +530,12 @@ __global__ void __launch_bounds__(1024, 1) layernorm_jvp_staged(const __grid_con
                 Pairs<T>::unpack(st[v], tv);
 #pragma unroll
                 for (int e = 0; e < NP; ++e) {
-                    const float2 tc = sub2(tv[e], tm2);                  // neither operand is a product
-                    yv[e] = mul2(si2, sub2_after_mul(tc, mul2(yv[e], d2)));
+                    if constexpr (FAST) {
+                        yv[e] = __ffma2_rn(yv[e], nsd2, __ffma2_rn(tv[e], si2, c02));
+                    } else {
+                        const float2 tc = sub2(tv[e], tm2);                  // neither operand is a product
+                        yv[e] = mul2(si2, sub2_after_mul(tc, mul2(yv[e], d2)));
+                    }
                 }
                 store_vec_streaming(gout + v, Pairs<T>::pack(yv));
             }

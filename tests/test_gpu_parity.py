@@ -626,6 +626,18 @@ def test_layernorm_forward_and_vjp(ops, rows, hidden, dtype):
         ty = ops.layernorm_jvp(y, dev(t, dtype), var, eps)
         want = O.layernorm_jvp(host(y), t, host(var), eps)
         assert_close(host(ty), O.bf16_bits_to_f32(O.f32_to_bf16_bits(want)), BF16_RTOL, 1e-2, "ty bf16")
+        # the strictly rounded 16-bit kernels ("bf16_strict") against the same references
+        ops.set_option("bf16_strict", 1)
+        try:
+            ys, means, vars_ = ops.layernorm_fwd(xd, eps)
+            dxs = ops.layernorm_bwd(xd, means, vars_, gyd, eps)
+            tys = ops.layernorm_jvp(ys, dev(t, dtype), vars_, eps)
+        finally:
+            ops.set_option("bf16_strict", 0)
+        assert_close(host(ys), O.bf16_bits_to_f32(O.f32_to_bf16_bits(ref["y"])), BF16_RTOL, 1e-6, "y bf16 strict")
+        assert_close(host(dxs), O.bf16_bits_to_f32(O.f32_to_bf16_bits(ref["dx"])), BF16_RTOL, 1e-2, "dx bf16 strict")
+        want_s = O.layernorm_jvp(host(ys), t, host(vars_), eps)
+        assert_close(host(tys), O.bf16_bits_to_f32(O.f32_to_bf16_bits(want_s)), BF16_RTOL, 1e-2, "ty bf16 strict")
 
 
 def test_bounded_wait_expiry_is_reported_and_the_context_survives(ops):
