@@ -1468,6 +1468,23 @@ int agb_row_reduce(int op, const void* x, void* out, int64_t rows, int64_t hidde
     int64_t g = (rows + rpc - 1) / rpc;
     const int64_t cap = static_cast<int64_t>(d->sms) * 8;
     const int grid = static_cast<int>(g < cap ? g : cap);
+    // rows of whole 16-byte vectors at an aligned base: the vector-load kernels
+    if (aligned16(x) && (hidden * elem) % 16 == 0 && !opt_force_generic.load()) {
+#define AGB_ROW_REDUCE_VEC(T, TPR)                                                                                       \
+    do {                                                                                                                 \
+        if (op == AGB_REDUCE_MAX) agb::row_reduce_vec_kernel<T, TPR, true><<<grid, 256, 0, st>>>((const T*)x, (T*)out, rows, (int)hidden, op); \
+        else agb::row_reduce_vec_kernel<T, TPR, false><<<grid, 256, 0, st>>>((const T*)x, (T*)out, rows, (int)hidden, op); \
+    } while (0)
+        if (dtype == AGB_F32) {
+            if (wide) AGB_ROW_REDUCE_VEC(float, 256);
+            else AGB_ROW_REDUCE_VEC(float, 32);
+        } else {
+            if (wide) AGB_ROW_REDUCE_VEC(bf16, 256);
+            else AGB_ROW_REDUCE_VEC(bf16, 32);
+        }
+#undef AGB_ROW_REDUCE_VEC
+        return after_launch("row_reduce_vec");
+    }
     if (dtype == AGB_F32) {
         if (wide) agb::row_reduce_kernel<float, 256><<<grid, 256, 0, st>>>((const float*)x, (float*)out, rows, (int)hidden, op);
         else agb::row_reduce_kernel<float, 32><<<grid, 256, 0, st>>>((const float*)x, (float*)out, rows, (int)hidden, op);
@@ -1483,7 +1500,7 @@ static inline void reduce_all_shape(int64_t n, int* nblocks, int64_t* chunk) {
     int64_t nb = (n + 16383) / 16384;
     if (nb > 1024) nb = 1024;
     if (nb < 1) nb = 1;
-    *chunk = (n + nb - 1) / nb;
+    *chunk = ((n + nb - 1) / nb + 7) / 8 * 8;   // whole 16-byte vectors per block, for either element size
     *nblocks = static_cast<int>((n + *chunk - 1) / *chunk);
     if (*nblocks < 1) *nblocks = 1;
 }

@@ -130,6 +130,69 @@ __global__ void __launch_bounds__(256) row_reduce_kernel(const T* __restrict__ x
     }
 }
 
+// The same for rows that are whole 16-byte vectors at a 16-byte aligned base: one 16-byte load per thread and
+// step, only the asked-for reduction is computed (MAXOP), and 16-bit values are pre-added in fp32 eight at a time
+// (bf16 has 8 significant bits: such a partial sum is exact unless the eight span more than 2^13 in magnitude)
+// before the fp64 accumulation, so the conversion and the fp64 addition are paid once per vector.
+template <typename T, int TPR, bool MAXOP>
+__global__ void __launch_bounds__(256) row_reduce_vec_kernel(const T* __restrict__ x, T* __restrict__ out, long long rows,
+                                                             int hidden, int op) {
+    __shared__ double s_sum[2][8];
+    __shared__ float s_max[2][8];
+    constexpr int RPC = 256 / TPR;
+    constexpr int EPV = Vec<T>::EPV;
+    const int nvec = hidden / EPV;
+    const int grp = threadIdx.x / TPR, tig = threadIdx.x % TPR;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int phase = 0;
+    for (long long row0 = static_cast<long long>(blockIdx.x) * RPC; row0 < rows;
+         row0 += static_cast<long long>(gridDim.x) * RPC, phase ^= 1) {
+        const long long row = row0 + grp;
+        double s0 = 0.0, s1 = 0.0;
+        float m = -INFINITY;
+        if (row < rows) {
+            const uint4* xr = reinterpret_cast<const uint4*>(x + row * hidden);
+#pragma unroll 4
+            for (int v = tig; v < nvec; v += TPR) {
+                float f[EPV];
+                Vec<T>::unpack(__ldg(xr + v), f);
+                if constexpr (MAXOP) {
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) m = fmaxf(m, f[e]);
+                } else if constexpr (sizeof(T) == 2) {
+                    s0 += static_cast<double>(((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7])));
+                } else {
+                    s0 += static_cast<double>(f[0]) + static_cast<double>(f[1]);
+                    s1 += static_cast<double>(f[2]) + static_cast<double>(f[3]);
+                }
+            }
+        }
+        double s = MAXOP ? 0.0 : warp_sum(s0 + s1);
+        if (MAXOP) m = warp_max(m);
+        if (TPR > 32) {
+            if (lane == 0) {
+                s_sum[phase][warp] = s;
+                s_max[phase][warp] = m;
+            }
+            __syncthreads();
+            s = 0.0;
+            m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {
+                s += s_sum[phase][w];
+                m = fmaxf(m, s_max[phase][w]);
+            }
+        }
+        if (row < rows && tig == 0) {
+            float r;
+            if (MAXOP) r = m;
+            else if (op == 1) r = static_cast<float>(s / static_cast<double>(hidden));
+            else r = static_cast<float>(s);
+            Vec<T>::store1(out + row, r);
+        }
+    }
+}
+
 // Global sum, stage 1: block b reduces elements [b*chunk, (b+1)*chunk) to partial[b].
 template <typename T>
 __global__ void __launch_bounds__(256) reduce_all_stage1(const T* __restrict__ x, double* __restrict__ partial,
@@ -139,7 +202,28 @@ __global__ void __launch_bounds__(256) reduce_all_stage1(const T* __restrict__ x
     long long i1 = i0 + chunk;
     if (i1 > n) i1 = n;
     double v = 0.0;
-    for (long long i = i0 + threadIdx.x; i < i1; i += 256) v += static_cast<double>(Vec<T>::load1(x + i));
+    constexpr int EPV = Vec<T>::EPV;
+    if ((reinterpret_cast<uintptr_t>(x) & 15u) == 0 && chunk % EPV == 0) {
+        // whole 16-byte vectors (every chunk starts on one): vector loads, 16-bit values pre-added in fp32 per vector
+        const long long nv = (i1 - i0) / EPV;
+        const uint4* xv = reinterpret_cast<const uint4*>(x + i0);
+        double v1 = 0.0;
+#pragma unroll 4
+        for (long long q = threadIdx.x; q < nv; q += 256) {
+            float f[EPV];
+            Vec<T>::unpack(__ldg(xv + q), f);
+            if constexpr (sizeof(T) == 2) {
+                v += static_cast<double>(((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7])));
+            } else {
+                v += static_cast<double>(f[0]) + static_cast<double>(f[1]);
+                v1 += static_cast<double>(f[2]) + static_cast<double>(f[3]);
+            }
+        }
+        v += v1;
+        for (long long i = i0 + nv * EPV + threadIdx.x; i < i1; i += 256) v += static_cast<double>(Vec<T>::load1(x + i));
+    } else {
+        for (long long i = i0 + threadIdx.x; i < i1; i += 256) v += static_cast<double>(Vec<T>::load1(x + i));
+    }
     v = warp_sum(v);
     if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
     __syncthreads();

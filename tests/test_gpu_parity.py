@@ -484,6 +484,26 @@ def test_elementwise_and_reductions(ops):
         assert np.array_equal(host(ops.row_reduce(xd, "max"))[:, 0], O.rowmax(x))
         assert abs(float(ops.reduce_all(xd, "sum")) - O.total_sum(x)) <= 1e-6 * max(1.0, abs(O.total_sum(x)))
         assert abs(float(ops.reduce_all(xd, "mean")) - O.mean_all(x)) <= 1e-6
+    # 16-bit rows (vector loads, values pre-added in fp32 eight at a time) and rows that are not whole vectors
+    for rows, hidden in ((37, 1000), (16, 8192), (9, 1001), (300, 512)):
+        x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(rng.standard_normal((rows, hidden)).astype(np.float32)))
+        xd = dev(x, torch.bfloat16)
+        rb = lambda a: O.bf16_bits_to_f32(O.f32_to_bf16_bits(np.asarray(a, dtype=np.float32)))
+        assert_close(host(ops.row_reduce(xd, "sum"))[:, 0], rb(O.rowsum(x)), 8e-3, 1e-6, "rowsum bf16")
+        assert_close(host(ops.row_reduce(xd, "mean"))[:, 0], rb(O.rowmean(x)), 8e-3, 1e-6, "rowmean bf16")
+        assert np.array_equal(host(ops.row_reduce(xd, "max"))[:, 0], O.rowmax(x))
+        assert abs(float(ops.reduce_all(xd, "sum")) - O.total_sum(x)) <= 8e-3 * max(1.0, abs(O.total_sum(x)))
+    # the unstaged kernels agree with the vector-load ones
+    x = rng.standard_normal((33, 4096)).astype(np.float32)
+    xd = dev(x)
+    want = [host(ops.row_reduce(xd, k)) for k in ("sum", "mean", "max")]
+    ops.set_option("force_generic", 1)
+    try:
+        got = [host(ops.row_reduce(xd, k)) for k in ("sum", "mean", "max")]
+    finally:
+        ops.set_option("force_generic", 0)
+    for a, b in zip(want, got):
+        assert np.array_equal(a, b)
     big = rng.standard_normal(3_000_001).astype(np.float32)
     s1, s2 = ops.reduce_all(dev(big), "sum"), ops.reduce_all(dev(big), "sum")
     assert torch.equal(s1, s2)
