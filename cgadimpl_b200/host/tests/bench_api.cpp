@@ -71,6 +71,30 @@ int main(int argc, char** argv) {
         cudaEventElapsedTime(&ms_eager, e0, e1);
         cudaEventElapsedTime(&ms_eager_head, e0, em);
 
+        // The reference's own composition of the same layer -- ag::rms (no gamma, its hard-coded eps) followed by
+        // ag::mul with the [H] gamma, differentiated by vjp_Mul (incl. the reduction over the broadcast rows) and
+        // vjp_RMSNorm -- on this library's kernels, for comparison with the fused node (fp32 only: like the
+        // fused node, a 16-bit gamma takes no gradient through the graph API).
+        float ms_composed = 0;
+        uint64_t launches_composed = 0;
+        const int citers = iters < 200 ? iters : 200;
+        if (!bf16) {
+            auto cstep = [&] {
+                Value y = mul(rms(x), gamma);
+                zero_grad(y);
+                backward(y, &gy);
+            };
+            for (int i = 0; i < warmup; ++i) cstep();
+            cudaDeviceSynchronize();
+            const uint64_t c0 = agb_launch_count();
+            cudaEventRecord(e0, nullptr);
+            for (int i = 0; i < citers; ++i) cstep();
+            cudaEventRecord(e1, nullptr);
+            cudaDeviceSynchronize();
+            launches_composed = agb_launch_count() - c0;
+            cudaEventElapsedTime(&ms_composed, e0, e1);
+        }
+
         // captured: warm the allocator pool of the runner's stream, then record one step and replay it
         CudaGraphRunner runner;
         set_current_stream(reinterpret_cast<ag_cuda_stream_t>(runner.get_stream()));
@@ -104,10 +128,12 @@ int main(int argc, char** argv) {
         const int status = agb_device_status();
         std::printf("{\"rows\": %lld, \"hidden\": %lld, \"io_dtype\": \"%s\", \"iters\": %d, \"warmup\": %d, "
                     "\"eager_ms_per_step\": %.6f, \"eager_first_steps_ms\": %.6f, \"eager_gbs\": %.2f, \"graph_ms_per_step\": %.6f, \"graph_gbs\": %.2f, "
-                    "\"graph_nodes\": %zu, \"launches_per_step\": %.2f, \"device_status\": %d}\n",
+                    "\"graph_nodes\": %zu, \"launches_per_step\": %.2f, \"composed_ms_per_step\": %.6f, "
+                    "\"composed_launches_per_step\": %.2f, \"device_status\": %d}\n",
                     (long long)R, (long long)H, bf16 ? "bfloat16" : "float32", iters, warmup, pe, ms_eager_head / head,
                     bytes / (pe * 1e-3) / 1e9, pg,
-                    bytes / (pg * 1e-3) / 1e9, runner.num_nodes(), double(launches_eager) / iters, status);
+                    bytes / (pg * 1e-3) / 1e9, runner.num_nodes(), double(launches_eager) / iters, ms_composed / citers,
+                    double(launches_composed) / citers, status);
         return status == 0 ? 0 : 1;
     } catch (const std::exception& e) {
         std::fprintf(stderr, "bench_api: %s\n", e.what());
