@@ -6,9 +6,9 @@
 // different arithmetic: every sum is carried in fp32 (packed two-lane FMA chains, fp32 warp
 // shuffles), multiply-adds are fused, and no value passes through fp64 until the per-CTA dgamma
 // partial row is written.  That is what "bf16 I/O with fp32 accumulation" asks for, and it is what
-// makes these kernels bandwidth-bound: the strictly rounded kernels spend two fp32->fp64
-// conversions and two fp64 additions per element (the conversion unit alone is 40 % busy), these
-// spend about 7 fp32 instructions per element.
+// takes these kernels from 0.6-0.8 to 0.9-1.0 of the copy bandwidth: the strictly rounded backward
+// spends two fp32->fp64 conversions and two fp64 additions per element (23 instructions per element,
+// the conversion unit alone 40 % busy), this one 13, the forward 11, with no fp64 at all.
 //
 // Results differ from the strictly rounded kernels in the last bits of fp32 intermediates (fused
 // multiply-adds, fp32 sums); outputs are rounded to the 16-bit type once.  The fp32 kernels of
