@@ -4,8 +4,9 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 A "step" is one forward + VJP pass over the workload's rows: rmsnorm_fwd, rmsnorm_bwd (dx fused
-with the dgamma partials), the fixed-order dgamma reduction and, for N > 1, the all-reduce of the
-fp64 dgamma sums.  N > 1 is launched by torchrun, one rank per GPU.
+with the dgamma partials), the fixed-order dgamma reduction and, for N > 1, the exchange of the
+fp64 dgamma sums between the ranks (the library's push exchange over peer memory by default, an
+NCCL all-reduce with --exchange collective).  N > 1 is launched by torchrun, one rank per GPU.
 
 Workload (default): the row-sharded configuration -- x [64,8192,8192] bf16 ~ N(0,1) (524288 rows),
 gamma = 1 + 0.02 N(0,1), gy ~ N(0,1), eps 1e-6, synthetic, seeded; the rows are split evenly over the
@@ -16,7 +17,9 @@ Timing: after W warm-up steps the K-step block is timed with CUDA events, bracke
 device synchronize on both sides, max over ranks; the block is repeated until about one second has been
 timed and the MEDIAN block is reported (every block's time is in `timing.block_ms`).
 
-At N = 1 the line also carries the other single-GPU configurations (`other_configs`).
+At N = 1 the line also carries the other single-GPU configurations (`other_configs`) and the same step
+through the C++ graph API (`api_path`); at N > 1 every rank's own pace with the exchange switched off
+(`no_exchange`: one short block before the timed region, and as many blocks as it had right after it).
 
 Prints ONE JSON line on rank 0.
 """
