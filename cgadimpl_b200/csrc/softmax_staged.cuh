@@ -104,6 +104,12 @@ __device__ __forceinline__ float exp_approx_nonpositive(float x) {
     return x < -86.0f ? 0.0f : y;
 }
 
+__device__ __forceinline__ float ex2_approx(float u) {
+    float p;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(u));
+    return p;
+}
+
 // e = exp(x - mx) for 16-bit I/O: one multiply-add and the hardware 2^u approximation, with nmx2 = -mx*log2(e)
 // computed once per row.  The argument's rounding (2^-24 of |x - mx| <= 126) bounds the relative error by
 // ~3e-6, three orders below the 16-bit output's own rounding; results under the normal range flush to zero.
@@ -522,15 +528,31 @@ __global__ void __launch_bounds__(1024, 1) softmax_fwd_online(const __grid_const
         const float ms = m == -INFINITY ? 0.0f : m;    // the shift this thread uses (a thread of -inf shifts by 0: e = 0)
         const float nms2 = -ms * kLog2e;
         float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        if constexpr (sizeof(T) == 2) {
+            // 16-bit I/O: the exponent's multiply-add and the sums as packed two-lane instructions (the two values
+            // of a 32-bit input word sit in neighbouring registers anyway); only the 2^u itself is per element
+            const float2 l2 = make_float2(kLog2e, kLog2e), n2 = make_float2(nms2, nms2);
+            float2 p0 = make_float2(0.f, 0.f), p1 = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int i = 0; i < KV * EPV; i += 4) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if constexpr (sizeof(T) == 2) f[i + e] = exp_rel16(f[i + e], nms2);
-                else if constexpr (MODE == 1) f[i + e] = exp_for_sum(f[i + e] - ms);
-                else f[i + e] = exp_approx_nonpositive(f[i + e] - ms);
+            for (int i = 0; i < KV * EPV; i += 4) {
+                const float2 u0 = __ffma2_rn(make_float2(f[i], f[i + 1]), l2, n2);
+                const float2 u1 = __ffma2_rn(make_float2(f[i + 2], f[i + 3]), l2, n2);
+                f[i] = ex2_approx(u0.x); f[i + 1] = ex2_approx(u0.y);
+                f[i + 2] = ex2_approx(u1.x); f[i + 3] = ex2_approx(u1.y);
+                p0 = __fadd2_rn(p0, make_float2(f[i], f[i + 1]));
+                p1 = __fadd2_rn(p1, make_float2(f[i + 2], f[i + 3]));
             }
-            a0 += f[i]; a1 += f[i + 1]; a2 += f[i + 2]; a3 += f[i + 3];
+            a0 = p0.x; a1 = p0.y; a2 = p1.x; a3 = p1.y;
+        } else {
+#pragma unroll
+            for (int i = 0; i < KV * EPV; i += 4) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if constexpr (MODE == 1) f[i + e] = exp_for_sum(f[i + e] - ms);
+                    else f[i + e] = exp_approx_nonpositive(f[i + e] - ms);
+                }
+                a0 += f[i]; a1 += f[i + 1]; a2 += f[i + 2]; a3 += f[i + 3];
+            }
         }
         const float st = (a0 + a1) + (a2 + a3);
         // merge inside the warp
