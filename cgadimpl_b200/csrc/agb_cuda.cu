@@ -332,11 +332,11 @@ void plan_bwd(int64_t rows, int64_t hidden, int elem, int narr, int ngamma, cons
         // 64 elements per thread halve the fixed cost per row and thread (barrier, two reductions): measured
         // +10 % at 4096 columns, +2 % at 8192, but -8 % at 12288, where a row group of 192 threads is all an SM
         // can hold.  Taken when every thread's vectors exist, a row is at most 16 KB and 256 threads stay resident.
-        if (want_keep == 3 || want_keep == 0) {
+        if (want_keep == 3 || want_keep == 0 || want_keep == 4) {
             Plan pw;
             plan_launch(kBwd, rows, hidden, elem, narr, ngamma, d, &pw, 0, false, 3);
             const bool fits = !pw.generic && pw.full;
-            if (fits && (want_keep == 3 || (hidden * elem <= 16384 && pw.block * pw.ctas >= 256))) { *p = pw; return; }
+            if (fits && (want_keep >= 3 || (hidden * elem <= 16384 && pw.block * pw.ctas >= 256))) { *p = pw; return; }
         }
         if (want_keep == 1) *keep = !pk.generic;
         else if (want_keep == 2) *keep = pn.generic && !pk.generic;
@@ -571,7 +571,13 @@ int launch_bwd(const void* x, const void* gamma, const float* rstd, const void* 
         else AGB_LAUNCH_FAST(false, false, MT, KP);                \
     } while (0)
         if (p.vpt == 2 * kV) {   // 64 elements per thread (planned only when full)
-            if (gamma && p.g.early_refill) AGB_LAUNCH_FAST_V(2 * kV, true, true, 384, false, 1);
+            // With at most 256 resident threads per SM a thread may use 255 registers: x (unpacked) and gy (as loaded)
+            // stay in registers between the passes as well (224 registers), so pass 2 reads only gamma from shared
+            // memory and unpacks only gy.  Measured settled at 65536 x 8192 bf16: step 855.5 against 881.6 us, the
+            // backward alone 508.6 against 533.7 us.  "bwd_keep" 3 forces the re-reading form, 4 this one.
+            if (gamma && p.g.early_refill && opt_bwd_keep.load() != 3 && p.block * p.ctas <= 256)
+                AGB_LAUNCH_FAST_V(2 * kV, true, true, 256, true, 1);
+            else if (gamma && p.g.early_refill) AGB_LAUNCH_FAST_V(2 * kV, true, true, 384, false, 1);
             else if (gamma) AGB_LAUNCH_FAST_V(2 * kV, true, true, 384, false, 0);
             else AGB_LAUNCH_FAST_V(2 * kV, false, true, 384, false, 0);
         } else if (!keep && gamma && p.full && p.g.early_refill && p.block * p.ctas <= 384) {

@@ -79,7 +79,8 @@ int agb_selftest_bounded_wait(int poll_limit, int* polls_done, agb_stream_t stre
  * AGB_ERR_INVALID_ARG.
  *   launch-plan knobs for sweeps: "stages", "ctas_per_sm", "threads", "ept" (elements per thread of the
  *     strict backward), "rows_per_warp" (strict backward, one-warp rows), "bwd_keep" (16-bit backward:
- *     1 keep x/gy in registers, 2 re-read the tile, 3 64 elements per thread), "lone_ring" (2: a single
+ *     1 keep x/gy in registers, 2 re-read the tile, 3 64 elements per thread re-reading the tile, 4 64 elements
+ *     per thread with x/gy kept where 256 resident threads allow it), "lone_ring" (2: a single
  *     CTA per SM may run a two-slot ring), "reserve_sms" (SMs the persistent grids leave free),
  *     "bwd_refill" (16-bit backward: 1 thread 0 refills a ring slot after the mid-tile barrier, 2 the
  *     last warp out of the slot does wherever that form is built), "softmax_two_pass" (approximate softmax / logsumexp forward:

@@ -137,15 +137,16 @@ def test_bf16_parity_with_outlier_rows(ops, hidden, strict):
 
 @pytest.mark.parametrize("rows,hidden", [(700, 8192), (513, 4096), (300, 12288), (1000, 1000)])
 def test_bf16_backward_variants_agree(ops, rows, hidden):
-    """The fp32-accumulating backward exists with three register budgets (x and gy kept in registers between the
-    passes; tile re-read; 64 elements per thread).  They share the arithmetic per element and differ only in how
-    a row's dot product and a column's sum are split over threads, so they agree to fp32 rounding."""
+    """The fp32-accumulating backward exists with several register budgets (x and gy kept in registers between the
+    passes; tile re-read; 64 elements per thread re-reading; 64 elements per thread keeping).  They share the
+    arithmetic per element and differ only in how a row's dot product and a column's sum are split over threads,
+    so they agree to fp32 rounding."""
     x, gamma, gy = make_inputs(rows, hidden, seed=rows, x_std=3.0, gamma_std=0.1, outlier_frac=0.01)
     xd, gd, gyd = dev(x, torch.bfloat16), dev(gamma, torch.bfloat16), dev(gy, torch.bfloat16)
     _, rstd = ops.rmsnorm_fwd(xd, gd, 1e-6)
     outs = []
     try:
-        for keep in (1, 2, 3):
+        for keep in (1, 2, 3, 4):
             ops.set_option("bwd_keep", keep)
             dx, dg = ops.rmsnorm_bwd(xd, gd, rstd, gyd)
             dxa, _ = ops.rmsnorm_bwd(xd, gd, rstd, gyd, dx_add=gyd)          # the residual-stream form

@@ -35,12 +35,12 @@ def test_hot_path_kernels_do_not_spill():
             hot = True
         elif kernel == "rmsnorm_bwd_fast" and len(args) == 7:
             # <T, VPT, HAS_GAMMA, FULL, MAXT, KEEP, REL>: the fp32-accumulating 16-bit backward in all its register
-            # budgets (80 registers at 768 threads, 102 at 640, 128 at 512, 168 at 384), with gamma
+            # budgets (80 registers at 768 threads, 102 at 640, 128 at 512, 168 at 384, 255 at 256), with gamma
             hot = args[2] == "1"
             if hot:
                 checked += 1
                 assert r.get("spill_stores", 0) == 0 and r.get("spill_loads", 0) == 0, f"{name} spills: {r}"
-                assert r.get("registers", 0) <= {"768": 80, "640": 102, "512": 128, "384": 168}[args[4]], f"{name}: {r}"
+                assert r.get("registers", 0) <= {"768": 80, "640": 102, "512": 128, "384": 168, "256": 255}[args[4]], f"{name}: {r}"
             continue
         elif kernel == "rmsnorm_fwd_fast" and len(args) == 6:
             # <T, VPT, HAS_GAMMA, FUSE_ADD, FULL, FREE>: four vectors per thread with gamma; a register or two
