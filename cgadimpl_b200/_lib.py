@@ -79,6 +79,7 @@ SHARD_SIGNATURES = {
     "agb_peer_acquire": (_i, [_vp, _vp, C.POINTER(_vp)]),
     "agb_peer_exchange": (_i, [_vp, _vp, _i64, _i, _vp, _vp]),
     "agb_peer_rmsnorm_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i64, _i64, _i, _vp]),
+    "agb_peer_rmsnorm_bwd_overlapped": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i64, _i64, _i, _vp, _vp]),
     "agb_peer_publish": (_i, [_vp, _vp]),
     "agb_peer_sum": (_i, [_vp, _vp, _i64, _i, _vp]),
     "agb_peer_block": (_i, [_vp, C.POINTER(_vp)]),

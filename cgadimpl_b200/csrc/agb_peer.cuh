@@ -22,6 +22,11 @@ struct agb_peer {
     bool ipc_opened[AGB_SHARD_MAX] = {};
     agb::PeerBlocks blk{};          // blk.base[rank] is this rank's own allocation
     cudaEvent_t ev_pub = nullptr;
+    // agb_peer_rmsnorm_bwd_overlapped: the stream the publishing reduction of the open step was put on, and the
+    // event behind the last kernel that read the caller's partial rows there
+    cudaStream_t pub_stream = nullptr;
+    bool pub_on_side = false, side_pending = false;
+    cudaEvent_t ev_side = nullptr;
 };
 
 namespace {
@@ -59,6 +64,7 @@ int agb_peer_create(int rank, int world, int64_t max_hidden, agb_peer_t** out, u
     if (e == cudaSuccess) e = cudaMalloc(&mem, peer_block_bytes(world, max_hidden));
     if (e == cudaSuccess) e = cudaMemset(mem, 0, peer_block_bytes(world, max_hidden));
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->ev_pub, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->ev_side, cudaEventDisableTiming);
     if (e == cudaSuccess && handle) {
         cudaIpcMemHandle_t h;
         memset(handle, 0, AGB_PEER_HANDLE_BYTES);
@@ -68,6 +74,7 @@ int agb_peer_create(int rank, int world, int64_t max_hidden, agb_peer_t** out, u
     if (e != cudaSuccess) {
         if (mem) cudaFree(mem);
         if (p->ev_pub) cudaEventDestroy(p->ev_pub);
+        if (p->ev_side) cudaEventDestroy(p->ev_side);
         delete p;
         return cuda_fail(e, "agb_peer_create");
     }
@@ -161,6 +168,47 @@ int agb_peer_rmsnorm_bwd(agb_peer_t* p, const void* x, const void* gamma, const 
     return AGB_OK;
 }
 
+// The same step with the column reduction, and with it the stores into the peers' blocks and their system-scope
+// fences, on `side_stream`: `stream` carries only the backward kernel, so the next forward does not wait for
+// the publication (among eight ranks that wait is about 40 us of a 0.9 ms step).  The partial rows in
+// `workspace` are read on the side stream; the next call makes `stream` wait for that reader before its
+// backward overwrites them.  agb_peer_exchange must then be given the same side stream.
+int agb_peer_rmsnorm_bwd_overlapped(agb_peer_t* p, const void* x, const void* gamma, const float* rstd, const void* gy,
+                                    const void* dx_add, void* dx, void* workspace, size_t workspace_bytes, int64_t rows,
+                                    int64_t hidden, int dtype, agb_stream_t stream, agb_stream_t side_stream) {
+    if (rows == 0 || side_stream == stream)
+        return agb_peer_rmsnorm_bwd(p, x, gamma, rstd, gy, dx_add, dx, workspace, workspace_bytes, rows, hidden, dtype, stream);
+    AGB_TRY(peer_check(p, true));
+    if (p->acquired) return fail(AGB_ERR_INVALID_ARG, "a step is already open (agb_peer_acquire without agb_peer_sum)");
+    if (!gamma) return fail(AGB_ERR_INVALID_ARG, "gamma is NULL: without gamma there is no dgamma to exchange");
+    if (hidden <= 0 || hidden > p->max_hidden)
+        return fail(AGB_ERR_WORKSPACE, "hidden %lld outside (0, max_hidden %lld]", (long long)hidden, (long long)p->max_hidden);
+    cudaStream_t st = static_cast<cudaStream_t>(stream), sd = static_cast<cudaStream_t>(side_stream);
+    if (p->side_pending) AGB_CUDA(cudaStreamWaitEvent(st, p->ev_side, 0));   // the last reader of the partial rows
+    int P = 0;
+    AGB_TRY(agb_rmsnorm_bwd_partials(x, gamma, rstd, gy, dx_add, dx, workspace, workspace_bytes, rows, hidden, dtype, stream, &P));
+    AGB_CUDA(cudaEventRecord(p->ev_pub, st));
+    AGB_CUDA(cudaStreamWaitEvent(sd, p->ev_pub, 0));
+    const unsigned long long t = p->step + 1;
+    const int b = static_cast<int>(t % agb::kPeerBuffers);
+    agb::PeerHook hook{p->blk, p->world, p->rank, b, (p->world > 1 && t > agb::kPeerBuffers) ? t - agb::kPeerBuffers : 0ull, t,
+                       static_cast<long long>(p->max_hidden), peer_poll_limit()};
+    double* sums = reinterpret_cast<double*>(p->blk.base[p->rank] + agb::peer_sums_offset(p->rank, b, p->max_hidden));
+    t_reduce_hook = &hook;
+    t_reduce_hook_used = false;
+    const int rc = agb_dgamma_reduce(workspace, P, hidden, sums, AGB_F64, 0, side_stream);
+    t_reduce_hook = nullptr;
+    if (rc != AGB_OK) return rc;
+    if (!t_reduce_hook_used) return fail(AGB_ERR_CUDA, "internal: the column reduction did not publish");
+    AGB_CUDA(cudaEventRecord(p->ev_side, sd));
+    p->side_pending = true;
+    p->acquired = true;
+    p->published = true;
+    p->pub_on_side = true;
+    p->pub_stream = sd;
+    return AGB_OK;
+}
+
 int agb_peer_publish(agb_peer_t* p, agb_stream_t stream) {
     AGB_TRY(peer_check(p, true));
     if (!p->acquired || p->published) return fail(AGB_ERR_INVALID_ARG, "agb_peer_publish needs one agb_peer_acquire before it");
@@ -193,6 +241,13 @@ int agb_peer_sum(agb_peer_t* p, float* dgamma, int64_t hidden, int accumulate, a
 int agb_peer_exchange(agb_peer_t* p, float* dgamma, int64_t hidden, int accumulate, agb_stream_t stream,
                       agb_stream_t sum_stream) {
     if (!p || !p->published) AGB_TRY(agb_peer_publish(p, stream));   // (agb_peer_rmsnorm_bwd has published already)
+    if (p->pub_on_side) {
+        // the publishing reduction already runs on a side stream: the sum follows it there, no event needed
+        p->pub_on_side = false;
+        if (static_cast<cudaStream_t>(sum_stream) != p->pub_stream)
+            return fail(AGB_ERR_INVALID_ARG, "agb_peer_exchange: sum_stream must be the side stream given to agb_peer_rmsnorm_bwd_overlapped");
+        return agb_peer_sum(p, dgamma, hidden, accumulate, sum_stream);
+    }
     if (sum_stream != stream) {
         AGB_CUDA(cudaEventRecord(p->ev_pub, static_cast<cudaStream_t>(stream)));
         AGB_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(sum_stream), p->ev_pub, 0));
@@ -224,6 +279,7 @@ int agb_peer_destroy(agb_peer_t* p) {
         if (p->ipc_opened[r]) cudaIpcCloseMemHandle(p->blk.base[r]);
     if (p->blk.base[p->rank]) cudaFree(p->blk.base[p->rank]);
     if (p->ev_pub) cudaEventDestroy(p->ev_pub);
+    if (p->ev_side) cudaEventDestroy(p->ev_side);
     delete p;
     return AGB_OK;
 }

@@ -177,10 +177,11 @@ class RowShardedRMSNorm:
         caller's stream does not wait for the exchange: call wait_dgamma() before reading dgamma."""
         cur = torch.cuda.current_stream(self.device)
         if self._peer is not None:
-            # the library's own exchange: the backward's last kernel waits for the buffer (two steps old) and
-            # publishes the sums; the summing kernel, which waits for the other ranks, runs on the side stream
+            # the library's own exchange: the backward's column reduction waits for the buffer (eight steps old)
+            # and publishes the sums -- on the side stream, like the summing kernel that waits for the other
+            # ranks, so that the caller's stream carries the backward kernel only
             dx = torch.empty_like(x) if dx is None else dx
-            self._peer.rmsnorm_bwd(x, gamma, rstd, gy, dx, self._workspace(x), stream=cur)
+            self._peer.rmsnorm_bwd(x, gamma, rstd, gy, dx, self._workspace(x), stream=cur, side_stream=self._side)
             self._peer.exchange(dgamma, self.hidden, stream=cur, sum_stream=self._side)
             return dx
         slot = self._turn
@@ -262,7 +263,7 @@ class RowShardedRMSNorm:
         main, side = vp(cur.cuda_stream), vp(self._side.cuda_stream)
         fwd_args = (p(x), p(gamma), p(y), p(rstd), rows, hidden, C.c_float(self.eps), ops._dt(x), main)
         bwd_args = (self._peer._h, p(x), p(gamma), p(rstd), p(gy), None, p(dx), p(ws), ws.numel() * ws.element_size(),
-                    rows, hidden, ops._dt(x), main)
+                    rows, hidden, ops._dt(x), main, side)
         exc_args = (self._peer._h, p(dgamma), hidden, 0, main, side)
         keep = (x, gy, gamma, y, rstd, dx, dgamma, ws)     # the prebuilt pointers must stay valid
 
@@ -273,7 +274,7 @@ class RowShardedRMSNorm:
                 _lib.check(lib.agb_rmsnorm_fwd(*fwd_args))
 
             def bwd(self_inner):
-                _lib.check(lib.agb_peer_rmsnorm_bwd(*bwd_args))
+                _lib.check(lib.agb_peer_rmsnorm_bwd_overlapped(*bwd_args))
                 _lib.check(lib.agb_peer_exchange(*exc_args))
 
         return _Fast()

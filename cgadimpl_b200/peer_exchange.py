@@ -70,9 +70,11 @@ class PeerExchange:
         check(_lib.lib().agb_peer_acquire(self._h, C.c_void_p(s.cuda_stream), C.byref(out)))
         return out.value
 
-    def rmsnorm_bwd(self, x, gamma, rstd, gy, dx, workspace, dx_add=None, stream=None):
+    def rmsnorm_bwd(self, x, gamma, rstd, gy, dx, workspace, dx_add=None, stream=None, side_stream=None):
         """The VJP of this rank's rows with the exchange's bookkeeping fused into its last kernel
-        (agb_peer_rmsnorm_bwd): no extra launch on the backward's stream.  Follow with exchange()."""
+        (agb_peer_rmsnorm_bwd): no extra launch on the backward's stream.  With side_stream that last kernel,
+        the publishing column reduction, runs there (agb_peer_rmsnorm_bwd_overlapped).  Follow with exchange()
+        (with sum_stream=side_stream in the second case)."""
         from . import ops
 
         rows, hidden = ops._rows_hidden(x)
@@ -81,6 +83,12 @@ class PeerExchange:
         ops._vec(x, rows, torch.float32, rstd)
         s = torch.cuda.current_stream(self.device) if stream is None else stream
         p = ops._p
+        if side_stream is not None:
+            check(_lib.lib().agb_peer_rmsnorm_bwd_overlapped(self._h, p(x), p(gamma), p(rstd), p(gy), p(dx_add), p(dx),
+                                                             p(workspace), workspace.numel() * workspace.element_size(),
+                                                             rows, hidden, ops._dt(x), C.c_void_p(s.cuda_stream),
+                                                             C.c_void_p(side_stream.cuda_stream)))
+            return dx
         check(_lib.lib().agb_peer_rmsnorm_bwd(self._h, p(x), p(gamma), p(rstd), p(gy), p(dx_add), p(dx), p(workspace),
                                               workspace.numel() * workspace.element_size(), rows, hidden, ops._dt(x),
                                               C.c_void_p(s.cuda_stream)))

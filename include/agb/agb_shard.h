@@ -124,6 +124,15 @@ int agb_peer_exchange(agb_peer_t* p, float* dgamma, int64_t hidden, int accumula
 int agb_peer_rmsnorm_bwd(agb_peer_t* p, const void* x, const void* gamma, const float* rstd, const void* gy,
                          const void* dx_add, void* dx, void* workspace, size_t workspace_bytes, int64_t rows,
                          int64_t hidden, int dtype, agb_stream_t stream);
+/* The same with the column reduction -- and with it the stores into the peers' blocks and their system-scope
+ * fences -- on `side_stream`: `stream` carries only the backward kernel, so the kernels that follow on it do not
+ * wait for the publication (among eight ranks about 40 us of a 0.9 ms step).  The partial rows in `workspace`
+ * are then read on the side stream; the next call orders `stream` after that reader before its backward
+ * overwrites them.  Follow with agb_peer_exchange(p, ..., stream, side_stream) with the SAME side stream (the
+ * summing kernel simply follows the reduction there).  side_stream == stream, or rows == 0: agb_peer_rmsnorm_bwd. */
+int agb_peer_rmsnorm_bwd_overlapped(agb_peer_t* p, const void* x, const void* gamma, const float* rstd, const void* gy,
+                                    const void* dx_add, void* dx, void* workspace, size_t workspace_bytes, int64_t rows,
+                                    int64_t hidden, int dtype, agb_stream_t stream, agb_stream_t side_stream);
 /* agb_peer_exchange is these two, with an event between them when the streams differ. */
 int agb_peer_publish(agb_peer_t* p, agb_stream_t stream);
 int agb_peer_sum(agb_peer_t* p, float* dgamma, int64_t hidden, int accumulate, agb_stream_t stream);
