@@ -144,6 +144,11 @@ int agb_peer_rmsnorm_bwd(agb_peer_t* p, const void* x, const void* gamma, const 
     if (!gamma) return fail(AGB_ERR_INVALID_ARG, "gamma is NULL: without gamma there is no dgamma to exchange");
     if (hidden <= 0 || hidden > p->max_hidden)
         return fail(AGB_ERR_WORKSPACE, "hidden %lld outside (0, max_hidden %lld]", (long long)hidden, (long long)p->max_hidden);
+    if (p->side_pending && rows > 0) {
+        // an earlier agb_peer_rmsnorm_bwd_overlapped may still be reading the partial rows on its side stream
+        AGB_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), p->ev_side, 0));
+        p->side_pending = false;
+    }
     if (rows == 0) {   // no reduction kernel runs for an empty shard: the plain sequence
         double* sums = nullptr;
         AGB_TRY(agb_peer_acquire(p, stream, &sums));
