@@ -67,6 +67,23 @@ def test_shard_argument_validation_needs_no_device(lib):
     assert lib.agb_shard_run_fwd_bwd(None, io, 4096, 1e-5, 0, 0) == 1
 
 
+def test_peer_argument_validation_needs_no_device(lib):
+    out = C.c_void_p()
+    handle = C.create_string_buffer(64)
+    assert lib.agb_peer_create(0, 0, 4096, C.byref(out), handle) == 1        # world must be >= 1
+    assert lib.agb_peer_create(2, 2, 4096, C.byref(out), handle) == 1        # rank outside the world
+    assert lib.agb_peer_create(0, 17, 4096, C.byref(out), handle) == 1       # more ranks than AGB_SHARD_MAX
+    assert lib.agb_peer_create(0, 2, 0, C.byref(out), handle) == 1           # max_hidden must be positive
+    assert lib.agb_peer_create(0, 2, 4096, None, handle) == 1
+    assert out.value is None
+    one = C.c_void_p(16)
+    for fn, extra in ((lib.agb_peer_rmsnorm_bwd, ()), (lib.agb_peer_rmsnorm_bwd_overlapped, (one,))):
+        assert fn(None, one, one, one, one, None, one, one, 1 << 20, 8, 64, 0, None, *extra) == 1   # no exchange object
+    assert lib.agb_peer_exchange(None, one, 64, 0, None, None) == 1
+    assert lib.agb_peer_sum(None, one, 64, 0, None) == 1 and lib.agb_peer_publish(None, None) == 1
+    assert lib.agb_peer_destroy(None) == 0 and lib.agb_peer_disconnect(None) == 0
+
+
 def test_version_and_strings(lib):
     assert lib.agb_version() >= 100
     assert lib.agb_status_string(0) == b"ok"
